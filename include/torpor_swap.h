@@ -1,0 +1,174 @@
+/* torpor_swap.h -- C ABI of the B200 swap engine (libtorpor_swap.so).
+ *
+ * The library replaces one path of Torpor's server: swapping a function's
+ * weights between the host model store and the pooled GPU memory manager.
+ * In the reference that path is the C++ class server::manager::MemoryManager
+ * (include/server/memory_manager.hpp) with its allocator
+ * (include/server/block_manager.hpp) and tables (include/server/model_repo.hpp),
+ * plus the eviction policy (include/server/evictor.hpp) and the swap decision
+ * of the controller (include/server/controller.hpp:296-453).  The reference has
+ * no FFI on this path: the executor calls MemoryManager's public methods
+ * directly.  Each entry point below therefore stands for one of those methods
+ * and cites it; the header-only adapter torpor_b200/adapter/memory_manager.hpp
+ * turns them back into the reference's class so src/server compiles unchanged.
+ *
+ * Conventions: plain pointers and sizes only; every function returns a
+ * tsw_status (0 = ok, negative = error) unless stated otherwise; device
+ * pointers travel as uint64_t.  Nothing here falls back to the CPU: an engine
+ * created on a CUDA device moves bytes only with the library's own sm_100a
+ * kernels and fails with TSW_ERR_CUDA / TSW_ERR_NO_DEVICE when it cannot.
+ */
+#ifndef TORPOR_SWAP_H_
+#define TORPOR_SWAP_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tsw_engine tsw_engine;
+typedef struct tsw_evictor tsw_evictor;
+typedef struct tsw_scheduler tsw_scheduler;
+
+typedef enum {
+    TSW_OK = 0,
+    TSW_ERR_INVALID = -1,         /* bad argument or handle */
+    TSW_ERR_NO_DEVICE = -2,       /* data call on a plan-only engine, or no usable CUDA device */
+    TSW_ERR_CUDA = -3,            /* a CUDA runtime call failed; see tsw_last_error() */
+    TSW_ERR_POOL_EXHAUSTED = -4,  /* the reference exits here (block_manager.hpp:343-352) */
+    TSW_ERR_UNKNOWN_MODEL = -5,
+    TSW_ERR_TIMEOUT = -6,         /* a bounded wait ran out (the reference blocks forever, memory_manager.hpp:531) */
+    TSW_ERR_NOT_FOUND = -7,       /* address is not inside any block of the model */
+    TSW_ERR_BUFFER = -8,          /* caller's output buffer is too small */
+    TSW_ERR_STATE = -9,           /* call not valid in the current state */
+    TSW_ERR_KERNEL = -10          /* a kernel reported an error status */
+} tsw_status;
+
+/* Parameter readiness, as in memory_manager.hpp:29-31. */
+enum { TSW_READY_HOST = 0, TSW_READY_PINNED = 1, TSW_READY_CUDA = 2 };
+/* Model status, as in model_repo.hpp:32-35. */
+enum { TSW_MODEL_FULL = 0, TSW_MODEL_INCOMPLETE = 1, TSW_MODEL_PARTIAL = 2, TSW_MODEL_NODATA = 3 };
+/* Pool policy: memory_manager.hpp:46-52 (env BLOCK_MANAGER). */
+enum { TSW_POOL_BUDDY = 0, TSW_POOL_FIXED = 1 };
+
+typedef struct {
+    int device;             /* CUDA device ordinal, or -1 for a plan-only engine: placement and
+                               tables are computed, no CUDA call is made and no byte moves */
+    int server_id;          /* executor id (MemoryManager::set_server_id, :62-65) */
+    int gpu_count;          /* start_trans_thread(gpu_count), :168 */
+    uint64_t budget_bytes;  /* MemoryManager(budget), :38-54; 5 GiB are added as the reference does */
+    int pool_policy;        /* TSW_POOL_BUDDY | TSW_POOL_FIXED */
+    uint64_t host_arena_bytes; /* page-locked host model store carved from one arena of this size;
+                               0 = one page-locked allocation per model block */
+    const char* host_arena_shm; /* optional POSIX shm name: the arena is created there so that other
+                               processes can attach it (tsw_arena_attach) for sharded swaps */
+    int grid_ctas;          /* persistent CTAs of the placement kernel; 0 = default */
+    int tile_bytes_host;    /* bytes per tile when the source is host memory; 0 = default */
+    int tile_bytes_device;  /* bytes per tile when the source is device memory; 0 = default */
+} tsw_config;
+
+void tsw_config_default(tsw_config* cfg);
+
+const char* tsw_last_error(void);       /* thread-local text of the last failure */
+const char* tsw_version(void);
+
+/* Process-wide model repository (ModelRepo::getInstance(), model_repo.hpp:67-72). */
+int tsw_repo_reset(void);                                        /* forget every model (tests) */
+int tsw_repo_add_model_info(const char* func, int gpu);          /* model_repo.hpp:82-85 */
+int tsw_repo_remove_model_info(const char* func, int gpu);       /* model_repo.hpp:87-90 */
+int tsw_repo_model_status(const char* func, int gpu);            /* DeviceModelInfo::status_, or <0 */
+uint64_t tsw_repo_total_size(const char* func);                  /* HostModelInfo::total_size_ */
+int tsw_repo_active_devices(const char* func, int* gpus, int cap); /* model_active_device_map_ */
+
+/* Engine life cycle: MemoryManager(budget) + set_server_id + start_trans_thread
+ * (memory_manager.hpp:38-65,168-193) / destroy_trans_thread (:229-232). */
+int tsw_engine_create(const tsw_config* cfg, tsw_engine** out);
+int tsw_engine_destroy(tsw_engine* e);
+
+/* Cold start recorders. */
+int tsw_track_begin(tsw_engine* e, const char* func);            /* set_track_model_memory, :67-71 */
+int tsw_track_end(tsw_engine* e, const char* func);              /* unset_track_model_memory, :73-80 */
+int tsw_malloc(tsw_engine* e, const char* func, uint64_t size, int load_model_flag,
+               uint64_t* vptr);                                   /* cudaMallocBackend, :85-94 */
+int tsw_free(tsw_engine* e, const char* func, uint64_t vptr);    /* cudaFreeBackend, :97-110 */
+/* cudaMemcpyAsyncBackendHtoD with load_model_flag = true (:124-135,141): records the
+ * parameter in the host store and uploads it.  stream is a cudaStream_t. */
+int tsw_memcpy_h2d_model(tsw_engine* e, const char* func, uint64_t dst_vptr,
+                         const void* payload, uint64_t size, void* stream);
+int tsw_sync_done(tsw_engine* e, const char* func);              /* init_model_readiness(func), :234-238 */
+int tsw_mark_access(tsw_engine* e, uint64_t vptr);               /* try_insert_model_access, :273-284; 1/0 */
+
+/* Forwarded client copies after translation (:112-122,136-163). */
+int tsw_memcpy_h2d(tsw_engine* e, const char* func, uint64_t dst_vptr, const void* src, uint64_t size, void* stream);
+int tsw_memcpy_d2h(tsw_engine* e, const char* func, void* dst, uint64_t src_vptr, uint64_t size, void* stream);
+int tsw_memcpy_d2d(tsw_engine* e, const char* func, uint64_t dst_vptr, uint64_t src_vptr, uint64_t size, void* stream);
+int tsw_memset(tsw_engine* e, const char* func, uint64_t vptr, int value, uint64_t size, void* stream);
+
+/* Swap-in: sig_trans_thread(func, src_gpu) (:213-227) = check_and_malloc_model
+ * (:451-507) + transfer_model (:331-438).  Returns once blocks are placed, the
+ * pointer table is rebound and the placement kernel is enqueued; readiness is
+ * published per parameter by the kernel.  src_gpu < 0: from the host store;
+ * otherwise from the resident replica of engine `src_gpu` in this process. */
+int tsw_swap_in(tsw_engine* e, const char* func, int src_gpu);
+/* Sharded swap-in: the tiles of one swap are dealt out to `n_helpers` + 1 engines of
+ * this process; every engine reads its share of the host store over its own PCIe
+ * link and stores it straight into the target's pool blocks over NVLink.  No
+ * counterpart in the reference; the result equals tsw_swap_in(e, func, -1). */
+int tsw_swap_in_sharded(tsw_engine* e, const char* func, tsw_engine* const* helpers, int n_helpers);
+/* Wait until every accessed parameter of func is on the device (bounded). */
+int tsw_wait_ready(tsw_engine* e, const char* func, int64_t timeout_ns);
+int tsw_check_alloc(tsw_engine* e, const char* func);            /* check_model_alloc_status, :195-210; 1/0 */
+
+/* Swap-out: evict_model(func) (:240-259).  The reference moves no bytes; with
+ * writeback != 0 the resident parameter bytes are first written back to the
+ * host store by the D2H kernel. */
+int tsw_evict(tsw_engine* e, const char* func, int writeback);
+
+/* get_cuda_addr (:261-271): client pointer -> current device pointer.  For a
+ * model parameter that is being swapped in this waits (at most timeout_ns) for
+ * its readiness flag, as check_param_readiness does (:527-540). */
+int tsw_translate(tsw_engine* e, const char* func, uint64_t vptr, int search_amid,
+                  int64_t timeout_ns, uint64_t* out);
+int tsw_is_model_address(tsw_engine* e, const char* func, uint64_t vptr);    /* :286-291; 1/0 */
+int tsw_valid_memory_address(tsw_engine* e, const char* func, uint64_t vptr); /* :293-298; always 0 */
+
+/* Introspection for parity checks.  Layouts as in the checkers' scenario ABI:
+ * blocks (6 words): vaddr, size, is_model, in_cuda, cuda_addr, in_pin(=0), in the order
+ *   swap-in requests pool blocks; params (7 words): vaddr, size, block_vaddr, cuda_addr,
+ *   readiness_flag, readiness_addr, accessed -- access order first, then the rest by vaddr.
+ * Both return the number of rows (also when out == NULL). */
+int tsw_dump_blocks(tsw_engine* e, const char* func, uint64_t* out, int cap);
+int tsw_dump_params(tsw_engine* e, const char* func, uint64_t* out, int cap);
+/* Pool geometry: base of the pool, number of 128 MiB chunks, and the canonical base that
+ * addresses are keyed by internally (so that table order does not depend on where the
+ * driver happened to map the pool). */
+int tsw_pool_info(tsw_engine* e, uint64_t* pool_base, uint64_t* n_chunks, uint64_t* canon_base);
+int tsw_read_phys(tsw_engine* e, uint64_t addr, void* out, uint64_t size);
+int tsw_read_host_store(tsw_engine* e, const char* func, uint64_t vptr, void* out, uint64_t size);
+/* Per-parameter 2 x 64-bit checksum of the RESIDENT bytes, computed on the device
+ * (s1 = sum of 32-bit words, s2 = sum of (index+1)*word, both mod 2^64; a ragged tail is
+ * zero-extended).  out holds 2 words per parameter in tsw_dump_params order. */
+int tsw_checksum_resident(tsw_engine* e, const char* func, uint64_t* out, int cap);
+
+/* Counters: kernels launched by this engine, bytes they were asked to move, and device
+ * time of the last swap on the transfer stream (CUDA events), in nanoseconds. */
+int tsw_stats(tsw_engine* e, uint64_t* kernel_launches, uint64_t* bytes_moved, uint64_t* last_swap_device_ns);
+
+/* Eviction policy: Evictor / LRUEvictor / InterferenceAwareEvictor (evictor.hpp:14-264).
+ * kind: "LRU" or "IA".  check_and_add returns the number of victims and writes their names
+ * '\n'-joined; unlike the reference it returns TSW_ERR_STATE instead of spinning when
+ * nothing can be evicted (evictor.hpp:211-224). */
+int tsw_evictor_create(const char* kind, int gpu_count, uint64_t budget, tsw_evictor** out);
+int tsw_evictor_destroy(tsw_evictor* ev);
+int tsw_evictor_check_and_add(tsw_evictor* ev, int gpu, const char* func, uint64_t size, int level,
+                              char* victims, int cap);
+int tsw_evictor_force_evict(tsw_evictor* ev, int gpu, const char* func);
+int tsw_evictor_lock(tsw_evictor* ev, int gpu, const char* func);
+int tsw_evictor_unlock(tsw_evictor* ev, int gpu, const char* func);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TORPOR_SWAP_H_ */

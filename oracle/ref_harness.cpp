@@ -1,0 +1,355 @@
+// TEST INFRASTRUCTURE ONLY -- never linked into the shipped library.
+//
+// Exposes the reference's own swap path through the scenario ABI of
+// tso_abi.h.  The reference sources are NOT copied: this translation unit
+// includes include/server/{memory_manager,block_manager,model_repo,evictor}.hpp
+// from the read-only reference tree (see the Makefile's REF variable), with
+// ref_shim/cuda_common.hpp shadowing the one header that needs protoc.
+// Private members are opened in this TU only so that tables can be dumped.
+
+#include "cuda_common.hpp"
+#include "utils.hpp"
+#include "safe_ptr.hpp"
+#include "spdlog/spdlog.h"
+#include "spdlog/sinks/null_sink.h"
+#include <sstream>
+#include <list>
+#include <map>
+#include <thread>
+#include <chrono>
+
+#define private public
+#define protected public
+#include "model_repo.hpp"
+#include "block_manager.hpp"
+#include "memory_manager.hpp"
+#include "evictor.hpp"
+#undef private
+#undef protected
+
+#include "tso_abi.h"
+
+using server::manager::MemoryManager;
+using server::manager::ModelRepo;
+using server::manager::BuddyBasedBlockManager;
+
+namespace {
+
+struct Handle {
+    std::unique_ptr<MemoryManager> mm;
+    int server_id = 0;
+    std::vector<uint64_t> chunks;  // pool chunk bases in allocation order
+    bool started = false;
+};
+
+struct QuietCout {
+    std::streambuf* old = nullptr;
+    std::ostringstream sink;
+    QuietCout() {
+        if (!getenv("TORPOR_REF_VERBOSE")) old = std::cout.rdbuf(nullptr);
+    }
+};
+QuietCout g_quiet;
+
+logger null_logger() {
+    static logger lg = std::make_shared<spdlog::logger>("torpor_ref", std::make_shared<spdlog::sinks::null_sink_mt>());
+    return lg;
+}
+
+ModelRepo& repo() { return ModelRepo::getInstance(); }
+
+}  // namespace
+
+extern "C" {
+
+const char* tso_impl_name(void) {
+#ifdef TORPOR_REF_FAKE_CUDA
+    return "reference-headers/fake-cuda";
+#else
+    return "reference-headers/cuda";
+#endif
+}
+
+void tso_reset_world(void) {
+    ModelRepo& r = repo();
+    r.model_access_order_map_.clear();
+    r.model_host_info_map_.clear();  // host mirrors are leaked, as the reference never frees them
+    r.model_meta_data_info_map_.clear();
+    r.device_model_info_map_.clear();
+    r.model_active_device_map_.clear();
+#ifdef TORPOR_REF_FAKE_CUDA
+    torpor_ref_fake::reset_world();
+#endif
+}
+
+void* tso_create(int server_id, uint64_t budget_bytes, int gpu_count, const char* block_manager,
+                 uint64_t buffer_size, int io_threads) {
+    if (block_manager && std::string(block_manager) == "Fixed") setenv("BLOCK_MANAGER", "Fixed", 1);
+    else unsetenv("BLOCK_MANAGER");
+    setenv("BUFFER_SIZE", std::to_string(buffer_size).c_str(), 1);
+    setenv("IO_THREAD_NUM", std::to_string(io_threads).c_str(), 1);
+
+    auto* h = new Handle();
+    h->server_id = server_id;
+    cudaCheck(cudaSetDevice(server_id));
+    h->mm.reset(new MemoryManager((size_t)budget_bytes));
+    h->mm->set_logger(null_logger());
+    h->mm->set_server_id(server_id);
+    h->mm->start_trans_thread(gpu_count);
+    h->started = true;
+    if (auto* b = dynamic_cast<BuddyBasedBlockManager*>(h->mm->block_manager_.get())) {
+        for (void* p : b->free_block_pool_) h->chunks.push_back((uint64_t)p);
+    }
+    return h;
+}
+
+void tso_destroy(void* hv) {
+    auto* h = (Handle*)hv;
+    if (h->started) {
+        h->mm->destroy_trans_thread();
+    }
+    // The manager object itself is leaked on purpose: the reference has no
+    // teardown for its pool, and its staging threads cannot be stopped (their
+    // exit test `size_ < 0` is on an unsigned field, memory_manager.hpp:314).
+    h->mm.release();
+    delete h;
+}
+
+void tso_track_begin(void* hv, const char* func) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    h->mm->set_track_model_memory(f);
+}
+
+uint64_t tso_malloc(void* hv, const char* func, uint64_t size, int load_model_flag) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    cudaSetDevice(h->server_id);
+    return (uint64_t)h->mm->cudaMallocBackend((size_t)size, load_model_flag != 0, f);
+}
+
+void tso_free(void* hv, const char* func, uint64_t vptr) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    h->mm->cudaFreeBackend((void*)vptr, f);
+}
+
+int tso_memcpy_h2d_model(void* hv, const char* func, uint64_t dst, const void* payload, uint64_t size) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    string pl((const char*)payload, (size_t)size);
+    h->mm->cudaMemcpyAsyncBackendHtoD((void*)dst, pl, (cudaStream_t)0, true, f);
+    cudaCheck(cudaDeviceSynchronize());
+    return repo().model_host_info_map_[f].model_param_info_.count((void*)dst) ? 0 : -1;
+}
+
+void tso_sync_done(void* hv, const char* func) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    h->mm->init_model_readiness(f);
+}
+
+int tso_mark_access(void* hv, uint64_t vptr) {
+    auto* h = (Handle*)hv;
+    return h->mm->try_insert_model_access((void*)vptr) ? 1 : 0;
+}
+
+void tso_track_end(void* hv, const char* func) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    h->mm->unset_track_model_memory(f);
+}
+
+void tso_swap_in(void* hv, const char* func, int src_gpu) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    cudaSetDevice(h->server_id);
+    h->mm->sig_trans_thread(f, src_gpu);
+}
+
+static int64_t wait_last_param(Handle* h, string& f) {
+    auto t0 = std::chrono::steady_clock::now();
+    auto& order = repo().model_access_order_map_[f];
+    if (!order.empty()) h->mm->get_cuda_addr(f, order.back());
+    return std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+}
+
+static void wait_staging_recycled(Handle* h, string& f) {
+    // memory_manager.hpp:414-423 runs on the transfer thread after the last
+    // readiness publish; an evict issued before it finishes would read in_pin_.
+    auto& blocks = repo().device_model_info_map_[h->server_id][f].block_virtual_to_cuda_;
+    for (int spin = 0; spin < 200000; ++spin) {
+        bool any = false;
+        for (auto& kv : blocks) any = any || kv.second.in_pin_;
+        if (!any) return;
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+}
+
+int64_t tso_wait_ready(void* hv, const char* func) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    int64_t us = wait_last_param(h, f);
+    wait_staging_recycled(h, f);
+    return us;
+}
+
+int64_t tso_swap_in_timed(void* hv, const char* func, int src_gpu) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    cudaSetDevice(h->server_id);
+    auto t0 = std::chrono::steady_clock::now();
+    h->mm->sig_trans_thread(f, src_gpu);
+    wait_last_param(h, f);
+    int64_t us = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+    wait_staging_recycled(h, f);
+    return us;
+}
+
+void tso_evict(void* hv, const char* func) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    h->mm->evict_model(f);
+}
+
+uint64_t tso_translate(void* hv, const char* func, uint64_t vptr) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    return (uint64_t)h->mm->get_cuda_addr(f, (void*)vptr);
+}
+
+int tso_check_alloc(void* hv, const char* func) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    return h->mm->check_model_alloc_status(f) ? 1 : 0;
+}
+
+int tso_is_model_address(void* hv, const char* func, uint64_t vptr) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    return h->mm->is_model_address(f, (void*)vptr) ? 1 : 0;
+}
+
+void tso_set_model_status(const char* func, int gpu, int full) {
+    string f(func);
+    if (full) repo().add_model_info(f, gpu);
+    else repo().remove_model_info(f, gpu);
+}
+
+uint64_t tso_total_size(const char* func) {
+    string f(func);
+    return repo().model_host_info_map_[f].total_size_;
+}
+
+int tso_pool_chunks(void* hv, uint64_t* out, int cap) {
+    auto* h = (Handle*)hv;
+    int n = (int)h->chunks.size();
+    for (int i = 0; i < n && i < cap; ++i) out[i] = h->chunks[i];
+    return n;
+}
+
+int tso_dump_blocks(void* hv, const char* func, uint64_t* out, int cap) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    auto& host = repo().model_host_info_map_[f];
+    auto& dev = repo().device_model_info_map_[h->server_id][f];
+    int n = 0;
+    for (auto& kv : host.virtual_blocks_) {
+        if (n < cap) {
+            uint64_t* o = out + 6 * n;
+            o[0] = (uint64_t)kv.first;
+            o[1] = kv.second.size_;
+            o[2] = kv.second.is_model_;
+            auto it = dev.block_virtual_to_cuda_.find(kv.first);
+            if (it == dev.block_virtual_to_cuda_.end()) { o[3] = 0; o[4] = 0; o[5] = 0; }
+            else { o[3] = it->second.in_cuda_; o[4] = (uint64_t)it->second.cuda_addr_; o[5] = it->second.in_pin_; }
+        }
+        ++n;
+    }
+    return n;
+}
+
+int tso_dump_params(void* hv, const char* func, uint64_t* out, int cap) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    auto& host = repo().model_host_info_map_[f];
+    auto& dev = repo().device_model_info_map_[h->server_id][f];
+    std::vector<void*> order = repo().model_access_order_map_[f];
+    std::unordered_set<void*> accessed(order.begin(), order.end());
+    std::vector<void*> rest;
+    for (auto& kv : host.model_param_info_) if (!accessed.count(kv.first)) rest.push_back(kv.first);
+    std::sort(rest.begin(), rest.end(), [](void* a, void* b) { return (uint64_t)a < (uint64_t)b; });
+    size_t n_acc = order.size();
+    order.insert(order.end(), rest.begin(), rest.end());
+    int n = 0;
+    for (void* p : order) {
+        if (n < cap) {
+            uint64_t* o = out + 7 * n;
+            o[0] = (uint64_t)p;
+            o[1] = host.model_param_info_[p].size_;
+            o[2] = (uint64_t)host.virtual_data_block_mapping_[p];
+            auto it = dev.param_virtual_to_cuda_.find(p);
+            o[3] = it == dev.param_virtual_to_cuda_.end() ? 0 : (uint64_t)it->second.cuda_addr_;
+            o[4] = (uint64_t)-1; o[5] = 0;
+            auto rit = h->mm->model_param_readiness_.find(f);
+            if (rit != h->mm->model_param_readiness_.end() && rit->second->find(p) != rit->second->end()) {
+                auto pr = rit->second->at(p);
+                o[4] = (uint64_t)pr.first;
+                o[5] = (uint64_t)pr.second;
+            }
+            o[6] = (size_t)n < n_acc ? 1 : 0;
+        }
+        ++n;
+    }
+    return n;
+}
+
+int tso_read_phys(void* hv, uint64_t addr, void* out, uint64_t size) {
+    auto* h = (Handle*)hv;
+    cudaSetDevice(h->server_id);
+    return (int)cudaMemcpy(out, (void*)addr, (size_t)size, cudaMemcpyDeviceToHost);
+}
+
+int tso_read_host_store(void* hv, const char* func, uint64_t vptr, void* out, uint64_t size) {
+    (void)hv;
+    string f(func);
+    auto& host = repo().model_host_info_map_[f];
+    auto it = host.model_param_info_.find((void*)vptr);
+    if (it == host.model_param_info_.end() || it->second.size_ < size) return -1;
+    memcpy(out, it->second.host_addr_, (size_t)size);
+    return 0;
+}
+
+// ---------------------------------------------------------------- evictor
+
+struct EvictorHandle {
+    std::shared_ptr<server::Evictor> ev;
+    map<string, int> levels;
+};
+
+void* tso_evictor_create(const char* kind, int gpu_count, uint64_t budget) {
+    auto* e = new EvictorHandle();
+    if (kind && std::string(kind) == "LRU") e->ev = std::make_shared<server::LRUEvictor>(gpu_count, (size_t)budget);
+    else e->ev = std::make_shared<server::InterferenceAwareEvictor>(gpu_count, (size_t)budget);
+    return e;
+}
+
+void tso_evictor_destroy(void* ev) { delete (EvictorHandle*)ev; }
+
+int tso_evictor_check_and_add(void* ev, int gpu, const char* func, uint64_t size, int level, char* victims, int cap) {
+    auto* e = (EvictorHandle*)ev;
+    string f(func);
+    e->levels[f] = level;
+    auto v = e->ev->check_and_add(gpu, f, (size_t)size, e->levels);
+    std::string joined;
+    for (size_t i = 0; i < v.size(); ++i) { if (i) joined += "\n"; joined += v[i]; }
+    if ((int)joined.size() + 1 > cap) return -1;
+    memcpy(victims, joined.c_str(), joined.size() + 1);
+    return (int)v.size();
+}
+
+void tso_evictor_force_evict(void* ev, int gpu, const char* func) { string f(func); ((EvictorHandle*)ev)->ev->force_evict(gpu, f); }
+void tso_evictor_lock(void* ev, int gpu, const char* func) { string f(func); ((EvictorHandle*)ev)->ev->lock(gpu, f); }
+void tso_evictor_unlock(void* ev, int gpu, const char* func) { string f(func); ((EvictorHandle*)ev)->ev->unlock(gpu, f); }
+
+}  // extern "C"

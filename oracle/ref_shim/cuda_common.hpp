@@ -1,0 +1,161 @@
+// TEST INFRASTRUCTURE ONLY -- never linked into the shipped library.
+//
+// Shadow of the reference's common/include/cuda_common.hpp, placed FIRST on the
+// include path when the reference's swap-path headers
+// (include/server/{memory_manager,block_manager,model_repo}.hpp) are compiled
+// where they lie, unmodified.  The real header pulls in protoc-generated
+// cudarpc.pb.h / signal.pb.h (protoc is not available) and cuDNN/cuBLAS; none
+// of those types are used by the three swap-path headers, which only need the
+// CUDA runtime calls below and the cudaCheck macro
+// (common/include/cuda_common.hpp:108-114).
+//
+// Two variants:
+//   -DTORPOR_REF_FAKE_CUDA : a host-memory stand-in for the CUDA runtime with a
+//        DETERMINISTIC address space, so that the reference's pointer-keyed
+//        hash maps iterate in a reproducible order.  "Device" memory of GPU g
+//        is a lazily committed mmap at kCanonBase + g * kCanonStride, handed
+//        out by a 2 MiB-aligned bump allocator.
+//   (default)               : the real <cuda_runtime.h>; used for the timed
+//        reference arm on a GPU machine.
+#ifndef TORPOR_REF_SHIM_CUDA_COMMON_HPP_
+#define TORPOR_REF_SHIM_CUDA_COMMON_HPP_
+
+#include "types.hpp"
+
+#include <cassert>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <chrono>
+#include <thread>
+#include <memory>
+#include <iostream>
+#include <functional>
+#include <algorithm>
+
+#ifndef TORPOR_REF_FAKE_CUDA
+
+#include <cuda_runtime.h>
+#include <cuda_runtime_api.h>
+
+#else  // ---------------------------------------------------------------- fake
+
+#include <sys/mman.h>
+#include <mutex>
+
+typedef int cudaError_t;
+static const cudaError_t cudaSuccess = 0;
+static const cudaError_t cudaErrorMemoryAllocation = 2;
+typedef void* cudaStream_t;
+typedef void* cudaEvent_t;
+enum cudaMemcpyKind {
+    cudaMemcpyHostToHost = 0,
+    cudaMemcpyHostToDevice = 1,
+    cudaMemcpyDeviceToHost = 2,
+    cudaMemcpyDeviceToDevice = 3,
+    cudaMemcpyDefault = 4
+};
+static const unsigned int cudaStreamNonBlocking = 1;
+
+namespace torpor_ref_fake {
+
+static const uint64_t kCanonBase = 0x600000000000ull;    // canonical device VA of GPU 0
+static const uint64_t kCanonStride = 0x010000000000ull;  // 1 TiB of VA per fake GPU
+static const uint64_t kAlign = 2ull << 20;
+static const int kMaxDev = 16;
+
+struct DevSpace {
+    uint64_t mapped_end = 0;  // bytes of VA currently mmap'ed from the base
+    uint64_t bump = 0;        // next offset handed out
+};
+
+struct World {
+    std::mutex mu;
+    DevSpace dev[kMaxDev];
+};
+
+inline World& world() {
+    static World w;
+    return w;
+}
+
+inline int& cur_device() {
+    thread_local int d = 0;
+    return d;
+}
+
+inline void* dev_alloc(size_t size) {
+    World& w = world();
+    std::lock_guard<std::mutex> g(w.mu);
+    int d = cur_device();
+    DevSpace& s = w.dev[d];
+    uint64_t base = kCanonBase + (uint64_t)d * kCanonStride;
+    uint64_t off = s.bump;
+    uint64_t need = (size + kAlign - 1) / kAlign * kAlign;
+    if (off + need > kCanonStride) return nullptr;
+    if (off + need > s.mapped_end) {
+        // grow the mapping in 1 GiB steps; pages are committed only when touched
+        uint64_t grow_to = ((off + need) + (1ull << 30) - 1) / (1ull << 30) * (1ull << 30);
+        void* want = (void*)(base + s.mapped_end);
+        void* got = mmap(want, grow_to - s.mapped_end, PROT_READ | PROT_WRITE,
+                         MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE | MAP_FIXED_NOREPLACE, -1, 0);
+        if (got != want) {
+            fprintf(stderr, "torpor_ref_fake: cannot map canonical device range at %p\n", want);
+            abort();
+        }
+        s.mapped_end = grow_to;
+    }
+    s.bump = off + need;
+    return (void*)(base + off);
+}
+
+// Drop every fake device mapping and restart the bump allocators.
+inline void reset_world() {
+    World& w = world();
+    std::lock_guard<std::mutex> g(w.mu);
+    for (int d = 0; d < kMaxDev; ++d) {
+        if (w.dev[d].mapped_end) {
+            munmap((void*)(kCanonBase + (uint64_t)d * kCanonStride), w.dev[d].mapped_end);
+        }
+        w.dev[d] = DevSpace();
+    }
+}
+
+}  // namespace torpor_ref_fake
+
+inline const char* cudaGetErrorString(cudaError_t e) { return e == 0 ? "no error" : "fake cuda error"; }
+inline cudaError_t cudaSetDevice(int d) { torpor_ref_fake::cur_device() = d; return cudaSuccess; }
+inline cudaError_t cudaGetDevice(int* d) { *d = torpor_ref_fake::cur_device(); return cudaSuccess; }
+inline cudaError_t cudaMalloc(void** p, size_t size) {
+    *p = torpor_ref_fake::dev_alloc(size);
+    return *p ? cudaSuccess : cudaErrorMemoryAllocation;
+}
+template <class T> inline cudaError_t cudaMalloc(T** p, size_t size) { return cudaMalloc((void**)p, size); }
+inline cudaError_t cudaFree(void*) { return cudaSuccess; }  // address space is never reused
+inline cudaError_t cudaMallocHost(void** p, size_t size) {
+    *p = aligned_alloc(4096, (size + 4095) / 4096 * 4096);
+    return *p ? cudaSuccess : cudaErrorMemoryAllocation;
+}
+inline cudaError_t cudaFreeHost(void* p) { free(p); return cudaSuccess; }
+inline cudaError_t cudaMemcpy(void* dst, const void* src, size_t n, cudaMemcpyKind) { memcpy(dst, src, n); return cudaSuccess; }
+inline cudaError_t cudaMemcpyAsync(void* dst, const void* src, size_t n, cudaMemcpyKind, cudaStream_t = nullptr) { memcpy(dst, src, n); return cudaSuccess; }
+inline cudaError_t cudaMemcpyPeerAsync(void* dst, int, const void* src, int, size_t n, cudaStream_t = nullptr) { memcpy(dst, src, n); return cudaSuccess; }
+inline cudaError_t cudaMemsetAsync(void* p, int v, size_t n, cudaStream_t = nullptr) { memset(p, v, n); return cudaSuccess; }
+inline cudaError_t cudaStreamCreateWithPriority(cudaStream_t* s, unsigned int, int) { *s = nullptr; return cudaSuccess; }
+inline cudaError_t cudaEventCreate(cudaEvent_t* e) { *e = nullptr; return cudaSuccess; }
+inline cudaError_t cudaEventRecord(cudaEvent_t, cudaStream_t = nullptr) { return cudaSuccess; }
+inline cudaError_t cudaEventSynchronize(cudaEvent_t) { return cudaSuccess; }
+inline cudaError_t cudaDeviceSynchronize() { return cudaSuccess; }
+
+#endif  // TORPOR_REF_FAKE_CUDA
+
+#define cudaCheck(ans) { cudaAssert((ans), __FILE__, __LINE__); }
+inline void cudaAssert(cudaError_t err, const char* file, int line, bool abort_flag = false) {
+    if (err != cudaSuccess) {
+        fprintf(stderr, "cuda assert: %s %s %d\n", cudaGetErrorString(err), file, line);
+        if (abort_flag) assert(0);
+    }
+}
+
+#endif  // TORPOR_REF_SHIM_CUDA_COMMON_HPP_

@@ -1,0 +1,199 @@
+"""TEST INFRASTRUCTURE ONLY -- ctypes binding of the checkers' scenario ABI (tso_abi.h).
+
+Loads either the CPU restatement (``libtorpor_oracle.so``) or the reference's
+own headers compiled against a host-memory CUDA stand-in / the real CUDA
+runtime (``_ref/libtorpor_ref_{fake,cuda}.so``).  Only tests, the smoke check
+and the benchmark's CPU-baseline / reference legs may import this module; the
+shipped package never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from typing import List, Optional
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REFERENCE_TREE = "/root/reference"
+
+LIBS = {
+    "oracle": os.path.join(HERE, "libtorpor_oracle.so"),
+    "ref_fake": os.path.join(HERE, "_ref", "libtorpor_ref_fake.so"),
+    "ref_cuda": os.path.join(HERE, "_ref", "libtorpor_ref_cuda.so"),
+}
+
+
+def build(targets=("oracle", "ref")) -> None:
+    """Compile the checkers in place (``make -C oracle``).  The ``ref`` target
+    is a no-op when the reference tree is not present."""
+    subprocess.run(["make", "-C", HERE, *targets], check=True, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+
+
+def available(kind: str) -> bool:
+    return os.path.exists(LIBS[kind])
+
+
+_loaded = {}
+
+
+def load(kind: str) -> "TsoLib":
+    if kind not in _loaded:
+        if not available(kind) and kind == "oracle":
+            build(("oracle",))
+        _loaded[kind] = TsoLib(LIBS[kind])
+    return _loaded[kind]
+
+
+class TsoLib:
+    def __init__(self, path: str):
+        self.path = path
+        L = self.lib = C.CDLL(path)
+        u64, i32, i64, vp, cp = C.c_uint64, C.c_int, C.c_int64, C.c_void_p, C.c_char_p
+        sig = {
+            "tso_reset_world": (None, []),
+            "tso_create": (vp, [i32, u64, i32, cp, u64, i32]),
+            "tso_destroy": (None, [vp]),
+            "tso_track_begin": (None, [vp, cp]),
+            "tso_malloc": (u64, [vp, cp, u64, i32]),
+            "tso_free": (None, [vp, cp, u64]),
+            "tso_memcpy_h2d_model": (i32, [vp, cp, u64, vp, u64]),
+            "tso_sync_done": (None, [vp, cp]),
+            "tso_mark_access": (i32, [vp, u64]),
+            "tso_track_end": (None, [vp, cp]),
+            "tso_swap_in": (None, [vp, cp, i32]),
+            "tso_wait_ready": (i64, [vp, cp]),
+            "tso_swap_in_timed": (i64, [vp, cp, i32]),
+            "tso_evict": (None, [vp, cp]),
+            "tso_translate": (u64, [vp, cp, u64]),
+            "tso_check_alloc": (i32, [vp, cp]),
+            "tso_is_model_address": (i32, [vp, cp, u64]),
+            "tso_set_model_status": (None, [cp, i32, i32]),
+            "tso_total_size": (u64, [cp]),
+            "tso_pool_chunks": (i32, [vp, vp, i32]),
+            "tso_dump_blocks": (i32, [vp, cp, vp, i32]),
+            "tso_dump_params": (i32, [vp, cp, vp, i32]),
+            "tso_read_phys": (i32, [vp, u64, vp, u64]),
+            "tso_read_host_store": (i32, [vp, cp, u64, vp, u64]),
+            "tso_evictor_create": (vp, [cp, i32, u64]),
+            "tso_evictor_destroy": (None, [vp]),
+            "tso_evictor_check_and_add": (i32, [vp, i32, cp, u64, i32, vp, i32]),
+            "tso_evictor_force_evict": (None, [vp, i32, cp]),
+            "tso_evictor_lock": (None, [vp, i32, cp]),
+            "tso_evictor_unlock": (None, [vp, i32, cp]),
+            "tso_impl_name": (cp, []),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+
+    @property
+    def impl_name(self) -> str:
+        return self.lib.tso_impl_name().decode()
+
+    def reset_world(self) -> None:
+        self.lib.tso_reset_world()
+
+    def manager(self, server_id=0, budget=0, gpu_count=1, block_manager="Buddy",
+                buffer_size=2 << 20, io_threads=4) -> "TsoManager":
+        return TsoManager(self, server_id, budget, gpu_count, block_manager, buffer_size, io_threads)
+
+    def evictor(self, kind: str, gpu_count: int, budget: int) -> "TsoEvictor":
+        return TsoEvictor(self, kind, gpu_count, budget)
+
+    def set_model_status(self, func: str, gpu: int, full: bool) -> None:
+        self.lib.tso_set_model_status(func.encode(), gpu, 1 if full else 0)
+
+    def total_size(self, func: str) -> int:
+        return self.lib.tso_total_size(func.encode())
+
+
+class TsoManager:
+    """One memory manager of a checker, with the method names of tso_abi.h."""
+
+    def __init__(self, lib: TsoLib, server_id, budget, gpu_count, block_manager, buffer_size, io_threads):
+        self.L = lib.lib
+        self.server_id = server_id
+        self.h = self.L.tso_create(server_id, budget, gpu_count, block_manager.encode(), buffer_size, io_threads)
+        if not self.h:
+            raise RuntimeError("tso_create failed")
+
+    def close(self):
+        if self.h:
+            self.L.tso_destroy(self.h)
+            self.h = None
+
+    def track_begin(self, f): self.L.tso_track_begin(self.h, f.encode())
+    def malloc(self, f, size, is_model): return self.L.tso_malloc(self.h, f.encode(), size, 1 if is_model else 0)
+    def free(self, f, vptr): self.L.tso_free(self.h, f.encode(), vptr)
+
+    def memcpy_h2d_model(self, f, dst, data: np.ndarray) -> int:
+        data = np.ascontiguousarray(data).view(np.uint8)
+        return self.L.tso_memcpy_h2d_model(self.h, f.encode(), dst, data.ctypes.data, data.nbytes)
+
+    def sync_done(self, f): self.L.tso_sync_done(self.h, f.encode())
+    def mark_access(self, vptr): return self.L.tso_mark_access(self.h, vptr)
+    def track_end(self, f): self.L.tso_track_end(self.h, f.encode())
+    def swap_in(self, f, src_gpu=-1): self.L.tso_swap_in(self.h, f.encode(), src_gpu)
+    def wait_ready(self, f): return self.L.tso_wait_ready(self.h, f.encode())
+    def swap_in_timed(self, f, src_gpu=-1): return self.L.tso_swap_in_timed(self.h, f.encode(), src_gpu)
+    def evict(self, f): self.L.tso_evict(self.h, f.encode())
+    def translate(self, f, vptr): return self.L.tso_translate(self.h, f.encode(), vptr)
+    def check_alloc(self, f): return bool(self.L.tso_check_alloc(self.h, f.encode()))
+    def is_model_address(self, f, vptr): return bool(self.L.tso_is_model_address(self.h, f.encode(), vptr))
+
+    def pool_chunks(self) -> np.ndarray:
+        n = self.L.tso_pool_chunks(self.h, None, 0)
+        out = np.zeros(max(n, 1), dtype=np.uint64)
+        self.L.tso_pool_chunks(self.h, out.ctypes.data, n)
+        return out[:n]
+
+    def dump_blocks(self, f) -> np.ndarray:
+        n = self.L.tso_dump_blocks(self.h, f.encode(), None, 0)
+        out = np.zeros((max(n, 1), 6), dtype=np.uint64)
+        self.L.tso_dump_blocks(self.h, f.encode(), out.ctypes.data, n)
+        return out[:n]
+
+    def dump_params(self, f) -> np.ndarray:
+        n = self.L.tso_dump_params(self.h, f.encode(), None, 0)
+        out = np.zeros((max(n, 1), 7), dtype=np.uint64)
+        self.L.tso_dump_params(self.h, f.encode(), out.ctypes.data, n)
+        return out[:n]
+
+    def read_phys(self, addr, size) -> np.ndarray:
+        out = np.empty(size, dtype=np.uint8)
+        rc = self.L.tso_read_phys(self.h, addr, out.ctypes.data, size)
+        if rc != 0:
+            raise RuntimeError(f"tso_read_phys failed: {rc}")
+        return out
+
+    def read_host_store(self, f, vptr, size) -> np.ndarray:
+        out = np.empty(size, dtype=np.uint8)
+        rc = self.L.tso_read_host_store(self.h, f.encode(), vptr, out.ctypes.data, size)
+        if rc != 0:
+            raise RuntimeError(f"tso_read_host_store failed: {rc}")
+        return out
+
+
+class TsoEvictor:
+    def __init__(self, lib: TsoLib, kind, gpu_count, budget):
+        self.L = lib.lib
+        self.h = self.L.tso_evictor_create(kind.encode(), gpu_count, budget)
+
+    def close(self):
+        if self.h:
+            self.L.tso_evictor_destroy(self.h)
+            self.h = None
+
+    def check_and_add(self, gpu, func, size, level=1) -> List[str]:
+        buf = C.create_string_buffer(1 << 16)
+        n = self.L.tso_evictor_check_and_add(self.h, gpu, func.encode(), size, level, buf, len(buf))
+        if n < 0:
+            raise RuntimeError("victim buffer too small")
+        return buf.value.decode().split("\n") if n else []
+
+    def force_evict(self, gpu, func): self.L.tso_evictor_force_evict(self.h, gpu, func.encode())
+    def lock(self, gpu, func): self.L.tso_evictor_lock(self.h, gpu, func.encode())
+    def unlock(self, gpu, func): self.L.tso_evictor_unlock(self.h, gpu, func.encode())

@@ -1,0 +1,123 @@
+"""ctypes binding of libtorpor_swap.so (include/torpor_swap.h).
+
+The library is the product: there is no Python or CPU implementation behind
+these calls.  Importing this module fails loudly when the library has not been
+built (``python -c "import __graft_entry__ as g; g.build()"`` or
+``make -C torpor_b200/csrc``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libtorpor_swap.so")
+
+OK = 0
+ERR_INVALID, ERR_NO_DEVICE, ERR_CUDA, ERR_POOL_EXHAUSTED, ERR_UNKNOWN_MODEL = -1, -2, -3, -4, -5
+ERR_TIMEOUT, ERR_NOT_FOUND, ERR_BUFFER, ERR_STATE, ERR_KERNEL = -6, -7, -8, -9, -10
+READY_HOST, READY_PINNED, READY_CUDA = 0, 1, 2
+MODEL_FULL, MODEL_INCOMPLETE, MODEL_PARTIAL, MODEL_NODATA = 0, 1, 2, 3
+POOL_BUDDY, POOL_FIXED = 0, 1
+
+_ERR_NAMES = {
+    -1: "TSW_ERR_INVALID", -2: "TSW_ERR_NO_DEVICE", -3: "TSW_ERR_CUDA", -4: "TSW_ERR_POOL_EXHAUSTED",
+    -5: "TSW_ERR_UNKNOWN_MODEL", -6: "TSW_ERR_TIMEOUT", -7: "TSW_ERR_NOT_FOUND", -8: "TSW_ERR_BUFFER",
+    -9: "TSW_ERR_STATE", -10: "TSW_ERR_KERNEL",
+}
+
+
+class SwapError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{_ERR_NAMES.get(code, code)}: {message}")
+        self.code = code
+
+
+class Config(C.Structure):
+    _fields_ = [
+        ("device", C.c_int),
+        ("server_id", C.c_int),
+        ("gpu_count", C.c_int),
+        ("budget_bytes", C.c_uint64),
+        ("pool_policy", C.c_int),
+        ("host_arena_bytes", C.c_uint64),
+        ("host_arena_shm", C.c_char_p),
+        ("grid_ctas", C.c_int),
+        ("tile_bytes_host", C.c_int),
+        ("tile_bytes_device", C.c_int),
+    ]
+
+
+# Every symbol include/torpor_swap.h declares: name -> (restype, argtypes)
+_u64, _i32, _i64, _vp, _cp = C.c_uint64, C.c_int, C.c_int64, C.c_void_p, C.c_char_p
+_pu64 = C.POINTER(C.c_uint64)
+SIGNATURES = {
+    "tsw_config_default": (None, [C.POINTER(Config)]),
+    "tsw_last_error": (_cp, []),
+    "tsw_version": (_cp, []),
+    "tsw_repo_reset": (_i32, []),
+    "tsw_repo_add_model_info": (_i32, [_cp, _i32]),
+    "tsw_repo_remove_model_info": (_i32, [_cp, _i32]),
+    "tsw_repo_model_status": (_i32, [_cp, _i32]),
+    "tsw_repo_total_size": (_u64, [_cp]),
+    "tsw_repo_active_devices": (_i32, [_cp, C.POINTER(C.c_int), _i32]),
+    "tsw_engine_create": (_i32, [C.POINTER(Config), C.POINTER(_vp)]),
+    "tsw_engine_destroy": (_i32, [_vp]),
+    "tsw_track_begin": (_i32, [_vp, _cp]),
+    "tsw_track_end": (_i32, [_vp, _cp]),
+    "tsw_malloc": (_i32, [_vp, _cp, _u64, _i32, _pu64]),
+    "tsw_free": (_i32, [_vp, _cp, _u64]),
+    "tsw_memcpy_h2d_model": (_i32, [_vp, _cp, _u64, _vp, _u64, _vp]),
+    "tsw_sync_done": (_i32, [_vp, _cp]),
+    "tsw_mark_access": (_i32, [_vp, _u64]),
+    "tsw_memcpy_h2d": (_i32, [_vp, _cp, _u64, _vp, _u64, _vp]),
+    "tsw_memcpy_d2h": (_i32, [_vp, _cp, _vp, _u64, _u64, _vp]),
+    "tsw_memcpy_d2d": (_i32, [_vp, _cp, _u64, _u64, _u64, _vp]),
+    "tsw_memset": (_i32, [_vp, _cp, _u64, _i32, _u64, _vp]),
+    "tsw_swap_in": (_i32, [_vp, _cp, _i32]),
+    "tsw_swap_in_sharded": (_i32, [_vp, _cp, C.POINTER(_vp), _i32]),
+    "tsw_wait_ready": (_i32, [_vp, _cp, _i64]),
+    "tsw_check_alloc": (_i32, [_vp, _cp]),
+    "tsw_evict": (_i32, [_vp, _cp, _i32]),
+    "tsw_translate": (_i32, [_vp, _cp, _u64, _i32, _i64, _pu64]),
+    "tsw_is_model_address": (_i32, [_vp, _cp, _u64]),
+    "tsw_valid_memory_address": (_i32, [_vp, _cp, _u64]),
+    "tsw_dump_blocks": (_i32, [_vp, _cp, _vp, _i32]),
+    "tsw_dump_params": (_i32, [_vp, _cp, _vp, _i32]),
+    "tsw_pool_info": (_i32, [_vp, _pu64, _pu64, _pu64]),
+    "tsw_read_phys": (_i32, [_vp, _u64, _vp, _u64]),
+    "tsw_read_host_store": (_i32, [_vp, _cp, _u64, _vp, _u64]),
+    "tsw_checksum_resident": (_i32, [_vp, _cp, _vp, _i32]),
+    "tsw_stats": (_i32, [_vp, _pu64, _pu64, _pu64]),
+    "tsw_evictor_create": (_i32, [_cp, _i32, _u64, C.POINTER(_vp)]),
+    "tsw_evictor_destroy": (_i32, [_vp]),
+    "tsw_evictor_check_and_add": (_i32, [_vp, _i32, _cp, _u64, _i32, _vp, _i32]),
+    "tsw_evictor_force_evict": (_i32, [_vp, _i32, _cp]),
+    "tsw_evictor_lock": (_i32, [_vp, _i32, _cp]),
+    "tsw_evictor_unlock": (_i32, [_vp, _i32, _cp]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library, with argument types set."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: the swap engine has no fallback path. Build it with "
+                "`make -C torpor_b200/csrc` (needs nvcc).")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(rc: int) -> int:
+    if rc < 0:
+        raise SwapError(rc, lib().tsw_last_error().decode(errors="replace"))
+    return rc

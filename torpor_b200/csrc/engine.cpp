@@ -1,0 +1,1232 @@
+// Swap engine + C ABI.  See include/torpor_swap.h for the contract of every
+// entry point and the reference method it stands for.
+
+#include "engine.hpp"
+#include "kernels.hpp"
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <thread>
+
+#include <cuda_runtime.h>
+
+namespace tsw {
+
+static thread_local std::string g_err;
+int fail(int code, const std::string& msg) {
+    g_err = msg;
+    return code;
+}
+const std::string& last_error() { return g_err; }
+
+Repo& repo() {
+    static Repo r;
+    return r;
+}
+
+static std::mutex g_engines_mu;
+static std::map<int, tsw_engine*> g_engines;  // server id -> engine of this process
+
+#define TSW_CUDA(call)                                                                             \
+    do {                                                                                           \
+        cudaError_t _e = (call);                                                                   \
+        if (_e != cudaSuccess)                                                                     \
+            return fail(TSW_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(_e));         \
+    } while (0)
+
+namespace {
+
+class CudaMemory : public DeviceMemory {
+public:
+    explicit CudaMemory(int device) : device_(device) {}
+    int alloc(uint64_t size, uint64_t* phys) override {
+        void* p = nullptr;
+        if (cudaSetDevice(device_) != cudaSuccess) return -1;
+        cudaError_t e = cudaMalloc(&p, size);
+        if (e != cudaSuccess) {
+            fail(TSW_ERR_CUDA, std::string("cudaMalloc: ") + cudaGetErrorString(e));
+            return -1;
+        }
+        *phys = (uint64_t)p;
+        return 0;
+    }
+    int release(uint64_t phys) override {
+        cudaSetDevice(device_);
+        return cudaFree((void*)phys) == cudaSuccess ? 0 : -1;
+    }
+    bool plan_only() const override { return false; }
+private:
+    int device_;
+};
+
+class PlanMemory : public DeviceMemory {
+public:
+    int alloc(uint64_t, uint64_t*) override { return -1; }
+    int release(uint64_t) override { return 0; }
+    bool plan_only() const override { return true; }
+};
+
+using Lock = std::lock_guard<std::recursive_mutex>;
+
+int64_t now_ns() {
+    return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch())
+        .count();
+}
+
+Placement& placement(Model* m, int server_id) { return m->place[server_id]; }
+
+void size_placement(Model* m, Placement& pl) {
+    if (pl.blocks.size() < m->blocks.size()) pl.blocks.resize(m->blocks.size());
+    if (pl.params.size() < m->params.size()) pl.params.resize(m->params.size());
+    if (pl.has_row.size() < m->params.size()) pl.has_row.resize(m->params.size(), false);
+}
+
+// Make room for one pointer-table row per parameter.
+int ensure_rows(tsw_engine* e, Model* m, Placement& pl) {
+    size_placement(m, pl);
+    uint32_t need = (uint32_t)m->params.size();
+    if (need <= pl.capacity) return TSW_OK;
+    uint32_t cap = std::max<uint32_t>(need, 16);
+    volatile uint32_t* flag;
+    volatile uint64_t* phys;
+    if (e->plan) {
+        flag = (volatile uint32_t*)calloc(cap, sizeof(uint32_t));
+        phys = (volatile uint64_t*)calloc(cap, sizeof(uint64_t));
+        if (!flag || !phys) return fail(TSW_ERR_INVALID, "out of host memory for the pointer table");
+    } else {
+        flag = (volatile uint32_t*)e->host_slab.take(sizeof(uint32_t) * cap);
+        phys = (volatile uint64_t*)e->host_slab.take(sizeof(uint64_t) * cap);
+        void* hd = e->host_slab.take(sizeof(PlaceDesc) * cap);
+        void* hf = e->host_slab.take(sizeof(uint32_t) * (cap + 1));
+        void* dp = e->dev_slab.take(sizeof(uint64_t) * cap);
+        void* df = e->dev_slab.take(sizeof(uint32_t) * cap);
+        void* dc = e->dev_slab.take(sizeof(uint32_t) * cap);
+        void* dd = e->dev_slab.take(sizeof(PlaceDesc) * cap);
+        void* dt = e->dev_slab.take(sizeof(uint32_t) * (cap + 1));
+        if (!flag || !phys || !hd || !hf || !dp || !df || !dc || !dd || !dt)
+            return fail(TSW_ERR_POOL_EXHAUSTED, "pointer-table slab exhausted");
+        memset((void*)flag, 0, sizeof(uint32_t) * cap);
+        memset((void*)phys, 0, sizeof(uint64_t) * cap);
+        pl.h_descs = hd;
+        pl.h_first = (uint32_t*)hf;
+        pl.d_table_phys = (uint64_t*)dp;
+        pl.d_table_flag = (uint32_t*)df;
+        pl.d_done = (uint32_t*)dc;
+        pl.d_descs = dd;
+        pl.d_first = (uint32_t*)dt;
+        // the device slab is zero-filled at creation, so the tile counters start at 0
+    }
+    for (uint32_t i = 0; i < pl.capacity; ++i) {
+        flag[i] = pl.flag[i];
+        phys[i] = pl.phys[i];
+    }
+    pl.flag = flag;
+    pl.phys = phys;
+    pl.capacity = cap;
+    return TSW_OK;
+}
+
+void set_row(Placement& pl, int idx, uint32_t flag, uint64_t phys) {
+    pl.phys[idx] = phys;
+    pl.flag[idx] = flag;
+}
+
+// init_model_readiness (memory_manager.hpp:234-238): add a row for every parameter
+// that has none yet; existing rows keep their state.
+int init_readiness(tsw_engine* e, Model* m, Placement& pl, uint32_t flag) {
+    int rc = ensure_rows(e, m, pl);
+    if (rc != TSW_OK) return rc;
+    for (size_t i = 0; i < m->params.size(); ++i) {
+        if (!pl.has_row[i]) {
+            pl.has_row[i] = true;
+            set_row(pl, (int)i, flag, m->params[i].vaddr);
+        }
+    }
+    pl.readiness_init = true;
+    return TSW_OK;
+}
+
+uint8_t* alloc_mirror(tsw_engine* e, uint64_t size) {
+    if (e->plan) return (uint8_t*)malloc(size ? size : 1);
+    if (e->arena.base) {
+        uint64_t off = (e->arena.used + 4095) / 4096 * 4096;
+        if (off + size <= e->arena.size) {
+            e->arena.used = off + size;
+            return e->arena.base + off;
+        }
+    }
+    void* p = nullptr;
+    cudaSetDevice(e->cfg.device);
+    cudaError_t err = cudaHostAlloc(&p, size ? size : 1, cudaHostAllocPortable | cudaHostAllocMapped);
+    if (err != cudaSuccess) {
+        fail(TSW_ERR_CUDA, std::string("cudaHostAlloc(model store): ") + cudaGetErrorString(err));
+        return nullptr;
+    }
+    e->loose_host.push_back(p);
+    return (uint8_t*)p;
+}
+
+// Device-visible address of a byte of the host store.
+uint64_t host_dev_addr(tsw_engine* owner, const uint8_t* p) {
+    if (owner && owner->arena.base && p >= owner->arena.base && p < owner->arena.base + owner->arena.size)
+        return (uint64_t)((int64_t)(uint64_t)p + owner->arena.dev_delta);
+    return (uint64_t)p;  // cudaHostAlloc'ed memory is addressed identically on host and device
+}
+
+// find_block_ephe_ptr_mapping (model_repo.hpp:111-122)
+bool cache_interior_pointer(Model* m, uint64_t addr) {
+    if (m->data_block.count(addr)) return true;
+    for (auto& kv : m->block_order) {
+        VBlock& b = m->blocks[kv.second];
+        if (addr >= b.vaddr && addr < b.vaddr + b.size) {
+            m->data_block[addr] = kv.second;
+            b.ephe.push_back(addr);
+            return true;
+        }
+    }
+    return false;
+}
+
+// get_phy_address (memory_manager.hpp:542-568)
+uint64_t phy_address(tsw_engine* e, Model* m, uint64_t ptr, bool search_amid) {
+    if (!m) return ptr;
+    auto it = m->data_block.find(ptr);
+    if (it == m->data_block.end()) {
+        // The reference's valid_memory_address caches the mapping but always answers
+        // "no" (:293-298), so an interior pointer is returned untranslated the first
+        // time it is seen and translated from then on.
+        if (search_amid) cache_interior_pointer(m, ptr);
+        return ptr;
+    }
+    Placement& pl = placement(m, e->server_id);
+    size_placement(m, pl);
+    const Placement::B& b = pl.blocks[it->second];
+    if (b.in_cuda && b.cuda != 0) return ptr - m->blocks[it->second].vaddr + b.cuda;
+    return ptr;
+}
+
+struct WaitResult { int rc; uint64_t phys; };
+
+WaitResult wait_row(tsw_engine* e, Placement& pl, int idx, int64_t timeout_ns) {
+    const int64_t deadline = now_ns() + (timeout_ns < 0 ? 0 : timeout_ns);
+    int spins = 0;
+    while (pl.flag[idx] != TSW_READY_CUDA) {
+        if (e->h_status && *e->h_status) return {fail(TSW_ERR_KERNEL, "placement kernel reported an inconsistent tile table"), 0};
+        if ((++spins & 63) == 0) {
+            if (now_ns() > deadline) return {fail(TSW_ERR_TIMEOUT, "parameter did not become ready in time"), 0};
+            if (spins > 4096) std::this_thread::yield();
+        }
+    }
+    std::atomic_thread_fence(std::memory_order_acquire);
+    return {TSW_OK, pl.phys[idx]};
+}
+
+int make_arena(tsw_engine* e) {
+    const uint64_t size = e->cfg.host_arena_bytes;
+    if (size == 0) return TSW_OK;
+    HostArena& a = e->arena;
+    if (e->cfg.host_arena_shm && e->cfg.host_arena_shm[0]) {
+        a.shm_name = e->cfg.host_arena_shm;
+        a.shm_fd = shm_open(a.shm_name.c_str(), O_CREAT | O_RDWR, 0600);
+        if (a.shm_fd < 0) return fail(TSW_ERR_INVALID, "shm_open failed for the host arena");
+        if (ftruncate(a.shm_fd, (off_t)size) != 0) return fail(TSW_ERR_INVALID, "ftruncate failed for the host arena");
+        void* p = mmap(nullptr, size, PROT_READ | PROT_WRITE, MAP_SHARED, a.shm_fd, 0);
+        if (p == MAP_FAILED) return fail(TSW_ERR_INVALID, "mmap failed for the host arena");
+        a.base = (uint8_t*)p;
+        a.size = size;
+        a.owner = true;
+        TSW_CUDA(cudaHostRegister(p, size, cudaHostRegisterPortable | cudaHostRegisterMapped));
+        void* dp = nullptr;
+        TSW_CUDA(cudaHostGetDevicePointer(&dp, p, 0));
+        a.dev_delta = (int64_t)(uint64_t)dp - (int64_t)(uint64_t)p;
+    } else {
+        void* p = nullptr;
+        TSW_CUDA(cudaHostAlloc(&p, size, cudaHostAllocPortable | cudaHostAllocMapped));
+        a.base = (uint8_t*)p;
+        a.size = size;
+        a.owner = true;
+        a.dev_delta = 0;
+    }
+    return TSW_OK;
+}
+
+tsw_engine* engine_of_block_mirror(const uint8_t* p) {
+    std::lock_guard<std::mutex> g(g_engines_mu);
+    for (auto& kv : g_engines) {
+        HostArena& a = kv.second->arena;
+        if (a.base && p >= a.base && p < a.base + a.size) return kv.second;
+    }
+    return nullptr;
+}
+
+// check_and_malloc_model (memory_manager.hpp:451-507): place every block that is not
+// resident, in the reference's block order, and rebind the parameters inside it.
+int place_blocks(tsw_engine* e, Model* m, Placement& pl) {
+    std::vector<std::pair<uint64_t, uint64_t>> taken;  // for roll-back
+    for (auto& kv : m->block_order) {
+        const int bi = kv.second;
+        VBlock& vb = m->blocks[bi];
+        Placement::B& b = pl.blocks[bi];
+        if (b.known && b.in_cuda) continue;
+        DevAddr a;
+        if (e->pool->acquire(vb.size, false, &a) != 0) {
+            for (auto& t : taken) e->pool->evict(t.first, t.second, false);
+            e->pool->finish_release_block();
+            return fail(TSW_ERR_POOL_EXHAUSTED, "pool exhausted while placing " + m->name + ": " + e->pool->last_warning);
+        }
+        taken.emplace_back(a.phys, vb.size);
+        b.known = true;
+        b.in_cuda = true;
+        b.cuda = a.phys;
+        if (vb.is_model) {
+            for (int pi : vb.params) {   // the rebind (:477-479)
+                pl.params[pi].known = true;
+                pl.params[pi].cuda = m->params[pi].vaddr - vb.vaddr + a.phys;
+            }
+        }
+    }
+    e->active_params.clear();
+    for (int pi : m->access_order) e->active_params.insert(m->params[pi].vaddr);
+    e->pool->finish_block_alloc();
+    return TSW_OK;
+}
+
+uint32_t pick_tile(tsw_engine* e, bool host_side) { return host_side ? e->tile_host : e->tile_dev; }
+
+struct Plan {
+    std::vector<PlaceDesc> descs;
+    std::vector<uint32_t> first;  // n + 1
+    uint64_t bytes = 0;
+};
+
+void finish_plan(Plan& p, uint32_t tile) {
+    p.first.assign(p.descs.size() + 1, 0);
+    uint64_t t = 0;
+    for (size_t i = 0; i < p.descs.size(); ++i) {
+        p.first[i] = (uint32_t)t;
+        t += (p.descs[i].bytes + tile - 1) / tile;
+        p.bytes += p.descs[i].bytes;
+    }
+    p.first[p.descs.size()] = (uint32_t)t;
+}
+
+int upload_plan(tsw_engine* e, Placement& pl, const Plan& p) {
+    memcpy(pl.h_descs, p.descs.data(), sizeof(PlaceDesc) * p.descs.size());
+    memcpy(pl.h_first, p.first.data(), sizeof(uint32_t) * p.first.size());
+    cudaStream_t s = (cudaStream_t)e->stream;
+    TSW_CUDA(cudaMemcpyAsync(pl.d_descs, pl.h_descs, sizeof(PlaceDesc) * p.descs.size(), cudaMemcpyHostToDevice, s));
+    TSW_CUDA(cudaMemcpyAsync(pl.d_first, pl.h_first, sizeof(uint32_t) * p.first.size(), cudaMemcpyHostToDevice, s));
+    return TSW_OK;
+}
+
+}  // namespace
+}  // namespace tsw
+
+using namespace tsw;
+
+// =============================================================== C ABI
+
+extern "C" {
+
+const char* tsw_last_error(void) { return tsw::last_error().c_str(); }
+const char* tsw_version(void) { return "torpor-swap-b200 0.1 (sm_100a)"; }
+
+void tsw_config_default(tsw_config* c) {
+    memset(c, 0, sizeof(*c));
+    c->device = 0;
+    c->server_id = 0;
+    c->gpu_count = 1;
+    c->budget_bytes = 25ull << 30;  // default_gpu_mem_limit, controller.hpp:48
+    c->pool_policy = TSW_POOL_BUDDY;
+}
+
+int tsw_repo_reset(void) {
+    Repo& r = repo();
+    Lock g(r.mu);
+    // Page-locked mirrors belong to the engine that made them; only heap mirrors
+    // (plan-only engines) are released here.
+    for (auto& kv : r.models)
+        for (auto& b : kv.second->blocks)
+            if (b.mirror && b.mirror_heap) free(b.mirror);
+    r.models.clear();
+    r.active_devices.clear();
+    return TSW_OK;
+}
+
+int tsw_repo_add_model_info(const char* func, int gpu) {
+    Repo& r = repo();
+    Lock g(r.mu);
+    Model* m = r.get_or_create(func);
+    placement(m, gpu).status = TSW_MODEL_FULL;
+    r.active_devices[func].insert(gpu);
+    return TSW_OK;
+}
+
+int tsw_repo_remove_model_info(const char* func, int gpu) {
+    Repo& r = repo();
+    Lock g(r.mu);
+    Model* m = r.get_or_create(func);
+    placement(m, gpu).status = TSW_MODEL_NODATA;
+    r.active_devices[func].erase(gpu);
+    return TSW_OK;
+}
+
+int tsw_repo_model_status(const char* func, int gpu) {
+    Repo& r = repo();
+    Lock g(r.mu);
+    Model* m = r.find(func);
+    if (!m) return TSW_ERR_UNKNOWN_MODEL;
+    auto it = m->place.find(gpu);
+    if (it == m->place.end()) return TSW_ERR_NOT_FOUND;
+    return it->second.status;
+}
+
+uint64_t tsw_repo_total_size(const char* func) {
+    Repo& r = repo();
+    Lock g(r.mu);
+    Model* m = r.find(func);
+    return m ? m->total_size : 0;
+}
+
+int tsw_repo_active_devices(const char* func, int* gpus, int cap) {
+    Repo& r = repo();
+    Lock g(r.mu);
+    auto it = r.active_devices.find(func);
+    if (it == r.active_devices.end()) return 0;
+    int n = 0;
+    for (int gdev : it->second) {
+        if (n < cap && gpus) gpus[n] = gdev;
+        ++n;
+    }
+    return n;
+}
+
+int tsw_engine_create(const tsw_config* cfg, tsw_engine** out) {
+    if (!cfg || !out) return fail(TSW_ERR_INVALID, "null argument");
+    std::unique_ptr<tsw_engine> e(new tsw_engine());
+    e->cfg = *cfg;
+    e->plan = cfg->device < 0;
+    e->server_id = cfg->server_id;
+    e->tile_host = cfg->tile_bytes_host > 0 ? (uint32_t)cfg->tile_bytes_host : 64u * 1024;
+    e->tile_dev = cfg->tile_bytes_device > 0 ? (uint32_t)cfg->tile_bytes_device : 256u * 1024;
+    if ((e->tile_host & 15u) || (e->tile_dev & 15u)) return fail(TSW_ERR_INVALID, "tile sizes must be multiples of 16 bytes");
+    if (e->plan) {
+        e->mem.reset(new PlanMemory());
+    } else {
+        int n = 0;
+        cudaError_t err = cudaGetDeviceCount(&n);
+        if (err != cudaSuccess || cfg->device >= n)
+            return fail(TSW_ERR_NO_DEVICE, std::string("no usable CUDA device ") + std::to_string(cfg->device) +
+                                               (err != cudaSuccess ? std::string(": ") + cudaGetErrorString(err) : ""));
+        TSW_CUDA(cudaSetDevice(cfg->device));
+        e->mem.reset(new CudaMemory(cfg->device));
+        e->grid_ctas = cfg->grid_ctas > 0 ? cfg->grid_ctas : default_grid_ctas(cfg->device);
+        int lo = 0, hi = 0;
+        TSW_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        cudaStream_t s;
+        TSW_CUDA(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, hi));  // memory_manager.hpp:336
+        e->stream = s;
+        cudaEvent_t a, b;
+        TSW_CUDA(cudaEventCreate(&a));
+        TSW_CUDA(cudaEventCreate(&b));
+        e->ev_start = a;
+        e->ev_stop = b;
+        const uint64_t slab = 32ull << 20;
+        void* dp = nullptr;
+        TSW_CUDA(cudaMalloc(&dp, slab));
+        TSW_CUDA(cudaMemset(dp, 0, slab));
+        e->dev_slab.base = (uint8_t*)dp;
+        e->dev_slab.size = slab;
+        void* hp = nullptr;
+        TSW_CUDA(cudaHostAlloc(&hp, slab, cudaHostAllocPortable | cudaHostAllocMapped));
+        e->host_slab.base = (uint8_t*)hp;
+        e->host_slab.size = slab;
+        e->d_status = (uint32_t*)e->dev_slab.take(256);
+        e->h_status = (volatile uint32_t*)e->host_slab.take(256);
+        *e->h_status = 0;
+        int rc = make_arena(e.get());
+        if (rc != TSW_OK) return rc;
+        // all-pairs peer access, as the controller does at start-up (controller.hpp:63-75)
+        for (int j = 0; j < n; ++j) {
+            if (j == cfg->device) continue;
+            int can = 0;
+            if (cudaDeviceCanAccessPeer(&can, cfg->device, j) == cudaSuccess && can) {
+                cudaError_t pe = cudaDeviceEnablePeerAccess(j, 0);
+                if (pe != cudaSuccess) cudaGetLastError();  // already enabled is fine
+            }
+        }
+    }
+    const uint64_t total = cfg->budget_bytes + kHiddenBudget;  // memory_manager.hpp:43-44
+    e->pool = cfg->pool_policy == TSW_POOL_FIXED ? make_fixed_pool(total, cfg->server_id, e->mem.get())
+                                                 : make_buddy_pool(total, cfg->server_id, e->mem.get());
+    if (e->pool->init() != 0) return fail(TSW_ERR_CUDA, "pool allocation failed: " + tsw::last_error());
+    {
+        std::lock_guard<std::mutex> g(g_engines_mu);
+        g_engines[cfg->server_id] = e.get();
+    }
+    *out = e.release();
+    return TSW_OK;
+}
+
+int tsw_engine_destroy(tsw_engine* e) {
+    if (!e) return TSW_ERR_INVALID;
+    {
+        std::lock_guard<std::mutex> g(g_engines_mu);
+        auto it = g_engines.find(e->server_id);
+        if (it != g_engines.end() && it->second == e) g_engines.erase(it);
+    }
+    {
+        // rows of the pointer table live in this engine's slabs: drop its placements
+        Repo& r = repo();
+        Lock g(r.mu);
+        for (auto& kv : r.models) kv.second->place.erase(e->server_id);
+    }
+    if (!e->plan) {
+        cudaSetDevice(e->cfg.device);
+        if (e->stream) cudaStreamSynchronize((cudaStream_t)e->stream);
+        e->pool.reset();
+        if (e->dev_slab.base) cudaFree(e->dev_slab.base);
+        if (e->host_slab.base) cudaFreeHost(e->host_slab.base);
+        if (e->ev_start) cudaEventDestroy((cudaEvent_t)e->ev_start);
+        if (e->ev_stop) cudaEventDestroy((cudaEvent_t)e->ev_stop);
+        if (e->stream) cudaStreamDestroy((cudaStream_t)e->stream);
+        // The host model store outlives the engine only as long as the repository
+        // refers to it; callers reset the repository before destroying engines.
+        if (e->arena.base) {
+            if (e->arena.shm_fd >= 0) {
+                cudaHostUnregister(e->arena.base);
+                munmap(e->arena.base, e->arena.size);
+                close(e->arena.shm_fd);
+                if (e->arena.owner) shm_unlink(e->arena.shm_name.c_str());
+            } else {
+                cudaFreeHost(e->arena.base);
+            }
+        }
+        for (void* p : e->loose_host) cudaFreeHost(p);
+    }
+    delete e;
+    return TSW_OK;
+}
+
+int tsw_track_begin(tsw_engine* e, const char* func) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    e->tracking = true;
+    e->track_func = func;
+    repo().get_or_create(func)->status = TSW_MODEL_INCOMPLETE;  // start_model_load
+    return TSW_OK;
+}
+
+int tsw_track_end(tsw_engine* e, const char* func) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    if (e->tracking) repo().get_or_create(func)->status = TSW_MODEL_FULL;  // complete_model_load
+    e->tracking = false;
+    e->track_func.clear();
+    e->pool->finish_block_alloc();
+    return TSW_OK;
+}
+
+int tsw_malloc(tsw_engine* e, const char* func, uint64_t size, int load_model_flag, uint64_t* vptr) {
+    if (!e || !func || !vptr) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    DevAddr a;
+    if (e->pool->acquire(size, true, &a) != 0)
+        return fail(TSW_ERR_POOL_EXHAUSTED, "pool exhausted in malloc: " + e->pool->last_warning);
+    Model* m = repo().get_or_create(func);
+    // malloc_block_for_model (model_repo.hpp:133-141)
+    int bi;
+    auto known = m->block_by_vaddr.find(a.phys);
+    if (known != m->block_by_vaddr.end()) {
+        bi = known->second;
+    } else {
+        bi = (int)m->blocks.size();
+        m->blocks.emplace_back();
+        m->block_by_vaddr[a.phys] = bi;
+    }
+    VBlock& b = m->blocks[bi];
+    b.vaddr = a.phys;
+    b.canon = a.canon;
+    b.size = size;
+    b.is_model = load_model_flag != 0;
+    b.alive = true;
+    b.ephe.clear();
+    if (b.is_model) {
+        b.mirror = alloc_mirror(e, size);
+        b.mirror_heap = e->plan;
+        b.params.clear();
+        if (!b.mirror) {
+            e->pool->evict(a.phys, size, false);
+            return TSW_ERR_CUDA;
+        }
+    }
+    m->block_order[(void*)a.canon] = bi;
+    m->total_size += size;
+    Placement& pl = placement(m, e->server_id);
+    size_placement(m, pl);
+    pl.blocks[bi].known = true;
+    pl.blocks[bi].in_cuda = true;
+    pl.blocks[bi].cuda = a.phys;
+    *vptr = a.phys;
+    return TSW_OK;
+}
+
+int tsw_free(tsw_engine* e, const char* func, uint64_t vptr) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return TSW_OK;
+    auto it = m->block_by_vaddr.find(vptr);
+    if (it == m->block_by_vaddr.end()) return TSW_OK;
+    const int bi = it->second;
+    Placement& pl = placement(m, e->server_id);
+    size_placement(m, pl);
+    if (!pl.blocks[bi].known) return TSW_OK;
+    VBlock& b = m->blocks[bi];
+    if (b.is_model) return fail(TSW_ERR_STATE, "unexpected behaviour: free model block");
+    if (pl.blocks[bi].in_cuda) e->pool->evict(pl.blocks[bi].cuda, b.size, false);
+    // free_block_for_model (model_repo.hpp:144-149)
+    for (uint64_t p : b.ephe) m->data_block.erase(p);
+    b.ephe.clear();
+    b.alive = false;
+    m->block_order.erase((void*)b.canon);
+    m->block_by_vaddr.erase(it);
+    return TSW_OK;
+}
+
+int tsw_memcpy_h2d_model(tsw_engine* e, const char* func, uint64_t dst, const void* payload, uint64_t size,
+                         void* stream) {
+    if (!e || !func || (!payload && size)) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().get_or_create(func);
+    // load_model_h2d_at_start (model_repo.hpp:151-168): find the model block around dst
+    int bi = -1;
+    for (size_t i = 0; i < m->blocks.size(); ++i) {
+        const VBlock& b = m->blocks[i];
+        if (b.alive && b.is_model && dst >= b.vaddr && dst < b.vaddr + b.size) {
+            bi = (int)i;
+            break;
+        }
+    }
+    if (bi < 0) return fail(TSW_ERR_NOT_FOUND, "cudaMemcpy model fails to find malloc");
+    VBlock& b = m->blocks[bi];
+    if (dst + size > b.vaddr + b.size) return fail(TSW_ERR_INVALID, "upload runs past the end of its block");
+    uint8_t* host = b.mirror + (dst - b.vaddr);
+    if (size) memcpy(host, payload, size);
+    int pi;
+    auto pit = m->param_by_vaddr.find(dst);
+    if (pit == m->param_by_vaddr.end()) {
+        pi = (int)m->params.size();
+        m->params.emplace_back();
+        m->param_by_vaddr[dst] = pi;
+        b.params.push_back(pi);
+    } else {
+        pi = pit->second;
+        if (m->params[pi].block != bi) {
+            b.params.push_back(pi);
+        }
+    }
+    VParam& p = m->params[pi];
+    p.vaddr = dst;
+    p.size = size;
+    p.block = bi;
+    p.host = host;
+    m->data_block[dst] = bi;
+    Placement& pl = placement(m, e->server_id);
+    size_placement(m, pl);
+    pl.params[pi].known = true;
+    pl.params[pi].cuda = dst;  // param_virtual_to_cuda_[dst] = {nullptr, dst} (memory_manager.hpp:129)
+    if (!e->plan && size) {
+        // Upload from the page-locked copy just made, so the transfer is truly asynchronous.
+        TSW_CUDA(cudaSetDevice(e->cfg.device));
+        TSW_CUDA(cudaMemcpyAsync((void*)dst, host, size, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    }
+    return TSW_OK;
+}
+
+int tsw_sync_done(tsw_engine* e, const char* func) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().get_or_create(func);
+    return init_readiness(e, m, placement(m, e->server_id), TSW_READY_CUDA);
+}
+
+int tsw_mark_access(tsw_engine* e, uint64_t vptr) {
+    if (!e) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    if (!e->tracking) return 1;
+    Model* m = repo().get_or_create(e->track_func);
+    auto it = m->param_by_vaddr.find(vptr);
+    if (it == m->param_by_vaddr.end()) return 0;
+    // check_add_model_access_order (model_repo.hpp:102-109)
+    m->has_access_order = true;
+    VParam& p = m->params[it->second];
+    if (!p.accessed) {
+        p.accessed = true;
+        m->access_order.push_back(it->second);
+    }
+    return 1;
+}
+
+static int translated(tsw_engine* e, const char* func, uint64_t vptr, uint64_t* out) {
+    Model* m = repo().find(func);
+    *out = phy_address(e, m, vptr, true);
+    return TSW_OK;
+}
+
+int tsw_memcpy_h2d(tsw_engine* e, const char* func, uint64_t dst, const void* src, uint64_t size, void* stream) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine moves no bytes");
+    uint64_t phys;
+    {
+        Lock g1(repo().mu);
+        Lock g2(e->mu);
+        translated(e, func, dst, &phys);
+    }
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    TSW_CUDA(cudaMemcpyAsync((void*)phys, src, size, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    return TSW_OK;
+}
+
+int tsw_memcpy_d2h(tsw_engine* e, const char* func, void* dst, uint64_t src, uint64_t size, void* stream) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine moves no bytes");
+    uint64_t phys;
+    {
+        Lock g1(repo().mu);
+        Lock g2(e->mu);
+        translated(e, func, src, &phys);
+    }
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    TSW_CUDA(cudaMemcpyAsync(dst, (void*)phys, size, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return TSW_OK;
+}
+
+int tsw_memcpy_d2d(tsw_engine* e, const char* func, uint64_t dst, uint64_t src, uint64_t size, void* stream) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine moves no bytes");
+    uint64_t psrc = src, pdst = dst;
+    int is_param = tsw_is_model_address(e, func, src);
+    if (is_param == 1) {
+        // memory_manager.hpp:148-152: a parameter source is recorded as accessed and waited for
+        tsw_mark_access(e, src);
+        int rc = tsw_translate(e, func, src, 1, 5000000000ll, &psrc);
+        if (rc != TSW_OK) return rc;
+    } else {
+        Lock g1(repo().mu);
+        Lock g2(e->mu);
+        translated(e, func, src, &psrc);
+    }
+    {
+        Lock g1(repo().mu);
+        Lock g2(e->mu);
+        translated(e, func, dst, &pdst);
+    }
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    TSW_CUDA(cudaMemcpyAsync((void*)pdst, (void*)psrc, size, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return TSW_OK;
+}
+
+int tsw_memset(tsw_engine* e, const char* func, uint64_t vptr, int value, uint64_t size, void* stream) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine moves no bytes");
+    uint64_t phys;
+    {
+        Lock g1(repo().mu);
+        Lock g2(e->mu);
+        translated(e, func, vptr, &phys);
+    }
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    TSW_CUDA(cudaMemsetAsync((void*)phys, value, size, (cudaStream_t)stream));
+    return TSW_OK;
+}
+
+// --------------------------------------------------------------- swap-in
+
+static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine* const* helpers, int n_helpers) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, std::string("model ") + func + " not found in model repo");
+
+    // sig_trans_thread (memory_manager.hpp:213-227): an unhealthy source replica falls back to the host store
+    Placement* src_pl = nullptr;
+    tsw_engine* src_engine = nullptr;
+    if (src_gpu >= 0) {
+        auto it = m->place.find(src_gpu);
+        if (it != m->place.end() && it->second.status == TSW_MODEL_FULL) {
+            src_pl = &it->second;
+            std::lock_guard<std::mutex> g(g_engines_mu);
+            auto eit = g_engines.find(src_gpu);
+            if (eit != g_engines.end()) src_engine = eit->second;
+        }
+        if (!src_pl || (!e->plan && !src_engine)) {
+            src_pl = nullptr;
+            src_gpu = -1;
+        }
+    }
+
+    const bool first_time_here = m->place.find(e->server_id) == m->place.end();
+    Placement& pl = placement(m, e->server_id);
+    if (first_time_here) pl.status = TSW_MODEL_NODATA;  // init_device_model_info (model_repo.hpp:78-80)
+    size_placement(m, pl);
+    int rc;
+    if (!pl.readiness_init) {
+        rc = init_readiness(e, m, pl, TSW_READY_HOST);
+        if (rc != TSW_OK) return rc;
+    } else {
+        rc = ensure_rows(e, m, pl);
+        if (rc != TSW_OK) return rc;
+    }
+    if (!e->plan && pl.in_flight) {
+        TSW_CUDA(cudaSetDevice(e->cfg.device));
+        TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+        pl.in_flight = false;
+    }
+    rc = place_blocks(e, m, pl);
+    if (rc != TSW_OK) return rc;
+
+    // transfer_model (:331-438): every accessed parameter that is not on the device yet, in access order
+    const bool from_host = src_gpu < 0;
+    const uint32_t tile = pick_tile(e, from_host);
+    Plan plan;
+    for (int pi : m->access_order) {
+        if (!pl.has_row[pi] || pl.flag[pi] == TSW_READY_CUDA) continue;
+        const VParam& p = m->params[pi];
+        const uint64_t dst = pl.params[pi].cuda;
+        if (e->plan || p.size == 0) {
+            set_row(pl, pi, TSW_READY_CUDA, dst);
+            continue;
+        }
+        PlaceDesc d;
+        d.src = from_host ? host_dev_addr(engine_of_block_mirror(p.host), p.host) : src_pl->params[pi].cuda;
+        d.dst = dst;
+        d.bytes = p.size;
+        d.param = (uint32_t)pi;
+        d.pad = 0;
+        plan.descs.push_back(d);
+    }
+    if (e->plan || plan.descs.empty()) return TSW_OK;
+
+    finish_plan(plan, tile);
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    cudaStream_t s = (cudaStream_t)e->stream;
+    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_start, s));
+    rc = upload_plan(e, pl, plan);
+    if (rc != TSW_OK) return rc;
+
+    PlaceArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = (const PlaceDesc*)pl.d_descs;
+    a.first_tile = pl.d_first;
+    a.n_descs = (uint32_t)plan.descs.size();
+    a.tile_bytes = tile;
+    a.tile_lo = 0;
+    a.tile_hi = plan.first.back();
+    a.tile_stride = 1;
+    a.done_count = pl.d_done;
+    a.table_phys = pl.d_table_phys;
+    a.table_flag = pl.d_table_flag;
+    a.host_phys = (uint64_t*)pl.phys;
+    a.host_flag = (uint32_t*)pl.flag;
+    a.flag_value = TSW_READY_CUDA;
+    a.system_scope = (n_helpers > 0) ? 1u : 0u;
+    a.status = e->d_status;
+
+    if (n_helpers > 0) {
+        // Deal tiles round-robin over the participating GPUs: GPU r takes tiles r, r + n, ...
+        // so that every link works on the front of the access order at the same time.
+        const int n = n_helpers + 1;
+        TSW_CUDA(cudaStreamSynchronize(s));  // descriptors must be on the target before peers read them
+        a.tile_stride = (uint32_t)n;
+        for (int r = n - 1; r >= 0; --r) {
+            tsw_engine* w = r == 0 ? e : helpers[r - 1];
+            if (!w || w->plan) return fail(TSW_ERR_INVALID, "sharded swap needs CUDA engines as helpers");
+            PlaceArgs ar = a;
+            ar.tile_lo = (uint32_t)r;
+            TSW_CUDA(cudaSetDevice(w->cfg.device));
+            cudaError_t le = launch_place(ar, w->grid_ctas, (cudaStream_t)w->stream);
+            if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
+            w->kernel_launches++;
+        }
+        TSW_CUDA(cudaSetDevice(e->cfg.device));
+    } else {
+        cudaError_t le = launch_place(a, e->grid_ctas, s);
+        if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
+        e->kernel_launches++;
+    }
+    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_stop, s));
+    e->ev_valid = true;
+    e->bytes_moved += plan.bytes;
+    pl.in_flight = true;
+    return TSW_OK;
+}
+
+int tsw_swap_in(tsw_engine* e, const char* func, int src_gpu) { return swap_in_impl(e, func, src_gpu, nullptr, 0); }
+
+int tsw_swap_in_sharded(tsw_engine* e, const char* func, tsw_engine* const* helpers, int n_helpers) {
+    if (n_helpers < 0 || (n_helpers > 0 && !helpers)) return fail(TSW_ERR_INVALID, "bad helper list");
+    return swap_in_impl(e, func, -1, helpers, n_helpers);
+}
+
+int tsw_wait_ready(tsw_engine* e, const char* func, int64_t timeout_ns) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Placement* pl;
+    std::vector<int> order;
+    {
+        Lock g1(repo().mu);
+        Lock g2(e->mu);
+        Model* m = repo().find(func);
+        if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
+        pl = &placement(m, e->server_id);
+        if (!pl->readiness_init) return fail(TSW_ERR_STATE, "model has no readiness rows on this engine");
+        for (int pi : m->access_order)
+            if (pl->has_row[pi]) order.push_back(pi);
+    }
+    const int64_t deadline = now_ns() + timeout_ns;
+    // the kernel completes parameters roughly in access order: wait from the back
+    for (auto it = order.rbegin(); it != order.rend(); ++it) {
+        int64_t left = deadline - now_ns();
+        WaitResult w = wait_row(e, *pl, *it, left > 0 ? left : 0);
+        if (w.rc != TSW_OK) return w.rc;
+    }
+    return TSW_OK;
+}
+
+int tsw_check_alloc(tsw_engine* e, const char* func) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return 0;
+    auto it = m->place.find(e->server_id);
+    if (it == m->place.end()) return 0;
+    Placement& pl = it->second;
+    size_placement(m, pl);
+    for (auto& kv : m->block_order) {
+        const Placement::B& b = pl.blocks[kv.second];
+        if (!b.known || !b.in_cuda) return 0;
+    }
+    return 1;
+}
+
+// --------------------------------------------------------------- swap-out
+
+int tsw_evict(tsw_engine* e, const char* func, int writeback) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "try to evict unrecognized model");
+    auto pit = m->place.find(e->server_id);
+    if (pit == m->place.end() || !pit->second.readiness_init)
+        return fail(TSW_ERR_UNKNOWN_MODEL, "try to evict unrecognized model");  // memory_manager.hpp:241-244
+    Placement& pl = pit->second;
+    size_placement(m, pl);
+
+    if (!e->plan) {
+        TSW_CUDA(cudaSetDevice(e->cfg.device));
+        if (pl.in_flight) {
+            TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+            pl.in_flight = false;
+        }
+        if (writeback) {
+            // Eviction write-back: resident parameter bytes -> host store, through the same kernel.
+            Plan plan;
+            for (size_t pi = 0; pi < m->params.size(); ++pi) {
+                if (!pl.has_row[pi] || pl.flag[pi] != TSW_READY_CUDA) continue;
+                const VParam& p = m->params[pi];
+                const Placement::B& b = pl.blocks[p.block];
+                if (!b.in_cuda || p.size == 0) continue;
+                PlaceDesc d;
+                d.src = pl.params[pi].cuda;
+                d.dst = host_dev_addr(engine_of_block_mirror(p.host), p.host);
+                d.bytes = p.size;
+                d.param = (uint32_t)pi;
+                d.pad = 0;
+                plan.descs.push_back(d);
+            }
+            if (!plan.descs.empty()) {
+                int rc = ensure_rows(e, m, pl);
+                if (rc != TSW_OK) return rc;
+                finish_plan(plan, e->tile_host);
+                rc = upload_plan(e, pl, plan);
+                if (rc != TSW_OK) return rc;
+                PlaceArgs a;
+                memset(&a, 0, sizeof(a));
+                a.descs = (const PlaceDesc*)pl.d_descs;
+                a.first_tile = pl.d_first;
+                a.n_descs = (uint32_t)plan.descs.size();
+                a.tile_bytes = e->tile_host;
+                a.tile_lo = 0;
+                a.tile_hi = plan.first.back();
+                a.tile_stride = 1;
+                a.system_scope = 1;
+                a.status = e->d_status;
+                cudaError_t le = launch_place(a, e->grid_ctas, (cudaStream_t)e->stream);
+                if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("write-back kernel launch: ") + cudaGetErrorString(le));
+                e->kernel_launches++;
+                e->bytes_moved += plan.bytes;
+                TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+            }
+        }
+    }
+
+    // evict_model (:247-256): release every resident block, in the reference's block order
+    for (auto& kv : m->block_order) {
+        const int bi = kv.second;
+        Placement::B& b = pl.blocks[bi];
+        if (!b.in_cuda) continue;
+        b.in_cuda = false;
+        e->pool->evict(b.cuda, m->blocks[bi].size, false);
+        if (m->blocks[bi].is_model) {
+            for (int pi : m->blocks[bi].params)  // reset_model_readiness (:301-309)
+                if (pl.has_row[pi]) set_row(pl, pi, TSW_READY_HOST, 0);
+        }
+    }
+    e->pool->finish_release_block();
+    return TSW_OK;
+}
+
+// --------------------------------------------------------------- translation
+
+int tsw_translate(tsw_engine* e, const char* func, uint64_t vptr, int search_amid, int64_t timeout_ns, uint64_t* out) {
+    if (!e || !func || !out) return fail(TSW_ERR_INVALID, "null argument");
+    Placement* wait_pl = nullptr;
+    int wait_idx = -1;
+    {
+        Lock g1(repo().mu);
+        Lock g2(e->mu);
+        Model* m = repo().find(func);
+        if (!m || m->place.find(e->server_id) == m->place.end()) {
+            *out = vptr;  // memory_manager.hpp:270
+            return TSW_OK;
+        }
+        auto pit = m->param_by_vaddr.find(vptr);
+        if (pit == m->param_by_vaddr.end()) {
+            *out = phy_address(e, m, vptr, search_amid != 0);
+            return TSW_OK;
+        }
+        // check_param_readiness (:527-540)
+        Placement& pl = placement(m, e->server_id);
+        size_placement(m, pl);
+        const int pi = pit->second;
+        if (!pl.readiness_init) {
+            *out = vptr;
+            return TSW_OK;
+        }
+        if (e->active_params.count(vptr) && pl.has_row[pi]) {
+            wait_pl = &pl;
+            wait_idx = pi;
+        } else {
+            *out = pl.params[pi].cuda;
+            return TSW_OK;
+        }
+    }
+    WaitResult w = wait_row(e, *wait_pl, wait_idx, timeout_ns);
+    if (w.rc != TSW_OK) return w.rc;
+    *out = w.phys;
+    return TSW_OK;
+}
+
+int tsw_is_model_address(tsw_engine* e, const char* func, uint64_t vptr) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Model* m = repo().find(func);
+    return (m && m->param_by_vaddr.count(vptr)) ? 1 : 0;
+}
+
+int tsw_valid_memory_address(tsw_engine* e, const char* func, uint64_t vptr) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Model* m = repo().find(func);
+    if (m) cache_interior_pointer(m, vptr);
+    return 0;
+}
+
+// --------------------------------------------------------------- introspection
+
+int tsw_dump_blocks(tsw_engine* e, const char* func, uint64_t* out, int cap) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return 0;
+    auto pit = m->place.find(e->server_id);
+    int n = 0;
+    for (auto& kv : m->block_order) {
+        if (out && n < cap) {
+            const VBlock& b = m->blocks[kv.second];
+            uint64_t* o = out + 6 * n;
+            o[0] = b.vaddr;
+            o[1] = b.size;
+            o[2] = b.is_model;
+            o[3] = o[4] = o[5] = 0;
+            if (pit != m->place.end() && (size_t)kv.second < pit->second.blocks.size() && pit->second.blocks[kv.second].known) {
+                o[3] = pit->second.blocks[kv.second].in_cuda;
+                o[4] = pit->second.blocks[kv.second].cuda;
+            }
+        }
+        ++n;
+    }
+    return n;
+}
+
+static std::vector<int> dump_order(Model* m) {
+    std::vector<int> order = m->access_order;
+    std::vector<int> rest;
+    for (size_t i = 0; i < m->params.size(); ++i)
+        if (!m->params[i].accessed) rest.push_back((int)i);
+    std::sort(rest.begin(), rest.end(), [m](int a, int b) { return m->params[a].vaddr < m->params[b].vaddr; });
+    order.insert(order.end(), rest.begin(), rest.end());
+    return order;
+}
+
+int tsw_dump_params(tsw_engine* e, const char* func, uint64_t* out, int cap) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return 0;
+    auto pit = m->place.find(e->server_id);
+    std::vector<int> order = dump_order(m);
+    int n = 0;
+    for (int pi : order) {
+        if (out && n < cap) {
+            const VParam& p = m->params[pi];
+            uint64_t* o = out + 7 * n;
+            o[0] = p.vaddr;
+            o[1] = p.size;
+            o[2] = m->blocks[p.block].vaddr;
+            o[3] = 0;
+            o[4] = (uint64_t)-1;
+            o[5] = 0;
+            if (pit != m->place.end()) {
+                const Placement& pl = pit->second;
+                if ((size_t)pi < pl.params.size() && pl.params[pi].known) o[3] = pl.params[pi].cuda;
+                if ((size_t)pi < pl.has_row.size() && pl.has_row[pi]) {
+                    o[4] = pl.flag[pi];
+                    o[5] = pl.phys[pi];
+                }
+            }
+            o[6] = p.accessed ? 1 : 0;
+        }
+        ++n;
+    }
+    return n;
+}
+
+int tsw_pool_info(tsw_engine* e, uint64_t* pool_base, uint64_t* n_chunks, uint64_t* canon_base) {
+    if (!e) return fail(TSW_ERR_INVALID, "null argument");
+    if (pool_base) *pool_base = e->pool->pool_base();
+    if (n_chunks) *n_chunks = e->pool->pool_chunks();
+    if (canon_base) *canon_base = kCanonBase + (uint64_t)e->server_id * kCanonStride;
+    return TSW_OK;
+}
+
+int tsw_read_phys(tsw_engine* e, uint64_t addr, void* out, uint64_t size) {
+    if (!e || !out) return fail(TSW_ERR_INVALID, "null argument");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine holds no bytes");
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    TSW_CUDA(cudaMemcpy(out, (void*)addr, size, cudaMemcpyDeviceToHost));
+    return TSW_OK;
+}
+
+int tsw_read_host_store(tsw_engine* e, const char* func, uint64_t vptr, void* out, uint64_t size) {
+    if (!e || !func || !out) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Model* m = repo().find(func);
+    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
+    auto it = m->param_by_vaddr.find(vptr);
+    if (it == m->param_by_vaddr.end() || m->params[it->second].size < size) return fail(TSW_ERR_NOT_FOUND, "no such parameter");
+    memcpy(out, m->params[it->second].host, size);
+    return TSW_OK;
+}
+
+int tsw_checksum_resident(tsw_engine* e, const char* func, uint64_t* out, int cap) {
+    if (!e || !func || !out) return fail(TSW_ERR_INVALID, "null argument");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine holds no bytes");
+    std::vector<SumDesc> descs;
+    int n_rows = 0;
+    const uint32_t tile = 256u * 1024;
+    {
+        Lock g1(repo().mu);
+        Lock g2(e->mu);
+        Model* m = repo().find(func);
+        if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
+        Placement& pl = placement(m, e->server_id);
+        size_placement(m, pl);
+        std::vector<int> order = dump_order(m);
+        n_rows = (int)order.size();
+        if (n_rows > cap) return fail(TSW_ERR_BUFFER, "checksum buffer too small");
+        uint64_t t = 0;
+        for (int row = 0; row < n_rows; ++row) {
+            const int pi = order[row];
+            const VParam& p = m->params[pi];
+            if (!pl.params[pi].known || !pl.blocks[p.block].in_cuda || p.size == 0) continue;
+            SumDesc d;
+            d.addr = pl.params[pi].cuda;
+            d.bytes = p.size;
+            d.first_tile = (uint32_t)t;
+            d.row = (uint32_t)row;
+            descs.push_back(d);
+            t += (p.size + tile - 1) / tile;
+        }
+        memset(out, 0, sizeof(uint64_t) * 2 * n_rows);
+        if (descs.empty()) return n_rows;
+        TSW_CUDA(cudaSetDevice(e->cfg.device));
+        cudaStream_t s = (cudaStream_t)e->stream;
+        TSW_CUDA(cudaStreamSynchronize(s));
+        void* d_descs = nullptr;
+        void* d_out = nullptr;
+        TSW_CUDA(cudaMalloc(&d_descs, sizeof(SumDesc) * descs.size()));
+        TSW_CUDA(cudaMalloc(&d_out, sizeof(uint64_t) * 2 * n_rows));
+        TSW_CUDA(cudaMemcpyAsync(d_descs, descs.data(), sizeof(SumDesc) * descs.size(), cudaMemcpyHostToDevice, s));
+        TSW_CUDA(cudaMemsetAsync(d_out, 0, sizeof(uint64_t) * 2 * n_rows, s));
+        cudaError_t le = launch_checksum((const SumDesc*)d_descs, (uint32_t)descs.size(), (uint32_t)t, tile,
+                                         (unsigned long long*)d_out, e->grid_ctas, s);
+        if (le == cudaSuccess) le = cudaMemcpyAsync(out, d_out, sizeof(uint64_t) * 2 * n_rows, cudaMemcpyDeviceToHost, s);
+        if (le == cudaSuccess) le = cudaStreamSynchronize(s);
+        cudaFree(d_descs);
+        cudaFree(d_out);
+        if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("checksum: ") + cudaGetErrorString(le));
+        e->kernel_launches++;
+    }
+    return n_rows;
+}
+
+int tsw_stats(tsw_engine* e, uint64_t* kernel_launches, uint64_t* bytes_moved, uint64_t* last_swap_device_ns) {
+    if (!e) return fail(TSW_ERR_INVALID, "null argument");
+    if (kernel_launches) *kernel_launches = e->kernel_launches.load();
+    if (bytes_moved) *bytes_moved = e->bytes_moved.load();
+    if (last_swap_device_ns) {
+        *last_swap_device_ns = 0;
+        if (!e->plan && e->ev_valid) {
+            cudaSetDevice(e->cfg.device);
+            if (cudaEventSynchronize((cudaEvent_t)e->ev_stop) == cudaSuccess) {
+                float ms = 0;
+                if (cudaEventElapsedTime(&ms, (cudaEvent_t)e->ev_start, (cudaEvent_t)e->ev_stop) == cudaSuccess)
+                    *last_swap_device_ns = (uint64_t)(ms * 1e6);
+            }
+        }
+    }
+    return TSW_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,79 @@
+// The swap engine: one per GPU, the counterpart of the reference's
+// server::manager::MemoryManager (include/server/memory_manager.hpp:36-598).
+#ifndef TORPOR_SWAP_ENGINE_HPP_
+#define TORPOR_SWAP_ENGINE_HPP_
+
+#include <atomic>
+#include <cstdint>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <unordered_set>
+#include <vector>
+
+#include "../../include/torpor_swap.h"
+#include "pool.hpp"
+#include "repo.hpp"
+
+namespace tsw {
+
+int fail(int code, const std::string& msg);
+const std::string& last_error();
+
+// Bump allocator over one allocation; rows of the pointer table and launch
+// descriptors are carved from two of these (device, host-mapped) so that a swap
+// never calls the CUDA allocator.
+struct Slab {
+    uint8_t* base = nullptr;
+    uint64_t size = 0, used = 0;
+    void* take(uint64_t n, uint64_t align = 256) {
+        uint64_t off = (used + align - 1) / align * align;
+        if (off + n > size) return nullptr;
+        used = off + n;
+        return base + off;
+    }
+};
+
+struct HostArena {
+    uint8_t* base = nullptr;      // host address
+    int64_t dev_delta = 0;        // device-visible address = host address + dev_delta
+    uint64_t size = 0, used = 0;
+    std::string shm_name;
+    int shm_fd = -1;
+    bool owner = false;
+};
+
+}  // namespace tsw
+
+struct tsw_engine {
+    tsw_config cfg;
+    bool plan = false;
+    int server_id = 0;
+    std::unique_ptr<tsw::DeviceMemory> mem;
+    std::unique_ptr<tsw::Pool> pool;
+    std::recursive_mutex mu;
+
+    // set_track_model_memory state (memory_manager.hpp:576)
+    bool tracking = false;
+    std::string track_func;
+    // active_model_params_ (:591): parameters of the model swapped in last
+    std::unordered_set<uint64_t> active_params;
+
+    void* stream = nullptr;       // transfer stream (cudaStream_t), high priority
+    void* ev_start = nullptr;     // cudaEvent_t pair around the last swap
+    void* ev_stop = nullptr;
+    bool ev_valid = false;
+    tsw::Slab dev_slab, host_slab;
+    tsw::HostArena arena;
+    uint32_t* d_status = nullptr;
+    volatile uint32_t* h_status = nullptr;
+
+    int grid_ctas = 0;
+    uint32_t tile_host = 0, tile_dev = 0;
+
+    std::atomic<uint64_t> kernel_launches{0};
+    std::atomic<uint64_t> bytes_moved{0};
+    std::vector<void*> loose_host;   // page-locked mirrors outside the arena
+};
+
+#endif

@@ -1,0 +1,244 @@
+// sm_100a kernels of the swap engine.
+//
+// place_kernel is the one data mover: a persistent grid walks the tiles of a
+// swap in first-run access order, copies each tile with 16-byte vector
+// loads/stores, and -- fused into the same kernel -- counts finished tiles per
+// parameter; whoever finishes a parameter's last tile rewrites its row of the
+// device-pointer table (rebound address, readiness) and the host-visible mirror
+// of that row.  It replaces, in the reference, the per-parameter
+// cudaMemcpyAsync / cudaMemcpyPeerAsync loop with its host-side staging copy and
+// per-group event round trip (include/server/memory_manager.hpp:311-329,
+// 375-409,441-449).  Source and destination may each be page-locked host memory
+// (read or written across PCIe by the SMs), this GPU's pool, or a peer GPU's pool
+// across NVLink; nothing in it waits on another kernel.
+//
+// The work is byte movement bound by PCIe, NVLink or HBM; there is no
+// contraction in it, so no tensor-core path.
+
+#include "kernels.hpp"
+
+namespace tsw {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 8;
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void st_stream16(void* p, const uint4& v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+// Bytes [0, len) from src to dst where src and dst are congruent modulo 16.
+__device__ __forceinline__ void copy_span16(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                            uint32_t len) {
+    const uint32_t tid = threadIdx.x;
+    uint32_t head = (16u - (uint32_t)((uintptr_t)dst & 15u)) & 15u;
+    if (head > len) head = len;
+    if (tid < head) dst[tid] = src[tid];
+    const uint32_t n16 = (len - head) >> 4;
+    const uint8_t* s = src + head;
+    uint8_t* d = dst + head;
+    for (uint32_t i = tid; i < n16; i += kThreads * kUnroll) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            uint32_t idx = i + u * kThreads;
+            if (idx < n16) v[u] = ld_stream16(s + ((size_t)idx << 4));
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            uint32_t idx = i + u * kThreads;
+            if (idx < n16) st_stream16(d + ((size_t)idx << 4), v[u]);
+        }
+    }
+    const uint32_t done = head + (n16 << 4);
+    const uint32_t tail = len - done;
+    if (tid < tail) dst[done + tid] = src[done + tid];
+}
+
+// Same for the rare case of a source and destination that disagree modulo 16:
+// fall back to the widest word both sides can be aligned to.
+template <typename T>
+__device__ __forceinline__ void copy_span_narrow(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                 uint32_t len) {
+    constexpr uint32_t W = sizeof(T);
+    const uint32_t tid = threadIdx.x;
+    uint32_t head = (W - (uint32_t)((uintptr_t)dst & (W - 1))) & (W - 1);
+    if (head > len) head = len;
+    if (tid < head) dst[tid] = src[tid];
+    const uint32_t n = (len - head) / W;
+    const T* s = reinterpret_cast<const T*>(src + head);
+    T* d = reinterpret_cast<T*>(dst + head);
+    for (uint32_t i = tid; i < n; i += kThreads) d[i] = s[i];
+    const uint32_t done = head + n * W;
+    const uint32_t tail = len - done;
+    if (tid < tail) dst[done + tid] = src[done + tid];
+}
+
+__device__ __forceinline__ void copy_span(uint64_t src, uint64_t dst, uint32_t len) {
+    const uint8_t* s = reinterpret_cast<const uint8_t*>(src);
+    uint8_t* d = reinterpret_cast<uint8_t*>(dst);
+    const uint32_t diff = (uint32_t)((src ^ dst) & 15u);
+    if (diff == 0) copy_span16(s, d, len);
+    else if ((diff & 7u) == 0) copy_span_narrow<uint2>(s, d, len);
+    else if ((diff & 3u) == 0) copy_span_narrow<uint32_t>(s, d, len);
+    else if ((diff & 1u) == 0) copy_span_narrow<uint16_t>(s, d, len);
+    else copy_span_narrow<uint8_t>(s, d, len);
+}
+
+// Largest k in [0, n) with first[k] <= t (first[] is non-decreasing, first[0] == 0).
+__device__ __forceinline__ uint32_t owner_of_tile(const uint32_t* first, uint32_t n, uint32_t t) {
+    uint32_t lo = 0, hi = n;
+    while (hi - lo > 1) {
+        uint32_t mid = (lo + hi) >> 1;
+        if (first[mid] <= t) lo = mid;
+        else hi = mid;
+    }
+    return lo;
+}
+
+__global__ void __launch_bounds__(kThreads) place_kernel(const PlaceArgs a) {
+    extern __shared__ uint32_t s_first[];  // n_descs + 1 tile prefix sums
+    for (uint32_t i = threadIdx.x; i <= a.n_descs; i += kThreads) s_first[i] = a.first_tile[i];
+    __syncthreads();
+
+    const uint64_t step = (uint64_t)gridDim.x * a.tile_stride;
+    for (uint64_t t64 = a.tile_lo + (uint64_t)blockIdx.x * a.tile_stride; t64 < a.tile_hi; t64 += step) {
+        const uint32_t t = (uint32_t)t64;
+        const uint32_t k = owner_of_tile(s_first, a.n_descs, t);
+        const PlaceDesc d = a.descs[k];
+        const uint64_t off = (uint64_t)(t - s_first[k]) * a.tile_bytes;
+        if (off >= d.bytes) {  // table and tile numbering disagree: report, move nothing
+            if (threadIdx.x == 0 && a.status) atomicExch(a.status, 1u);
+            continue;
+        }
+        const uint64_t left = d.bytes - off;
+        const uint32_t len = left < a.tile_bytes ? (uint32_t)left : a.tile_bytes;
+        copy_span(d.src + off, d.dst + off, len);
+
+        if (a.done_count) {
+            if (a.system_scope) __threadfence_system();
+            else __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const uint32_t n_tiles = s_first[k + 1] - s_first[k];
+                const uint32_t before =
+                    a.system_scope ? atomicAdd_system(&a.done_count[k], 1u) : atomicAdd(&a.done_count[k], 1u);
+                if (before + 1 == n_tiles) {
+                    // Last tile of this parameter, possibly finished by another GPU's
+                    // CTAs: re-arm the counter, rebind the table row, then raise the flag.
+                    a.done_count[k] = 0;
+                    __threadfence_system();
+                    a.table_phys[d.param] = d.dst;
+                    if (a.host_phys) a.host_phys[d.param] = d.dst;
+                    __threadfence_system();
+                    a.table_flag[d.param] = a.flag_value;
+                    if (a.host_flag) a.host_flag[d.param] = a.flag_value;
+                    __threadfence_system();
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ checksum
+
+__device__ __forceinline__ uint32_t load_word(const uint8_t* base, uint64_t byte_off, uint64_t total, bool aligned) {
+    if (aligned && byte_off + 4 <= total) return *reinterpret_cast<const uint32_t*>(base + byte_off);
+    uint32_t w = 0;
+    for (int b = 0; b < 4; ++b)
+        if (byte_off + b < total) w |= (uint32_t)base[byte_off + b] << (8 * b);
+    return w;
+}
+
+__global__ void __launch_bounds__(kThreads) checksum_kernel(const SumDesc* descs, uint32_t n_descs,
+                                                            uint32_t total_tiles, uint32_t tile_bytes,
+                                                            unsigned long long* out) {
+    __shared__ unsigned long long red[2][kThreads / 32];
+    for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        uint32_t lo = 0, hi = n_descs;
+        while (hi - lo > 1) {
+            uint32_t mid = (lo + hi) >> 1;
+            if (descs[mid].first_tile <= t) lo = mid;
+            else hi = mid;
+        }
+        const SumDesc d = descs[lo];
+        const uint64_t off = (uint64_t)(t - d.first_tile) * tile_bytes;
+        unsigned long long s1 = 0, s2 = 0;
+        if (off < d.bytes) {
+            const uint64_t left = d.bytes - off;
+            const uint64_t len = left < tile_bytes ? left : tile_bytes;
+            const uint64_t n_words = (len + 3) >> 2;
+            const uint8_t* base = reinterpret_cast<const uint8_t*>(d.addr);
+            const bool aligned = (d.addr & 3ull) == 0;
+            const uint64_t word0 = off >> 2;
+            for (uint64_t i = threadIdx.x; i < n_words; i += kThreads) {
+                const unsigned long long w = load_word(base, off + (i << 2), d.bytes, aligned);
+                s1 += w;
+                s2 += (word0 + i + 1ull) * w;
+            }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            s1 += __shfl_down_sync(0xffffffffu, s1, o);
+            s2 += __shfl_down_sync(0xffffffffu, s2, o);
+        }
+        if ((threadIdx.x & 31) == 0) {
+            red[0][threadIdx.x >> 5] = s1;
+            red[1][threadIdx.x >> 5] = s2;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned long long a1 = 0, a2 = 0;
+            for (int w = 0; w < kThreads / 32; ++w) {
+                a1 += red[0][w];
+                a2 += red[1][w];
+            }
+            atomicAdd(&out[2 * d.row], a1);
+            atomicAdd(&out[2 * d.row + 1], a2);
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace
+
+int default_grid_ctas(int device) {
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    return sms * 4;
+}
+
+cudaError_t launch_place(const PlaceArgs& a, int grid_ctas, cudaStream_t stream) {
+    if (a.n_descs == 0 || a.tile_hi <= a.tile_lo) return cudaSuccess;
+    if (a.tile_bytes == 0 || (a.tile_bytes & 15u) || a.tile_stride == 0) return cudaErrorInvalidValue;
+    const uint64_t mine = ((uint64_t)(a.tile_hi - a.tile_lo) + a.tile_stride - 1) / a.tile_stride;
+    int grid = grid_ctas > 0 ? grid_ctas : 592;
+    if ((uint64_t)grid > mine) grid = (int)mine;
+    const size_t smem = sizeof(uint32_t) * ((size_t)a.n_descs + 1);
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    place_kernel<<<grid, kThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_checksum(const SumDesc* descs, uint32_t n_descs, uint32_t total_tiles, uint32_t tile_bytes,
+                            unsigned long long* out, int grid_ctas, cudaStream_t stream) {
+    if (n_descs == 0 || total_tiles == 0) return cudaSuccess;
+    int grid = grid_ctas > 0 ? grid_ctas : 592;
+    if ((uint32_t)grid > total_tiles) grid = (int)total_tiles;
+    checksum_kernel<<<grid, kThreads, 0, stream>>>(descs, n_descs, total_tiles, tile_bytes, out);
+    return cudaGetLastError();
+}
+
+}  // namespace tsw

@@ -1,0 +1,58 @@
+// Launch interface of the sm_100a kernels (kernels.cu).
+#ifndef TORPOR_SWAP_KERNELS_HPP_
+#define TORPOR_SWAP_KERNELS_HPP_
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace tsw {
+
+// One parameter's move.  Tiles are numbered over the whole swap: parameter k
+// owns tiles [first_tile[k], first_tile[k+1]).
+struct PlaceDesc {
+    uint64_t src;    // host-mapped, local or peer address
+    uint64_t dst;    // local pool, peer pool or host-mapped address
+    uint64_t bytes;
+    uint32_t param;  // row of the pointer table this move completes
+    uint32_t pad;
+};
+
+struct PlaceArgs {
+    const PlaceDesc* descs;       // device-readable, n_descs entries
+    const uint32_t* first_tile;   // device-readable, n_descs + 1 entries
+    uint32_t n_descs;
+    uint32_t tile_bytes;          // multiple of 16
+    uint32_t tile_lo, tile_hi;    // this launch handles tiles tile_lo + i * tile_stride < tile_hi
+    uint32_t tile_stride;
+    // Completion and rebind.  done_count lives with the TARGET of the swap so that
+    // several GPUs can finish tiles of the same parameter; may be null (then nothing
+    // is published and the launch is just a copy).
+    uint32_t* done_count;         // per desc, must be 0 at launch, left 0 on completion
+    uint64_t* table_phys;         // device pointer table: rebound address per param
+    uint32_t* table_flag;         //                       readiness per param
+    uint64_t* host_phys;          // host-mapped mirror of the two columns (may be null)
+    uint32_t* host_flag;
+    uint32_t flag_value;          // written to the flag columns when a param completes
+    uint32_t system_scope;        // 1: stores may target a peer GPU / host memory
+    uint32_t* status;             // device word, set non-zero on an internal inconsistency
+};
+
+// Descriptor-driven placement copy: host store -> pool blocks (swap-in), pool ->
+// pool across NVLink (replica swap / gather), pool -> host store (write-back).
+cudaError_t launch_place(const PlaceArgs& a, int grid_ctas, cudaStream_t stream);
+
+// Per-parameter checksums of device-resident bytes; out has 2 words per row and must be
+// zeroed by the caller.
+struct SumDesc {
+    uint64_t addr;
+    uint64_t bytes;
+    uint32_t first_tile;
+    uint32_t row;
+};
+cudaError_t launch_checksum(const SumDesc* descs, uint32_t n_descs, uint32_t total_tiles, uint32_t tile_bytes,
+                            unsigned long long* out, int grid_ctas, cudaStream_t stream);
+
+int default_grid_ctas(int device);
+
+}  // namespace tsw
+#endif

@@ -1,0 +1,197 @@
+// Eviction policy of the swap path: which resident models make room for a swap-in.
+//
+// Same decisions as the reference's LRUEvictor and InterferenceAwareEvictor
+// (include/server/evictor.hpp:14-264), kept as recency stamps on flat per-GPU
+// tables instead of linked lists: "front of the list" is the largest stamp,
+// the eviction scan "from the back" visits entries by increasing stamp.
+// Where the reference would spin forever because nothing can be evicted
+// (evictor.hpp:84-95,211-224) these return TSW_ERR_STATE and change nothing.
+
+#include "engine.hpp"
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <set>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+namespace {
+
+constexpr int kLevelMedian = 1;  // ModelLevel_Median (evictor.hpp:10-12)
+
+struct Entry {
+    uint64_t size = 0;
+    uint64_t stamp = 0;
+    int cls = 2;  // IA: 1 = first class (sole replica of a non-light model), 2 = second class
+};
+
+struct GpuState {
+    std::unordered_map<std::string, Entry> items;
+    std::unordered_set<std::string> locked;
+    uint64_t cur = 0;
+};
+
+}  // namespace
+
+struct tsw_evictor {
+    bool lru = true;
+    uint64_t budget = 0;
+    uint64_t clock = 0;
+    std::vector<GpuState> gpu;
+    std::unordered_map<std::string, std::set<int>> where;   // IA: model_to_gpus
+    std::unordered_map<std::string, int> level;
+
+    // least recently used, unlocked entry of a class (0 = any class)
+    const std::string* victim(const GpuState& g, int cls) const {
+        const std::string* best = nullptr;
+        uint64_t best_stamp = ~0ull;
+        for (auto& kv : g.items) {
+            if (cls && kv.second.cls != cls) continue;
+            if (g.locked.count(kv.first)) continue;
+            if (kv.second.stamp < best_stamp) {
+                best_stamp = kv.second.stamp;
+                best = &kv.first;
+            }
+        }
+        return best;
+    }
+
+    // Pick victims until `size` fits, first from `order[0]`, then `order[1]`...; -1 if it cannot fit.
+    int choose(const GpuState& g, uint64_t size, const std::vector<int>& class_order, std::vector<std::string>* out) const {
+        GpuState probe = g;  // work on a copy: nothing changes unless the request can be satisfied
+        for (int cls : class_order) {
+            while (probe.cur + size >= budget) {  // `>=` as in evictor.hpp:65,85,211
+                const std::string* v = victim(probe, cls);
+                if (!v) break;
+                out->push_back(*v);
+                probe.cur -= probe.items[*v].size;
+                probe.items.erase(*v);
+            }
+        }
+        return probe.cur + size >= budget ? -1 : 0;
+    }
+};
+
+extern "C" {
+
+int tsw_evictor_create(const char* kind, int gpu_count, uint64_t budget, tsw_evictor** out) {
+    if (!out || gpu_count <= 0) return tsw::fail(TSW_ERR_INVALID, "bad evictor arguments");
+    auto* ev = new tsw_evictor();
+    ev->lru = kind && std::string(kind) == "LRU";  // EVICT_POLICY=LRU, else interference-aware (controller.hpp:103-109)
+    ev->budget = budget;
+    ev->gpu.resize(gpu_count);
+    *out = ev;
+    return TSW_OK;
+}
+
+int tsw_evictor_destroy(tsw_evictor* ev) {
+    delete ev;
+    return TSW_OK;
+}
+
+int tsw_evictor_check_and_add(tsw_evictor* ev, int gpu_idx, const char* func, uint64_t size, int level, char* victims,
+                              int cap) {
+    if (!ev || !func || gpu_idx < 0 || gpu_idx >= (int)ev->gpu.size()) return tsw::fail(TSW_ERR_INVALID, "bad evictor arguments");
+    const std::string f(func);
+    ev->level[f] = level;
+    GpuState& g = ev->gpu[gpu_idx];
+    if (victims && cap > 0) victims[0] = 0;
+
+    // a hit only refreshes recency
+    const bool present = ev->lru ? g.items.count(f) > 0 : (ev->where.count(f) && ev->where[f].count(gpu_idx));
+    if (present) {
+        auto it = g.items.find(f);
+        if (it != g.items.end()) it->second.stamp = ++ev->clock;
+        return 0;
+    }
+
+    std::vector<std::string> out;
+    const std::vector<int> order = ev->lru ? std::vector<int>{0} : std::vector<int>{2, 1};
+    if (ev->choose(g, size, order, &out) != 0)
+        return tsw::fail(TSW_ERR_STATE, "nothing left to evict: every resident model is locked or the model exceeds the budget");
+    std::string joined;
+    for (size_t i = 0; i < out.size(); ++i) {
+        if (i) joined += "\n";
+        joined += out[i];
+    }
+    if (victims && (int)joined.size() + 1 > cap) return tsw::fail(TSW_ERR_BUFFER, "victim buffer too small");
+
+    for (auto& v : out) {
+        g.cur -= g.items[v].size;
+        g.items.erase(v);
+    }
+    Entry en;
+    en.size = size;
+    en.stamp = ++ev->clock;
+    if (!ev->lru) {
+        auto& homes = ev->where[f];
+        if (level >= kLevelMedian && homes.empty()) {
+            en.cls = 1;
+        } else {
+            en.cls = 2;
+            if (level >= kLevelMedian) {
+                // another replica exists: the former sole replica elsewhere is no longer precious
+                for (int other : homes) {
+                    auto it = ev->gpu[other].items.find(f);
+                    if (it != ev->gpu[other].items.end() && it->second.cls == 1) {
+                        it->second.cls = 2;
+                        it->second.stamp = ++ev->clock;
+                    }
+                }
+            }
+        }
+        homes.insert(gpu_idx);
+    }
+    g.items[f] = en;
+    g.cur += size;
+    if (!ev->lru) {
+        for (auto& v : out) {
+            auto& homes = ev->where[v];
+            homes.erase(gpu_idx);
+            if (ev->level[v] >= kLevelMedian && homes.size() == 1) {
+                const int other = *homes.begin();
+                auto it = ev->gpu[other].items.find(v);
+                if (it != ev->gpu[other].items.end() && it->second.cls == 2) {
+                    it->second.cls = 1;
+                    it->second.stamp = ++ev->clock;
+                }
+            }
+        }
+    }
+    if (victims) memcpy(victims, joined.c_str(), joined.size() + 1);
+    return (int)out.size();
+}
+
+int tsw_evictor_force_evict(tsw_evictor* ev, int gpu_idx, const char* func) {
+    if (!ev || !func || gpu_idx < 0 || gpu_idx >= (int)ev->gpu.size()) return tsw::fail(TSW_ERR_INVALID, "bad evictor arguments");
+    GpuState& g = ev->gpu[gpu_idx];
+    auto it = g.items.find(func);
+    if (it != g.items.end()) {
+        g.cur -= it->second.size;
+        g.items.erase(it);
+    }
+    if (!ev->lru) {
+        auto w = ev->where.find(func);
+        if (w != ev->where.end()) w->second.erase(gpu_idx);
+    }
+    return TSW_OK;
+}
+
+int tsw_evictor_lock(tsw_evictor* ev, int gpu_idx, const char* func) {
+    if (!ev || !func || gpu_idx < 0 || gpu_idx >= (int)ev->gpu.size()) return tsw::fail(TSW_ERR_INVALID, "bad evictor arguments");
+    GpuState& g = ev->gpu[gpu_idx];
+    // the LRU policy only locks what it holds (evictor.hpp:246-251); the interference-aware one always locks (:174-176)
+    if (!ev->lru || g.items.count(func)) g.locked.insert(func);
+    return TSW_OK;
+}
+
+int tsw_evictor_unlock(tsw_evictor* ev, int gpu_idx, const char* func) {
+    if (!ev || !func || gpu_idx < 0 || gpu_idx >= (int)ev->gpu.size()) return tsw::fail(TSW_ERR_INVALID, "bad evictor arguments");
+    ev->gpu[gpu_idx].locked.erase(func);
+    return TSW_OK;
+}
+
+}  // extern "C"

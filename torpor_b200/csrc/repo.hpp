@@ -1,0 +1,108 @@
+// Host model store and address-translation tables of the swap engine.
+//
+// Holds what the reference keeps in ModelRepo (include/server/model_repo.hpp:12-186)
+// -- per function: the client's device blocks, the parameters uploaded into them,
+// the authoritative host copy and the first-run access order; per (GPU, function):
+// where every block and parameter currently lives -- as flat, index-linked arrays.
+// The host copy is page-locked, device-mapped memory so that the placement kernel
+// can read it in place; the reference keeps it pageable and stages it through a
+// pinned mirror on every swap (model_repo.hpp:173-177, memory_manager.hpp:311-329).
+#ifndef TORPOR_SWAP_REPO_HPP_
+#define TORPOR_SWAP_REPO_HPP_
+
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <set>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+namespace tsw {
+
+struct VBlock {                 // GeneralBlockInfo + ModelBlockInfo (model_repo.hpp:12-23)
+    uint64_t vaddr = 0;         // client-visible device pointer (= first placement)
+    uint64_t canon = 0;         // the same in the canonical address space (table key)
+    uint64_t size = 0;
+    bool is_model = false;
+    bool alive = true;
+    uint8_t* mirror = nullptr;  // host copy of a model block
+    bool mirror_heap = false;   // mirror came from malloc (plan-only engines)
+    std::vector<int> params;    // parameters uploaded into this block
+    std::vector<uint64_t> ephe; // interior pointers cached for this block
+};
+
+struct VParam {                 // ModelParamInfo (model_repo.hpp:25-30)
+    uint64_t vaddr = 0;
+    uint64_t size = 0;
+    int block = -1;
+    uint8_t* host = nullptr;    // inside the block's mirror
+    bool accessed = false;
+};
+
+// Per (engine, function) placement: DeviceModelInfo (model_repo.hpp:48-65) plus the
+// readiness map the reference keeps in the manager (memory_manager.hpp:33,590).
+struct Placement {
+    int status = 1;  // TSW_MODEL_INCOMPLETE until the controller marks it (model_repo.hpp:64)
+    struct B { bool known = false, in_cuda = false; uint64_t cuda = 0; };
+    struct P { bool known = false; uint64_t cuda = 0; };
+    std::vector<B> blocks;
+    std::vector<P> params;
+    bool readiness_init = false;
+    // Pointer-table columns, one row per parameter.  On a CUDA engine they are
+    // host-mapped page-locked arrays written by the placement kernel; on a plan-only
+    // engine plain memory written by the planner.
+    uint32_t capacity = 0;
+    volatile uint32_t* flag = nullptr;   // TSW_READY_*
+    volatile uint64_t* phys = nullptr;   // readiness address (0 = none)
+    std::vector<bool> has_row;           // row exists in the readiness map
+    // device-side twins and launch scratch (CUDA engines only)
+    uint64_t* d_table_phys = nullptr;
+    uint32_t* d_table_flag = nullptr;
+    uint32_t* d_done = nullptr;
+    void* d_descs = nullptr;
+    uint32_t* d_first = nullptr;
+    void* h_descs = nullptr;
+    uint32_t* h_first = nullptr;
+    bool in_flight = false;
+};
+
+struct Model {                  // HostModelInfo (model_repo.hpp:37-46)
+    std::string name;
+    int status = 1;             // TSW_MODEL_INCOMPLETE
+    uint64_t total_size = 0;
+    std::vector<VBlock> blocks;
+    std::vector<VParam> params;
+    // Iteration order of the reference's pointer-keyed block map; swap-in requests
+    // pool blocks, and evict releases them, in this order (memory_manager.hpp:461,247).
+    std::unordered_map<void*, int> block_order;
+    std::unordered_map<uint64_t, int> block_by_vaddr;
+    std::unordered_map<uint64_t, int> param_by_vaddr;
+    std::unordered_map<uint64_t, int> data_block;   // virtual_data_block_mapping_: pointer -> block
+    std::vector<int> access_order;                   // model_access_order_map_
+    bool has_access_order = false;
+    std::map<int, Placement> place;                  // by server id
+};
+
+struct Repo {
+    std::recursive_mutex mu;
+    std::unordered_map<std::string, std::unique_ptr<Model>> models;
+    std::map<std::string, std::set<int>> active_devices;  // model_active_device_map_
+
+    Model* find(const std::string& f) {
+        auto it = models.find(f);
+        return it == models.end() ? nullptr : it->second.get();
+    }
+    Model* get_or_create(const std::string& f) {
+        auto& m = models[f];
+        if (!m) { m.reset(new Model()); m->name = f; }
+        return m.get();
+    }
+};
+
+Repo& repo();
+
+}  // namespace tsw
+#endif

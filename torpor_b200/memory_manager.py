@@ -1,0 +1,263 @@
+"""Host-side mirror of the reference's ``MemoryManager`` over the C ABI.
+
+``MemoryManager`` carries the public method names of
+``server::manager::MemoryManager`` (include/server/memory_manager.hpp:36-298)
+with the same argument meaning, so that a scenario written against the
+reference reads the same here.  The short aliases (``malloc``, ``swap_in`` ...)
+are the names the test scenarios and ``workloads.cold_start`` use for every
+implementation of the path.
+
+Nothing in this module moves bytes itself: every call goes into
+``libtorpor_swap.so``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import numpy as np
+
+from . import _cabi
+from ._cabi import SwapError, check
+
+DEFAULT_TIMEOUT_NS = 30_000_000_000
+
+
+def repo_reset() -> None:
+    check(_cabi.lib().tsw_repo_reset())
+
+
+class ModelRepo:
+    """The process-wide fields the controller reads (include/server/model_repo.hpp:82-90,180-185)."""
+
+    @staticmethod
+    def add_model_info(func: str, gpu: int) -> None:
+        check(_cabi.lib().tsw_repo_add_model_info(func.encode(), gpu))
+
+    @staticmethod
+    def remove_model_info(func: str, gpu: int) -> None:
+        check(_cabi.lib().tsw_repo_remove_model_info(func.encode(), gpu))
+
+    @staticmethod
+    def status(func: str, gpu: int) -> int:
+        return _cabi.lib().tsw_repo_model_status(func.encode(), gpu)
+
+    @staticmethod
+    def total_size(func: str) -> int:
+        return _cabi.lib().tsw_repo_total_size(func.encode())
+
+    @staticmethod
+    def active_devices(func: str) -> List[int]:
+        buf = (C.c_int * 64)()
+        n = _cabi.lib().tsw_repo_active_devices(func.encode(), buf, 64)
+        return sorted(buf[i] for i in range(min(n, 64)))
+
+
+class MemoryManager:
+    """One swap engine (one per GPU).
+
+    ``device=-1`` gives a plan-only engine: it places blocks and rebinds the
+    pointer table exactly as a CUDA engine would, makes no CUDA call and moves
+    no byte; every data call on it raises ``TSW_ERR_NO_DEVICE``.
+    """
+
+    def __init__(self, budget: int = 25 << 30, *, device: int = 0, server_id: int = 0, gpu_count: int = 1,
+                 block_manager: str = "Buddy", host_arena_bytes: int = 0, host_arena_shm: Optional[str] = None,
+                 grid_ctas: int = 0, tile_bytes_host: int = 0, tile_bytes_device: int = 0):
+        self.L = _cabi.lib()
+        cfg = _cabi.Config()
+        self.L.tsw_config_default(C.byref(cfg))
+        cfg.device = device
+        cfg.server_id = server_id
+        cfg.gpu_count = gpu_count
+        cfg.budget_bytes = budget
+        cfg.pool_policy = _cabi.POOL_FIXED if block_manager == "Fixed" else _cabi.POOL_BUDDY
+        cfg.host_arena_bytes = host_arena_bytes
+        self._shm = host_arena_shm.encode() if host_arena_shm else None
+        cfg.host_arena_shm = self._shm
+        cfg.grid_ctas = grid_ctas
+        cfg.tile_bytes_host = tile_bytes_host
+        cfg.tile_bytes_device = tile_bytes_device
+        h = C.c_void_p()
+        check(self.L.tsw_engine_create(C.byref(cfg), C.byref(h)))
+        self.h = h
+        self.device = device
+        self.server_id = server_id
+
+    # ---- life cycle
+    def close(self) -> None:
+        if self.h:
+            self.L.tsw_engine_destroy(self.h)
+            self.h = None
+
+    destroy_trans_thread = close
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # ---- reference method names
+    def set_track_model_memory(self, func: str) -> None:
+        check(self.L.tsw_track_begin(self.h, func.encode()))
+
+    def unset_track_model_memory(self, func: str) -> None:
+        check(self.L.tsw_track_end(self.h, func.encode()))
+
+    def cudaMallocBackend(self, size: int, load_model_flag: bool, func: str) -> int:
+        out = C.c_uint64()
+        check(self.L.tsw_malloc(self.h, func.encode(), size, 1 if load_model_flag else 0, C.byref(out)))
+        return out.value
+
+    def cudaFreeBackend(self, ptr: int, func: str) -> None:
+        check(self.L.tsw_free(self.h, func.encode(), ptr))
+
+    def cudaMemcpyAsyncBackendHtoD(self, dst: int, payload, stream: int, load_model_flag: bool, func: str) -> int:
+        data = np.ascontiguousarray(payload).view(np.uint8).reshape(-1)
+        fn = self.L.tsw_memcpy_h2d_model if load_model_flag else self.L.tsw_memcpy_h2d
+        return fn(self.h, func.encode(), dst, data.ctypes.data, data.nbytes, stream)
+
+    def cudaMemcpyAsyncBackendDtoH(self, src: int, count: int, stream: int, func: str) -> np.ndarray:
+        out = np.empty(count, dtype=np.uint8)
+        check(self.L.tsw_memcpy_d2h(self.h, func.encode(), out.ctypes.data, src, count, stream))
+        return out
+
+    def cudaMemcpyAsyncBackendDtoD(self, dst: int, src: int, count: int, stream: int, func: str) -> None:
+        check(self.L.tsw_memcpy_d2d(self.h, func.encode(), dst, src, count, stream))
+
+    def cudaMemsetAsyncBackend(self, ptr: int, value: int, count: int, stream: int, func: str) -> None:
+        check(self.L.tsw_memset(self.h, func.encode(), ptr, value, count, stream))
+
+    def init_model_readiness(self, func: str) -> None:
+        check(self.L.tsw_sync_done(self.h, func.encode()))
+
+    def try_insert_model_access(self, ptr: int) -> bool:
+        return check(self.L.tsw_mark_access(self.h, ptr)) == 1
+
+    def check_model_alloc_status(self, func: str) -> bool:
+        return check(self.L.tsw_check_alloc(self.h, func.encode())) == 1
+
+    def sig_trans_thread(self, func: str, src_gpu: int = -1) -> None:
+        check(self.L.tsw_swap_in(self.h, func.encode(), src_gpu))
+
+    def evict_model(self, func: str, free_memory: bool = False, writeback: bool = False) -> None:
+        check(self.L.tsw_evict(self.h, func.encode(), 1 if writeback else 0))
+
+    def get_cuda_addr(self, func: str, ptr: int, search_amid: bool = True,
+                      timeout_ns: int = DEFAULT_TIMEOUT_NS) -> int:
+        out = C.c_uint64()
+        check(self.L.tsw_translate(self.h, func.encode(), ptr, 1 if search_amid else 0, timeout_ns, C.byref(out)))
+        return out.value
+
+    def is_model_address(self, func: str, ptr: int) -> bool:
+        return check(self.L.tsw_is_model_address(self.h, func.encode(), ptr)) == 1
+
+    def valid_memory_address(self, func: str, ptr: int) -> bool:
+        return check(self.L.tsw_valid_memory_address(self.h, func.encode(), ptr)) == 1
+
+    # ---- scenario aliases shared with the checkers
+    def track_begin(self, f): self.set_track_model_memory(f)
+    def track_end(self, f): self.unset_track_model_memory(f)
+    def malloc(self, f, size, is_model): return self.cudaMallocBackend(size, is_model, f)
+    def free(self, f, vptr): self.cudaFreeBackend(vptr, f)
+    def memcpy_h2d_model(self, f, dst, data): return self.cudaMemcpyAsyncBackendHtoD(dst, data, 0, True, f)
+    def sync_done(self, f): self.init_model_readiness(f)
+    def mark_access(self, vptr): return 1 if self.try_insert_model_access(vptr) else 0
+    def swap_in(self, f, src_gpu=-1): self.sig_trans_thread(f, src_gpu)
+    def evict(self, f, writeback=False): self.evict_model(f, writeback=writeback)
+    def translate(self, f, vptr): return self.get_cuda_addr(f, vptr)
+    def check_alloc(self, f): return self.check_model_alloc_status(f)
+
+    def swap_in_sharded(self, func: str, helpers: Sequence["MemoryManager"]) -> None:
+        arr = (C.c_void_p * max(1, len(helpers)))(*[h.h for h in helpers])
+        check(self.L.tsw_swap_in_sharded(self.h, func.encode(), arr, len(helpers)))
+
+    def wait_ready(self, func: str, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+        check(self.L.tsw_wait_ready(self.h, func.encode(), timeout_ns))
+
+    # ---- introspection
+    def pool_info(self):
+        a, b, c = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        check(self.L.tsw_pool_info(self.h, C.byref(a), C.byref(b), C.byref(c)))
+        return a.value, b.value, c.value
+
+    def pool_chunks(self) -> np.ndarray:
+        base, n, _ = self.pool_info()
+        return np.uint64(base) + np.arange(n, dtype=np.uint64) * np.uint64(128 << 20)
+
+    def dump_blocks(self, func: str) -> np.ndarray:
+        n = self.L.tsw_dump_blocks(self.h, func.encode(), None, 0)
+        out = np.zeros((max(n, 1), 6), dtype=np.uint64)
+        self.L.tsw_dump_blocks(self.h, func.encode(), out.ctypes.data, n)
+        return out[:n]
+
+    def dump_params(self, func: str) -> np.ndarray:
+        n = self.L.tsw_dump_params(self.h, func.encode(), None, 0)
+        out = np.zeros((max(n, 1), 7), dtype=np.uint64)
+        self.L.tsw_dump_params(self.h, func.encode(), out.ctypes.data, n)
+        return out[:n]
+
+    def read_phys(self, addr: int, size: int) -> np.ndarray:
+        out = np.empty(size, dtype=np.uint8)
+        check(self.L.tsw_read_phys(self.h, addr, out.ctypes.data, size))
+        return out
+
+    def read_host_store(self, func: str, vptr: int, size: int) -> np.ndarray:
+        out = np.empty(size, dtype=np.uint8)
+        check(self.L.tsw_read_host_store(self.h, func.encode(), vptr, out.ctypes.data, size))
+        return out
+
+    def checksum_resident(self, func: str) -> np.ndarray:
+        n = self.L.tsw_dump_params(self.h, func.encode(), None, 0)
+        out = np.zeros((max(n, 1), 2), dtype=np.uint64)
+        check(self.L.tsw_checksum_resident(self.h, func.encode(), out.ctypes.data, n))
+        return out[:n]
+
+    def stats(self):
+        a, b, c = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        check(self.L.tsw_stats(self.h, C.byref(a), C.byref(b), C.byref(c)))
+        return {"kernel_launches": a.value, "bytes_moved": b.value, "last_swap_device_ns": c.value}
+
+
+class Evictor:
+    """LRUEvictor / InterferenceAwareEvictor (include/server/evictor.hpp)."""
+
+    def __init__(self, kind: str, gpu_count: int, budget: int):
+        self.L = _cabi.lib()
+        h = C.c_void_p()
+        check(self.L.tsw_evictor_create(kind.encode(), gpu_count, budget, C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if self.h:
+            self.L.tsw_evictor_destroy(self.h)
+            self.h = None
+
+    def check_and_add(self, gpu: int, func: str, size: int, level: int = 1) -> List[str]:
+        buf = C.create_string_buffer(1 << 16)
+        n = check(self.L.tsw_evictor_check_and_add(self.h, gpu, func.encode(), size, level, buf, len(buf)))
+        return buf.value.decode().split("\n") if n else []
+
+    def force_evict(self, gpu, func): check(self.L.tsw_evictor_force_evict(self.h, gpu, func.encode()))
+    def lock(self, gpu, func): check(self.L.tsw_evictor_lock(self.h, gpu, func.encode()))
+    def unlock(self, gpu, func): check(self.L.tsw_evictor_unlock(self.h, gpu, func.encode()))
+
+
+def checksum_host(data: np.ndarray) -> np.ndarray:
+    """The checksum of ``tsw_checksum_resident`` computed with numpy on host bytes."""
+    b = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+    pad = (-b.size) % 4
+    if pad:
+        b = np.concatenate([b, np.zeros(pad, dtype=np.uint8)])
+    w = b.view(np.uint32).astype(np.uint64)
+    s1 = np.uint64(0)
+    s2 = np.uint64(0)
+    step = 1 << 22
+    with np.errstate(over="ignore"):
+        for i in range(0, w.size, step):
+            c = w[i:i + step]
+            s1 = s1 + c.sum(dtype=np.uint64)
+            idx = np.arange(i + 1, i + 1 + c.size, dtype=np.uint64)
+            s2 = s2 + (c * idx).sum(dtype=np.uint64)
+    return np.array([s1, s2], dtype=np.uint64)
