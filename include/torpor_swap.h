@@ -134,17 +134,23 @@ int tsw_translate(tsw_engine* e, const char* func, uint64_t vptr, int search_ami
 int tsw_is_model_address(tsw_engine* e, const char* func, uint64_t vptr);    /* :286-291; 1/0 */
 int tsw_valid_memory_address(tsw_engine* e, const char* func, uint64_t vptr); /* :293-298; always 0 */
 
-/* Introspection for parity checks.  Layouts as in the checkers' scenario ABI:
+/* Introspection for parity checks: the tables of model_repo.hpp:37-65 and the readiness
+ * map (memory_manager.hpp:33,590) as rows of 64-bit words.
  * blocks (6 words): vaddr, size, is_model, in_cuda, cuda_addr, in_pin(=0), in the order
  *   swap-in requests pool blocks; params (7 words): vaddr, size, block_vaddr, cuda_addr,
  *   readiness_flag, readiness_addr, accessed -- access order first, then the rest by vaddr.
+ * canonical != 0 rewrites every address into the canonical address space (pool base ->
+ * fixed base), which makes the tables of two runs comparable word for word.
  * Both return the number of rows (also when out == NULL). */
-int tsw_dump_blocks(tsw_engine* e, const char* func, uint64_t* out, int cap);
-int tsw_dump_params(tsw_engine* e, const char* func, uint64_t* out, int cap);
+int tsw_dump_blocks(tsw_engine* e, const char* func, int canonical, uint64_t* out, int cap);
+int tsw_dump_params(tsw_engine* e, const char* func, int canonical, uint64_t* out, int cap);
 /* Pool geometry: base of the pool, number of 128 MiB chunks, and the canonical base that
  * addresses are keyed by internally (so that table order does not depend on where the
  * driver happened to map the pool). */
 int tsw_pool_info(tsw_engine* e, uint64_t* pool_base, uint64_t* n_chunks, uint64_t* canon_base);
+/* The canonical form of one address: inside a block the pool has handed out, else inside a
+ * block of `func` as the client knows it; any other value comes back unchanged. */
+int tsw_canonical_address(tsw_engine* e, const char* func, uint64_t addr, uint64_t* out);
 int tsw_read_phys(tsw_engine* e, uint64_t addr, void* out, uint64_t size);
 int tsw_read_host_store(tsw_engine* e, const char* func, uint64_t vptr, void* out, uint64_t size);
 /* Per-parameter 2 x 64-bit checksum of the RESIDENT bytes, computed on the device

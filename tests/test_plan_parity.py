@@ -1,0 +1,131 @@
+"""Host logic of the shipped engine -- pool placement, table rebind, translation,
+eviction order -- against the golden tables of the reference and against the CPU
+restatement, on plan-only engines (no GPU, no byte moves)."""
+import numpy as np
+import pytest
+
+import scenarios
+from torpor_b200 import _cabi
+from torpor_b200 import workloads as W
+from torpor_b200.memory_manager import MemoryManager, SwapError, repo_reset
+
+
+@pytest.fixture(scope="module")
+def plan_backend(built):
+    return scenarios.EngineBackend(device=-1)
+
+
+@pytest.mark.parametrize("name", list(scenarios.SCENARIOS))
+def test_engine_tables_match_reference_golden(plan_backend, name):
+    scenarios.assert_same(scenarios.run(plan_backend, name), scenarios.load_golden(name), f"engine/{name}")
+
+
+@pytest.mark.parametrize("name", ["churn_buddy", "workspace"])
+def test_engine_tables_match_oracle_live(plan_backend, oracle_backend, name):
+    scenarios.assert_same(scenarios.run(plan_backend, name), scenarios.run(oracle_backend, name), f"engine-vs-oracle/{name}")
+
+
+def test_pool_geometry(built):
+    repo_reset()
+    for budget, chunks in ((0, 40), (25 << 30, 240), (40 << 30, 360), (40 * 10**9, 338)):
+        m = MemoryManager(budget, device=-1)
+        base, n, canon = m.pool_info()
+        assert n == chunks and base == canon == 0x600000000000
+        m.close()
+
+
+def test_plan_only_engine_moves_no_bytes(built):
+    repo_reset()
+    m = MemoryManager(0, device=-1)
+    ws = W.weight_set("bert_tiny")
+    W.cold_start(m, "f", ws)
+    p = m.dump_params("f")
+    with pytest.raises(SwapError) as e:
+        m.read_phys(int(p[0, 3]), 16)
+    assert e.value.code == _cabi.ERR_NO_DEVICE
+    with pytest.raises(SwapError):
+        m.checksum_resident("f")
+    # the host store is still the authoritative copy
+    for i in (0, 7, len(ws.tensors) - 1):
+        assert np.array_equal(m.read_host_store("f", int(p[i, 0]), int(p[i, 1])), W.tensor_bytes(ws, i))
+    m.close()
+    repo_reset()
+
+
+def test_pool_exhaustion_is_an_error_not_an_exit(built):
+    repo_reset()
+    m = MemoryManager(0, device=-1)  # 40 chunks = 5 GiB
+    ws = W.weight_set("llama_tiny")
+    zeros = lambda i: np.zeros(ws.tensors[i].nbytes, dtype=np.uint8)
+    with pytest.raises(SwapError) as e:
+        for k in range(200):
+            W.cold_start(m, f"f{k}", ws, tensor_data=zeros, workspace_blocks=(100 << 20,))
+    assert e.value.code == _cabi.ERR_POOL_EXHAUSTED
+    m.close()
+    repo_reset()
+
+
+def test_failed_swap_in_rolls_back(built):
+    """A swap-in that does not fit leaves pool and tables as they were."""
+    repo_reset()
+    m = MemoryManager(0, device=-1)
+    ws = W.weight_set("llama_tiny")
+    zeros = lambda i: np.zeros(ws.tensors[i].nbytes, dtype=np.uint8)
+    big = (100 << 20,) * 4
+    n = 0
+    W.cold_start(m, "victim", ws, tensor_data=zeros, workspace_blocks=big)
+    m.evict("victim")
+    try:
+        while True:
+            W.cold_start(m, f"f{n}", ws, tensor_data=zeros, workspace_blocks=big)
+            n += 1
+    except SwapError:
+        pass
+    before = m.dump_blocks("victim")
+    with pytest.raises(SwapError) as e:
+        m.swap_in("victim")
+    assert e.value.code == _cabi.ERR_POOL_EXHAUSTED
+    assert np.array_equal(before[:, 3], m.dump_blocks("victim")[:, 3])
+    m.evict(f"f{n - 1}")
+    m.evict(f"f{n - 2}")
+    m.swap_in("victim")
+    assert m.check_alloc("victim")
+    m.close()
+    repo_reset()
+
+
+def test_small_irregular_request_takes_a_whole_slot(built):
+    """Requests of 8 MiB or less that are not 2 MiB: the reference hands the chunk base out
+    twice (block_manager.hpp:75-104 with a zero step); the engine gives each its own slot."""
+    repo_reset()
+    m = MemoryManager(0, device=-1)
+    m.track_begin("f")
+    a = m.malloc("f", 4 << 20, False)
+    b = m.malloc("f", 6 << 20, False)
+    c = m.malloc("f", 1 << 20, False)
+    m.track_end("f")
+    assert len({a, b, c}) == 3 and abs(a - b) >= (16 << 20) and abs(b - c) >= (16 << 20)
+    m.close()
+    repo_reset()
+
+
+def test_unknown_model_and_bad_arguments(built):
+    repo_reset()
+    m = MemoryManager(0, device=-1)
+    with pytest.raises(SwapError) as e:
+        m.swap_in("nope")
+    assert e.value.code == _cabi.ERR_UNKNOWN_MODEL
+    with pytest.raises(SwapError) as e:
+        m.evict("nope")
+    assert e.value.code == _cabi.ERR_UNKNOWN_MODEL
+    assert m.get_cuda_addr("nope", 0x1234) == 0x1234          # memory_manager.hpp:270
+    m.track_begin("f")
+    blk = m.malloc("f", 2 << 20, True)
+    assert m.memcpy_h2d_model("f", blk + (4 << 20), np.zeros(16, np.uint8)) == _cabi.ERR_NOT_FOUND
+    assert m.memcpy_h2d_model("f", blk + (2 << 20) - 8, np.zeros(16, np.uint8)) == _cabi.ERR_INVALID
+    assert m.memcpy_h2d_model("f", blk, np.zeros(0, np.uint8)) == 0   # empty upload is a parameter of size 0
+    assert m.mark_access(blk) == 1 and m.mark_access(blk + 64) == 0
+    m.track_end("f")
+    m.evict("f") if False else None
+    m.close()
+    repo_reset()

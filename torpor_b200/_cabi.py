@@ -82,9 +82,10 @@ SIGNATURES = {
     "tsw_translate": (_i32, [_vp, _cp, _u64, _i32, _i64, _pu64]),
     "tsw_is_model_address": (_i32, [_vp, _cp, _u64]),
     "tsw_valid_memory_address": (_i32, [_vp, _cp, _u64]),
-    "tsw_dump_blocks": (_i32, [_vp, _cp, _vp, _i32]),
-    "tsw_dump_params": (_i32, [_vp, _cp, _vp, _i32]),
+    "tsw_dump_blocks": (_i32, [_vp, _cp, _i32, _vp, _i32]),
+    "tsw_dump_params": (_i32, [_vp, _cp, _i32, _vp, _i32]),
     "tsw_pool_info": (_i32, [_vp, _pu64, _pu64, _pu64]),
+    "tsw_canonical_address": (_i32, [_vp, _cp, _u64, _pu64]),
     "tsw_read_phys": (_i32, [_vp, _u64, _vp, _u64]),
     "tsw_read_host_store": (_i32, [_vp, _cp, _u64, _vp, _u64]),
     "tsw_checksum_resident": (_i32, [_vp, _cp, _vp, _i32]),

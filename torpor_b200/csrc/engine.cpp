@@ -286,10 +286,12 @@ int place_blocks(tsw_engine* e, Model* m, Placement& pl) {
         b.known = true;
         b.in_cuda = true;
         b.cuda = a.phys;
+        b.canon = a.canon;
         if (vb.is_model) {
             for (int pi : vb.params) {   // the rebind (:477-479)
                 pl.params[pi].known = true;
                 pl.params[pi].cuda = m->params[pi].vaddr - vb.vaddr + a.phys;
+                pl.params[pi].canon = m->params[pi].vaddr - vb.vaddr + a.canon;
             }
         }
     }
@@ -578,6 +580,7 @@ int tsw_malloc(tsw_engine* e, const char* func, uint64_t size, int load_model_fl
     pl.blocks[bi].known = true;
     pl.blocks[bi].in_cuda = true;
     pl.blocks[bi].cuda = a.phys;
+    pl.blocks[bi].canon = a.canon;
     *vptr = a.phys;
     return TSW_OK;
 }
@@ -644,11 +647,13 @@ int tsw_memcpy_h2d_model(tsw_engine* e, const char* func, uint64_t dst, const vo
     p.size = size;
     p.block = bi;
     p.host = host;
+    p.canon = b.canon + (dst - b.vaddr);
     m->data_block[dst] = bi;
     Placement& pl = placement(m, e->server_id);
     size_placement(m, pl);
     pl.params[pi].known = true;
     pl.params[pi].cuda = dst;  // param_virtual_to_cuda_[dst] = {nullptr, dst} (memory_manager.hpp:129)
+    pl.params[pi].canon = p.canon;
     if (!e->plan && size) {
         // Upload from the page-locked copy just made, so the transfer is truly asynchronous.
         TSW_CUDA(cudaSetDevice(e->cfg.device));
@@ -1062,7 +1067,7 @@ int tsw_valid_memory_address(tsw_engine* e, const char* func, uint64_t vptr) {
 
 // --------------------------------------------------------------- introspection
 
-int tsw_dump_blocks(tsw_engine* e, const char* func, uint64_t* out, int cap) {
+int tsw_dump_blocks(tsw_engine* e, const char* func, int canonical, uint64_t* out, int cap) {
     if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
     Lock g1(repo().mu);
     Lock g2(e->mu);
@@ -1074,13 +1079,14 @@ int tsw_dump_blocks(tsw_engine* e, const char* func, uint64_t* out, int cap) {
         if (out && n < cap) {
             const VBlock& b = m->blocks[kv.second];
             uint64_t* o = out + 6 * n;
-            o[0] = b.vaddr;
+            o[0] = canonical ? b.canon : b.vaddr;
             o[1] = b.size;
             o[2] = b.is_model;
             o[3] = o[4] = o[5] = 0;
             if (pit != m->place.end() && (size_t)kv.second < pit->second.blocks.size() && pit->second.blocks[kv.second].known) {
-                o[3] = pit->second.blocks[kv.second].in_cuda;
-                o[4] = pit->second.blocks[kv.second].cuda;
+                const Placement::B& pb = pit->second.blocks[kv.second];
+                o[3] = pb.in_cuda;
+                o[4] = canonical ? pb.canon : pb.cuda;
             }
         }
         ++n;
@@ -1098,7 +1104,7 @@ static std::vector<int> dump_order(Model* m) {
     return order;
 }
 
-int tsw_dump_params(tsw_engine* e, const char* func, uint64_t* out, int cap) {
+int tsw_dump_params(tsw_engine* e, const char* func, int canonical, uint64_t* out, int cap) {
     if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
     Lock g1(repo().mu);
     Lock g2(e->mu);
@@ -1111,18 +1117,24 @@ int tsw_dump_params(tsw_engine* e, const char* func, uint64_t* out, int cap) {
         if (out && n < cap) {
             const VParam& p = m->params[pi];
             uint64_t* o = out + 7 * n;
-            o[0] = p.vaddr;
+            o[0] = canonical ? p.canon : p.vaddr;
             o[1] = p.size;
-            o[2] = m->blocks[p.block].vaddr;
+            o[2] = canonical ? m->blocks[p.block].canon : m->blocks[p.block].vaddr;
             o[3] = 0;
             o[4] = (uint64_t)-1;
             o[5] = 0;
             if (pit != m->place.end()) {
                 const Placement& pl = pit->second;
-                if ((size_t)pi < pl.params.size() && pl.params[pi].known) o[3] = pl.params[pi].cuda;
+                const bool known = (size_t)pi < pl.params.size() && pl.params[pi].known;
+                if (known) o[3] = canonical ? pl.params[pi].canon : pl.params[pi].cuda;
                 if ((size_t)pi < pl.has_row.size() && pl.has_row[pi]) {
                     o[4] = pl.flag[pi];
-                    o[5] = pl.phys[pi];
+                    uint64_t r = pl.phys[pi];
+                    if (canonical && r != 0) {
+                        if (known && r == pl.params[pi].cuda) r = pl.params[pi].canon;
+                        else if (r == p.vaddr) r = p.canon;
+                    }
+                    o[5] = r;
                 }
             }
             o[6] = p.accessed ? 1 : 0;
@@ -1137,6 +1149,24 @@ int tsw_pool_info(tsw_engine* e, uint64_t* pool_base, uint64_t* n_chunks, uint64
     if (pool_base) *pool_base = e->pool->pool_base();
     if (n_chunks) *n_chunks = e->pool->pool_chunks();
     if (canon_base) *canon_base = kCanonBase + (uint64_t)e->server_id * kCanonStride;
+    return TSW_OK;
+}
+
+int tsw_canonical_address(tsw_engine* e, const char* func, uint64_t addr, uint64_t* out) {
+    if (!e || !out) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    uint64_t c = e->pool->canon_inside(addr);
+    if (!c && func) {
+        Model* m = repo().find(func);
+        if (m)
+            for (auto& b : m->blocks)
+                if (b.alive && addr >= b.vaddr && addr < b.vaddr + b.size) {
+                    c = b.canon + (addr - b.vaddr);
+                    break;
+                }
+    }
+    *out = c ? c : addr;
     return TSW_OK;
 }
 

@@ -136,6 +136,13 @@ public:
         return it == oversize_live_.end() ? 0 : it->second.canon;
     }
 
+    uint64_t canon_inside(uint64_t phys) const override {
+        if (phys >= base_ && phys < base_ + n_chunks_ * kChunkBytes) return canon_base_ + (phys - base_);
+        for (auto& kv : oversize_live_)
+            if (phys >= kv.first && phys < kv.first + kv.second.size) return kv.second.canon + (phys - kv.first);
+        return 0;
+    }
+
     // acquire_block (:288-301)
     int acquire(uint64_t size, bool, DevAddr* out) override {
         if (size == kRegular2MiB || size == kRegular20MiB) return acquire_class(size, true, out);
@@ -156,6 +163,7 @@ public:
         } else if (mem_->alloc(size, &a.phys) != 0) {
             return -1;
         }
+        a.size = size;
         oversize_live_[a.phys] = a;
         *out = a;
         return 0;
@@ -304,7 +312,12 @@ public:
 
     uint64_t canon_of(uint64_t phys) const override {
         auto it = live_.find(phys);
-        return it == live_.end() ? 0 : it->second;
+        return it == live_.end() ? 0 : it->second.canon;
+    }
+    uint64_t canon_inside(uint64_t phys) const override {
+        for (auto& kv : live_)
+            if (phys >= kv.first && phys < kv.first + kv.second.size) return kv.second.canon + (phys - kv.first);
+        return 0;
     }
 
     int acquire(uint64_t size, bool external_call, DevAddr* out) override {
@@ -312,7 +325,7 @@ public:
         if (!idle.empty()) {
             out->phys = idle.back();
             idle.pop_back();
-            out->canon = live_[out->phys];
+            out->canon = live_[out->phys].canon;
             return 0;
         }
         if (budget_ < size) {
@@ -352,7 +365,8 @@ private:
         out->canon = canon_.bump(size);
         if (mem_->plan_only()) out->phys = out->canon;
         else if (mem_->alloc(size, &out->phys) != 0) return -1;
-        live_[out->phys] = out->canon;
+        out->size = size;
+        live_[out->phys] = *out;
         return 0;
     }
 
@@ -360,7 +374,7 @@ private:
     CanonSpace canon_;
     DeviceMemory* mem_;
     std::map<uint64_t, std::vector<uint64_t>, std::greater<uint64_t>> idle_;  // largest size first
-    std::unordered_map<uint64_t, uint64_t> live_;  // phys -> canon
+    std::unordered_map<uint64_t, DevAddr> live_;  // by phys
 };
 
 }  // namespace

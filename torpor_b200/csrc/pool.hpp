@@ -37,6 +37,7 @@ constexpr uint64_t kDevAllocAlign = 2 * kMiB;
 struct DevAddr {
     uint64_t phys = 0;
     uint64_t canon = 0;
+    uint64_t size = 0;  // filled for allocations outside the chunked pool
 };
 
 // Source of raw device memory: the CUDA runtime, or (plan-only engines) nothing
@@ -80,6 +81,8 @@ public:
     virtual uint64_t pool_chunks() const { return 0; }
     // canon of an address this pool handed out (0 if unknown)
     virtual uint64_t canon_of(uint64_t phys) const = 0;
+    // canon of any address inside a block this pool currently has handed out (0 if unknown)
+    virtual uint64_t canon_inside(uint64_t phys) const = 0;
     std::string last_warning;
 };
 

@@ -38,6 +38,7 @@ struct VParam {                 // ModelParamInfo (model_repo.hpp:25-30)
     uint64_t vaddr = 0;
     uint64_t size = 0;
     int block = -1;
+    uint64_t canon = 0;         // vaddr in the canonical address space
     uint8_t* host = nullptr;    // inside the block's mirror
     bool accessed = false;
 };
@@ -46,8 +47,8 @@ struct VParam {                 // ModelParamInfo (model_repo.hpp:25-30)
 // readiness map the reference keeps in the manager (memory_manager.hpp:33,590).
 struct Placement {
     int status = 1;  // TSW_MODEL_INCOMPLETE until the controller marks it (model_repo.hpp:64)
-    struct B { bool known = false, in_cuda = false; uint64_t cuda = 0; };
-    struct P { bool known = false; uint64_t cuda = 0; };
+    struct B { bool known = false, in_cuda = false; uint64_t cuda = 0, canon = 0; };
+    struct P { bool known = false; uint64_t cuda = 0, canon = 0; };
     std::vector<B> blocks;
     std::vector<P> params;
     bool readiness_init = false;

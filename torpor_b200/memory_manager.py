@@ -186,17 +186,24 @@ class MemoryManager:
         base, n, _ = self.pool_info()
         return np.uint64(base) + np.arange(n, dtype=np.uint64) * np.uint64(128 << 20)
 
-    def dump_blocks(self, func: str) -> np.ndarray:
-        n = self.L.tsw_dump_blocks(self.h, func.encode(), None, 0)
+    def dump_blocks(self, func: str, canonical: bool = False) -> np.ndarray:
+        c = 1 if canonical else 0
+        n = self.L.tsw_dump_blocks(self.h, func.encode(), c, None, 0)
         out = np.zeros((max(n, 1), 6), dtype=np.uint64)
-        self.L.tsw_dump_blocks(self.h, func.encode(), out.ctypes.data, n)
+        self.L.tsw_dump_blocks(self.h, func.encode(), c, out.ctypes.data, n)
         return out[:n]
 
-    def dump_params(self, func: str) -> np.ndarray:
-        n = self.L.tsw_dump_params(self.h, func.encode(), None, 0)
+    def dump_params(self, func: str, canonical: bool = False) -> np.ndarray:
+        c = 1 if canonical else 0
+        n = self.L.tsw_dump_params(self.h, func.encode(), c, None, 0)
         out = np.zeros((max(n, 1), 7), dtype=np.uint64)
-        self.L.tsw_dump_params(self.h, func.encode(), out.ctypes.data, n)
+        self.L.tsw_dump_params(self.h, func.encode(), c, out.ctypes.data, n)
         return out[:n]
+
+    def canonical_address(self, func: str, addr: int) -> int:
+        out = C.c_uint64()
+        check(self.L.tsw_canonical_address(self.h, func.encode(), addr, C.byref(out)))
+        return out.value
 
     def read_phys(self, addr: int, size: int) -> np.ndarray:
         out = np.empty(size, dtype=np.uint8)
@@ -209,7 +216,7 @@ class MemoryManager:
         return out
 
     def checksum_resident(self, func: str) -> np.ndarray:
-        n = self.L.tsw_dump_params(self.h, func.encode(), None, 0)
+        n = self.L.tsw_dump_params(self.h, func.encode(), 0, None, 0)
         out = np.zeros((max(n, 1), 2), dtype=np.uint64)
         check(self.L.tsw_checksum_resident(self.h, func.encode(), out.ctypes.data, n))
         return out[:n]
