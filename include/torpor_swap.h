@@ -158,6 +158,35 @@ int tsw_read_host_store(tsw_engine* e, const char* func, uint64_t vptr, void* ou
  * zero-extended).  out holds 2 words per parameter in tsw_dump_params order. */
 int tsw_checksum_resident(tsw_engine* e, const char* func, uint64_t* out, int cap);
 
+/* The data mover on its own: copy `n` segments with the placement kernel on this engine's
+ * transfer stream.  Addresses are device-visible: page-locked host memory, this GPU's memory
+ * or a peer's (peer access or an opened IPC handle).  Tiles of `tile_bytes` are numbered over
+ * the whole list; this call moves tiles tile_first, tile_first + tile_stride, ... so that
+ * several engines -- in one process or one per process -- can share a list.  With `pub`, the
+ * kernel counts finished tiles per table row in done_count (zeroed memory on the target GPU,
+ * shared by all participants) and whoever finishes the last tile of a row writes row_dst and
+ * flag_value into that row of the table columns.  This is the building block of
+ * tsw_swap_in_sharded and of multi-process sharded swaps; it has no counterpart in the
+ * reference, whose mover is cudaMemcpyAsync per parameter (memory_manager.hpp:389-396). */
+typedef struct {
+    uint64_t src, dst, bytes;
+    uint64_t row_dst;    /* address published for the row; used when row_tiles != 0 */
+    uint32_t row;        /* row of the table this segment contributes to */
+    uint32_t row_tiles;  /* tiles that complete the row over all segments and participants;
+                            0 = count the tiles of this row in this list, publish the first dst */
+} tsw_segment;
+typedef struct {
+    uint64_t done_count;   /* uint32 per row, device memory of the target, zero before the swap */
+    uint64_t table_phys;   /* uint64 per row, device memory of the target */
+    uint64_t table_flag;   /* uint32 per row, device memory of the target */
+    uint64_t host_phys;    /* optional host-mapped mirrors of the two columns (0 = none) */
+    uint64_t host_flag;
+    uint32_t flag_value;
+    uint32_t pad;
+} tsw_publish;
+int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
+                       uint32_t tile_stride, const tsw_publish* pub, int sync);
+
 /* Counters: kernels launched by this engine, bytes they were asked to move, and device
  * time of the last swap on the transfer stream (CUDA events), in nanoseconds. */
 int tsw_stats(tsw_engine* e, uint64_t* kernel_launches, uint64_t* bytes_moved, uint64_t* last_swap_device_ns);

@@ -1,0 +1,326 @@
+"""Parity tests proper: the CUDA engine, through the C ABI, against the CPU checker and
+the golden tables of the reference -- resident bytes, rebound pointer table, host bytes
+after swap-out -- on the benchmark's weight sets."""
+import ctypes
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+import pytest
+
+import scenarios
+from torpor_b200 import _cabi
+from torpor_b200 import workloads as W
+from torpor_b200.memory_manager import MemoryManager, ModelRepo, SwapError, checksum_host, repo_reset
+
+pytestmark = pytest.mark.gpu
+
+MiB = 1 << 20
+
+
+@pytest.fixture(scope="module")
+def gpu_backend(built):
+    import torch
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    assert "libtorpor_swap.so" in _cabi.lib()._name
+    return scenarios.EngineBackend(device=0)
+
+
+@pytest.fixture()
+def fresh(built):
+    repo_reset()
+    yield
+    repo_reset()
+
+
+# ---------------------------------------------------------------- tables
+
+@pytest.mark.parametrize("name", list(scenarios.SCENARIOS))
+def test_pointer_tables_match_reference_golden(gpu_backend, name):
+    """Same scenarios as on the plan-only engine, now with real placement and the kernel
+    publishing readiness: canonical tables equal the reference's word for word."""
+    scenarios.assert_same(scenarios.run(gpu_backend, name), scenarios.load_golden(name), f"gpu/{name}")
+
+
+# ---------------------------------------------------------------- bytes
+
+def load_both(eng, orc, func, ws, **kw):
+    lm = W.cold_start(eng, func, ws, **kw)
+    W.cold_start(orc, func, ws, **kw)
+    return lm
+
+
+def assert_resident_equal(eng, orc, func, ws, full=True):
+    """Pointer table equal to the checker's, bytes at every translated address equal to the
+    bytes the checker holds at the corresponding address."""
+    tab = eng.dump_params(func, canonical=True)
+    want = orc.dump_params(func)
+    assert np.array_equal(tab, want)
+    assert np.array_equal(eng.dump_blocks(func, canonical=True), orc.dump_blocks(func))
+    phys = eng.dump_params(func)
+    if full:
+        for i in range(len(phys)):
+            n = int(phys[i, 1])
+            have = eng.read_phys(eng.get_cuda_addr(func, int(phys[i, 0])), n)
+            assert np.array_equal(have, orc.read_phys(int(want[i, 3]), n)), f"tensor {i}"
+    sums = eng.checksum_resident(func)
+    for i in range(len(phys)):
+        ref = checksum_host(orc.read_phys(int(want[i, 3]), int(want[i, 1])))
+        assert np.array_equal(sums[i], ref), f"checksum of tensor {i}"
+
+
+def test_config1_resnet50_swap_in(fresh, oracle_backend):
+    """ResNet-50 fp32 set (161 tensors, 102,228,128 B): host store -> 2 MiB-block pool with rebind."""
+    oracle_backend.reset()
+    ws = W.weight_set("resnet50")
+    eng, orc = MemoryManager(0, device=0), oracle_backend.manager(budget=0)
+    load_both(eng, orc, "r50", ws)
+    assert_resident_equal(eng, orc, "r50", ws)           # after cold start
+    for _ in range(2):
+        eng.evict("r50"); orc.evict("r50")
+        eng.swap_in("r50"); eng.wait_ready("r50"); orc.swap_in("r50")
+        assert_resident_equal(eng, orc, "r50", ws)
+    st = eng.stats()
+    assert st["kernel_launches"] >= 2 and st["bytes_moved"] >= 2 * ws.nbytes
+    eng.close()
+    oracle_backend.reset()
+
+
+def test_config2_bert_base_round_trip(fresh, oracle_backend):
+    """BERT-base fp32 set: swap-in, then swap-out with write-back; bit-exact both ways.  The
+    reference's swap-out moves nothing, so host bytes after it are the uploaded bytes."""
+    oracle_backend.reset()
+    ws = W.weight_set("bert_base")
+    eng, orc = MemoryManager(0, device=0), oracle_backend.manager(budget=0)
+    lm = load_both(eng, orc, "bert", ws)
+    eng.evict("bert"); orc.evict("bert")
+    eng.swap_in("bert"); eng.wait_ready("bert"); orc.swap_in("bert")
+    assert_resident_equal(eng, orc, "bert", ws)
+    eng.evict("bert", writeback=True); orc.evict("bert")
+    assert np.array_equal(eng.dump_params("bert", canonical=True), orc.dump_params("bert"))
+    for i, v in enumerate(lm.tensor_vaddr):
+        n = ws.tensors[i].nbytes
+        assert np.array_equal(eng.read_host_store("bert", v, n), orc.read_host_store("bert", v, n)), f"tensor {i}"
+    eng.swap_in("bert"); eng.wait_ready("bert"); orc.swap_in("bert")
+    assert_resident_equal(eng, orc, "bert", ws, full=False)
+    eng.close()
+    oracle_backend.reset()
+
+
+def test_writeback_carries_device_side_changes(fresh):
+    """The write-back kernel really moves resident bytes: change a tensor on the device,
+    evict with write-back, and the host store (and the next swap-in) shows the change."""
+    ws = W.weight_set("bert_tiny")
+    eng = MemoryManager(0, device=0)
+    lm = W.cold_start(eng, "f", ws)
+    k = 9
+    new = (np.arange(ws.tensors[k].nbytes) % 251).astype(np.uint8)
+    assert eng.cudaMemcpyAsyncBackendHtoD(lm.tensor_vaddr[k], new, 0, False, "f") == 0
+    eng.evict("f", writeback=False)                       # the reference's swap-out: change is lost
+    assert np.array_equal(eng.read_host_store("f", lm.tensor_vaddr[k], new.size), W.tensor_bytes(ws, k))
+    eng.swap_in("f"); eng.wait_ready("f")
+    assert eng.cudaMemcpyAsyncBackendHtoD(lm.tensor_vaddr[k], new, 0, False, "f") == 0
+    eng.evict("f", writeback=True)
+    assert np.array_equal(eng.read_host_store("f", lm.tensor_vaddr[k], new.size), new)
+    assert np.array_equal(eng.read_host_store("f", lm.tensor_vaddr[k + 1], 64), W.tensor_bytes(ws, k + 1)[:64])
+    eng.swap_in("f"); eng.wait_ready("f")
+    assert np.array_equal(eng.read_phys(eng.get_cuda_addr("f", lm.tensor_vaddr[k]), new.size), new)
+    eng.close()
+
+
+def test_config3_bert_large_fp16(fresh, oracle_backend):
+    oracle_backend.reset()
+    ws = W.weight_set("bert_large")
+    eng, orc = MemoryManager(0, device=0), oracle_backend.manager(budget=0)
+    load_both(eng, orc, "bl", ws)
+    eng.evict("bl"); orc.evict("bl")
+    eng.swap_in("bl"); eng.wait_ready("bl"); orc.swap_in("bl")
+    assert_resident_equal(eng, orc, "bl", ws, full=False)
+    eng.close()
+    oracle_backend.reset()
+
+
+def test_replica_swap_on_device(fresh, oracle_backend):
+    """Swap-in from a resident replica held by a second engine (the reference's GPU-to-GPU
+    path, memory_manager.hpp:394-396); both engines sit on cuda:0 here."""
+    oracle_backend.reset()
+    ws = W.weight_set("llama_tiny")
+    a, b = MemoryManager(0, device=0, server_id=0, gpu_count=2), MemoryManager(0, device=0, server_id=1, gpu_count=2)
+    oa, ob = oracle_backend.manager(server_id=0, budget=0, gpu_count=2), oracle_backend.manager(server_id=1, budget=0, gpu_count=2)
+    W.cold_start(b, "m", ws); W.cold_start(ob, "m", ws)
+    ModelRepo.add_model_info("m", 1); oracle_backend.set_status("m", 1, True)
+    a.swap_in("m", 1); a.wait_ready("m"); oa.swap_in("m", 1)
+    assert_resident_equal(a, oa, "m", ws)
+    assert ModelRepo.active_devices("m") == [1]
+    a.close(); b.close()
+    oracle_backend.reset()
+
+
+def test_unaccessed_parameters_are_not_moved(fresh):
+    """Only parameters the first run touched travel (memory_manager.hpp:356,378); the others
+    translate to their rebound address, which holds whatever the pool block held."""
+    ws = W.weight_set("bert_tiny")
+    eng = MemoryManager(0, device=0)
+    data = lambda i: np.full(ws.tensors[i].nbytes, 1 + i % 200, dtype=np.uint8)
+    lm = scenarios.cold_start_partial(eng, "f", ws, data, (2 * MiB,), lambda i: i % 2 == 0)
+    eng.evict("f")
+    other = W.cold_start(eng, "g", W.weight_set("bert_tiny"), tensor_data=lambda i: np.zeros(ws.tensors[i].nbytes, np.uint8))
+    eng.evict("g")
+    eng.swap_in("f"); eng.wait_ready("f")
+    tab = eng.dump_params("f")
+    moved = 0
+    for row in tab:
+        i = lm.tensor_vaddr.index(int(row[0]))
+        got = eng.read_phys(eng.get_cuda_addr("f", int(row[0])), int(row[1]))
+        if i % 2 == 0:
+            assert row[4] == _cabi.READY_CUDA and np.array_equal(got, data(i))
+            moved += int(row[1])
+        else:
+            assert row[4] == _cabi.READY_HOST and row[6] == 0
+    assert moved == sum(t.nbytes for i, t in enumerate(ws.tensors) if i % 2 == 0)
+    eng.close()
+
+
+def test_llama_shaped_blocks_beyond_a_chunk(fresh, oracle_backend):
+    """Llama-shaped set with tensors larger than a 128 MiB chunk (embedding / lm_head, 250 MiB):
+    the reference leaves the pool for them (block_manager.hpp:295-300); tables still agree,
+    bytes are checked by checksum, and repeated cycles reuse instead of leaking."""
+    oracle_backend.reset()
+    ws = W.weight_set("llama_mid")
+    eng, orc = MemoryManager(0, device=0), oracle_backend.manager(budget=0)
+    pool = ThreadPoolExecutor(8)
+    data = list(pool.map(lambda i: W.tensor_bytes(ws, i), range(len(ws.tensors))))
+    W.cold_start(eng, "l", ws, tensor_data=lambda i: data[i])
+    W.cold_start(orc, "l", ws, tensor_data=lambda i: data[i])
+    host_sums = np.array([checksum_host(d) for d in data])
+    import torch
+    free0 = None
+    for it in range(3):
+        eng.evict("l", writeback=(it == 1)); orc.evict("l")
+        eng.swap_in("l"); eng.wait_ready("l"); orc.swap_in("l")
+        assert np.array_equal(eng.dump_params("l", canonical=True), orc.dump_params("l"))
+        assert np.array_equal(eng.dump_blocks("l", canonical=True), orc.dump_blocks("l"))
+        assert np.array_equal(eng.checksum_resident("l"), host_sums)
+        free = torch.cuda.mem_get_info()[0]
+        if free0 is None:
+            free0 = free
+        assert free >= free0 - 64 * MiB, "device memory keeps shrinking across swap cycles"
+    eng.close()
+    oracle_backend.reset()
+
+
+# ---------------------------------------------------------------- the mover alone
+
+def test_placement_kernel_alignments_and_ragged_sizes(fresh):
+    """Every head/tail/width path of the kernel: all 16 relative alignments of source and
+    destination, sizes from 0 to a few tiles, with guard bytes on both sides."""
+    import torch
+    eng = MemoryManager(0, device=0)
+    rng = np.random.default_rng(5)
+    sizes = [0, 1, 2, 3, 15, 16, 17, 31, 255, 4096, 4097, 65535, 65536, 65537, 200001]
+    span = 256 * 1024
+    n = len(sizes) * 16
+    src_host = torch.from_numpy(rng.integers(0, 256, size=n * span, dtype=np.uint8))
+    src = src_host.cuda()
+    dst = torch.full((n * span,), 0xEE, dtype=torch.uint8, device="cuda")
+    s_list, d_list, b_list = [], [], []
+    k = 0
+    for size in sizes:
+        for rel in range(16):
+            so = k * span + 64 + (rel * 7) % 16
+            do = k * span + 64 + (rel * 11 + 5) % 16
+            s_list.append(src.data_ptr() + so); d_list.append(dst.data_ptr() + do); b_list.append(size)
+            k += 1
+    eng.place_segments(s_list, d_list, b_list, tile_bytes=65536)
+    out = dst.cpu().numpy()
+    inp = src_host.numpy()
+    want = np.full(n * span, 0xEE, dtype=np.uint8)
+    for s, d, b in zip(s_list, d_list, b_list):
+        so, do = s - src.data_ptr(), d - dst.data_ptr()
+        want[do:do + b] = inp[so:so + b]
+    assert np.array_equal(out, want)
+    eng.close()
+
+
+def test_tiles_dealt_to_several_launches_publish_once(fresh):
+    """Sharding primitive: the same segment list run as 3 strided launches covers every byte
+    exactly once, and each row of the pointer table is published by whoever finishes last."""
+    import torch
+    eng = MemoryManager(0, device=0)
+    rng = np.random.default_rng(6)
+    sizes = [5, 70000, 1 << 20, 333333, 16, (3 << 20) + 48]
+    offs = np.cumsum([0] + [((s + 511) // 512) * 512 for s in sizes])
+    total = int(offs[-1])
+    src = torch.from_numpy(rng.integers(0, 256, size=total, dtype=np.uint8)).cuda()
+    dst = torch.zeros(total, dtype=torch.uint8, device="cuda")
+    done = torch.zeros(len(sizes), dtype=torch.int32, device="cuda")
+    t_phys = torch.zeros(len(sizes), dtype=torch.int64, device="cuda")
+    t_flag = torch.zeros(len(sizes), dtype=torch.int32, device="cuda")
+    pub = _cabi.Publish(done.data_ptr(), t_phys.data_ptr(), t_flag.data_ptr(), 0, 0, _cabi.READY_CUDA, 0)
+    s_list = [src.data_ptr() + int(o) for o in offs[:-1]]
+    d_list = [dst.data_ptr() + int(o) for o in offs[:-1]]
+    for r in range(3):
+        eng.place_segments(s_list, d_list, sizes, tile_bytes=65536, tile_first=r, tile_stride=3, publish=pub)
+        if r < 2:
+            assert int(t_flag[2].item()) == 0          # the 1 MiB segment has tiles in every share
+    for o, s in zip(offs[:-1], sizes):
+        assert torch.equal(dst[int(o):int(o) + s], src[int(o):int(o) + s])
+    assert t_flag.tolist() == [_cabi.READY_CUDA] * len(sizes)
+    assert t_phys.tolist() == d_list
+    assert done.tolist() == [0] * len(sizes)           # counters re-arm themselves
+    eng.close()
+
+
+# ---------------------------------------------------------------- bounded waits, errors
+
+def test_waits_are_bounded(fresh):
+    ws = W.weight_set("bert_tiny")
+    eng = MemoryManager(0, device=0)
+    W.cold_start(eng, "f", ws)
+    eng.evict("f")
+    with pytest.raises(SwapError) as e:
+        eng.wait_ready("f", timeout_ns=20_000_000)      # nothing was asked to swap in
+    assert e.value.code == _cabi.ERR_TIMEOUT
+    eng.swap_in("f"); eng.wait_ready("f")                # engine still usable
+    assert eng.check_alloc("f")
+    eng.close()
+
+
+def test_full_size_llama2_7b_properties(fresh):
+    """The 13.5 GB Llama-2-7B-shaped set at full size: per-tensor checksums of the resident
+    bytes equal the host-side checksums after swap-in, every parameter is rebound into the
+    placed blocks, write-back leaves the host store unchanged, and a second cycle lands on
+    the same tables (idempotence)."""
+    ws = W.weight_set("llama2_7b")
+    eng = MemoryManager(12 << 30, device=0, host_arena_bytes=14 << 30)
+    sums = {}
+
+    def data(i):
+        b = W.tensor_bytes(ws, i)
+        sums[i] = checksum_host(b)
+        return b
+
+    with ThreadPoolExecutor(12) as pool:
+        cache = {}
+        futs = {i: pool.submit(data, i) for i in range(len(ws.tensors))}
+        lm = W.cold_start(eng, "llama", ws, tensor_data=lambda i: futs.pop(i).result())
+    host_sums = np.array([sums[i] for i in range(len(ws.tensors))])
+    assert np.array_equal(eng.checksum_resident("llama"), host_sums)
+    tables = []
+    for it in range(2):
+        eng.evict("llama", writeback=(it == 0))
+        eng.swap_in("llama"); eng.wait_ready("llama")
+        tab = eng.dump_params("llama", canonical=True)
+        blk = eng.dump_blocks("llama", canonical=True)
+        assert (tab[:, 4] == _cabi.READY_CUDA).all() and (tab[:, 3] == tab[:, 5]).all()
+        starts = {int(b[0]): (int(b[4]), int(b[1])) for b in blk}
+        for row in tab:                                   # rebind: same offset inside the new block
+            cuda, size = starts[int(row[2])]
+            assert int(row[3]) - cuda == int(row[0]) - int(row[2]) and int(row[3]) + int(row[1]) <= cuda + size
+        assert np.array_equal(eng.checksum_resident("llama"), host_sums)
+        tables.append((tab, blk))
+    assert eng.stats()["bytes_moved"] >= 3 * ws.nbytes
+    # host store untouched by the write-back of unmodified weights
+    for i in (0, 1, 150, 290):
+        v, n = lm.tensor_vaddr[i], min(ws.tensors[i].nbytes, 1 << 20)
+        assert np.array_equal(eng.read_host_store("llama", v, n), W.tensor_bytes(ws, i)[:n])
+    eng.close()

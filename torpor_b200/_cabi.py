@@ -48,6 +48,16 @@ class Config(C.Structure):
     ]
 
 
+class Segment(C.Structure):
+    _fields_ = [("src", C.c_uint64), ("dst", C.c_uint64), ("bytes", C.c_uint64), ("row_dst", C.c_uint64),
+                ("row", C.c_uint32), ("row_tiles", C.c_uint32)]
+
+
+class Publish(C.Structure):
+    _fields_ = [("done_count", C.c_uint64), ("table_phys", C.c_uint64), ("table_flag", C.c_uint64),
+                ("host_phys", C.c_uint64), ("host_flag", C.c_uint64), ("flag_value", C.c_uint32), ("pad", C.c_uint32)]
+
+
 # Every symbol include/torpor_swap.h declares: name -> (restype, argtypes)
 _u64, _i32, _i64, _vp, _cp = C.c_uint64, C.c_int, C.c_int64, C.c_void_p, C.c_char_p
 _pu64 = C.POINTER(C.c_uint64)
@@ -89,6 +99,7 @@ SIGNATURES = {
     "tsw_read_phys": (_i32, [_vp, _u64, _vp, _u64]),
     "tsw_read_host_store": (_i32, [_vp, _cp, _u64, _vp, _u64]),
     "tsw_checksum_resident": (_i32, [_vp, _cp, _vp, _i32]),
+    "tsw_place_segments": (_i32, [_vp, _vp, _i32, C.c_uint32, C.c_uint32, C.c_uint32, _vp, _i32]),
     "tsw_stats": (_i32, [_vp, _pu64, _pu64, _pu64]),
     "tsw_evictor_create": (_i32, [_cp, _i32, _u64, C.POINTER(_vp)]),
     "tsw_evictor_destroy": (_i32, [_vp]),

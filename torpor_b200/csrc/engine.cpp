@@ -309,15 +309,28 @@ struct Plan {
     uint64_t bytes = 0;
 };
 
+// Number the tiles; where a segment does not say how many tiles complete its row, count
+// them over the segments of this list and publish the first segment's destination.
 void finish_plan(Plan& p, uint32_t tile) {
     p.first.assign(p.descs.size() + 1, 0);
     uint64_t t = 0;
+    std::unordered_map<uint32_t, std::pair<uint32_t, uint64_t>> rows;  // row -> (tiles, first dst)
     for (size_t i = 0; i < p.descs.size(); ++i) {
         p.first[i] = (uint32_t)t;
-        t += (p.descs[i].bytes + tile - 1) / tile;
+        const uint64_t n = (p.descs[i].bytes + tile - 1) / tile;
+        t += n;
         p.bytes += p.descs[i].bytes;
+        auto it = rows.find(p.descs[i].row);
+        if (it == rows.end()) rows[p.descs[i].row] = std::make_pair((uint32_t)n, p.descs[i].dst);
+        else it->second.first += (uint32_t)n;
     }
     p.first[p.descs.size()] = (uint32_t)t;
+    for (auto& d : p.descs) {
+        if (d.row_tiles == 0) {
+            d.row_tiles = rows[d.row].first;
+            d.row_dst = rows[d.row].second;
+        }
+    }
 }
 
 int upload_plan(tsw_engine* e, Placement& pl, const Plan& p) {
@@ -495,6 +508,9 @@ int tsw_engine_destroy(tsw_engine* e) {
         cudaSetDevice(e->cfg.device);
         if (e->stream) cudaStreamSynchronize((cudaStream_t)e->stream);
         e->pool.reset();
+        if (e->raw_d_descs) cudaFree(e->raw_d_descs);
+        if (e->raw_d_first) cudaFree(e->raw_d_first);
+        if (e->raw_h) cudaFreeHost(e->raw_h);
         if (e->dev_slab.base) cudaFree(e->dev_slab.base);
         if (e->host_slab.base) cudaFreeHost(e->host_slab.base);
         if (e->ev_start) cudaEventDestroy((cudaEvent_t)e->ev_start);
@@ -823,8 +839,9 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
         d.src = from_host ? host_dev_addr(engine_of_block_mirror(p.host), p.host) : src_pl->params[pi].cuda;
         d.dst = dst;
         d.bytes = p.size;
-        d.param = (uint32_t)pi;
-        d.pad = 0;
+        d.row_dst = dst;
+        d.row = (uint32_t)pi;
+        d.row_tiles = 0;
         plan.descs.push_back(d);
     }
     if (e->plan || plan.descs.empty()) return TSW_OK;
@@ -963,8 +980,9 @@ int tsw_evict(tsw_engine* e, const char* func, int writeback) {
                 d.src = pl.params[pi].cuda;
                 d.dst = host_dev_addr(engine_of_block_mirror(p.host), p.host);
                 d.bytes = p.size;
-                d.param = (uint32_t)pi;
-                d.pad = 0;
+                d.row_dst = d.dst;
+                d.row = (uint32_t)pi;
+                d.row_tiles = 0;
                 plan.descs.push_back(d);
             }
             if (!plan.descs.empty()) {
@@ -1239,6 +1257,73 @@ int tsw_checksum_resident(tsw_engine* e, const char* func, uint64_t* out, int ca
         e->kernel_launches++;
     }
     return n_rows;
+}
+
+int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
+                       uint32_t tile_stride, const tsw_publish* pub, int sync) {
+    if (!e || (n > 0 && !segs) || n < 0) return fail(TSW_ERR_INVALID, "bad segment list");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine moves no bytes");
+    if (n == 0) return TSW_OK;
+    if (tile_bytes == 0) tile_bytes = e->tile_host;
+    if ((tile_bytes & 15u) || tile_stride == 0) return fail(TSW_ERR_INVALID, "tile size must be a multiple of 16 and stride positive");
+    static_assert(sizeof(tsw_segment) == sizeof(PlaceDesc), "segment layout");
+    Lock g2(e->mu);
+    Plan plan;
+    plan.descs.resize(n);
+    memcpy(plan.descs.data(), segs, sizeof(PlaceDesc) * n);
+    finish_plan(plan, tile_bytes);
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    cudaStream_t s = (cudaStream_t)e->stream;
+    // launch scratch: grown on demand, reused by the next call once the stream has drained
+    const uint64_t need_d = sizeof(PlaceDesc) * (uint64_t)n, need_f = sizeof(uint32_t) * ((uint64_t)n + 1);
+    if (e->raw_cap < (uint64_t)n) {
+        TSW_CUDA(cudaStreamSynchronize(s));
+        if (e->raw_d_descs) cudaFree(e->raw_d_descs);
+        if (e->raw_d_first) cudaFree(e->raw_d_first);
+        if (e->raw_h) cudaFreeHost(e->raw_h);
+        e->raw_cap = 0;
+        const uint64_t cap = std::max<uint64_t>((uint64_t)n, 1024);
+        TSW_CUDA(cudaMalloc(&e->raw_d_descs, sizeof(PlaceDesc) * cap));
+        TSW_CUDA(cudaMalloc(&e->raw_d_first, sizeof(uint32_t) * (cap + 1)));
+        TSW_CUDA(cudaHostAlloc(&e->raw_h, sizeof(PlaceDesc) * cap + sizeof(uint32_t) * (cap + 1), cudaHostAllocDefault));
+        e->raw_cap = cap;
+    } else {
+        TSW_CUDA(cudaStreamSynchronize(s));  // the staging buffer may still feed the previous launch
+    }
+    uint8_t* hs = (uint8_t*)e->raw_h;
+    memcpy(hs, plan.descs.data(), need_d);
+    memcpy(hs + sizeof(PlaceDesc) * e->raw_cap, plan.first.data(), need_f);
+    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_start, s));
+    TSW_CUDA(cudaMemcpyAsync(e->raw_d_descs, hs, need_d, cudaMemcpyHostToDevice, s));
+    TSW_CUDA(cudaMemcpyAsync(e->raw_d_first, hs + sizeof(PlaceDesc) * e->raw_cap, need_f, cudaMemcpyHostToDevice, s));
+    PlaceArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = (const PlaceDesc*)e->raw_d_descs;
+    a.first_tile = (const uint32_t*)e->raw_d_first;
+    a.n_descs = (uint32_t)n;
+    a.tile_bytes = tile_bytes;
+    a.tile_lo = tile_first;
+    a.tile_hi = plan.first.back();
+    a.tile_stride = tile_stride;
+    a.system_scope = 1;
+    a.status = e->d_status;
+    if (pub) {
+        a.done_count = (uint32_t*)pub->done_count;
+        a.table_phys = (uint64_t*)pub->table_phys;
+        a.table_flag = (uint32_t*)pub->table_flag;
+        a.host_phys = (uint64_t*)pub->host_phys;
+        a.host_flag = (uint32_t*)pub->host_flag;
+        a.flag_value = pub->flag_value;
+        if (a.done_count && (!a.table_phys || !a.table_flag)) return fail(TSW_ERR_INVALID, "publish block needs both table columns");
+    }
+    cudaError_t le = launch_place(a, e->grid_ctas, s);
+    if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
+    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_stop, s));
+    e->ev_valid = true;
+    if (a.tile_hi > a.tile_lo) e->kernel_launches++;
+    e->bytes_moved += plan.bytes / tile_stride;
+    if (sync) TSW_CUDA(cudaStreamSynchronize(s));
+    return TSW_OK;
 }
 
 int tsw_stats(tsw_engine* e, uint64_t* kernel_launches, uint64_t* bytes_moved, uint64_t* last_swap_device_ns) {

@@ -74,6 +74,12 @@ struct tsw_engine {
     std::atomic<uint64_t> kernel_launches{0};
     std::atomic<uint64_t> bytes_moved{0};
     std::vector<void*> loose_host;   // page-locked mirrors outside the arena
+
+    // launch scratch of tsw_place_segments
+    void* raw_d_descs = nullptr;
+    void* raw_d_first = nullptr;
+    void* raw_h = nullptr;
+    uint64_t raw_cap = 0;
 };
 
 #endif

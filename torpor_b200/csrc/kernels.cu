@@ -129,19 +129,19 @@ __global__ void __launch_bounds__(kThreads) place_kernel(const PlaceArgs a) {
             else __threadfence();
             __syncthreads();
             if (threadIdx.x == 0) {
-                const uint32_t n_tiles = s_first[k + 1] - s_first[k];
-                const uint32_t before =
-                    a.system_scope ? atomicAdd_system(&a.done_count[k], 1u) : atomicAdd(&a.done_count[k], 1u);
-                if (before + 1 == n_tiles) {
-                    // Last tile of this parameter, possibly finished by another GPU's
-                    // CTAs: re-arm the counter, rebind the table row, then raise the flag.
-                    a.done_count[k] = 0;
+                const uint32_t before = a.system_scope ? atomicAdd_system(&a.done_count[d.row], 1u)
+                                                       : atomicAdd(&a.done_count[d.row], 1u);
+                if (before + 1 == d.row_tiles) {
+                    // Last tile of this parameter -- the others may have been moved by other
+                    // segments, launches or GPUs: re-arm the counter, rebind the table row,
+                    // then raise the flag.
+                    a.done_count[d.row] = 0;
                     __threadfence_system();
-                    a.table_phys[d.param] = d.dst;
-                    if (a.host_phys) a.host_phys[d.param] = d.dst;
+                    a.table_phys[d.row] = d.row_dst;
+                    if (a.host_phys) a.host_phys[d.row] = d.row_dst;
                     __threadfence_system();
-                    a.table_flag[d.param] = a.flag_value;
-                    if (a.host_flag) a.host_flag[d.param] = a.flag_value;
+                    a.table_flag[d.row] = a.flag_value;
+                    if (a.host_flag) a.host_flag[d.row] = a.flag_value;
                     __threadfence_system();
                 }
             }

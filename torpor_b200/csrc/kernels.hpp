@@ -10,11 +10,12 @@ namespace tsw {
 // One parameter's move.  Tiles are numbered over the whole swap: parameter k
 // owns tiles [first_tile[k], first_tile[k+1]).
 struct PlaceDesc {
-    uint64_t src;    // host-mapped, local or peer address
-    uint64_t dst;    // local pool, peer pool or host-mapped address
+    uint64_t src;       // host-mapped, local or peer address
+    uint64_t dst;       // local pool, peer pool or host-mapped address
     uint64_t bytes;
-    uint32_t param;  // row of the pointer table this move completes
-    uint32_t pad;
+    uint64_t row_dst;   // address published for the row (start of the whole parameter)
+    uint32_t row;       // row of the pointer table this move contributes to
+    uint32_t row_tiles; // tiles of that row over ALL segments and participants
 };
 
 struct PlaceArgs {
@@ -27,7 +28,7 @@ struct PlaceArgs {
     // Completion and rebind.  done_count lives with the TARGET of the swap so that
     // several GPUs can finish tiles of the same parameter; may be null (then nothing
     // is published and the launch is just a copy).
-    uint32_t* done_count;         // per desc, must be 0 at launch, left 0 on completion
+    uint32_t* done_count;         // per row, must be 0 at launch, left 0 on completion
     uint64_t* table_phys;         // device pointer table: rebound address per param
     uint32_t* table_flag;         //                       readiness per param
     uint64_t* host_phys;          // host-mapped mirror of the two columns (may be null)

@@ -173,6 +173,17 @@ class MemoryManager:
         arr = (C.c_void_p * max(1, len(helpers)))(*[h.h for h in helpers])
         check(self.L.tsw_swap_in_sharded(self.h, func.encode(), arr, len(helpers)))
 
+    def place_segments(self, src, dst, nbytes, rows=None, tile_bytes: int = 0, tile_first: int = 0,
+                       tile_stride: int = 1, publish: Optional[_cabi.Publish] = None, sync: bool = True) -> None:
+        """Run the placement kernel over explicit (src, dst, bytes) segments."""
+        n = len(src)
+        segs = (_cabi.Segment * max(n, 1))()
+        for i in range(n):
+            segs[i].src, segs[i].dst, segs[i].bytes = int(src[i]), int(dst[i]), int(nbytes[i])
+            segs[i].row = int(rows[i]) if rows is not None else i
+        check(self.L.tsw_place_segments(self.h, segs, n, tile_bytes, tile_first, tile_stride,
+                                        C.byref(publish) if publish is not None else None, 1 if sync else 0))
+
     def wait_ready(self, func: str, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
         check(self.L.tsw_wait_ready(self.h, func.encode(), timeout_ns))
 

@@ -356,3 +356,29 @@ def cold_start(mgr, func: str, ws: WeightSet, tensor_data=None,
             mgr.mark_access(tv[c.tensor])
     mgr.track_end(func)
     return LoadedModel(func, ws, bv, wv, tv)
+
+
+# ------------------------------------------------------------- sizing helpers
+
+def pool_budget_for(ws: WeightSet, workspace_blocks: Sequence[int] = (SMALL_BLOCK,), slack_chunks: int = 6) -> int:
+    """A memory budget (the engine adds the reference's hidden 5 GiB to it) whose pool of
+    128 MiB chunks holds ``ws`` once: 2 MiB / 20 MiB blocks as they are, other blocks up to a
+    chunk rounded to a power of two of at least 16 MiB, larger ones outside the pool."""
+    chunk = 128 * MiB
+    regular = irregular = 0
+    for size in [b.size for b in pack_blocks(ws)[0]] + list(workspace_blocks):
+        if size in (SMALL_BLOCK, LARGE_BLOCK):
+            regular += size if size == SMALL_BLOCK else chunk // 6 + 1   # six 20 MiB windows per chunk
+        elif size <= chunk:
+            r = 16 * MiB
+            while r < size:
+                r *= 2
+            irregular += r
+    chunks = -(-regular // chunk) + -(-irregular // chunk) + slack_chunks
+    return max(0, chunks * chunk - (5 << 30))
+
+
+def host_store_bytes(ws: WeightSet) -> int:
+    """Bytes of page-locked host store one copy of ``ws`` needs (block mirrors, 4 KiB aligned)."""
+    total = sum((b.size + 4095) // 4096 * 4096 for b in pack_blocks(ws)[0])
+    return ((total >> 30) + 1) << 30
