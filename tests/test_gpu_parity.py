@@ -44,9 +44,8 @@ def test_pointer_tables_match_reference_golden(gpu_backend, name):
 # ---------------------------------------------------------------- bytes
 
 def load_both(eng, orc, func, ws, **kw):
-    lm = W.cold_start(eng, func, ws, **kw)
-    W.cold_start(orc, func, ws, **kw)
-    return lm
+    """Cold start on the engine and on the checker; returns both address books."""
+    return W.cold_start(eng, func, ws, **kw), W.cold_start(orc, func, ws, **kw)
 
 
 def assert_resident_equal(eng, orc, func, ws, full=True):
@@ -91,15 +90,15 @@ def test_config2_bert_base_round_trip(fresh, oracle_backend):
     oracle_backend.reset()
     ws = W.weight_set("bert_base")
     eng, orc = MemoryManager(0, device=0), oracle_backend.manager(budget=0)
-    lm = load_both(eng, orc, "bert", ws)
+    lm, lm_orc = load_both(eng, orc, "bert", ws)
     eng.evict("bert"); orc.evict("bert")
     eng.swap_in("bert"); eng.wait_ready("bert"); orc.swap_in("bert")
     assert_resident_equal(eng, orc, "bert", ws)
     eng.evict("bert", writeback=True); orc.evict("bert")
     assert np.array_equal(eng.dump_params("bert", canonical=True), orc.dump_params("bert"))
-    for i, v in enumerate(lm.tensor_vaddr):
+    for i, (v, v_orc) in enumerate(zip(lm.tensor_vaddr, lm_orc.tensor_vaddr)):
         n = ws.tensors[i].nbytes
-        assert np.array_equal(eng.read_host_store("bert", v, n), orc.read_host_store("bert", v, n)), f"tensor {i}"
+        assert np.array_equal(eng.read_host_store("bert", v, n), orc.read_host_store("bert", v_orc, n)), f"tensor {i}"
     eng.swap_in("bert"); eng.wait_ready("bert"); orc.swap_in("bert")
     assert_resident_equal(eng, orc, "bert", ws, full=False)
     eng.close()
