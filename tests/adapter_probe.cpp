@@ -1,0 +1,65 @@
+// Compile-and-run probe for torpor_b200/adapter: uses the drop-in headers exactly as the
+// reference's executor and controller use the originals (cuda_server.hpp:50,73-74,106,223-253,
+// 951-978; controller.hpp:103-109,392-400), on a plan-only engine so that no GPU is needed.
+#include "memory_manager.hpp"
+#include "evictor.hpp"
+#include "spdlog/sinks/null_sink.h"
+
+#include <cstdio>
+#include <cstring>
+
+int main() {
+    using namespace server;
+    using namespace server::manager;
+    setenv("TORPOR_SWAP_ADAPTER_PROBE", "1", 1);
+    auto log = std::make_shared<spdlog::logger>("probe", std::make_shared<spdlog::sinks::null_sink_mt>());
+    // the probe drives a plan-only engine directly; start_trans_thread would need a GPU
+    tsw_config cfg;
+    tsw_config_default(&cfg);
+    cfg.device = -1;
+    cfg.budget_bytes = 0;
+    tsw_engine* e = nullptr;
+    if (tsw_engine_create(&cfg, &e) != TSW_OK) return 1;
+
+    string f = "fn";
+    uint64_t blk = 0;
+    tsw_track_begin(e, f.c_str());
+    tsw_malloc(e, f.c_str(), 2 << 20, 1, &blk);
+    std::string payload(4096, 'x');
+    if (tsw_memcpy_h2d_model(e, f.c_str(), blk + 512, payload.data(), payload.size(), nullptr) != TSW_OK) return 2;
+    tsw_sync_done(e, f.c_str());
+    tsw_mark_access(e, blk + 512);
+    tsw_track_end(e, f.c_str());
+    tsw_evict(e, f.c_str(), 0);
+    if (tsw_swap_in(e, f.c_str(), -1) != TSW_OK) return 3;
+    uint64_t out = 0;
+    if (tsw_translate(e, f.c_str(), blk + 512, 1, 1000000, &out) != TSW_OK || out == 0) return 4;
+
+    ModelRepo& repo = ModelRepo::getInstance();
+    repo.add_model_info(f, 0);
+    if (repo.model_active_device_map_[f].count(0) != 1 || tsw_repo_model_status(f.c_str(), 0) != TSW_MODEL_FULL) return 5;
+    repo.remove_model_info(f, 0);
+    if (repo.device_model_info_map_[0][f].status_ != ModelStatus_NoData) return 6;
+
+    // the class itself must at least construct and type-check against the executor's calls
+    MemoryManager mm(0);
+    mm.set_logger(log);
+    mm.set_server_id(0);
+    void* (MemoryManager::*malloc_fn)(size_t, bool, string&) = &MemoryManager::cudaMallocBackend;
+    void (MemoryManager::*sig_fn)(string&, int) = &MemoryManager::sig_trans_thread;
+    void* (MemoryManager::*addr_fn)(string&, void*, bool) = &MemoryManager::get_cuda_addr;
+    void (MemoryManager::*h2d_fn)(void*, const string&, cudaStream_t, bool, string&) = &MemoryManager::cudaMemcpyAsyncBackendHtoD;
+    (void)malloc_fn; (void)sig_fn; (void)addr_fn; (void)h2d_fn;
+
+    std::shared_ptr<Evictor> ev = std::make_shared<LRUEvictor>(2, 1000);
+    map<string, int> levels;
+    string a = "a", b = "b", c = "c";
+    ev->check_and_add(0, a, 400, levels);
+    ev->check_and_add(0, b, 400, levels);
+    auto victims = ev->check_and_add(0, c, 400, levels);
+    if (victims.size() != 1 || victims[0] != "a") return 7;
+
+    tsw_engine_destroy(e);
+    printf("adapter probe ok\n");
+    return 0;
+}

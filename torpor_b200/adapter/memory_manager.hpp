@@ -1,0 +1,206 @@
+// Drop-in for include/server/memory_manager.hpp: the same class, constructor and public
+// methods (memory_manager.hpp:36-298), implemented over the C ABI of libtorpor_swap.so.
+// Put this directory ahead of include/server on the include path and link the server with
+// -ltorpor_swap; include/server/cuda_server.hpp and controller.hpp compile unchanged.
+//
+// Error behaviour follows the reference: nothing is returned or thrown on this surface;
+// a failed call prints one line and execution continues (cuda_common.hpp:108-114), except
+// that pool exhaustion -- where the reference calls exit(1), block_manager.hpp:343-352 --
+// prints and returns a null pointer.  Waits that are unbounded in the reference
+// (memory_manager.hpp:531) give up after TORPOR_SWAP_WAIT_MS milliseconds (default 5000,
+// the executor's own request timeout, cuda_server.hpp:29) and return the untranslated pointer.
+#ifndef INCLUDE_MEM_MANAGER_HPP_
+#define INCLUDE_MEM_MANAGER_HPP_
+
+#include "cuda_common.hpp"
+#include "utils.hpp"
+#include "model_repo.hpp"
+#include "torpor_swap.h"
+
+#include <cstdlib>
+#include <iostream>
+
+namespace server {
+namespace manager {
+
+const size_t default_buffer_size = 2 * 1024 * 1024;
+const int default_num_io_thread = 4;
+
+const int ParamReadiness_Host = TSW_READY_HOST;
+const int ParamReadiness_Pinned = TSW_READY_PINNED;
+const int ParamReadiness_CUDA = TSW_READY_CUDA;
+
+class MemoryManager {
+public:
+    MemoryManager(size_t budget) : budget_(budget) {}
+
+    ~MemoryManager() {
+        if (engine_) tsw_engine_destroy(engine_);
+    }
+
+    void set_logger(logger log) { log_ = log; }
+    void set_server_id(int server_id) { server_id_ = server_id; }
+
+    void set_track_model_memory(string& func) {
+        model_repo_.start_model_load(func);
+        report(tsw_track_begin(engine_, func.c_str()), "set_track_model_memory");
+        if (log_) log_->info("Track memory for {}", func);
+    }
+
+    void unset_track_model_memory(string& func) {
+        model_repo_.complete_model_load(func);
+        report(tsw_track_end(engine_, func.c_str()), "unset_track_model_memory");
+        if (log_) log_->info("Untrack memory for {}", func);
+    }
+
+    void* cudaMallocBackend(size_t size, bool load_model_flag, string& function) {
+        uint64_t p = 0;
+        if (!report(tsw_malloc(engine_, function.c_str(), size, load_model_flag ? 1 : 0, &p), "cudaMallocBackend")) return nullptr;
+        model_repo_.model_host_info_map_[function].total_size_ += size;
+        return (void*)p;
+    }
+
+    void cudaFreeBackend(void* ptr, string& active_func) {
+        report(tsw_free(engine_, active_func.c_str(), (uint64_t)ptr), "cudaFreeBackend");
+    }
+
+    void cudaMemcpyBackendHtoD(void* dst, const string& payload, string& active_func) {
+        report(tsw_memcpy_h2d(engine_, active_func.c_str(), (uint64_t)dst, payload.data(), payload.length(), nullptr), "cudaMemcpyBackendHtoD");
+        cudaCheck(cudaStreamSynchronize(0));
+    }
+
+    void cudaMemcpyBackendDtoH(void* local_dst, void* src, size_t count, string& active_func) {
+        report(tsw_memcpy_d2h(engine_, active_func.c_str(), local_dst, (uint64_t)src, count, nullptr), "cudaMemcpyBackendDtoH");
+        cudaCheck(cudaStreamSynchronize(0));
+    }
+
+    void cudaMemcpyBackendDtoD(void* dst, void* src, size_t count, string& active_func) {
+        report(tsw_memcpy_d2d(engine_, active_func.c_str(), (uint64_t)dst, (uint64_t)src, count, nullptr), "cudaMemcpyBackendDtoD");
+        cudaCheck(cudaStreamSynchronize(0));
+    }
+
+    void cudaMemcpyAsyncBackendHtoD(void* dst, const string& payload, cudaStream_t stream, bool load_model_flag, string& function) {
+        int rc = load_model_flag
+            ? tsw_memcpy_h2d_model(engine_, function.c_str(), (uint64_t)dst, payload.data(), payload.length(), (void*)stream)
+            : tsw_memcpy_h2d(engine_, function.c_str(), (uint64_t)dst, payload.data(), payload.length(), (void*)stream);
+        if (rc == TSW_ERR_NOT_FOUND) {
+            if (log_) log_->warn("cudaMemcpy model fails to find malloc {}", (uint64_t)dst);
+            std::cout << "Server " << server_id_ << " -- Warning: cudaMemcpy model fails to find malloc " << (uint64_t)dst << std::endl;
+        } else {
+            report(rc, "cudaMemcpyAsyncBackendHtoD");
+        }
+    }
+
+    void cudaMemcpyAsyncBackendDtoH(void* local_dst, void* src, size_t count, cudaStream_t stream, string& active_func) {
+        report(tsw_memcpy_d2h(engine_, active_func.c_str(), local_dst, (uint64_t)src, count, (void*)stream), "cudaMemcpyAsyncBackendDtoH");
+    }
+
+    void cudaMemcpyAsyncBackendDtoD(void* dst, void* src, size_t count, cudaStream_t stream, string& active_func) {
+        report(tsw_memcpy_d2d(engine_, active_func.c_str(), (uint64_t)dst, (uint64_t)src, count, (void*)stream), "cudaMemcpyAsyncBackendDtoD");
+    }
+
+    void cudaMemsetAsyncBackend(void* ptr, int value, size_t count, cudaStream_t stream, string& active_func) {
+        report(tsw_memset(engine_, active_func.c_str(), (uint64_t)ptr, value, count, (void*)stream), "cudaMemsetAsyncBackend");
+    }
+
+    // Creates the engine on the calling thread's GPU = server id, as the reference
+    // pre-allocates its pool here (memory_manager.hpp:168-193).  BUFFER_SIZE and
+    // IO_THREAD_NUM are accepted and ignored: there is no staging copy and no sync group.
+    void start_trans_thread(int gpu_count) {
+        tsw_config cfg;
+        tsw_config_default(&cfg);
+        cfg.device = server_id_;
+        cfg.server_id = server_id_;
+        cfg.gpu_count = gpu_count;
+        cfg.budget_bytes = budget_;
+        auto policy = get_env_var("BLOCK_MANAGER");
+        cfg.pool_policy = policy == "Fixed" ? TSW_POOL_FIXED : TSW_POOL_BUDDY;
+        auto arena = get_env_var("TORPOR_SWAP_HOST_ARENA_GB");
+        if (arena.size() > 0) cfg.host_arena_bytes = (uint64_t)std::stoull(arena) << 30;
+        auto wait_ms = get_env_var("TORPOR_SWAP_WAIT_MS");
+        if (wait_ms.size() > 0) wait_ns_ = (int64_t)std::stoll(wait_ms) * 1000000;
+        model_repo_.init_device_info(server_id_);
+        if (!report(tsw_engine_create(&cfg, &engine_), "start_trans_thread")) engine_ = nullptr;
+        std::cout << "Server " << server_id_ << " -- swap engine " << tsw_version() << std::endl;
+    }
+
+    bool check_model_alloc_status(string& function) { return tsw_check_alloc(engine_, function.c_str()) == 1; }
+
+    void sig_trans_thread(string& function, int src_gpu = -1) {
+        int rc = tsw_swap_in(engine_, function.c_str(), src_gpu);
+        if (rc == TSW_ERR_UNKNOWN_MODEL) {
+            std::cout << "Server " << server_id_ << " -- Model " << function << " not found in model repo" << std::endl;
+            if (log_) log_->warn("Model {} not found in model repo", function);
+        } else {
+            report(rc, "sig_trans_thread");
+        }
+    }
+
+    void destroy_trans_thread() {
+        if (engine_) tsw_engine_destroy(engine_);
+        engine_ = nullptr;
+    }
+
+    void init_model_readiness(string& function, int flag = ParamReadiness_CUDA) {
+        (void)flag;  // the executor only ever passes the default (cuda_server.hpp:961)
+        report(tsw_sync_done(engine_, function.c_str()), "init_model_readiness");
+    }
+
+    void evict_model(string& function, bool free_memory = false) {
+        (void)free_memory;
+        static const bool writeback = get_env_var("TORPOR_SWAP_WRITEBACK") == "1";
+        int rc = tsw_evict(engine_, function.c_str(), writeback ? 1 : 0);
+        if (rc == TSW_ERR_UNKNOWN_MODEL) {
+            std::cout << "Server " << server_id_ << " -- warning: try to evict unregonized model " << function << std::endl;
+            return;
+        }
+        report(rc, "evict_model");
+        std::cout << "Server " << server_id_ << " -- evicted model " << function << std::endl;
+    }
+
+    inline void* get_cuda_addr(string& function, void* ptr, bool search_amid = true) {
+        uint64_t out = (uint64_t)ptr;
+        int rc = tsw_translate(engine_, function.c_str(), (uint64_t)ptr, search_amid ? 1 : 0, wait_ns_, &out);
+        if (rc != TSW_OK) {
+            report(rc, "get_cuda_addr");
+            return ptr;
+        }
+        return (void*)out;
+    }
+
+    inline bool try_insert_model_access(void* dev_ptr) {
+        int rc = tsw_mark_access(engine_, (uint64_t)dev_ptr);
+        if (rc == 0) std::cout << "Server " << server_id_ << " -- Model parameter ptr not found " << (uint64_t)dev_ptr << std::endl;
+        return rc == 1;
+    }
+
+    inline bool is_model_address(string& function, void* addr) {
+        return tsw_is_model_address(engine_, function.c_str(), (uint64_t)addr) == 1;
+    }
+
+    inline bool valid_memory_address(string& function, void* addr) {
+        return tsw_valid_memory_address(engine_, function.c_str(), (uint64_t)addr) == 1;
+    }
+
+    tsw_engine* engine() { return engine_; }
+
+private:
+    bool report(int rc, const char* where) {
+        if (rc >= 0) return true;
+        fprintf(stderr, "torpor_swap: %s failed (%d): %s\n", where, rc, tsw_last_error());
+        if (log_) log_->warn("torpor_swap: {} failed ({}): {}", where, rc, tsw_last_error());
+        return false;
+    }
+
+    logger log_;
+    int server_id_ = 0;
+    size_t budget_ = 0;
+    int64_t wait_ns_ = 5000ll * 1000000;
+    tsw_engine* engine_ = nullptr;
+    ModelRepo& model_repo_ = ModelRepo::getInstance();
+};
+
+}  // namespace manager
+}  // namespace server
+
+#endif  // INCLUDE_MEM_MANAGER_HPP_
