@@ -187,6 +187,26 @@ typedef struct {
 int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
                        uint32_t tile_stride, const tsw_publish* pub, int sync);
 
+/* tsw_place_segments for callers that must not allocate.  No counterpart in the reference.
+ *
+ * Meant for code on the steady-state swap path of a GPU-sharing server -- an executor that
+ * forwards intercepted client CUDA calls, a plugin in a process whose device memory already
+ * belongs to the block pool, a helper that only lends its PCIe link to a sharded swap --
+ * where a device allocation would synchronise the GPU under the running inference kernels,
+ * could fail because the pool owns the memory, or would be intercepted itself.  It needs no
+ * engine: it takes the device ordinal and a cudaStream_t, and calls neither cudaMalloc nor
+ * cudaFree nor any allocating routine.  The descriptor table the kernel reads lives in a
+ * fixed 1 MiB array inside the loaded module (so every GPU that uses the library gives up
+ * 1 MiB until the process exits), which limits one call to 16384 segments; more are refused
+ * with TSW_ERR_BUFFER.  All calls on a device share that array: calls whose GPU work overlaps
+ * (different streams or threads) corrupt each other's table -- issue them on one stream or
+ * serialise them.  The array's device address is looked up during the first call made for a
+ * device; make that first call outside of any stream capture.
+ * Differences from tsw_place_segments: a segment with row_tiles == 0 completes its own row
+ * (rows are not summed over the list), and no device timing is recorded. */
+int tsw_place_segments_static(int device, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
+                              uint32_t tile_stride, const tsw_publish* pub, void* stream);
+
 /* Counters: kernels launched by this engine, bytes they were asked to move, and device
  * time of the last swap on the transfer stream (CUDA events), in nanoseconds. */
 int tsw_stats(tsw_engine* e, uint64_t* kernel_launches, uint64_t* bytes_moved, uint64_t* last_swap_device_ns);

@@ -100,6 +100,7 @@ SIGNATURES = {
     "tsw_read_host_store": (_i32, [_vp, _cp, _u64, _vp, _u64]),
     "tsw_checksum_resident": (_i32, [_vp, _cp, _vp, _i32]),
     "tsw_place_segments": (_i32, [_vp, _vp, _i32, C.c_uint32, C.c_uint32, C.c_uint32, _vp, _i32]),
+    "tsw_place_segments_static": (_i32, [_i32, _vp, _i32, C.c_uint32, C.c_uint32, C.c_uint32, _vp, _vp]),
     "tsw_stats": (_i32, [_vp, _pu64, _pu64, _pu64]),
     "tsw_evictor_create": (_i32, [_cp, _i32, _u64, C.POINTER(_vp)]),
     "tsw_evictor_destroy": (_i32, [_vp]),

@@ -17,6 +17,16 @@
 
 #include "kernels.hpp"
 
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "../../include/torpor_swap.h"
+
+namespace tsw {
+int fail(int code, const std::string& msg);  // records the thread's last error text (engine.cpp)
+}
+
 namespace tsw {
 namespace {
 
@@ -242,3 +252,132 @@ cudaError_t launch_checksum(const SumDesc* descs, uint32_t n_descs, uint32_t tot
 }
 
 }  // namespace tsw
+
+// =====================================================================================
+// tsw_place_segments_static: the placement mover for callers that must not allocate.
+//
+// Who that is: code running inside a GPU-sharing server once it is in steady state.  A
+// remoting executor that forwards a client's intercepted CUDA calls, a plugin loaded
+// into a process whose device memory has been handed over to the block pool in full, or
+// a helper rank that only lends its PCIe link to a sharded swap, cannot afford a device
+// allocation on the swap path: cudaMalloc synchronises the whole device (stalling the
+// inference kernels that share it), may fail because the pool already owns the memory,
+// and in an interposed process may be routed back to the very server that is calling.
+// tsw_place_segments grows a device-side descriptor table with cudaMalloc and a pinned
+// staging buffer with cudaHostAlloc; this variant keeps the same table in a fixed
+// array that is part of the loaded module instead.
+//
+// The scratch: kStaticScratchBytes (1 MiB) of device memory per GPU that loads this
+// library, held until the process exits.  It bounds one call to kStaticMaxSegments
+// segments.  Every call on a device uses the same array and finds the previous call's
+// table in it; a call rewrites all of the table it uses, so nothing needs clearing, but
+// two calls whose work overlaps on the GPU (different streams, or several host threads)
+// overwrite each other's table: keep calls on one device in one stream, or serialise them.
+//
+// The array's name below is only meaningful in device code.  Host code must not pass it
+// to a kernel: the host-side symbol is a stand-in, not a device address.  The address is
+// looked up once per device, with that device current, by cudaGetSymbolAddress; that
+// happens in the first call made for a device, so make that first call outside of any
+// stream capture.
+namespace tsw {
+namespace {
+
+constexpr uint32_t kStaticMaxSegments = 16384;
+constexpr size_t kStaticDescBytes = sizeof(PlaceDesc) * kStaticMaxSegments;              // 640 KiB
+constexpr size_t kStaticFirstBytes = sizeof(uint32_t) * (kStaticMaxSegments + 1);        // 64 KiB + 4
+constexpr size_t kStaticScratchBytes = 1u << 20;
+static_assert(kStaticDescBytes + kStaticFirstBytes <= kStaticScratchBytes, "static scratch too small");
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+unsigned char* g_static_scratch_addr[kMaxDevices];   // device address of the array, per device
+bool g_static_scratch_known[kMaxDevices];
+std::mutex g_static_mu;
+
+// Host-side staging of one call's table; guarded by g_static_mu.
+PlaceDesc g_static_host_descs[kStaticMaxSegments];
+uint32_t g_static_host_first[kStaticMaxSegments + 1];
+
+}  // namespace
+}  // namespace tsw
+
+extern "C" int tsw_place_segments_static(int device, const tsw_segment* segs, int n, uint32_t tile_bytes,
+                                         uint32_t tile_first, uint32_t tile_stride, const tsw_publish* pub,
+                                         void* stream) {
+    using namespace tsw;
+    static_assert(sizeof(tsw_segment) == sizeof(PlaceDesc), "segment layout");
+    if (n < 0 || (n > 0 && !segs)) return fail(TSW_ERR_INVALID, "bad segment list");
+    if (device < 0 || device >= kMaxDevices) return fail(TSW_ERR_INVALID, "device ordinal out of range");
+    if ((uint32_t)n > kStaticMaxSegments)
+        return fail(TSW_ERR_BUFFER, "tsw_place_segments_static: " + std::to_string(n) + " segments exceed the static scratch limit of " +
+                                        std::to_string(kStaticMaxSegments) + "; split the list or use tsw_place_segments");
+    if (tile_bytes == 0) tile_bytes = 64u * 1024;
+    if ((tile_bytes & 15u) || tile_stride == 0)
+        return fail(TSW_ERR_INVALID, "tile size must be a multiple of 16 and stride positive");
+    if (pub && pub->done_count && (!pub->table_phys || !pub->table_flag))
+        return fail(TSW_ERR_INVALID, "publish block needs both table columns");
+    if (n == 0) return TSW_OK;
+
+    std::lock_guard<std::mutex> guard(g_static_mu);
+    cudaError_t err = cudaSetDevice(device);
+    if (err != cudaSuccess) return fail(TSW_ERR_NO_DEVICE, std::string("cudaSetDevice: ") + cudaGetErrorString(err));
+    if (!g_static_scratch_known[device]) {
+        // set-up, once per device, with that device current
+        unsigned char* p = nullptr;
+        err = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+        if (err != cudaSuccess || !p)
+            return fail(TSW_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(err));
+        g_static_scratch_addr[device] = p;
+        g_static_scratch_known[device] = true;
+    }
+    unsigned char* scratch = g_static_scratch_addr[device];
+
+    // Tile numbering.  A segment that does not say how many tiles complete its row is its own row.
+    uint64_t t = 0;
+    for (int i = 0; i < n; ++i) {
+        PlaceDesc& d = g_static_host_descs[i];
+        memcpy(&d, &segs[i], sizeof(PlaceDesc));
+        const uint64_t tiles = (d.bytes + tile_bytes - 1) / tile_bytes;
+        g_static_host_first[i] = (uint32_t)t;
+        t += tiles;
+        if (d.row_tiles == 0) {
+            d.row_tiles = (uint32_t)tiles;
+            d.row_dst = d.dst;
+        }
+    }
+    g_static_host_first[n] = (uint32_t)t;
+    if (t > 0xffffffffull) return fail(TSW_ERR_INVALID, "too many tiles for one call");
+
+    cudaStream_t s = (cudaStream_t)stream;
+    PlaceDesc* d_descs = reinterpret_cast<PlaceDesc*>(scratch);
+    uint32_t* d_first = reinterpret_cast<uint32_t*>(scratch + kStaticDescBytes);
+    // Pageable source: the runtime has taken its copy when these calls return, so the
+    // host-side staging arrays can be reused by the next call.
+    err = cudaMemcpyAsync(d_descs, g_static_host_descs, sizeof(PlaceDesc) * (size_t)n, cudaMemcpyHostToDevice, s);
+    if (err == cudaSuccess)
+        err = cudaMemcpyAsync(d_first, g_static_host_first, sizeof(uint32_t) * ((size_t)n + 1), cudaMemcpyHostToDevice, s);
+    if (err != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("table upload: ") + cudaGetErrorString(err));
+
+    PlaceArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = d_descs;
+    a.first_tile = d_first;
+    a.n_descs = (uint32_t)n;
+    a.tile_bytes = tile_bytes;
+    a.tile_lo = tile_first;
+    a.tile_hi = (uint32_t)t;
+    a.tile_stride = tile_stride;
+    a.system_scope = 1;
+    if (pub) {
+        a.done_count = (uint32_t*)pub->done_count;
+        a.table_phys = (uint64_t*)pub->table_phys;
+        a.table_flag = (uint32_t*)pub->table_flag;
+        a.host_phys = (uint64_t*)pub->host_phys;
+        a.host_flag = (uint32_t*)pub->host_flag;
+        a.flag_value = pub->flag_value;
+    }
+    err = launch_place(a, default_grid_ctas(device), s);
+    if (err != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(err));
+    return TSW_OK;
+}

@@ -238,6 +238,24 @@ class MemoryManager:
         return {"kernel_launches": a.value, "bytes_moved": b.value, "last_swap_device_ns": c.value}
 
 
+STATIC_MAX_SEGMENTS = 16384
+
+
+def place_segments_static(device: int, src, dst, nbytes, rows=None, tile_bytes: int = 0, tile_first: int = 0,
+                          tile_stride: int = 1, publish: Optional[_cabi.Publish] = None, stream: int = 0) -> None:
+    """The placement kernel over explicit segments without any allocation on the way
+    (``tsw_place_segments_static``): for callers on a server's steady-state path, where
+    cudaMalloc would stall or fail.  At most ``STATIC_MAX_SEGMENTS`` segments per call; the
+    call is asynchronous on ``stream``, and calls on one device must not overlap on the GPU."""
+    n = len(src)
+    segs = (_cabi.Segment * max(n, 1))()
+    for i in range(n):
+        segs[i].src, segs[i].dst, segs[i].bytes = int(src[i]), int(dst[i]), int(nbytes[i])
+        segs[i].row = int(rows[i]) if rows is not None else i
+    check(_cabi.lib().tsw_place_segments_static(device, segs, n, tile_bytes, tile_first, tile_stride,
+                                                C.byref(publish) if publish is not None else None, stream))
+
+
 class Evictor:
     """LRUEvictor / InterferenceAwareEvictor (include/server/evictor.hpp)."""
 
