@@ -161,8 +161,8 @@ int tsw_checksum_resident(tsw_engine* e, const char* func, uint64_t* out, int ca
 /* The data mover on its own: copy `n` segments with the placement kernel on this engine's
  * transfer stream.  Addresses are device-visible: page-locked host memory, this GPU's memory
  * or a peer's (peer access or an opened IPC handle).  Tiles of `tile_bytes` are numbered over
- * the whole list; this call moves tiles tile_first, tile_first + tile_stride, ... so that
- * several engines -- in one process or one per process -- can share a list.  With `pub`, the
+ * the whole list; this call moves tiles tile_first, tile_first + tile_stride, ... below
+ * tile_end (0 = to the end of the list), so that several engines -- in one process or one per process -- can share a list.  With `pub`, the
  * kernel counts finished tiles per table row in done_count (zeroed memory on the target GPU,
  * shared by all participants) and whoever finishes the last tile of a row writes row_dst and
  * flag_value into that row of the table columns.  This is the building block of
@@ -185,7 +185,27 @@ typedef struct {
     uint32_t pad;
 } tsw_publish;
 int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
-                       uint32_t tile_stride, const tsw_publish* pub, int sync);
+                       uint32_t tile_stride, uint32_t tile_end, const tsw_publish* pub, int sync);
+
+/* One process per GPU.  A swap-in can be carried out by several processes, each driving the
+ * placement kernel on its own GPU (tsw_place_segments with a tile stride): the target process
+ * places and rebinds with tsw_swap_plan, which returns the moves (addresses valid in the target
+ * process) instead of launching them; the others reach the target's pool and table through
+ * CUDA IPC (tsw_ipc_regions on the target, tsw_ipc_open elsewhere) and the host store through
+ * a shared-memory arena (config host_arena_shm on the target, tsw_arena_attach elsewhere), and
+ * rebase the addresses accordingly; when all are done the target calls tsw_swap_commit, which
+ * takes the rows the kernels published on the device over into its host-visible table.
+ * No counterpart in the reference (one process, one GPU per swap). */
+typedef struct {
+    uint64_t base, size;
+    unsigned char handle[64];   /* cudaIpcMemHandle_t */
+} tsw_ipc_region;
+int tsw_swap_plan(tsw_engine* e, const char* func, tsw_segment* segs, int cap, uint32_t* tile_bytes, tsw_publish* pub);
+int tsw_swap_commit(tsw_engine* e, const char* func);
+int tsw_ipc_regions(tsw_engine* e, tsw_ipc_region* out, int cap);   /* returns the number of regions */
+int tsw_ipc_open(tsw_engine* e, const void* handle, uint64_t* mapped_base);
+int tsw_arena_info(tsw_engine* e, uint64_t* host_base, uint64_t* dev_base, uint64_t* size, uint64_t* used);
+int tsw_arena_attach(tsw_engine* e, const char* shm_name, uint64_t size, uint64_t* dev_base);
 
 /* tsw_place_segments for callers that must not allocate.  No counterpart in the reference.
  *

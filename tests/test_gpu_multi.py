@@ -1,0 +1,123 @@
+"""Multi-GPU parity: a swap-in sharded over several GPUs' PCIe links, and a replica swap
+across NVLink, must leave exactly what a single-GPU swap-in leaves -- same pointer table as
+the CPU checker, same resident bytes.  Needs at least two GPUs (skipped otherwise)."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+import scenarios
+from torpor_b200 import _cabi
+from torpor_b200 import workloads as W
+from torpor_b200.memory_manager import MemoryManager, ModelRepo, checksum_host, repo_reset
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def gpu_count():
+    import torch
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+needs2 = pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+
+
+@needs2
+@pytest.mark.parametrize("name", ["resnet50", "llama_tiny"])
+def test_sharded_swap_in_process_equals_single_gpu_swap(built, oracle_backend, name):
+    n = min(gpu_count(), 8)
+    repo_reset(); oracle_backend.reset()
+    ws = W.weight_set(name)
+    engines = [MemoryManager(0, device=d, server_id=d, gpu_count=n, host_arena_bytes=(W.host_store_bytes(ws) if d == 0 else 0))
+               for d in range(n)]
+    orc = oracle_backend.manager(budget=0, gpu_count=n)
+    W.cold_start(engines[0], "m", ws); W.cold_start(orc, "m", ws)
+    sums = np.array([checksum_host(W.tensor_bytes(ws, i)) for i in range(len(ws.tensors))])
+    for cycle in range(3):
+        engines[0].evict("m"); orc.evict("m")
+        engines[0].swap_in_sharded("m", engines[1:]); engines[0].wait_ready("m"); orc.swap_in("m")
+        assert np.array_equal(engines[0].dump_params("m", canonical=True), orc.dump_params("m"))
+        assert np.array_equal(engines[0].dump_blocks("m", canonical=True), orc.dump_blocks("m"))
+        assert np.array_equal(engines[0].checksum_resident("m"), sums)
+    for d in range(1, n):
+        assert engines[d].stats()["kernel_launches"] >= 3       # every GPU took part
+    for e in engines:
+        e.close()
+    repo_reset(); oracle_backend.reset()
+
+
+@needs2
+def test_replica_swap_across_nvlink(built, oracle_backend):
+    repo_reset(); oracle_backend.reset()
+    ws = W.weight_set("bert_base")
+    a = MemoryManager(0, device=0, server_id=0, gpu_count=2)
+    b = MemoryManager(0, device=1, server_id=1, gpu_count=2)
+    oa, ob = oracle_backend.manager(server_id=0, budget=0, gpu_count=2), oracle_backend.manager(server_id=1, budget=0, gpu_count=2)
+    W.cold_start(b, "m", ws); W.cold_start(ob, "m", ws)
+    ModelRepo.add_model_info("m", 1); oracle_backend.set_status("m", 1, True)
+    a.swap_in("m", 1); a.wait_ready("m"); oa.swap_in("m", 1)
+    assert np.array_equal(a.dump_params("m", canonical=True), oa.dump_params("m"))
+    sums = np.array([checksum_host(W.tensor_bytes(ws, i)) for i in range(len(ws.tensors))])
+    assert np.array_equal(a.checksum_resident("m"), sums)
+    a.close(); b.close()
+    repo_reset(); oracle_backend.reset()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_main(rank, world, port, shm, out_dir):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    from torpor_b200 import sharded
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    ws = W.weight_set("llama_tiny")
+    repo_reset()
+    if rank == 0:
+        eng = MemoryManager(0, device=0, server_id=0, gpu_count=world, host_arena_bytes=W.host_store_bytes(ws), host_arena_shm=shm)
+        W.cold_start(eng, "m", ws)
+        eng.evict("m")
+    else:
+        eng = MemoryManager(0, device=rank, server_id=rank, gpu_count=world, block_manager="Fixed")
+    dist.barrier()
+    sw = sharded.ShardedSwap(eng, rank, world, None, shm_name=shm, max_segments=256)
+    sw.attach_arena(); sw.share_regions()
+    ok = True
+    sums = np.array([checksum_host(W.tensor_bytes(ws, i)) for i in range(len(ws.tensors))]) if rank == 0 else None
+    tables = []
+    for mode in ("direct", "staged", "direct", "staged"):
+        sw.swap_in("m", mode)
+        if rank == 0:
+            ok = ok and np.array_equal(eng.checksum_resident("m"), sums)
+            tab = eng.dump_params("m", canonical=True)
+            ok = ok and bool((tab[:, 4] == _cabi.READY_CUDA).all()) and bool((tab[:, 3] == tab[:, 5]).all())
+            ok = ok and eng.get_cuda_addr("m", int(eng.dump_params("m")[3, 0])) == int(eng.dump_params("m")[3, 3])
+        sw.evict("m")
+    launches = eng.stats()["kernel_launches"]
+    np.save(os.path.join(out_dir, f"r{rank}.npy"), np.array([int(ok), launches]))
+    dist.barrier()
+    eng.close()
+    dist.destroy_process_group()
+
+
+@needs2
+@pytest.mark.timeout(600)
+def test_sharded_swap_one_process_per_gpu(built, tmp_path):
+    """Two processes, one GPU each: pool opened over CUDA IPC, host store in shared memory."""
+    import torch.multiprocessing as mp
+    world = 2
+    shm = f"/torpor_swap_test_{os.getpid()}"
+    mp.spawn(_rank_main, args=(world, _free_port(), shm, str(tmp_path)), nprocs=world, join=True)
+    res = [np.load(os.path.join(str(tmp_path), f"r{r}.npy")) for r in range(world)]
+    assert res[0][0] == 1, "resident bytes or pointer table wrong after a sharded swap"
+    assert res[1][1] >= 4, "the helper rank launched no kernels"

@@ -58,6 +58,10 @@ class Publish(C.Structure):
                 ("host_phys", C.c_uint64), ("host_flag", C.c_uint64), ("flag_value", C.c_uint32), ("pad", C.c_uint32)]
 
 
+class IpcRegion(C.Structure):
+    _fields_ = [("base", C.c_uint64), ("size", C.c_uint64), ("handle", C.c_ubyte * 64)]
+
+
 # Every symbol include/torpor_swap.h declares: name -> (restype, argtypes)
 _u64, _i32, _i64, _vp, _cp = C.c_uint64, C.c_int, C.c_int64, C.c_void_p, C.c_char_p
 _pu64 = C.POINTER(C.c_uint64)
@@ -99,7 +103,13 @@ SIGNATURES = {
     "tsw_read_phys": (_i32, [_vp, _u64, _vp, _u64]),
     "tsw_read_host_store": (_i32, [_vp, _cp, _u64, _vp, _u64]),
     "tsw_checksum_resident": (_i32, [_vp, _cp, _vp, _i32]),
-    "tsw_place_segments": (_i32, [_vp, _vp, _i32, C.c_uint32, C.c_uint32, C.c_uint32, _vp, _i32]),
+    "tsw_place_segments": (_i32, [_vp, _vp, _i32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _vp, _i32]),
+    "tsw_swap_plan": (_i32, [_vp, _cp, _vp, _i32, C.POINTER(C.c_uint32), _vp]),
+    "tsw_swap_commit": (_i32, [_vp, _cp]),
+    "tsw_ipc_regions": (_i32, [_vp, _vp, _i32]),
+    "tsw_ipc_open": (_i32, [_vp, _vp, _pu64]),
+    "tsw_arena_info": (_i32, [_vp, _pu64, _pu64, _pu64, _pu64]),
+    "tsw_arena_attach": (_i32, [_vp, _cp, _u64, _pu64]),
     "tsw_place_segments_static": (_i32, [_i32, _vp, _i32, C.c_uint32, C.c_uint32, C.c_uint32, _vp, _vp]),
     "tsw_stats": (_i32, [_vp, _pu64, _pu64, _pu64]),
     "tsw_evictor_create": (_i32, [_cp, _i32, _u64, C.POINTER(_vp)]),

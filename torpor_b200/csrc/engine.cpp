@@ -508,6 +508,11 @@ int tsw_engine_destroy(tsw_engine* e) {
         cudaSetDevice(e->cfg.device);
         if (e->stream) cudaStreamSynchronize((cudaStream_t)e->stream);
         e->pool.reset();
+        for (auto& kv : e->ipc_open) cudaIpcCloseMemHandle((void*)kv.second);
+        for (auto& a : e->attached) {
+            cudaHostUnregister(a.first);
+            munmap(a.first, a.second);
+        }
         if (e->raw_d_descs) cudaFree(e->raw_d_descs);
         if (e->raw_d_first) cudaFree(e->raw_d_first);
         if (e->raw_h) cudaFreeHost(e->raw_h);
@@ -779,10 +784,32 @@ int tsw_memset(tsw_engine* e, const char* func, uint64_t vptr, int value, uint64
 
 // --------------------------------------------------------------- swap-in
 
-static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine* const* helpers, int n_helpers) {
-    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Lock g2(e->mu);
+struct Prepared {
+    Model* m = nullptr;
+    Placement* pl = nullptr;
+    Plan plan;
+    uint32_t tile = 0;
+};
+
+// Wait for whatever still writes into this placement's blocks: the engine's own stream and
+// the streams of helper engines of a sharded swap.
+static int drain_placement(tsw_engine* e, Placement& pl) {
+    if (e->plan || !pl.in_flight) return TSW_OK;
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+    for (tsw_engine* h : pl.helpers) {
+        TSW_CUDA(cudaSetDevice(h->cfg.device));
+        TSW_CUDA(cudaStreamSynchronize((cudaStream_t)h->stream));
+    }
+    pl.helpers.clear();
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    pl.in_flight = false;
+    return TSW_OK;
+}
+
+// Everything of a swap-in that precedes the data movement: source health check, block
+// placement with rebind, and the list of moves in access order.  Caller holds both locks.
+static int prepare_swap(tsw_engine* e, const char* func, int src_gpu, Prepared& out, bool defer = false) {
     Model* m = repo().find(func);
     if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, std::string("model ") + func + " not found in model repo");
 
@@ -815,23 +842,19 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
         rc = ensure_rows(e, m, pl);
         if (rc != TSW_OK) return rc;
     }
-    if (!e->plan && pl.in_flight) {
-        TSW_CUDA(cudaSetDevice(e->cfg.device));
-        TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
-        pl.in_flight = false;
-    }
+    rc = drain_placement(e, pl);
+    if (rc != TSW_OK) return rc;
     rc = place_blocks(e, m, pl);
     if (rc != TSW_OK) return rc;
 
     // transfer_model (:331-438): every accessed parameter that is not on the device yet, in access order
     const bool from_host = src_gpu < 0;
-    const uint32_t tile = pick_tile(e, from_host);
-    Plan plan;
+    out.tile = pick_tile(e, from_host);
     for (int pi : m->access_order) {
         if (!pl.has_row[pi] || pl.flag[pi] == TSW_READY_CUDA) continue;
         const VParam& p = m->params[pi];
         const uint64_t dst = pl.params[pi].cuda;
-        if (e->plan || p.size == 0) {
+        if ((e->plan && !defer) || p.size == 0) {
             set_row(pl, pi, TSW_READY_CUDA, dst);
             continue;
         }
@@ -842,11 +865,25 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
         d.row_dst = dst;
         d.row = (uint32_t)pi;
         d.row_tiles = 0;
-        plan.descs.push_back(d);
+        out.plan.descs.push_back(d);
     }
+    if (!out.plan.descs.empty()) finish_plan(out.plan, out.tile);
+    out.m = m;
+    out.pl = &pl;
+    return TSW_OK;
+}
+
+static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine* const* helpers, int n_helpers) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Prepared pr;
+    int rc = prepare_swap(e, func, src_gpu, pr);
+    if (rc != TSW_OK) return rc;
+    Placement& pl = *pr.pl;
+    Plan& plan = pr.plan;
     if (e->plan || plan.descs.empty()) return TSW_OK;
 
-    finish_plan(plan, tile);
     TSW_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = (cudaStream_t)e->stream;
     TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_start, s));
@@ -858,7 +895,7 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
     a.descs = (const PlaceDesc*)pl.d_descs;
     a.first_tile = pl.d_first;
     a.n_descs = (uint32_t)plan.descs.size();
-    a.tile_bytes = tile;
+    a.tile_bytes = pr.tile;
     a.tile_lo = 0;
     a.tile_hi = plan.first.back();
     a.tile_stride = 1;
@@ -883,8 +920,14 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
             PlaceArgs ar = a;
             ar.tile_lo = (uint32_t)r;
             TSW_CUDA(cudaSetDevice(w->cfg.device));
+            if (r != 0) TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_start, (cudaStream_t)w->stream));
             cudaError_t le = launch_place(ar, w->grid_ctas, (cudaStream_t)w->stream);
             if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
+            if (r != 0) {
+                TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_stop, (cudaStream_t)w->stream));
+                w->ev_valid = true;
+                pl.helpers.push_back(w);
+            }
             w->kernel_launches++;
         }
         TSW_CUDA(cudaSetDevice(e->cfg.device));
@@ -897,6 +940,68 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
     e->ev_valid = true;
     e->bytes_moved += plan.bytes;
     pl.in_flight = true;
+    return TSW_OK;
+}
+
+// Swap-in whose data movement is carried out by other parties (one process per GPU): this
+// engine places the blocks and rebinds exactly as tsw_swap_in does, then hands out the moves.
+int tsw_swap_plan(tsw_engine* e, const char* func, tsw_segment* segs, int cap, uint32_t* tile_bytes, tsw_publish* pub) {
+    if (!e || !func || !tile_bytes || !pub) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Prepared pr;
+    int rc = prepare_swap(e, func, -1, pr, true);
+    if (rc != TSW_OK) return rc;
+    Placement& pl = *pr.pl;
+    const int n = (int)pr.plan.descs.size();
+    if (n > cap || (n > 0 && !segs)) return fail(TSW_ERR_BUFFER, "segment buffer too small: need " + std::to_string(n));
+    static_assert(sizeof(tsw_segment) == sizeof(PlaceDesc), "segment layout");
+    if (n) memcpy(segs, pr.plan.descs.data(), sizeof(PlaceDesc) * n);
+    *tile_bytes = pr.tile;
+    memset(pub, 0, sizeof(*pub));
+    pub->done_count = (uint64_t)pl.d_done;
+    pub->table_phys = (uint64_t)pl.d_table_phys;
+    pub->table_flag = (uint64_t)pl.d_table_flag;
+    pub->flag_value = TSW_READY_CUDA;
+    pl.remote_rows.clear();
+    for (auto& d : pr.plan.descs) pl.remote_rows.push_back((int)d.row);
+    if (n && !e->plan) {
+        // stale flags of earlier swaps must not pass for this one's
+        TSW_CUDA(cudaSetDevice(e->cfg.device));
+        TSW_CUDA(cudaMemsetAsync(pl.d_table_flag, 0, sizeof(uint32_t) * pl.capacity, (cudaStream_t)e->stream));
+        TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+        e->bytes_moved += pr.plan.bytes;
+    }
+    return n;
+}
+
+// After every party has finished its share of a tsw_swap_plan: take the rows the kernels
+// published on the device over into the host-visible table.
+int tsw_swap_commit(tsw_engine* e, const char* func) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
+    Placement& pl = placement(m, e->server_id);
+    if (pl.remote_rows.empty()) return TSW_OK;
+    if (e->plan) {  // nothing moved, nothing to read back: the plan is the result
+        for (int row : pl.remote_rows) set_row(pl, row, TSW_READY_CUDA, pl.params[row].cuda);
+        pl.remote_rows.clear();
+        return TSW_OK;
+    }
+    std::vector<uint32_t> flag(pl.capacity);
+    std::vector<uint64_t> phys(pl.capacity);
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    TSW_CUDA(cudaMemcpy(flag.data(), pl.d_table_flag, sizeof(uint32_t) * pl.capacity, cudaMemcpyDeviceToHost));
+    TSW_CUDA(cudaMemcpy(phys.data(), pl.d_table_phys, sizeof(uint64_t) * pl.capacity, cudaMemcpyDeviceToHost));
+    int missing = 0;
+    for (int row : pl.remote_rows) {
+        if (flag[row] == TSW_READY_CUDA) set_row(pl, row, TSW_READY_CUDA, phys[row]);
+        else ++missing;
+    }
+    pl.remote_rows.clear();
+    if (missing) return fail(TSW_ERR_STATE, std::to_string(missing) + " parameters were not completed by the participants");
     return TSW_OK;
 }
 
@@ -963,11 +1068,9 @@ int tsw_evict(tsw_engine* e, const char* func, int writeback) {
     size_placement(m, pl);
 
     if (!e->plan) {
+        int drc = drain_placement(e, pl);
+        if (drc != TSW_OK) return drc;
         TSW_CUDA(cudaSetDevice(e->cfg.device));
-        if (pl.in_flight) {
-            TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
-            pl.in_flight = false;
-        }
         if (writeback) {
             // Eviction write-back: resident parameter bytes -> host store, through the same kernel.
             Plan plan;
@@ -1259,8 +1362,84 @@ int tsw_checksum_resident(tsw_engine* e, const char* func, uint64_t* out, int ca
     return n_rows;
 }
 
+// --------------------------------------------------------------- sharing with other processes
+
+int tsw_ipc_regions(tsw_engine* e, tsw_ipc_region* out, int cap) {
+    if (!e) return fail(TSW_ERR_INVALID, "null argument");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine has no device memory");
+    Lock g2(e->mu);
+    std::vector<std::pair<uint64_t, uint64_t>> regs;
+    e->pool->regions(&regs);
+    regs.emplace_back((uint64_t)e->dev_slab.base, e->dev_slab.size);
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    int n = 0;
+    for (auto& r : regs) {
+        if (out && n < cap) {
+            out[n].base = r.first;
+            out[n].size = r.second;
+            cudaIpcMemHandle_t h;
+            TSW_CUDA(cudaIpcGetMemHandle(&h, (void*)r.first));
+            static_assert(sizeof(h) == sizeof(out[n].handle), "IPC handle size");
+            memcpy(out[n].handle, &h, sizeof(h));
+        }
+        ++n;
+    }
+    return n;
+}
+
+int tsw_ipc_open(tsw_engine* e, const void* handle, uint64_t* mapped_base) {
+    if (!e || !handle || !mapped_base) return fail(TSW_ERR_INVALID, "null argument");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine has no device");
+    Lock g2(e->mu);
+    std::string key((const char*)handle, sizeof(cudaIpcMemHandle_t));
+    auto it = e->ipc_open.find(key);
+    if (it != e->ipc_open.end()) {
+        *mapped_base = it->second;
+        return TSW_OK;
+    }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    TSW_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    e->ipc_open[key] = (uint64_t)p;
+    *mapped_base = (uint64_t)p;
+    return TSW_OK;
+}
+
+int tsw_arena_info(tsw_engine* e, uint64_t* host_base, uint64_t* dev_base, uint64_t* size, uint64_t* used) {
+    if (!e) return fail(TSW_ERR_INVALID, "null argument");
+    if (host_base) *host_base = (uint64_t)e->arena.base;
+    if (dev_base) *dev_base = e->arena.base ? (uint64_t)((int64_t)(uint64_t)e->arena.base + e->arena.dev_delta) : 0;
+    if (size) *size = e->arena.size;
+    if (used) *used = e->arena.used;
+    return TSW_OK;
+}
+
+int tsw_arena_attach(tsw_engine* e, const char* shm_name, uint64_t size, uint64_t* dev_base) {
+    if (!e || !shm_name || !dev_base || size == 0) return fail(TSW_ERR_INVALID, "bad arguments");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine has no device");
+    Lock g2(e->mu);
+    int fd = shm_open(shm_name, O_RDWR, 0600);
+    if (fd < 0) return fail(TSW_ERR_NOT_FOUND, std::string("shm_open(") + shm_name + ") failed");
+    void* p = mmap(nullptr, size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+    close(fd);
+    if (p == MAP_FAILED) return fail(TSW_ERR_INVALID, "mmap of the shared host arena failed");
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    cudaError_t err = cudaHostRegister(p, size, cudaHostRegisterPortable | cudaHostRegisterMapped);
+    if (err != cudaSuccess) {
+        munmap(p, size);
+        return fail(TSW_ERR_CUDA, std::string("cudaHostRegister(shared arena): ") + cudaGetErrorString(err));
+    }
+    void* dp = nullptr;
+    TSW_CUDA(cudaHostGetDevicePointer(&dp, p, 0));
+    e->attached.emplace_back(p, size);
+    *dev_base = (uint64_t)dp;
+    return TSW_OK;
+}
+
 int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
-                       uint32_t tile_stride, const tsw_publish* pub, int sync) {
+                       uint32_t tile_stride, uint32_t tile_end, const tsw_publish* pub, int sync) {
     if (!e || (n > 0 && !segs) || n < 0) return fail(TSW_ERR_INVALID, "bad segment list");
     if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine moves no bytes");
     if (n == 0) return TSW_OK;
@@ -1278,6 +1457,11 @@ int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t t
     const uint64_t need_d = sizeof(PlaceDesc) * (uint64_t)n, need_f = sizeof(uint32_t) * ((uint64_t)n + 1);
     if (e->raw_cap < (uint64_t)n) {
         TSW_CUDA(cudaStreamSynchronize(s));
+        for (auto& kv : e->ipc_open) cudaIpcCloseMemHandle((void*)kv.second);
+        for (auto& a : e->attached) {
+            cudaHostUnregister(a.first);
+            munmap(a.first, a.second);
+        }
         if (e->raw_d_descs) cudaFree(e->raw_d_descs);
         if (e->raw_d_first) cudaFree(e->raw_d_first);
         if (e->raw_h) cudaFreeHost(e->raw_h);
@@ -1303,7 +1487,7 @@ int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t t
     a.n_descs = (uint32_t)n;
     a.tile_bytes = tile_bytes;
     a.tile_lo = tile_first;
-    a.tile_hi = plan.first.back();
+    a.tile_hi = (tile_end != 0 && tile_end < plan.first.back()) ? tile_end : plan.first.back();
     a.tile_stride = tile_stride;
     a.system_scope = 1;
     a.status = e->d_status;
@@ -1321,7 +1505,8 @@ int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t t
     TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_stop, s));
     e->ev_valid = true;
     if (a.tile_hi > a.tile_lo) e->kernel_launches++;
-    e->bytes_moved += plan.bytes / tile_stride;
+    if (a.tile_hi > a.tile_lo)
+        e->bytes_moved += (uint64_t)((double)plan.bytes * (double)(a.tile_hi - a.tile_lo) / (double)plan.first.back() / tile_stride);
     if (sync) TSW_CUDA(cudaStreamSynchronize(s));
     return TSW_OK;
 }

@@ -4,6 +4,7 @@
 #define TORPOR_SWAP_ENGINE_HPP_
 
 #include <atomic>
+#include <map>
 #include <cstdint>
 #include <memory>
 #include <mutex>
@@ -74,6 +75,9 @@ struct tsw_engine {
     std::atomic<uint64_t> kernel_launches{0};
     std::atomic<uint64_t> bytes_moved{0};
     std::vector<void*> loose_host;   // page-locked mirrors outside the arena
+
+    std::map<std::string, uint64_t> ipc_open;            // IPC handle bytes -> address mapped here
+    std::vector<std::pair<void*, uint64_t>> attached;    // shared host arenas registered here
 
     // launch scratch of tsw_place_segments
     void* raw_d_descs = nullptr;

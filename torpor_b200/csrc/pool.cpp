@@ -143,6 +143,14 @@ public:
         return 0;
     }
 
+    void regions(std::vector<std::pair<uint64_t, uint64_t>>* out) const override {
+        if (mem_->plan_only()) return;
+        if (base_) out->emplace_back(base_, n_chunks_ * kChunkBytes);
+        for (auto& kv : oversize_live_) out->emplace_back(kv.first, kv.second.size);
+        for (auto& kv : oversize_idle_)
+            for (auto& a : kv.second) out->emplace_back(a.phys, a.size);
+    }
+
     // acquire_block (:288-301)
     int acquire(uint64_t size, bool, DevAddr* out) override {
         if (size == kRegular2MiB || size == kRegular20MiB) return acquire_class(size, true, out);
@@ -318,6 +326,11 @@ public:
         for (auto& kv : live_)
             if (phys >= kv.first && phys < kv.first + kv.second.size) return kv.second.canon + (phys - kv.first);
         return 0;
+    }
+
+    void regions(std::vector<std::pair<uint64_t, uint64_t>>* out) const override {
+        if (mem_->plan_only()) return;
+        for (auto& kv : live_) out->emplace_back(kv.first, kv.second.size);
     }
 
     int acquire(uint64_t size, bool external_call, DevAddr* out) override {

@@ -83,6 +83,9 @@ public:
     virtual uint64_t canon_of(uint64_t phys) const = 0;
     // canon of any address inside a block this pool currently has handed out (0 if unknown)
     virtual uint64_t canon_inside(uint64_t phys) const = 0;
+    // every device allocation this pool holds, as (base, bytes): what another process has to
+    // map to reach any block the pool can hand out
+    virtual void regions(std::vector<std::pair<uint64_t, uint64_t>>* out) const = 0;
     std::string last_warning;
 };
 

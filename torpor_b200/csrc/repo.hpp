@@ -20,6 +20,8 @@
 #include <unordered_set>
 #include <vector>
 
+struct tsw_engine;
+
 namespace tsw {
 
 struct VBlock {                 // GeneralBlockInfo + ModelBlockInfo (model_repo.hpp:12-23)
@@ -68,6 +70,8 @@ struct Placement {
     void* h_descs = nullptr;
     uint32_t* h_first = nullptr;
     bool in_flight = false;
+    std::vector<tsw_engine*> helpers;   // engines whose kernels still write into these blocks
+    std::vector<int> remote_rows;       // rows handed out by a plan and not yet committed
 };
 
 struct Model {                  // HostModelInfo (model_repo.hpp:37-46)

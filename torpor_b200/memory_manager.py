@@ -22,6 +22,24 @@ from ._cabi import SwapError, check
 
 DEFAULT_TIMEOUT_NS = 30_000_000_000
 
+# tsw_segment as a numpy record (include/torpor_swap.h)
+SEGMENT_DTYPE = np.dtype([("src", "<u8"), ("dst", "<u8"), ("bytes", "<u8"), ("row_dst", "<u8"),
+                          ("row", "<u4"), ("row_tiles", "<u4")])
+
+
+def make_segments(src, dst, nbytes, rows=None, row_dst=None, row_tiles=None) -> np.ndarray:
+    n = len(src)
+    segs = np.zeros(n, dtype=SEGMENT_DTYPE)
+    segs["src"] = np.asarray(src, dtype=np.uint64)
+    segs["dst"] = np.asarray(dst, dtype=np.uint64)
+    segs["bytes"] = np.asarray(nbytes, dtype=np.uint64)
+    segs["row"] = np.arange(n, dtype=np.uint32) if rows is None else np.asarray(rows, dtype=np.uint32)
+    if row_dst is not None:
+        segs["row_dst"] = np.asarray(row_dst, dtype=np.uint64)
+    if row_tiles is not None:
+        segs["row_tiles"] = np.asarray(row_tiles, dtype=np.uint32)
+    return segs
+
 
 def repo_reset() -> None:
     check(_cabi.lib().tsw_repo_reset())
@@ -174,15 +192,56 @@ class MemoryManager:
         check(self.L.tsw_swap_in_sharded(self.h, func.encode(), arr, len(helpers)))
 
     def place_segments(self, src, dst, nbytes, rows=None, tile_bytes: int = 0, tile_first: int = 0,
-                       tile_stride: int = 1, publish: Optional[_cabi.Publish] = None, sync: bool = True) -> None:
+                       tile_stride: int = 1, tile_end: int = 0, publish: Optional[_cabi.Publish] = None,
+                       sync: bool = True, row_dst=None, row_tiles=None) -> None:
         """Run the placement kernel over explicit (src, dst, bytes) segments."""
-        n = len(src)
-        segs = (_cabi.Segment * max(n, 1))()
-        for i in range(n):
-            segs[i].src, segs[i].dst, segs[i].bytes = int(src[i]), int(dst[i]), int(nbytes[i])
-            segs[i].row = int(rows[i]) if rows is not None else i
-        check(self.L.tsw_place_segments(self.h, segs, n, tile_bytes, tile_first, tile_stride,
-                                        C.byref(publish) if publish is not None else None, 1 if sync else 0))
+        segs = make_segments(src, dst, nbytes, rows, row_dst, row_tiles)
+        self.place_segment_array(segs, tile_bytes, tile_first, tile_stride, tile_end, publish, sync)
+
+    def place_segment_array(self, segs: np.ndarray, tile_bytes: int = 0, tile_first: int = 0, tile_stride: int = 1,
+                            tile_end: int = 0, publish: Optional[_cabi.Publish] = None, sync: bool = True) -> None:
+        """Same, with the segments already in the ABI's layout (``SEGMENT_DTYPE``)."""
+        segs = np.ascontiguousarray(segs, dtype=SEGMENT_DTYPE)
+        check(self.L.tsw_place_segments(self.h, segs.ctypes.data, len(segs), tile_bytes, tile_first, tile_stride,
+                                        tile_end, C.byref(publish) if publish is not None else None,
+                                        1 if sync else 0))
+
+    # ---- one process per GPU: plan here, move elsewhere, commit here
+    def swap_plan(self, func: str):
+        """Place and rebind like ``sig_trans_thread`` but return the moves instead of running
+        them: (segments as ``SEGMENT_DTYPE`` array, tile bytes, publish block)."""
+        n_max = max(16, self.L.tsw_dump_params(self.h, func.encode(), 0, None, 0))
+        segs = np.zeros(n_max, dtype=SEGMENT_DTYPE)
+        tile = C.c_uint32()
+        pub = _cabi.Publish()
+        n = check(self.L.tsw_swap_plan(self.h, func.encode(), segs.ctypes.data, n_max, C.byref(tile), C.byref(pub)))
+        return segs[:n], tile.value, pub
+
+    def swap_commit(self, func: str) -> None:
+        check(self.L.tsw_swap_commit(self.h, func.encode()))
+
+    def ipc_regions(self):
+        """[(base, size, handle bytes)] of every device allocation a peer process must map."""
+        n = check(self.L.tsw_ipc_regions(self.h, None, 0))
+        arr = (_cabi.IpcRegion * max(n, 1))()
+        check(self.L.tsw_ipc_regions(self.h, arr, n))
+        return [(arr[i].base, arr[i].size, bytes(arr[i].handle)) for i in range(n)]
+
+    def ipc_open(self, handle: bytes) -> int:
+        out = C.c_uint64()
+        buf = C.create_string_buffer(handle, 64)
+        check(self.L.tsw_ipc_open(self.h, buf, C.byref(out)))
+        return out.value
+
+    def arena_info(self):
+        a, b, c, d = C.c_uint64(), C.c_uint64(), C.c_uint64(), C.c_uint64()
+        check(self.L.tsw_arena_info(self.h, C.byref(a), C.byref(b), C.byref(c), C.byref(d)))
+        return {"host_base": a.value, "dev_base": b.value, "size": c.value, "used": d.value}
+
+    def arena_attach(self, shm_name: str, size: int) -> int:
+        out = C.c_uint64()
+        check(self.L.tsw_arena_attach(self.h, shm_name.encode(), size, C.byref(out)))
+        return out.value
 
     def wait_ready(self, func: str, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
         check(self.L.tsw_wait_ready(self.h, func.encode(), timeout_ns))
@@ -247,12 +306,8 @@ def place_segments_static(device: int, src, dst, nbytes, rows=None, tile_bytes: 
     (``tsw_place_segments_static``): for callers on a server's steady-state path, where
     cudaMalloc would stall or fail.  At most ``STATIC_MAX_SEGMENTS`` segments per call; the
     call is asynchronous on ``stream``, and calls on one device must not overlap on the GPU."""
-    n = len(src)
-    segs = (_cabi.Segment * max(n, 1))()
-    for i in range(n):
-        segs[i].src, segs[i].dst, segs[i].bytes = int(src[i]), int(dst[i]), int(nbytes[i])
-        segs[i].row = int(rows[i]) if rows is not None else i
-    check(_cabi.lib().tsw_place_segments_static(device, segs, n, tile_bytes, tile_first, tile_stride,
+    segs = make_segments(src, dst, nbytes, rows)
+    check(_cabi.lib().tsw_place_segments_static(device, segs.ctypes.data, len(segs), tile_bytes, tile_first, tile_stride,
                                                 C.byref(publish) if publish is not None else None, stream))
 
 

@@ -1,0 +1,389 @@
+"""Sharded swap-in with one process per GPU.
+
+One rank (the *target*, rank 0) owns the pool the model ends up in; every rank lends its
+PCIe link.  Per swap the target places blocks and rebinds the pointer table
+(``tsw_swap_plan``), broadcasts the moves, and every rank runs the placement kernel on its
+own GPU over its share of the tiles: reading the shared page-locked host store across its
+own PCIe link and storing straight into the target's pool blocks across NVLink (the pool
+is opened through CUDA IPC).  Completion counters and the pointer table sit on the target,
+so whichever GPU finishes a parameter publishes it; the target then commits the rows
+(``tsw_swap_commit``).  No collective moves data: ``torch.distributed`` (a gloo group)
+carries only the few KB of control messages.
+
+Two ways of dealing out the tiles:
+  direct  tile t goes to rank t mod N; host store -> target pool in one kernel per rank.
+  staged  rank r owns the contiguous tile range r; its share is first pulled into local HBM
+          (``prepare``), and the timed move is local HBM -> target pool across NVLink -- the
+          gather stage on its own.
+
+The reference has no counterpart (its swap uses one GPU's link, memory_manager.hpp:331-438);
+the result must equal that single-GPU swap-in, which the tests check.
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+
+from . import _cabi
+from .memory_manager import SEGMENT_DTYPE, MemoryManager
+
+PUB_WORDS = 6          # tsw_publish as uint64 words: done, phys, flag, host_phys, host_flag, (flag_value|pad)
+HEADER_WORDS = 8       # n_segments, tile_bytes, regions_epoch, mode, 4 spare
+
+
+def tiles_of(segs: np.ndarray, tile: int) -> np.ndarray:
+    """Tile prefix sums of a segment list: segment k owns tiles [first[k], first[k+1])."""
+    n = (segs["bytes"].astype(np.uint64) + np.uint64(tile - 1)) // np.uint64(tile)
+    return np.concatenate([[0], np.cumsum(n)]).astype(np.int64)
+
+
+def fill_rows(segs: np.ndarray, tile: int) -> np.ndarray:
+    """Make ``row_tiles`` / ``row_dst`` explicit so that every rank launches the same table."""
+    segs = segs.copy()
+    first = tiles_of(segs, tile)
+    per_seg = np.diff(first).astype(np.uint32)
+    rows = segs["row"]
+    total: Dict[int, int] = {}
+    first_dst: Dict[int, int] = {}
+    for i in range(len(segs)):
+        r = int(rows[i])
+        total[r] = total.get(r, 0) + int(per_seg[i])
+        first_dst.setdefault(r, int(segs["dst"][i]))
+    for i in range(len(segs)):
+        if segs["row_tiles"][i] == 0:
+            segs["row_tiles"][i] = total[int(rows[i])]
+            segs["row_dst"][i] = first_dst[int(rows[i])]
+    return segs
+
+
+def contiguous_share(total_tiles: int, rank: int, world: int) -> Tuple[int, int]:
+    """Tile range [lo, hi) of ``rank`` when ``total_tiles`` are cut into ``world`` equal runs."""
+    lo = (total_tiles * rank) // world
+    hi = (total_tiles * (rank + 1)) // world
+    return lo, hi
+
+
+class AddressMap:
+    """Rebase addresses of the target process into this process: device regions opened over
+    IPC and the shared host arena."""
+
+    def __init__(self):
+        self.base0 = np.zeros(0, dtype=np.uint64)
+        self.size = np.zeros(0, dtype=np.uint64)
+        self.local = np.zeros(0, dtype=np.uint64)
+
+    def set(self, entries: List[Tuple[int, int, int]]):
+        entries = sorted(entries)
+        self.base0 = np.array([e[0] for e in entries], dtype=np.uint64)
+        self.size = np.array([e[1] for e in entries], dtype=np.uint64)
+        self.local = np.array([e[2] for e in entries], dtype=np.uint64)
+
+    def rebase(self, addr: np.ndarray) -> np.ndarray:
+        addr = np.asarray(addr, dtype=np.uint64)
+        if addr.size == 0:
+            return addr
+        idx = np.searchsorted(self.base0, addr, side="right").astype(np.int64) - 1
+        if (idx < 0).any():
+            raise ValueError("address below every shared region")
+        off = addr - self.base0[idx]
+        if (off >= self.size[idx]).any():
+            bad = int(addr[np.nonzero(off >= self.size[idx])[0][0]])
+            raise ValueError(f"address {bad:#x} is in no region shared by the target")
+        return self.local[idx] + off
+
+    def rebase_one(self, addr: int) -> int:
+        return int(self.rebase(np.array([addr], dtype=np.uint64))[0]) if addr else 0
+
+
+class ShardedSwap:
+    """Collective swap-in over the ranks of ``group`` (a gloo process group for control).
+
+    ``engine`` is this rank's engine on its own GPU; on rank 0 it is the target and was
+    created with ``host_arena_shm=shm_name``.  All ranks call the same methods in the same
+    order.  With ``engine=None`` (tests on CPU) only the planning and rebasing logic runs.
+    """
+
+    def __init__(self, engine: Optional[MemoryManager], rank: int, world: int, group=None,
+                 shm_name: Optional[str] = None, max_segments: int = 4096):
+        import torch.distributed as dist
+        self.dist = dist
+        self.engine = engine
+        self.rank, self.world, self.group = rank, world, group
+        self.shm_name = shm_name
+        self.max_segments = max_segments
+        self.map = AddressMap()
+        self.epoch = -1
+        self.region_bases: List[int] = []
+        self.arena_entry: Optional[Tuple[int, int, int]] = None
+        self.staging = {}           # (func, lo, hi, tile) -> torch uint8 buffer
+        self.last = {}
+        # without a CUDA engine only planning, sharing and rebasing run (CPU tests)
+        self.dry = engine is None or engine.device < 0
+
+    # ---- control plane
+    def _bcast_words(self, words: np.ndarray) -> np.ndarray:
+        import torch
+        t = torch.from_numpy(words.view(np.int64))
+        self.dist.broadcast(t, src=0, group=self.group)
+        return t.numpy().view(np.uint64)
+
+    def _bcast_obj(self, obj):
+        box = [obj]
+        self.dist.broadcast_object_list(box, src=0, group=self.group)
+        return box[0]
+
+    def _max_over_ranks(self, value: float) -> float:
+        import torch
+        t = torch.tensor([value], dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX, group=self.group)
+        return float(t[0])
+
+    def attach_arena(self):
+        """Map the target's host store into every rank (once)."""
+        info = self.engine.arena_info() if (self.rank == 0 and self.engine) else None
+        info = self._bcast_obj(info)
+        if self.dry:
+            self.arena_entry = None
+            return
+        if info is None or info["size"] == 0:
+            raise RuntimeError("the target engine has no shared host arena")
+        if self.rank == 0:
+            local = info["dev_base"]
+        else:
+            local = self.engine.arena_attach(self.shm_name, info["size"])
+        self.arena_entry = (info["dev_base"], info["size"], local)
+
+    def share_regions(self):
+        """(Re)open the target's device allocations in every rank."""
+        regs = self.engine.ipc_regions() if (self.rank == 0 and self.engine and not self.dry) else None
+        regs = self._bcast_obj(regs)
+        entries = [self.arena_entry] if self.arena_entry else []
+        for base, size, handle in regs or []:
+            if self.rank == 0:
+                entries.append((base, size, base))
+            else:
+                entries.append((base, size, self.engine.ipc_open(handle)))
+        self.map.set(entries)
+        self.region_bases = sorted(b for b, _, _ in (regs or []))
+
+    # ---- data plane
+    def plan(self, func: str, mode: int):
+        """Target: place + rebind and pack the moves; everyone: receive them."""
+        buf = np.zeros(HEADER_WORDS + PUB_WORDS + self.max_segments * (SEGMENT_DTYPE.itemsize // 8), dtype=np.uint64)
+        if self.rank == 0:
+            segs, tile, pub = self.engine.swap_plan(func)
+            if len(segs) > self.max_segments:
+                raise RuntimeError("raise max_segments")
+            segs = fill_rows(segs, tile)
+            bases = [] if self.dry else sorted(b for b, _, _ in self.engine.ipc_regions())
+            changed = bases != self.region_bases
+            buf[0], buf[1], buf[2], buf[3] = len(segs), tile, 1 if changed else 0, mode
+            buf[HEADER_WORDS:HEADER_WORDS + PUB_WORDS] = [pub.done_count, pub.table_phys, pub.table_flag, 0, 0, pub.flag_value]
+            raw = segs.view(np.uint64)
+            buf[HEADER_WORDS + PUB_WORDS:HEADER_WORDS + PUB_WORDS + raw.size] = raw
+        buf = self._bcast_words(buf)
+        n, tile, changed = int(buf[0]), int(buf[1]), int(buf[2])
+        if changed:
+            self.share_regions()
+        pubw = buf[HEADER_WORDS:HEADER_WORDS + PUB_WORDS]
+        w = SEGMENT_DTYPE.itemsize // 8
+        segs = buf[HEADER_WORDS + PUB_WORDS:HEADER_WORDS + PUB_WORDS + n * w].copy().view(SEGMENT_DTYPE)
+        return segs, tile, pubw
+
+    def _local_publish(self, pubw) -> _cabi.Publish:
+        m = self.map
+        return _cabi.Publish(m.rebase_one(int(pubw[0])), m.rebase_one(int(pubw[1])), m.rebase_one(int(pubw[2])),
+                             0, 0, int(pubw[5]), 0)
+
+    def localize(self, segs: np.ndarray) -> np.ndarray:
+        out = segs.copy()
+        out["src"] = self.map.rebase(segs["src"])
+        out["dst"] = self.map.rebase(segs["dst"])
+        out["row_dst"] = segs["row_dst"]          # published value: the TARGET's address, not ours
+        return out
+
+    def swap_in(self, func: str, mode: str = "direct") -> dict:
+        """Collective swap-in of ``func`` into the target's pool.  Returns timing of this rank's
+        kernel and the maximum over ranks (device time, CUDA events)."""
+        t0 = time.perf_counter()
+        segs, tile, pubw = self.plan(func, 0 if mode == "direct" else 1)
+        n_tiles = int(tiles_of(segs, tile)[-1]) if len(segs) else 0
+        dev_ns = 0.0
+        if mode == "direct":
+            self.my_tiles = range(self.rank, n_tiles, self.world)
+        else:
+            self.my_tiles = range(*contiguous_share(n_tiles, self.rank, self.world))
+        self.last_plan = (segs, tile)
+        if len(segs) and not self.dry:
+            local = self.localize(segs)
+            pub = self._local_publish(pubw)
+            if mode == "direct":
+                self.engine.place_segment_array(local, tile, self.rank, self.world, 0, pub, sync=True)
+            else:
+                lo, hi = contiguous_share(n_tiles, self.rank, self.world)
+                buf = self._staging(func, segs, tile, lo, hi)
+                first = tiles_of(segs, tile)[:-1]
+                local["src"] = (np.uint64(buf.data_ptr()) + ((first - lo) * tile).astype(np.int64).view(np.uint64))
+                if hi > lo:
+                    self.engine.place_segment_array(local, tile, lo, 1, hi, pub, sync=True)
+            dev_ns = float(self.engine.stats()["last_swap_device_ns"])
+        t_done = time.perf_counter()
+        dev_max = self._max_over_ranks(dev_ns)          # doubles as the completion barrier
+        if self.rank == 0 and self.engine is not None:
+            self.engine.swap_commit(func)
+        self.last = {"tiles": n_tiles, "segments": len(segs), "tile_bytes": tile, "device_ns": dev_ns,
+                     "device_ns_max": dev_max, "local_wall_s": t_done - t0, "wall_s": time.perf_counter() - t0}
+        return self.last
+
+    def _staging(self, func, segs, tile, lo, hi):
+        """This rank's contiguous share of the swap, resident in local HBM."""
+        import torch
+        key = (func, lo, hi, tile)
+        if key in self.staging:
+            return self.staging[key]
+        buf = torch.empty(max(1, (hi - lo) * tile), dtype=torch.uint8, device=f"cuda:{self.engine.device}")
+        pull = segs.copy()
+        first = tiles_of(segs, tile)[:-1]
+        pull["src"] = self.map.rebase(segs["src"])
+        pull["dst"] = (np.uint64(buf.data_ptr()) + ((first - lo) * tile).astype(np.int64).view(np.uint64))
+        if hi > lo:
+            self.engine.place_segment_array(pull, tile, lo, 1, hi, None, sync=True)
+        self.staging[key] = buf
+        return buf
+
+    def evict(self, func: str):
+        if self.rank == 0 and self.engine is not None:
+            self.engine.evict(func)
+
+
+# ------------------------------------------------------------------ benchmark driver (torchrun)
+
+def bench_main(args, bench):
+    """bench.py at N > 1: one rank per GPU; rank 0's GPU is the target."""
+    import statistics
+    import torch
+    import torch.distributed as dist
+    from . import workloads as W
+    from .memory_manager import ModelRepo, checksum_host, repo_reset
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if world == 1:
+        raise SystemExit("bench.py --gpus N with N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    ctrl = dist.new_group(backend="gloo")
+    ncpu = os.cpu_count() or 1
+    peaks, peak_kind = bench.measured_peaks()
+
+    ws = W.weight_set(args.workload)
+    shm = f"/torpor_swap_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}"
+    repo_reset()
+    if rank == 0:
+        eng = MemoryManager(W.pool_budget_for(ws), device=local_rank, server_id=0, gpu_count=world,
+                            host_arena_bytes=W.host_store_bytes(ws), host_arena_shm=shm)
+    else:
+        eng = MemoryManager(0, device=local_rank, server_id=rank, gpu_count=world, block_manager="Fixed")
+    sw = ShardedSwap(eng, rank, world, ctrl, shm_name=shm, max_segments=max(1024, len(ws.tensors) + 16))
+
+    sums = {}
+    cold_s = 0.0
+    if rank == 0:
+        pool, data = bench.generate_tensors(ws, min(ncpu, 16))
+
+        def data_and_sum(i):
+            b = data(i)
+            if i % 16 == 0:
+                sums[i] = checksum_host(b)
+            return b
+        t0 = time.time()
+        W.cold_start(eng, "model", ws, tensor_data=data_and_sum)
+        pool.shutdown()
+        torch.cuda.synchronize()
+        cold_s = time.time() - t0
+        eng.evict("model")
+    dist.barrier(group=ctrl)
+    sw.attach_arena()
+    sw.share_regions()
+
+    def verify():
+        if rank == 0:
+            got = eng.checksum_resident("model")
+            for i, s in sums.items():
+                if not np.array_equal(got[i], s):
+                    raise RuntimeError(f"resident bytes of tensor {i} differ from the host store")
+
+    def timed(mode, steps, warmup):
+        for _ in range(warmup):
+            sw.swap_in("model", mode); sw.evict("model")
+        dev = []
+        launches0 = eng.stats()["kernel_launches"]
+        dist.barrier(group=ctrl)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            r = sw.swap_in("model", mode)
+            dev.append(r["device_ns_max"])
+            sw.evict("model")
+        torch.cuda.synchronize()
+        dist.barrier(group=ctrl)
+        wall = time.perf_counter() - t0
+        wall = sw._max_over_ranks(wall)
+        return wall, dev, eng.stats()["kernel_launches"] - launches0
+
+    # correctness of both arms before anything is timed (also fills the staged shares)
+    sw.swap_in("model", "direct"); verify(); sw.evict("model")
+    sw.swap_in("model", "staged"); verify(); sw.evict("model")
+
+    sampler = bench.ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    wall_v, dev_v, launches_v = timed("staged", args.steps, args.warmup)
+    wall_e, dev_e, launches_e = timed("direct", args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+
+    total_launches = torch.tensor([launches_v, launches_e], dtype=torch.int64)
+    dist.all_reduce(total_launches, group=ctrl)
+
+    line = None
+    if rank == 0:
+        B = ws.nbytes
+        value = B * args.steps / wall_v / 1e9
+        e2e = B * args.steps / wall_e / 1e9
+        kern_v = statistics.mean(dev_v) / 1e9
+        kern_e = statistics.mean(dev_e) / 1e9
+        inbound = B * (world - 1) / world
+        line = {
+            "metric": "model_swap_in_throughput", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall_v / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": bench.workload_config(args, world),
+            "value_arm": f"gather stage: each rank's 1/{world} share resident in its HBM, stored into the target's pool over NVLink",
+            "e2e": {"value": e2e, "unit": "GB/s", "ms_per_model": wall_e / args.steps * 1e3,
+                    "h2d_bytes_per_step": B + 40 * len(ws.tensors) * world, "d2h_bytes_per_step": 12 * len(ws.tensors),
+                    "device_ms_per_model": kern_e * 1e3,
+                    "what": "sharded swap-in from the shared host store: every rank reads its tiles over its own PCIe link and stores them into the target's pool over NVLink; plan + control messages + commit + evict inside the timed region"},
+            "roofline": {"bound": "nvlink", "achieved": inbound / kern_v / 1e9, "peak": 770.0, "unit": "GB/s",
+                         "frac": inbound / kern_v / 1e9 / 770.0,
+                         "peak_kind": "measured peer-copy bandwidth per direction on this pool (nominal 900)",
+                         "kernel": "place_kernel (local HBM -> target pool over NVLink)",
+                         "algorithmic_bytes_per_launch": inbound, "launch_ms": kern_v * 1e3, "traffic": None},
+            "link_roofline": {"bound": "pcie", "achieved": B / kern_e / 1e9, "achieved_wall": e2e,
+                              "peak": bench.PCIE_GEN5_X16_GBS * world, "unit": "GB/s",
+                              "frac": (B / kern_e / 1e9) / (bench.PCIE_GEN5_X16_GBS * world),
+                              "frac_wall": e2e / (bench.PCIE_GEN5_X16_GBS * world),
+                              "peak_kind": f"theoretical PCIe Gen5 x16 x {world} participating GPUs",
+                              "kernel": "place_kernel (host store -> target pool, zero-copy over PCIe, peer stores over NVLink)"},
+            "cpu_baseline": None,
+            "gpu_launches": int(total_launches[0]), "gpu_launches_e2e": int(total_launches[1]),
+            "clocks": clocks, "host_cores": ncpu, "cold_start_s": cold_s,
+        }
+    dist.barrier(group=ctrl)
+    eng.close()
+    repo_reset()
+    dist.destroy_process_group()
+    return line
