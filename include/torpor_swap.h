@@ -204,6 +204,9 @@ int tsw_swap_plan(tsw_engine* e, const char* func, tsw_segment* segs, int cap, u
 int tsw_swap_commit(tsw_engine* e, const char* func);
 int tsw_ipc_regions(tsw_engine* e, tsw_ipc_region* out, int cap);   /* returns the number of regions */
 int tsw_ipc_open(tsw_engine* e, const void* handle, uint64_t* mapped_base);
+/* What the CUDA driver knows about an address in this process (cudaPointerGetAttributes):
+ * type 0 = unknown to the driver, 1 = page-locked host, 2 = device, 3 = managed. */
+int tsw_pointer_info(tsw_engine* e, uint64_t addr, int* type, int* device, uint64_t* device_pointer, uint64_t* host_pointer);
 int tsw_arena_info(tsw_engine* e, uint64_t* host_base, uint64_t* dev_base, uint64_t* size, uint64_t* used);
 int tsw_arena_attach(tsw_engine* e, const char* shm_name, uint64_t size, uint64_t* dev_base);
 

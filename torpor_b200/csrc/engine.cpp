@@ -229,6 +229,24 @@ WaitResult wait_row(tsw_engine* e, Placement& pl, int idx, int64_t timeout_ns) {
     return {TSW_OK, pl.phys[idx]};
 }
 
+// Map a shared-memory arena at an address far away from where the CUDA driver keeps its own
+// mappings.  A mapping that the kernel had placed next to the driver's was seen to vanish from
+// the process on the first kernel launch that followed (the driver re-maps ranges it considers
+// its own), which left the registered store unmapped under a running kernel.
+void* map_shared_far(int fd, uint64_t size, int slot) {
+    static std::atomic<uint64_t> next{0};
+    const uint64_t stride = 1ull << 40;
+    for (int attempt = 0; attempt < 64; ++attempt) {
+        const uint64_t hint = 0x200000000000ull + (uint64_t)((slot + 64 * (int)(next++ % 1024)) % 4096) * stride;
+        void* p = mmap((void*)hint, size, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED_NOREPLACE, fd, 0);
+        if (p != MAP_FAILED) {
+            if ((uint64_t)p == hint) return p;
+            munmap(p, size);  // an old kernel ignored the flag and placed it elsewhere
+        }
+    }
+    return mmap(nullptr, size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+}
+
 int make_arena(tsw_engine* e) {
     const uint64_t size = e->cfg.host_arena_bytes;
     if (size == 0) return TSW_OK;
@@ -238,7 +256,7 @@ int make_arena(tsw_engine* e) {
         a.shm_fd = shm_open(a.shm_name.c_str(), O_CREAT | O_RDWR, 0600);
         if (a.shm_fd < 0) return fail(TSW_ERR_INVALID, "shm_open failed for the host arena");
         if (ftruncate(a.shm_fd, (off_t)size) != 0) return fail(TSW_ERR_INVALID, "ftruncate failed for the host arena");
-        void* p = mmap(nullptr, size, PROT_READ | PROT_WRITE, MAP_SHARED, a.shm_fd, 0);
+        void* p = map_shared_far(a.shm_fd, size, e->server_id);
         if (p == MAP_FAILED) return fail(TSW_ERR_INVALID, "mmap failed for the host arena");
         a.base = (uint8_t*)p;
         a.size = size;
@@ -464,9 +482,41 @@ int tsw_engine_create(const tsw_config* cfg, tsw_engine** out) {
         TSW_CUDA(cudaHostAlloc(&hp, slab, cudaHostAllocPortable | cudaHostAllocMapped));
         e->host_slab.base = (uint8_t*)hp;
         e->host_slab.size = slab;
-        e->d_status = (uint32_t*)e->dev_slab.take(256);
+        // the kernels' error word lives in host-mapped memory: the device writes it, waiters read it
         e->h_status = (volatile uint32_t*)e->host_slab.take(256);
         *e->h_status = 0;
+        e->d_status = (uint32_t*)e->h_status;
+        // Launch scratch and the first kernel launch (module load) happen here, not on the
+        // first swap: both are one-time costs, and both must precede any attach of a shared arena.
+        {
+            const uint64_t cap = 4096;
+            TSW_CUDA(cudaMalloc(&e->raw_d_descs, sizeof(PlaceDesc) * cap));
+            TSW_CUDA(cudaMalloc(&e->raw_d_first, sizeof(uint32_t) * (cap + 1)));
+            TSW_CUDA(cudaHostAlloc(&e->raw_h, sizeof(PlaceDesc) * cap + sizeof(uint32_t) * (cap + 1), cudaHostAllocDefault));
+            e->raw_cap = cap;
+            uint8_t* warm = (uint8_t*)e->dev_slab.take(512);
+            PlaceDesc d;
+            memset(&d, 0, sizeof(d));
+            d.src = (uint64_t)warm;
+            d.dst = (uint64_t)warm + 256;
+            d.bytes = 16;
+            d.row_tiles = 1;
+            const uint32_t first[2] = {0, 1};
+            TSW_CUDA(cudaMemcpy(e->raw_d_descs, &d, sizeof(d), cudaMemcpyHostToDevice));
+            TSW_CUDA(cudaMemcpy(e->raw_d_first, first, sizeof(first), cudaMemcpyHostToDevice));
+            PlaceArgs a;
+            memset(&a, 0, sizeof(a));
+            a.descs = (const PlaceDesc*)e->raw_d_descs;
+            a.first_tile = (const uint32_t*)e->raw_d_first;
+            a.n_descs = 1;
+            a.tile_bytes = 64;
+            a.tile_hi = 1;
+            a.tile_stride = 1;
+            a.status = e->d_status;
+            cudaError_t le = launch_place(a, 1, s);
+            if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("warm-up launch: ") + cudaGetErrorString(le));
+            TSW_CUDA(cudaStreamSynchronize(s));
+        }
         int rc = make_arena(e.get());
         if (rc != TSW_OK) return rc;
         // all-pairs peer access, as the controller does at start-up (controller.hpp:63-75)
@@ -510,8 +560,8 @@ int tsw_engine_destroy(tsw_engine* e) {
         e->pool.reset();
         for (auto& kv : e->ipc_open) cudaIpcCloseMemHandle((void*)kv.second);
         for (auto& a : e->attached) {
-            cudaHostUnregister(a.first);
-            munmap(a.first, a.second);
+            cudaHostUnregister(a.host);
+            munmap(a.host, a.size);
         }
         if (e->raw_d_descs) cudaFree(e->raw_d_descs);
         if (e->raw_d_first) cudaFree(e->raw_d_first);
@@ -1407,6 +1457,23 @@ int tsw_ipc_open(tsw_engine* e, const void* handle, uint64_t* mapped_base) {
     return TSW_OK;
 }
 
+int tsw_pointer_info(tsw_engine* e, uint64_t addr, int* type, int* device, uint64_t* device_pointer, uint64_t* host_pointer) {
+    if (!e) return fail(TSW_ERR_INVALID, "null argument");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine has no device");
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    cudaPointerAttributes at;
+    cudaError_t err = cudaPointerGetAttributes(&at, (const void*)addr);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TSW_ERR_CUDA, std::string("cudaPointerGetAttributes: ") + cudaGetErrorString(err));
+    }
+    if (type) *type = (int)at.type;
+    if (device) *device = at.device;
+    if (device_pointer) *device_pointer = (uint64_t)at.devicePointer;
+    if (host_pointer) *host_pointer = (uint64_t)at.hostPointer;
+    return TSW_OK;
+}
+
 int tsw_arena_info(tsw_engine* e, uint64_t* host_base, uint64_t* dev_base, uint64_t* size, uint64_t* used) {
     if (!e) return fail(TSW_ERR_INVALID, "null argument");
     if (host_base) *host_base = (uint64_t)e->arena.base;
@@ -1422,7 +1489,7 @@ int tsw_arena_attach(tsw_engine* e, const char* shm_name, uint64_t size, uint64_
     Lock g2(e->mu);
     int fd = shm_open(shm_name, O_RDWR, 0600);
     if (fd < 0) return fail(TSW_ERR_NOT_FOUND, std::string("shm_open(") + shm_name + ") failed");
-    void* p = mmap(nullptr, size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+    void* p = map_shared_far(fd, size, e->server_id);
     close(fd);
     if (p == MAP_FAILED) return fail(TSW_ERR_INVALID, "mmap of the shared host arena failed");
     TSW_CUDA(cudaSetDevice(e->cfg.device));
@@ -1433,9 +1500,43 @@ int tsw_arena_attach(tsw_engine* e, const char* shm_name, uint64_t size, uint64_
     }
     void* dp = nullptr;
     TSW_CUDA(cudaHostGetDevicePointer(&dp, p, 0));
-    e->attached.emplace_back(p, size);
+    e->attached.push_back({p, size, (uint64_t)dp});
     *dev_base = (uint64_t)dp;
     return TSW_OK;
+}
+
+// Ask the driver what every address of a launch is before the kernel touches it.  Used when
+// TORPOR_SWAP_VALIDATE=1: a pointer the driver does not know (a stale IPC mapping, an
+// unregistered host range, an address of another process) is reported as an error instead
+// of faulting the GPU.
+static int validate_address(tsw_engine* e, const char* what, int index, uint64_t addr, uint64_t bytes) {
+    if (bytes == 0) return TSW_OK;
+    // Device-side aliases of registered host memory (where the device address differs from the
+    // host address) are not reported by the driver; the engine knows the ones it made.
+    if (e->arena.base) {
+        const uint64_t lo = (uint64_t)((int64_t)(uint64_t)e->arena.base + e->arena.dev_delta);
+        if (addr >= lo && addr + bytes <= lo + e->arena.size) return TSW_OK;
+    }
+    for (auto& a : e->attached)
+        if (addr >= a.dev && addr + bytes <= a.dev + a.size) return TSW_OK;
+    for (uint64_t probe : {addr, addr + bytes - 1}) {
+        cudaPointerAttributes at;
+        cudaError_t err = cudaPointerGetAttributes(&at, (const void*)probe);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            return fail(TSW_ERR_INVALID, std::string(what) + " " + std::to_string(index) + ": cudaPointerGetAttributes failed for " +
+                                             std::to_string(probe) + ": " + cudaGetErrorString(err));
+        }
+        if (at.type == cudaMemoryTypeUnregistered)
+            return fail(TSW_ERR_INVALID, std::string(what) + " " + std::to_string(index) + ": address " + std::to_string(probe) +
+                                             " is not known to the CUDA driver in this process");
+    }
+    return TSW_OK;
+}
+
+static bool validation_on() {
+    static const bool on = [] { const char* v = getenv("TORPOR_SWAP_VALIDATE"); return v && v[0] == '1'; }();
+    return on;
 }
 
 int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
@@ -1459,8 +1560,8 @@ int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t t
         TSW_CUDA(cudaStreamSynchronize(s));
         for (auto& kv : e->ipc_open) cudaIpcCloseMemHandle((void*)kv.second);
         for (auto& a : e->attached) {
-            cudaHostUnregister(a.first);
-            munmap(a.first, a.second);
+            cudaHostUnregister(a.host);
+            munmap(a.host, a.size);
         }
         if (e->raw_d_descs) cudaFree(e->raw_d_descs);
         if (e->raw_d_first) cudaFree(e->raw_d_first);
@@ -1499,6 +1600,26 @@ int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t t
         a.host_flag = (uint32_t*)pub->host_flag;
         a.flag_value = pub->flag_value;
         if (a.done_count && (!a.table_phys || !a.table_flag)) return fail(TSW_ERR_INVALID, "publish block needs both table columns");
+    }
+    if (validation_on()) {
+        uint32_t max_row = 0;
+        for (int i = 0; i < n; ++i) {
+            // only the part of the segment whose tiles this launch can touch
+            const uint64_t t0 = std::max<uint64_t>(plan.first[i], a.tile_lo), t1 = std::min<uint64_t>(plan.first[i + 1], a.tile_hi);
+            if (t0 >= t1) continue;
+            const uint64_t off = (t0 - plan.first[i]) * tile_bytes;
+            const uint64_t end = std::min<uint64_t>((t1 - plan.first[i]) * tile_bytes, plan.descs[i].bytes);
+            int rc = validate_address(e, "segment source", i, plan.descs[i].src + off, end - off);
+            if (rc == TSW_OK) rc = validate_address(e, "segment destination", i, plan.descs[i].dst + off, end - off);
+            if (rc != TSW_OK) return rc;
+            max_row = std::max(max_row, plan.descs[i].row);
+        }
+        if (a.done_count) {
+            int rc = validate_address(e, "tile counters", 0, (uint64_t)a.done_count, 4ull * (max_row + 1));
+            if (rc == TSW_OK) rc = validate_address(e, "table column phys", 0, (uint64_t)a.table_phys, 8ull * (max_row + 1));
+            if (rc == TSW_OK) rc = validate_address(e, "table column flag", 0, (uint64_t)a.table_flag, 4ull * (max_row + 1));
+            if (rc != TSW_OK) return rc;
+        }
     }
     cudaError_t le = launch_place(a, e->grid_ctas, s);
     if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));

@@ -77,7 +77,8 @@ struct tsw_engine {
     std::vector<void*> loose_host;   // page-locked mirrors outside the arena
 
     std::map<std::string, uint64_t> ipc_open;            // IPC handle bytes -> address mapped here
-    std::vector<std::pair<void*, uint64_t>> attached;    // shared host arenas registered here
+    struct Attached { void* host; uint64_t size; uint64_t dev; };
+    std::vector<Attached> attached;                      // shared host arenas registered here
 
     // launch scratch of tsw_place_segments
     void* raw_d_descs = nullptr;

@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(kThreads) place_kernel(const PlaceArgs a) {
         const PlaceDesc d = a.descs[k];
         const uint64_t off = (uint64_t)(t - s_first[k]) * a.tile_bytes;
         if (off >= d.bytes) {  // table and tile numbering disagree: report, move nothing
-            if (threadIdx.x == 0 && a.status) atomicExch(a.status, 1u);
+            if (threadIdx.x == 0 && a.status) *reinterpret_cast<volatile uint32_t*>(a.status) = 1u;
             continue;
         }
         const uint64_t left = d.bytes - off;

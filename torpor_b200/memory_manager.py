@@ -233,6 +233,11 @@ class MemoryManager:
         check(self.L.tsw_ipc_open(self.h, buf, C.byref(out)))
         return out.value
 
+    def pointer_info(self, addr: int):
+        t, d, dp, hp = C.c_int(), C.c_int(), C.c_uint64(), C.c_uint64()
+        check(self.L.tsw_pointer_info(self.h, addr, C.byref(t), C.byref(d), C.byref(dp), C.byref(hp)))
+        return {"type": t.value, "device": d.value, "device_pointer": dp.value, "host_pointer": hp.value}
+
     def arena_info(self):
         a, b, c, d = C.c_uint64(), C.c_uint64(), C.c_uint64(), C.c_uint64()
         check(self.L.tsw_arena_info(self.h, C.byref(a), C.byref(b), C.byref(c), C.byref(d)))
