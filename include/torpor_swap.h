@@ -67,6 +67,8 @@ typedef struct {
     int grid_ctas;          /* persistent CTAs of the placement kernel; 0 = default */
     int tile_bytes_host;    /* bytes per tile when the source is host memory; 0 = default */
     int tile_bytes_device;  /* bytes per tile when the source is device memory; 0 = default */
+    int shard_static;       /* tsw_swap_in_sharded: 0 = participants draw tiles from a shared counter
+                               (default), 1 = tile t is fixed to participant t mod n */
 } tsw_config;
 
 void tsw_config_default(tsw_config* cfg);
@@ -182,7 +184,10 @@ typedef struct {
     uint64_t host_phys;    /* optional host-mapped mirrors of the two columns (0 = none) */
     uint64_t host_flag;
     uint32_t flag_value;
-    uint32_t pad;
+    uint32_t ticket_chunk; /* tiles drawn per ticket (0 = 1) */
+    uint64_t ticket;       /* optional: uint32 on the target, set to tile_first before the swap.  When
+                              given, tile_stride is ignored and the CTAs of every participant draw
+                              their tiles from this counter, so faster links move more tiles */
 } tsw_publish;
 int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
                        uint32_t tile_stride, uint32_t tile_end, const tsw_publish* pub, int sync);

@@ -45,6 +45,7 @@ class Config(C.Structure):
         ("grid_ctas", C.c_int),
         ("tile_bytes_host", C.c_int),
         ("tile_bytes_device", C.c_int),
+        ("shard_static", C.c_int),
     ]
 
 
@@ -55,7 +56,8 @@ class Segment(C.Structure):
 
 class Publish(C.Structure):
     _fields_ = [("done_count", C.c_uint64), ("table_phys", C.c_uint64), ("table_flag", C.c_uint64),
-                ("host_phys", C.c_uint64), ("host_flag", C.c_uint64), ("flag_value", C.c_uint32), ("pad", C.c_uint32)]
+                ("host_phys", C.c_uint64), ("host_flag", C.c_uint64), ("flag_value", C.c_uint32),
+                ("ticket_chunk", C.c_uint32), ("ticket", C.c_uint64)]
 
 
 class IpcRegion(C.Structure):

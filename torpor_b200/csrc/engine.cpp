@@ -109,9 +109,10 @@ int ensure_rows(tsw_engine* e, Model* m, Placement& pl) {
         void* dp = e->dev_slab.take(sizeof(uint64_t) * cap);
         void* df = e->dev_slab.take(sizeof(uint32_t) * cap);
         void* dc = e->dev_slab.take(sizeof(uint32_t) * cap);
+        void* dk = e->dev_slab.take(256);
         void* dd = e->dev_slab.take(sizeof(PlaceDesc) * cap);
         void* dt = e->dev_slab.take(sizeof(uint32_t) * (cap + 1));
-        if (!flag || !phys || !hd || !hf || !dp || !df || !dc || !dd || !dt)
+        if (!flag || !phys || !hd || !hf || !dp || !df || !dc || !dd || !dt || !dk)
             return fail(TSW_ERR_POOL_EXHAUSTED, "pointer-table slab exhausted");
         memset((void*)flag, 0, sizeof(uint32_t) * cap);
         memset((void*)phys, 0, sizeof(uint64_t) * cap);
@@ -120,6 +121,7 @@ int ensure_rows(tsw_engine* e, Model* m, Placement& pl) {
         pl.d_table_phys = (uint64_t*)dp;
         pl.d_table_flag = (uint32_t*)df;
         pl.d_done = (uint32_t*)dc;
+        pl.d_ticket = (uint32_t*)dk;
         pl.d_descs = dd;
         pl.d_first = (uint32_t*)dt;
         // the device slab is zero-filled at creation, so the tile counters start at 0
@@ -962,13 +964,18 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
         // Deal tiles round-robin over the participating GPUs: GPU r takes tiles r, r + n, ...
         // so that every link works on the front of the access order at the same time.
         const int n = n_helpers + 1;
-        TSW_CUDA(cudaStreamSynchronize(s));  // descriptors must be on the target before peers read them
+        TSW_CUDA(cudaMemsetAsync(pl.d_ticket, 0, sizeof(uint32_t), s));
+        TSW_CUDA(cudaStreamSynchronize(s));  // descriptors and the tile dispenser must be on the target before peers read them
         a.tile_stride = (uint32_t)n;
+        if (e->cfg.shard_static == 0) {
+            a.ticket = pl.d_ticket;   // tiles are drawn, not dealt: faster links take more
+            a.ticket_chunk = 1;
+        }
         for (int r = n - 1; r >= 0; --r) {
             tsw_engine* w = r == 0 ? e : helpers[r - 1];
             if (!w || w->plan) return fail(TSW_ERR_INVALID, "sharded swap needs CUDA engines as helpers");
             PlaceArgs ar = a;
-            ar.tile_lo = (uint32_t)r;
+            ar.tile_lo = a.ticket ? 0u : (uint32_t)r;
             TSW_CUDA(cudaSetDevice(w->cfg.device));
             if (r != 0) TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_start, (cudaStream_t)w->stream));
             cudaError_t le = launch_place(ar, w->grid_ctas, (cudaStream_t)w->stream);
@@ -1013,12 +1020,15 @@ int tsw_swap_plan(tsw_engine* e, const char* func, tsw_segment* segs, int cap, u
     pub->table_phys = (uint64_t)pl.d_table_phys;
     pub->table_flag = (uint64_t)pl.d_table_flag;
     pub->flag_value = TSW_READY_CUDA;
+    pub->ticket = (uint64_t)pl.d_ticket;
+    pub->ticket_chunk = 1;
     pl.remote_rows.clear();
     for (auto& d : pr.plan.descs) pl.remote_rows.push_back((int)d.row);
     if (n && !e->plan) {
         // stale flags of earlier swaps must not pass for this one's
         TSW_CUDA(cudaSetDevice(e->cfg.device));
         TSW_CUDA(cudaMemsetAsync(pl.d_table_flag, 0, sizeof(uint32_t) * pl.capacity, (cudaStream_t)e->stream));
+        TSW_CUDA(cudaMemsetAsync(pl.d_ticket, 0, sizeof(uint32_t), (cudaStream_t)e->stream));
         TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
         e->bytes_moved += pr.plan.bytes;
     }
@@ -1599,6 +1609,8 @@ int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t t
         a.host_phys = (uint64_t*)pub->host_phys;
         a.host_flag = (uint32_t*)pub->host_flag;
         a.flag_value = pub->flag_value;
+        a.ticket = (uint32_t*)pub->ticket;
+        a.ticket_chunk = pub->ticket_chunk ? pub->ticket_chunk : 1;
         if (a.done_count && (!a.table_phys || !a.table_flag)) return fail(TSW_ERR_INVALID, "publish block needs both table columns");
     }
     if (validation_on()) {

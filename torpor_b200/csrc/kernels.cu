@@ -115,47 +115,66 @@ __device__ __forceinline__ uint32_t owner_of_tile(const uint32_t* first, uint32_
     return lo;
 }
 
+// Copy tile t and, when asked to, count it towards its row; the CTA that completes a row
+// rewrites that row of the pointer table.  Every thread of the CTA calls this with the same t.
+__device__ __forceinline__ void move_tile(const PlaceArgs& a, const uint32_t* s_first, uint32_t t) {
+    const uint32_t k = owner_of_tile(s_first, a.n_descs, t);
+    const PlaceDesc d = a.descs[k];
+    const uint64_t off = (uint64_t)(t - s_first[k]) * a.tile_bytes;
+    if (off >= d.bytes) {  // table and tile numbering disagree: report, move nothing
+        if (threadIdx.x == 0 && a.status) *reinterpret_cast<volatile uint32_t*>(a.status) = 1u;
+        return;
+    }
+    const uint64_t left = d.bytes - off;
+    const uint32_t len = left < a.tile_bytes ? (uint32_t)left : a.tile_bytes;
+    copy_span(d.src + off, d.dst + off, len);
+
+    if (a.done_count) {
+        if (a.system_scope) __threadfence_system();
+        else __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t before = a.system_scope ? atomicAdd_system(&a.done_count[d.row], 1u)
+                                                   : atomicAdd(&a.done_count[d.row], 1u);
+            if (before + 1 == d.row_tiles) {
+                // Last tile of this parameter -- the others may have been moved by other
+                // segments, launches or GPUs: re-arm the counter, rebind the table row,
+                // then raise the flag.
+                a.done_count[d.row] = 0;
+                __threadfence_system();
+                a.table_phys[d.row] = d.row_dst;
+                if (a.host_phys) a.host_phys[d.row] = d.row_dst;
+                __threadfence_system();
+                a.table_flag[d.row] = a.flag_value;
+                if (a.host_flag) a.host_flag[d.row] = a.flag_value;
+                __threadfence_system();
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) place_kernel(const PlaceArgs a) {
     extern __shared__ uint32_t s_first[];  // n_descs + 1 tile prefix sums
     for (uint32_t i = threadIdx.x; i <= a.n_descs; i += kThreads) s_first[i] = a.first_tile[i];
     __syncthreads();
 
-    const uint64_t step = (uint64_t)gridDim.x * a.tile_stride;
-    for (uint64_t t64 = a.tile_lo + (uint64_t)blockIdx.x * a.tile_stride; t64 < a.tile_hi; t64 += step) {
-        const uint32_t t = (uint32_t)t64;
-        const uint32_t k = owner_of_tile(s_first, a.n_descs, t);
-        const PlaceDesc d = a.descs[k];
-        const uint64_t off = (uint64_t)(t - s_first[k]) * a.tile_bytes;
-        if (off >= d.bytes) {  // table and tile numbering disagree: report, move nothing
-            if (threadIdx.x == 0 && a.status) *reinterpret_cast<volatile uint32_t*>(a.status) = 1u;
-            continue;
-        }
-        const uint64_t left = d.bytes - off;
-        const uint32_t len = left < a.tile_bytes ? (uint32_t)left : a.tile_bytes;
-        copy_span(d.src + off, d.dst + off, len);
-
-        if (a.done_count) {
-            if (a.system_scope) __threadfence_system();
-            else __threadfence();
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                const uint32_t before = a.system_scope ? atomicAdd_system(&a.done_count[d.row], 1u)
-                                                       : atomicAdd(&a.done_count[d.row], 1u);
-                if (before + 1 == d.row_tiles) {
-                    // Last tile of this parameter -- the others may have been moved by other
-                    // segments, launches or GPUs: re-arm the counter, rebind the table row,
-                    // then raise the flag.
-                    a.done_count[d.row] = 0;
-                    __threadfence_system();
-                    a.table_phys[d.row] = d.row_dst;
-                    if (a.host_phys) a.host_phys[d.row] = d.row_dst;
-                    __threadfence_system();
-                    a.table_flag[d.row] = a.flag_value;
-                    if (a.host_flag) a.host_flag[d.row] = a.flag_value;
-                    __threadfence_system();
-                }
-            }
-        }
+    if (a.ticket == nullptr) {
+        const uint64_t step = (uint64_t)gridDim.x * a.tile_stride;
+        for (uint64_t t64 = a.tile_lo + (uint64_t)blockIdx.x * a.tile_stride; t64 < a.tile_hi; t64 += step)
+            move_tile(a, s_first, (uint32_t)t64);
+        return;
+    }
+    // Dynamic dealing.  The counter starts at tile_lo and only grows; a CTA that draws a
+    // number at or beyond tile_hi is done, so the loop ends after at most one failed draw.
+    __shared__ uint32_t s_draw;
+    for (;;) {
+        if (threadIdx.x == 0) s_draw = atomicAdd_system(a.ticket, a.ticket_chunk);
+        __syncthreads();
+        const uint32_t first = s_draw;
+        __syncthreads();
+        if (first >= a.tile_hi) break;
+        const uint32_t last = (a.tile_hi - first < a.ticket_chunk) ? a.tile_hi : first + a.ticket_chunk;
+        for (uint32_t t = first; t < last; ++t) move_tile(a, s_first, t);
     }
 }
 
@@ -229,7 +248,9 @@ int default_grid_ctas(int device) {
 cudaError_t launch_place(const PlaceArgs& a, int grid_ctas, cudaStream_t stream) {
     if (a.n_descs == 0 || a.tile_hi <= a.tile_lo) return cudaSuccess;
     if (a.tile_bytes == 0 || (a.tile_bytes & 15u) || a.tile_stride == 0) return cudaErrorInvalidValue;
-    const uint64_t mine = ((uint64_t)(a.tile_hi - a.tile_lo) + a.tile_stride - 1) / a.tile_stride;
+    if (a.ticket && a.ticket_chunk == 0) return cudaErrorInvalidValue;
+    const uint64_t mine = a.ticket ? (uint64_t)(a.tile_hi - a.tile_lo)
+                                   : ((uint64_t)(a.tile_hi - a.tile_lo) + a.tile_stride - 1) / a.tile_stride;
     int grid = grid_ctas > 0 ? grid_ctas : 592;
     if ((uint64_t)grid > mine) grid = (int)mine;
     const size_t smem = sizeof(uint32_t) * ((size_t)a.n_descs + 1);
@@ -376,6 +397,8 @@ extern "C" int tsw_place_segments_static(int device, const tsw_segment* segs, in
         a.host_phys = (uint64_t*)pub->host_phys;
         a.host_flag = (uint32_t*)pub->host_flag;
         a.flag_value = pub->flag_value;
+        a.ticket = (uint32_t*)pub->ticket;
+        a.ticket_chunk = pub->ticket_chunk ? pub->ticket_chunk : 1;
     }
     err = launch_place(a, default_grid_ctas(device), s);
     if (err != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(err));

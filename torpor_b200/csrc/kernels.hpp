@@ -35,6 +35,11 @@ struct PlaceArgs {
     uint32_t* host_flag;
     uint32_t flag_value;          // written to the flag columns when a param completes
     uint32_t system_scope;        // 1: stores may target a peer GPU / host memory
+    // Dynamic dealing: when set, CTAs of every participating GPU draw the next `ticket_chunk`
+    // tiles from this counter (on the target GPU) instead of a fixed stride, so that a GPU
+    // with a faster path to the host store ends up moving more of the tiles.
+    uint32_t* ticket;
+    uint32_t ticket_chunk;
     uint32_t* status;             // device word, set non-zero on an internal inconsistency
 };
 

@@ -65,6 +65,7 @@ struct Placement {
     uint64_t* d_table_phys = nullptr;
     uint32_t* d_table_flag = nullptr;
     uint32_t* d_done = nullptr;
+    uint32_t* d_ticket = nullptr;   // tile dispenser of sharded swaps
     void* d_descs = nullptr;
     uint32_t* d_first = nullptr;
     void* h_descs = nullptr;

@@ -30,7 +30,7 @@ import numpy as np
 from . import _cabi
 from .memory_manager import SEGMENT_DTYPE, MemoryManager
 
-PUB_WORDS = 6          # tsw_publish as uint64 words: done, phys, flag, host_phys, host_flag, (flag_value|pad)
+PUB_WORDS = 8          # tsw_publish as words: done, phys, flag, host_phys, host_flag, flag_value, ticket_chunk, ticket
 HEADER_WORDS = 8       # n_segments, tile_bytes, regions_epoch, mode, 4 spare
 
 
@@ -122,6 +122,7 @@ class ShardedSwap:
         self.last = {}
         # without a CUDA engine only planning, sharing and rebasing run (CPU tests)
         self.dry = engine is None or engine.device < 0
+        self.dynamic = True         # direct mode: draw tiles from a shared counter instead of t mod N
 
     # ---- control plane
     def _bcast_words(self, words: np.ndarray) -> np.ndarray:
@@ -181,7 +182,8 @@ class ShardedSwap:
             bases = [] if self.dry else sorted(b for b, _, _ in self.engine.ipc_regions())
             changed = bases != self.region_bases
             buf[0], buf[1], buf[2], buf[3] = len(segs), tile, 1 if changed else 0, mode
-            buf[HEADER_WORDS:HEADER_WORDS + PUB_WORDS] = [pub.done_count, pub.table_phys, pub.table_flag, 0, 0, pub.flag_value]
+            buf[HEADER_WORDS:HEADER_WORDS + PUB_WORDS] = [pub.done_count, pub.table_phys, pub.table_flag, 0, 0,
+                                                          pub.flag_value, pub.ticket_chunk, pub.ticket]
             raw = segs.view(np.uint64)
             buf[HEADER_WORDS + PUB_WORDS:HEADER_WORDS + PUB_WORDS + raw.size] = raw
         buf = self._bcast_words(buf)
@@ -193,10 +195,10 @@ class ShardedSwap:
         segs = buf[HEADER_WORDS + PUB_WORDS:HEADER_WORDS + PUB_WORDS + n * w].copy().view(SEGMENT_DTYPE)
         return segs, tile, pubw
 
-    def _local_publish(self, pubw) -> _cabi.Publish:
+    def _local_publish(self, pubw, dynamic: bool) -> _cabi.Publish:
         m = self.map
         return _cabi.Publish(m.rebase_one(int(pubw[0])), m.rebase_one(int(pubw[1])), m.rebase_one(int(pubw[2])),
-                             0, 0, int(pubw[5]), 0)
+                             0, 0, int(pubw[5]), int(pubw[6]), m.rebase_one(int(pubw[7])) if dynamic else 0)
 
     def localize(self, segs: np.ndarray) -> np.ndarray:
         out = segs.copy()
@@ -219,8 +221,11 @@ class ShardedSwap:
         self.last_plan = (segs, tile)
         if len(segs) and not self.dry:
             local = self.localize(segs)
-            pub = self._local_publish(pubw)
-            if mode == "direct":
+            pub = self._local_publish(pubw, dynamic=(mode == "direct" and self.dynamic))
+            if mode == "direct" and self.dynamic:
+                # every rank draws tiles from the counter on the target: faster links move more
+                self.engine.place_segment_array(local, tile, 0, 1, 0, pub, sync=True)
+            elif mode == "direct":
                 self.engine.place_segment_array(local, tile, self.rank, self.world, 0, pub, sync=True)
             else:
                 lo, hi = contiguous_share(n_tiles, self.rank, self.world)
@@ -346,6 +351,21 @@ def bench_main(args, bench):
     wall_e, dev_e, launches_e = timed("direct", args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
 
+    # what the box's copy engines reach when every participating GPU pulls page-locked host
+    # memory at once: the practical ceiling of the links, next to the theoretical one
+    x = torch.empty(1 << 30, dtype=torch.uint8).pin_memory()
+    y = torch.empty(1 << 30, dtype=torch.uint8, device=f"cuda:{local_rank}")
+    dma_best = 0.0
+    for _ in range(4):
+        torch.cuda.synchronize()
+        dist.barrier(group=ctrl)
+        t0 = time.perf_counter()
+        y.copy_(x, non_blocking=True)
+        torch.cuda.synchronize()
+        dt = sw._max_over_ranks(time.perf_counter() - t0)
+        dma_best = max(dma_best, world * (1 << 30) / dt / 1e9)
+    del x, y
+
     total_launches = torch.tensor([launches_v, launches_e], dtype=torch.int64)
     dist.all_reduce(total_launches, group=ctrl)
 
@@ -377,6 +397,9 @@ def bench_main(args, bench):
                               "frac": (B / kern_e / 1e9) / (bench.PCIE_GEN5_X16_GBS * world),
                               "frac_wall": e2e / (bench.PCIE_GEN5_X16_GBS * world),
                               "peak_kind": f"theoretical PCIe Gen5 x16 x {world} participating GPUs",
+                              "cudaMemcpyAsync_pinned_h2d_concurrent_gbs": dma_best,
+                              "frac_of_concurrent_memcpy": e2e / dma_best if dma_best else None,
+                              "dealing": "tiles drawn from a shared counter on the target (faster links move more)",
                               "kernel": "place_kernel (host store -> target pool, zero-copy over PCIe, peer stores over NVLink)"},
             "cpu_baseline": None,
             "gpu_launches": int(total_launches[0]), "gpu_launches_e2e": int(total_launches[1]),
