@@ -251,6 +251,20 @@ int tsw_evictor_force_evict(tsw_evictor* ev, int gpu, const char* func);
 int tsw_evictor_lock(tsw_evictor* ev, int gpu, const char* func);
 int tsw_evictor_unlock(tsw_evictor* ev, int gpu, const char* func);
 
+/* Swap scheduler: the decision functions of the controller (controller.hpp:296-389) for any
+ * number of GPUs.  policy: "IA" (interference-aware, default) or "RAND".  pcie_pairs[i] = the
+ * GPU sharing GPU i's PCIe uplink and nvlink[i*n+j] in {-1,0,1,2} replace the reference's
+ * hard-coded 4-GPU tables (:116-118); NULL = NVSwitch defaults (all peers fast, sibling i^1).
+ * status values are the reference's ExecutorStatus_* (-1 available ... 5 cold start, :18-24).
+ * tsw_sched_decide answers gpu = -1 when no GPU is available (the caller queues the request);
+ * src_gpu >= 0 asks for a replica swap from that GPU; it reads the replicas of `func` from the
+ * process-wide repository (tsw_repo_add_model_info / tsw_repo_remove_model_info). */
+int tsw_sched_create(int gpu_count, const char* policy, const int* pcie_pairs, const int* nvlink, tsw_scheduler** out);
+int tsw_sched_destroy(tsw_scheduler* s);
+int tsw_sched_set_status(tsw_scheduler* s, int gpu, int status);
+int tsw_sched_set_level(tsw_scheduler* s, const char* func, int level);
+int tsw_sched_decide(tsw_scheduler* s, const char* func, int* gpu, int* src_gpu, int* status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,9 +8,13 @@
 //   model tables                 include/server/model_repo.hpp
 //   manager (swap-in / swap-out) include/server/memory_manager.hpp
 //   eviction policy              include/server/evictor.hpp
-// Parity is PINNED: tests/golden/ holds tables produced by the reference's own
-// headers compiled against a host-memory CUDA stand-in (ref_harness.cpp); this
-// restatement reproduces them bit for bit (tests/test_oracle_golden.py).
+//   swap scheduler               include/server/controller.hpp:296-389
+// Parity is PINNED for the first four: tests/golden/ holds tables produced by the
+// reference's own headers compiled against a host-memory CUDA stand-in
+// (ref_harness.cpp); this restatement reproduces them bit for bit
+// (tests/test_oracle_golden.py).  The scheduler section is "parity unpinned":
+// controller.hpp needs zmq and protobuf and cannot be compiled or run here, so
+// that section is a line-by-line restatement with nothing to check it against.
 //
 // "Device" memory here is a label space: addresses start at the same canonical
 // base as in the stand-in (0x600000000000 + 1 TiB per GPU), bytes live in a
@@ -261,7 +265,7 @@ struct Repo {
     std::unordered_map<string, std::vector<uint64_t>> access_order;
     std::unordered_map<string, HostModel> host;
     std::unordered_map<int, std::unordered_map<string, DevModel>> dev;
-    std::unordered_map<string, std::set<int>> active;
+    std::unordered_map<string, std::unordered_set<int>> active;   // model_active_device_map_ (model_repo.hpp:185)
 };
 Repo g_repo;
 
@@ -552,6 +556,45 @@ struct IaEvictor : EvictorBase {             // :28-188
     void lock(int g, const string& f) override { locked[g].insert(f); }                     // :166-168
 };
 
+// ---------------------------------------------------------------- swap scheduler (controller.hpp)
+struct Sched {
+    int n = 0;
+    bool random_policy = false;
+    std::vector<int> status;                 // executor_status_[i].status_ (:464)
+    std::vector<int> pcie_pairs;             // pcie_pairs_ (:117)
+    std::vector<std::vector<int>> nvlink;    // nvlink_topology_ (:118)
+    std::unordered_map<string, int> level;   // model_level_map_
+
+    static int level_to_status(int lv) { return (lv >= 0 && lv <= 2) ? lv + 2 : 3; }   // :26-33
+
+    void decide(const string& f, int out[3]) {
+        std::vector<int> avail;
+        for (int i = 0; i < n; ++i) if (status[i] == -1) avail.push_back(i);
+        if (avail.empty()) { out[0] = out[1] = out[2] = -1; return; }                    // :304-306,330-332
+        if (g_repo.active.count(f) && !g_repo.active[f].empty()) {
+            for (int g : g_repo.active[f])
+                if (status[g] == -1) { out[0] = g; out[1] = -1; out[2] = 0; return; }   // :308-314,334-341
+            if (!random_policy) {
+                std::vector<int> src(g_repo.active[f].begin(), g_repo.active[f].end());  // :342-343
+                int dst_gpu = avail[0], src_gpu = src[0];
+                for (int gi : avail)
+                    for (int gj : src)
+                        if (nvlink[gi][gj] == 2) { dst_gpu = gi; src_gpu = gj; break; } // :345-355
+                out[0] = dst_gpu; out[1] = src_gpu; out[2] = 1;                          // :375
+                return;
+            }
+        }
+        if (random_policy) {                                                              // :316-318
+            out[0] = avail[rand() % avail.size()]; out[1] = -1; out[2] = level_to_status(level[f]);
+            return;
+        }
+        int best = avail[0], best_status = status[pcie_pairs[avail[0]]];                  // :378-387
+        for (int g : avail)
+            if (status[pcie_pairs[g]] < best_status) { best_status = status[pcie_pairs[g]]; best = g; }
+        out[0] = best; out[1] = -1; out[2] = level_to_status(level[f]);
+    }
+};
+
 }  // namespace
 
 // ================================================================= scenario ABI
@@ -684,5 +727,21 @@ int tso_evictor_check_and_add(void* ev, int g, const char* f, uint64_t size, int
 void tso_evictor_force_evict(void* e, int g, const char* f) { ((EvictorBase*)e)->force(g, f); }
 void tso_evictor_lock(void* e, int g, const char* f) { ((EvictorBase*)e)->lock(g, f); }
 void tso_evictor_unlock(void* e, int g, const char* f) { ((EvictorBase*)e)->unlock(g, f); }
+
+// The controller cannot be compiled here (zmq, protobuf); its decision functions are restated above.
+void* tso_sched_create(int n, const char* policy, const int* pcie_pairs, const int* nvlink) {
+    Sched* s = new Sched();
+    s->n = n;
+    s->random_policy = policy && string(policy) == "RAND";
+    s->status.assign(n, -1);
+    s->pcie_pairs.assign(pcie_pairs, pcie_pairs + n);
+    s->nvlink.assign(n, std::vector<int>(n, 0));
+    for (int i = 0; i < n; ++i) for (int j = 0; j < n; ++j) s->nvlink[i][j] = nvlink[i * n + j];
+    return s;
+}
+void tso_sched_destroy(void* s) { delete (Sched*)s; }
+void tso_sched_set_status(void* s, int gpu, int status) { ((Sched*)s)->status[gpu] = status; }
+void tso_sched_set_level(void* s, const char* f, int level) { ((Sched*)s)->level[f] = level; }
+void tso_sched_decide(void* s, const char* f, int* out3) { ((Sched*)s)->decide(f, out3); }
 
 }  // extern "C"

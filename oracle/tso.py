@@ -84,6 +84,16 @@ class TsoLib:
             "tso_evictor_unlock": (None, [vp, i32, cp]),
             "tso_impl_name": (cp, []),
         }
+        sched = {
+            "tso_sched_create": (vp, [i32, cp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+            "tso_sched_destroy": (None, [vp]),
+            "tso_sched_set_status": (None, [vp, i32, i32]),
+            "tso_sched_set_level": (None, [vp, cp, i32]),
+            "tso_sched_decide": (None, [vp, cp, C.POINTER(C.c_int)]),
+        }
+        self.has_scheduler = hasattr(L, "tso_sched_create")   # the restatement only
+        if self.has_scheduler:
+            sig.update(sched)
         for name, (res, args) in sig.items():
             fn = getattr(L, name)
             fn.restype = res
@@ -102,6 +112,9 @@ class TsoLib:
 
     def evictor(self, kind: str, gpu_count: int, budget: int) -> "TsoEvictor":
         return TsoEvictor(self, kind, gpu_count, budget)
+
+    def scheduler(self, n, policy, pcie_pairs, nvlink) -> "TsoScheduler":
+        return TsoScheduler(self, n, policy, pcie_pairs, nvlink)
 
     def set_model_status(self, func: str, gpu: int, full: bool) -> None:
         self.lib.tso_set_model_status(func.encode(), gpu, 1 if full else 0)
@@ -175,6 +188,27 @@ class TsoManager:
         if rc != 0:
             raise RuntimeError(f"tso_read_host_store failed: {rc}")
         return out
+
+
+class TsoScheduler:
+    def __init__(self, lib: TsoLib, n, policy, pcie_pairs, nvlink):
+        self.L = lib.lib
+        pp = (C.c_int * n)(*pcie_pairs)
+        nv = (C.c_int * (n * n))(*[v for row in nvlink for v in row])
+        self.h = self.L.tso_sched_create(n, policy.encode(), pp, nv)
+
+    def close(self):
+        if self.h:
+            self.L.tso_sched_destroy(self.h)
+            self.h = None
+
+    def set_status(self, gpu, status): self.L.tso_sched_set_status(self.h, gpu, status)
+    def set_level(self, func, level): self.L.tso_sched_set_level(self.h, func.encode(), level)
+
+    def decide(self, func):
+        out = (C.c_int * 3)()
+        self.L.tso_sched_decide(self.h, func.encode(), out)
+        return out[0], out[1], out[2]
 
 
 class TsoEvictor:

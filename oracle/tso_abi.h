@@ -87,6 +87,16 @@ void tso_evictor_force_evict(void* e, int gpu, const char* func);
 void tso_evictor_lock(void* e, int gpu, const char* func);
 void tso_evictor_unlock(void* e, int gpu, const char* func);
 
+/* Swap decision of the controller (include/server/controller.hpp:296-389).  Exported by the
+ * CPU restatement only: controller.hpp itself needs zmq and protobuf and cannot be compiled
+ * here, so this part of the checker is NOT pinned against reference output.
+ * out3 = { gpu, src_gpu, status }; replicas are read from tso_set_model_status. */
+void* tso_sched_create(int n, const char* policy, const int* pcie_pairs, const int* nvlink);
+void tso_sched_destroy(void* s);
+void tso_sched_set_status(void* s, int gpu, int status);
+void tso_sched_set_level(void* s, const char* func, int level);
+void tso_sched_decide(void* s, const char* func, int* out3);
+
 const char* tso_impl_name(void);
 
 #ifdef __cplusplus

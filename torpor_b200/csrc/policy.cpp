@@ -195,3 +195,128 @@ int tsw_evictor_unlock(tsw_evictor* ev, int gpu_idx, const char* func) {
 }
 
 }  // extern "C"
+
+// =====================================================================================
+// Swap scheduler: which GPU runs a request, and where its weights come from.
+//
+// The decision functions of the reference's controller (include/server/controller.hpp:
+// random_schedule :296-318, interference_aware_schedule :321-389, model_level_to_exec_status
+// :26-33) for any number of GPUs.  The reference hard-codes a 4-GPU box (pcie_pairs_ and
+// nvlink_topology_, :116-118); here both tables are inputs.  With no tables given the
+// defaults describe an NVSwitch machine: every peer is a "fast" NVLink neighbour, and GPU i
+// shares its PCIe uplink with GPU i^1.
+namespace {
+constexpr int kAvail = -1, kRunLocal = 0, kRunNvlink = 1, kRunPcieLight = 2, kRunPcieMedian = 3;  // controller.hpp:18-24
+}
+
+struct tsw_scheduler {
+    int n = 0;
+    bool random_policy = false;
+    std::vector<int> status;                 // executor_status_[i].status_
+    std::vector<int> pcie_pair;
+    std::vector<std::vector<int>> nvlink;    // 0 self, 1 slow, 2 fast, -1 PCIe only
+    std::unordered_map<std::string, int> level;
+};
+
+extern "C" {
+
+int tsw_sched_create(int gpu_count, const char* policy, const int* pcie_pairs, const int* nvlink, tsw_scheduler** out) {
+    if (!out || gpu_count <= 0) return tsw::fail(TSW_ERR_INVALID, "bad scheduler arguments");
+    auto* s = new tsw_scheduler();
+    s->n = gpu_count;
+    s->random_policy = policy && std::string(policy) == "RAND";   // SCHEDULE_POLICY=RAND (controller.hpp:95-101)
+    s->status.assign(gpu_count, kAvail);
+    s->pcie_pair.resize(gpu_count);
+    s->nvlink.assign(gpu_count, std::vector<int>(gpu_count, 2));
+    for (int i = 0; i < gpu_count; ++i) {
+        const int sibling = (i ^ 1) < gpu_count ? (i ^ 1) : i;
+        s->pcie_pair[i] = pcie_pairs ? pcie_pairs[i] : sibling;
+        if (s->pcie_pair[i] < 0 || s->pcie_pair[i] >= gpu_count) {
+            delete s;
+            return tsw::fail(TSW_ERR_INVALID, "PCIe sibling out of range");
+        }
+        for (int j = 0; j < gpu_count; ++j) s->nvlink[i][j] = nvlink ? nvlink[i * gpu_count + j] : (i == j ? 0 : 2);
+    }
+    *out = s;
+    return TSW_OK;
+}
+
+int tsw_sched_destroy(tsw_scheduler* s) {
+    delete s;
+    return TSW_OK;
+}
+
+int tsw_sched_set_status(tsw_scheduler* s, int gpu, int status) {
+    if (!s || gpu < 0 || gpu >= s->n) return tsw::fail(TSW_ERR_INVALID, "bad scheduler arguments");
+    s->status[gpu] = status;
+    return TSW_OK;
+}
+
+int tsw_sched_set_level(tsw_scheduler* s, const char* func, int level) {
+    if (!s || !func) return tsw::fail(TSW_ERR_INVALID, "bad scheduler arguments");
+    s->level[func] = level;
+    return TSW_OK;
+}
+
+int tsw_sched_decide(tsw_scheduler* s, const char* func, int* gpu, int* src_gpu, int* status) {
+    if (!s || !func || !gpu || !src_gpu || !status) return tsw::fail(TSW_ERR_INVALID, "bad scheduler arguments");
+    *gpu = *src_gpu = *status = -1;
+    std::vector<int> avail;
+    for (int i = 0; i < s->n; ++i)
+        if (s->status[i] == kAvail) avail.push_back(i);
+    if (avail.empty()) return TSW_OK;   // caller queues the request (controller.hpp:176-178)
+
+    std::vector<int> homes;             // model_active_device_map_[func], in its iteration order
+    {
+        int buf[256];
+        int n = tsw_repo_active_devices(func, buf, 256);
+        for (int i = 0; i < n && i < 256; ++i)
+            if (buf[i] >= 0 && buf[i] < s->n) homes.push_back(buf[i]);
+    }
+    const int lv = s->level.count(func) ? s->level[func] : 0;
+    const int pcie_status = (lv >= 0 && lv <= 2) ? lv + kRunPcieLight : kRunPcieMedian;
+
+    for (int g : homes) {
+        if (s->status[g] == kAvail) {   // resident and idle: no swap
+            *gpu = g;
+            *status = kRunLocal;
+            return TSW_OK;
+        }
+    }
+    if (s->random_policy) {
+        *gpu = avail[rand() % avail.size()];
+        *status = pcie_status;
+        return TSW_OK;
+    }
+    if (!homes.empty()) {
+        // resident elsewhere: replica swap over NVLink, preferring a fast pair; the scan keeps
+        // the LAST idle GPU that has a fast neighbour among the replicas (controller.hpp:346-355)
+        int dst = avail[0], src = homes[0];
+        for (int gi : avail) {
+            for (int gj : homes) {
+                if (s->nvlink[gi][gj] == 2) {
+                    dst = gi;
+                    src = gj;
+                    break;
+                }
+            }
+        }
+        *gpu = dst;
+        *src_gpu = src;
+        *status = kRunNvlink;
+        return TSW_OK;
+    }
+    // from the host store: the idle GPU whose PCIe sibling is least busy (:379-385)
+    int best = avail[0], best_status = s->status[s->pcie_pair[avail[0]]];
+    for (int g : avail) {
+        if (s->status[s->pcie_pair[g]] < best_status) {
+            best_status = s->status[s->pcie_pair[g]];
+            best = g;
+        }
+    }
+    *gpu = best;
+    *status = pcie_status;
+    return TSW_OK;
+}
+
+}  // extern "C"

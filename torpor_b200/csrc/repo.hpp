@@ -95,7 +95,8 @@ struct Model {                  // HostModelInfo (model_repo.hpp:37-46)
 struct Repo {
     std::recursive_mutex mu;
     std::unordered_map<std::string, std::unique_ptr<Model>> models;
-    std::map<std::string, std::set<int>> active_devices;  // model_active_device_map_
+    // model_active_device_map_: hashed like the reference's, whose scheduler walks it in hash order
+    std::unordered_map<std::string, std::unordered_set<int>> active_devices;
 
     Model* find(const std::string& f) {
         auto it = models.find(f);

@@ -341,6 +341,36 @@ class Evictor:
     def unlock(self, gpu, func): check(self.L.tsw_evictor_unlock(self.h, gpu, func.encode()))
 
 
+# ExecutorStatus_* (include/server/controller.hpp:18-24)
+STATUS_AVAIL, STATUS_RUN_LOCAL, STATUS_RUN_NVLINK = -1, 0, 1
+STATUS_RUN_PCIE_LIGHT, STATUS_RUN_PCIE_MEDIAN, STATUS_RUN_PCIE_HEAVY, STATUS_RUN_COLD_START = 2, 3, 4, 5
+
+
+class Scheduler:
+    """The controller's swap decision (include/server/controller.hpp:296-389) for N GPUs."""
+
+    def __init__(self, gpu_count: int, policy: str = "IA", pcie_pairs=None, nvlink=None):
+        self.L = _cabi.lib()
+        h = C.c_void_p()
+        pp = (C.c_int * gpu_count)(*pcie_pairs) if pcie_pairs is not None else None
+        nv = (C.c_int * (gpu_count * gpu_count))(*[v for row in nvlink for v in row]) if nvlink is not None else None
+        check(self.L.tsw_sched_create(gpu_count, policy.encode(), pp, nv, C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if self.h:
+            self.L.tsw_sched_destroy(self.h)
+            self.h = None
+
+    def set_status(self, gpu: int, status: int): check(self.L.tsw_sched_set_status(self.h, gpu, status))
+    def set_level(self, func: str, level: int): check(self.L.tsw_sched_set_level(self.h, func.encode(), level))
+
+    def decide(self, func: str):
+        g, s, st = C.c_int(), C.c_int(), C.c_int()
+        check(self.L.tsw_sched_decide(self.h, func.encode(), C.byref(g), C.byref(s), C.byref(st)))
+        return g.value, s.value, st.value
+
+
 def checksum_host(data: np.ndarray) -> np.ndarray:
     """The checksum of ``tsw_checksum_resident`` computed with numpy on host bytes."""
     b = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
