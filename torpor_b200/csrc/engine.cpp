@@ -451,7 +451,7 @@ int tsw_engine_create(const tsw_config* cfg, tsw_engine** out) {
     e->plan = cfg->device < 0;
     e->server_id = cfg->server_id;
     e->tile_host = cfg->tile_bytes_host > 0 ? (uint32_t)cfg->tile_bytes_host : 64u * 1024;
-    e->tile_dev = cfg->tile_bytes_device > 0 ? (uint32_t)cfg->tile_bytes_device : 256u * 1024;
+    e->tile_dev = cfg->tile_bytes_device > 0 ? (uint32_t)cfg->tile_bytes_device : 512u * 1024;
     if ((e->tile_host & 15u) || (e->tile_dev & 15u)) return fail(TSW_ERR_INVALID, "tile sizes must be multiples of 16 bytes");
     if (e->plan) {
         e->mem.reset(new PlanMemory());
