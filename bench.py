@@ -42,7 +42,7 @@ NVLINK5_GBS = 900.0            # per direction per GPU (nominal)
 HBM_FALLBACK_GBS = 6650.0
 # DRAM bytes moved per algorithmic byte by place_kernel with both ends in HBM, from the ncu
 # capture summarised in profiles/place_kernel_hbm_llama_mid.md (read + write sectors).
-DRAM_TRAFFIC_PER_ALGO_BYTE = None
+DRAM_TRAFFIC_PER_ALGO_BYTE = 0.989
 
 
 def measured_peaks():
