@@ -121,6 +121,8 @@ int tsw_swap_in(tsw_engine* e, const char* func, int src_gpu);
 int tsw_swap_in_sharded(tsw_engine* e, const char* func, tsw_engine* const* helpers, int n_helpers);
 /* Wait until every accessed parameter of func is on the device (bounded). */
 int tsw_wait_ready(tsw_engine* e, const char* func, int64_t timeout_ns);
+/* Non-blocking form: the number of accessed parameters still on their way (0 = all there). */
+int tsw_poll_ready(tsw_engine* e, const char* func);
 int tsw_check_alloc(tsw_engine* e, const char* func);            /* check_model_alloc_status, :195-210; 1/0 */
 
 /* Swap-out: evict_model(func) (:240-259).  The reference moves no bytes; with

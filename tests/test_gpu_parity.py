@@ -323,3 +323,33 @@ def test_full_size_llama2_7b_properties(fresh):
         v, n = lm.tensor_vaddr[i], min(ws.tensors[i].nbytes, 1 << 20)
         assert np.array_equal(eng.read_host_store("llama", v, n), W.tensor_bytes(ws, i)[:n])
     eng.close()
+
+
+def test_mixed_request_stream_with_eviction(fresh):
+    """A short serverless stream (Zipf popularity, Poisson arrivals) over two engines with a
+    memory cap small enough to force LRU evictions: every request completes, swaps come both
+    from the host store and from replicas, and evicted models come back bit-exact."""
+    from torpor_b200 import serving
+    out = serving.run_stream(n_gpus=2, n_models=10, rate=300.0, duration_s=2.0, cap_bytes=300 << 20, seed=4,
+                             archs=("bert_tiny", "llama_tiny", "resnet50"), devices=[0, 0], zero_weights=True)
+    assert out["completed"] == out["requests"] > 400
+    assert out["swaps"] > 20 and out["evictions_in_service"] > 5
+    assert out["swaps_from_host"] > 0 and out["swap_ms_p99"] < 2000
+    assert out["sustained_swap_gbs"] > 0.1
+
+    # the same machinery with real weights: after churn the survivor's bytes are still right
+    srv = serving.SwapServer(2, 300 << 20, devices=[0, 0])
+    for i, a in enumerate(["resnet50", "llama_tiny", "resnet50", "llama_tiny"]):
+        srv.cold_start(f"fn{i}", a, 50 + i)
+    for f in ["fn0", "fn1", "fn2", "fn3", "fn0", "fn2", "fn1"]:
+        srv.submit(f, 0.0)
+        while srv.busy():
+            srv.poll()
+    ws = W.weight_set("llama_tiny", seed=51)
+    homes = ModelRepo.active_devices("fn1")
+    assert homes, "fn1 should be resident somewhere after its last request"
+    eng = srv.engines[homes[0]]
+    sums = np.array([checksum_host(W.tensor_bytes(ws, i)) for i in range(len(ws.tensors))])
+    assert np.array_equal(eng.checksum_resident("fn1"), sums)
+    assert srv.evictions > 0
+    srv.close()

@@ -93,6 +93,7 @@ SIGNATURES = {
     "tsw_swap_in": (_i32, [_vp, _cp, _i32]),
     "tsw_swap_in_sharded": (_i32, [_vp, _cp, C.POINTER(_vp), _i32]),
     "tsw_wait_ready": (_i32, [_vp, _cp, _i64]),
+    "tsw_poll_ready": (_i32, [_vp, _cp]),
     "tsw_check_alloc": (_i32, [_vp, _cp]),
     "tsw_evict": (_i32, [_vp, _cp, _i32]),
     "tsw_translate": (_i32, [_vp, _cp, _u64, _i32, _i64, _pu64]),

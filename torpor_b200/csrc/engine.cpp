@@ -1096,6 +1096,21 @@ int tsw_wait_ready(tsw_engine* e, const char* func, int64_t timeout_ns) {
     return TSW_OK;
 }
 
+int tsw_poll_ready(tsw_engine* e, const char* func) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
+    auto it = m->place.find(e->server_id);
+    if (it == m->place.end() || !it->second.readiness_init) return fail(TSW_ERR_STATE, "model has no readiness rows on this engine");
+    if (e->h_status && *e->h_status) return fail(TSW_ERR_KERNEL, "placement kernel reported an inconsistent tile table");
+    int waiting = 0;
+    for (int pi : m->access_order)
+        if (it->second.has_row[pi] && it->second.flag[pi] != TSW_READY_CUDA) ++waiting;
+    return waiting;
+}
+
 int tsw_check_alloc(tsw_engine* e, const char* func) {
     if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
     Lock g1(repo().mu);

@@ -249,6 +249,10 @@ class MemoryManager:
         check(self.L.tsw_arena_attach(self.h, shm_name.encode(), size, C.byref(out)))
         return out.value
 
+    def poll_ready(self, func: str) -> int:
+        """Accessed parameters of ``func`` not on the device yet (0 = swap-in complete)."""
+        return check(self.L.tsw_poll_ready(self.h, func.encode()))
+
     def wait_ready(self, func: str, timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
         check(self.L.tsw_wait_ready(self.h, func.encode(), timeout_ns))
 

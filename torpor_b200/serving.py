@@ -1,0 +1,207 @@
+"""Controller-level replay of a serverless request stream over the swap engines.
+
+Drives the swap path the way Torpor's controller does for every request
+(include/server/controller.hpp:163-262,392-453): ask the scheduler for a GPU and a source,
+pin the source replica, let the eviction policy make room (victims are unloaded first),
+signal the load, run, and on completion register the new replica and release the pin.
+Swap-ins are asynchronous (``tsw_swap_in`` returns once the kernel is enqueued), so swaps on
+different GPUs overlap for real and compete for PCIe / NVLink as they would in service.
+Requests arrive on the wall clock (optionally compressed by ``speedup``); the client's
+inference itself is not run -- it is modelled as ``exec_ms`` of GPU occupancy per request,
+a stated constant per architecture, because only the swap path is under test.
+
+    python -m torpor_b200.serving --gpus 8 --models 64 --rate 200 --duration 120 --cap-gb 40
+"""
+from __future__ import annotations
+
+import argparse
+import collections
+import json
+import os
+import time
+from typing import Dict, List, Optional
+
+import numpy as np
+
+from . import workloads as W
+from .memory_manager import (Evictor, MemoryManager, ModelRepo, Scheduler, SwapError, repo_reset,
+                             STATUS_AVAIL, STATUS_RUN_COLD_START, STATUS_RUN_LOCAL, STATUS_RUN_NVLINK)
+
+# GPU occupancy per request once the weights are there (ms).  Stand-ins for the client's
+# inference, in the range the reference's own node simulator uses (misc/tools/node_simu.py:98-99).
+EXEC_MS = {"resnet50": 8.0, "bert_base": 12.0, "bert_large": 25.0, "vgg19": 12.0,
+           "bert_tiny": 2.0, "llama_tiny": 4.0, "llama_mid": 20.0, "llama2_7b": 30.0}
+LEVEL = {"resnet50": 0, "bert_tiny": 0, "bert_base": 1, "vgg19": 1, "llama_tiny": 1, "bert_large": 2,
+         "llama_mid": 2, "llama2_7b": 2}
+
+
+class SwapServer:
+    def __init__(self, n_gpus: int, cap_bytes: int, evict_policy: str = "LRU", sched_policy: str = "IA",
+                 devices: Optional[List[int]] = None, host_arena_bytes: int = 0):
+        self.n = n_gpus
+        self.devices = devices or list(range(n_gpus))
+        self.engines = [MemoryManager(cap_bytes, device=self.devices[g], server_id=g, gpu_count=n_gpus,
+                                      host_arena_bytes=host_arena_bytes if g == 0 else 0)
+                        for g in range(n_gpus)]
+        self.evictor = Evictor(evict_policy, n_gpus, cap_bytes)
+        self.sched = Scheduler(n_gpus, sched_policy)
+        self.arch: Dict[str, str] = {}
+        self.nbytes: Dict[str, int] = {}
+        self.state = [dict(kind="idle") for _ in range(n_gpus)]
+        self.demand: Dict[int, tuple] = {}          # dst gpu -> (src gpu, func): executor_gpu_demand_
+        self.queue = collections.deque()
+        self.swaps: List[dict] = []
+        self.evictions = 0
+        self.local_hits = 0
+        self.completed = 0
+        self.next_cold = 0
+
+    def close(self):
+        for e in self.engines:
+            e.close()
+        self.evictor.close()
+        self.sched.close()
+        repo_reset()
+
+    # ---- ExecuteAfterLoad (controller.hpp:141-162, 223-227): load once, anywhere
+    def cold_start(self, func: str, arch: str, seed: int, tensor_data=None):
+        ws = W.weight_set(arch, seed=seed)
+        g = self.next_cold % self.n                                   # round-robin placement (:283-294)
+        self.next_cold += 1
+        self.arch[func], self.nbytes[func] = arch, ws.nbytes
+        self.sched.set_level(func, LEVEL.get(arch, 1))
+        W.cold_start(self.engines[g], func, ws, tensor_data=tensor_data)
+        ModelRepo.add_model_info(func, g)
+        for v in self._make_room(g, func):
+            self._unload(v, g)
+
+    def _make_room(self, g: int, func: str) -> List[str]:               # check_eviction (:392-400)
+        return self.evictor.check_and_add(g, func, ModelRepo.total_size(func), LEVEL.get(self.arch[func], 1))
+
+    def _unload(self, func: str, g: int):
+        ModelRepo.remove_model_info(func, g)
+        self.engines[g].evict(func)
+        self.evictions += 1
+
+    # ---- Execute (controller.hpp:163-185)
+    def submit(self, func: str, now: float) -> bool:
+        g, src, status = self.sched.decide(func)
+        if g < 0:
+            self.queue.append((func, now))
+            return False
+        self._start(func, g, src, status, now)
+        return True
+
+    def _start(self, func: str, g: int, src: int, status: int, t_arrival: float):
+        self.sched.set_status(g, status)
+        st = dict(kind="exec", func=func, t_arrival=t_arrival)
+        if status == STATUS_RUN_LOCAL:
+            self.local_hits += 1
+            self.evictor.check_and_add(g, func, ModelRepo.total_size(func), LEVEL.get(self.arch[func], 1))  # refresh recency
+            st["until"] = time.perf_counter() + EXEC_MS.get(self.arch[func], 10.0) / 1e3
+        else:
+            if src >= 0:                                               # lock_src_func (:437-440)
+                self.demand[g] = (src, func)
+                self.evictor.lock(src, func)
+            for v in self._make_room(g, func):                         # victims go first (:394-399)
+                self._unload(v, g)
+            st.update(kind="swap", t_signal=time.perf_counter(), src=src)
+            self.engines[g].swap_in(func, src)                         # asynchronous: kernel enqueued
+        self.state[g] = st
+
+    def poll(self):
+        """Advance every GPU: finished swaps start executing, finished executions complete."""
+        now = time.perf_counter()
+        for g in range(self.n):
+            st = self.state[g]
+            if st["kind"] == "swap" and self.engines[g].poll_ready(st["func"]) == 0:
+                self.swaps.append(dict(func=st["func"], gpu=g, src=st["src"], bytes=self.nbytes[st["func"]],
+                                       ms=(now - st["t_signal"]) * 1e3, t=st["t_signal"]))
+                st["kind"] = "exec"
+                st["until"] = now + EXEC_MS.get(self.arch[st["func"]], 10.0) / 1e3
+            if st["kind"] == "exec" and now >= st["until"]:
+                func = st["func"]
+                ModelRepo.add_model_info(func, g)                      # completion (:223-230)
+                if g in self.demand:                                   # unlock_src_func (:442-447)
+                    s, f = self.demand.pop(g)
+                    self.evictor.unlock(s, f)
+                self.sched.set_status(g, STATUS_AVAIL)
+                self.state[g] = dict(kind="idle")
+                self.completed += 1
+                if self.queue:                                         # queued request takes the freed GPU (:242-262)
+                    qf, qt = self.queue.popleft()
+                    g2, src, status = self.sched.decide(qf)
+                    if g2 != g:
+                        src, status = -1, 2 + LEVEL.get(self.arch[qf], 1)
+                        if g in ModelRepo.active_devices(qf):
+                            status = STATUS_RUN_LOCAL
+                    self._start(qf, g, src, status, qt)
+
+    def busy(self) -> bool:
+        return any(st["kind"] != "idle" for st in self.state) or bool(self.queue)
+
+
+def run_stream(n_gpus: int, n_models: int, rate: float, duration_s: float, cap_bytes: int, seed: int = 4,
+               speedup: float = 1.0, archs=("resnet50", "bert_base", "bert_large", "vgg19"),
+               evict_policy: str = "LRU", zero_weights: bool = True, devices: Optional[List[int]] = None) -> dict:
+    """The mixed serverless stream: ``n_models`` functions, Zipf popularity, Poisson arrivals."""
+    arch_of, times, picks = W.mixed_stream(seed=seed, n_models=n_models, rate=rate, duration_s=duration_s, archs=archs)
+    store = sum(W.host_store_bytes(W.weight_set(a)) for a in arch_of)
+    srv = SwapServer(n_gpus, cap_bytes, evict_policy=evict_policy, host_arena_bytes=0, devices=devices)
+    t0 = time.time()
+    for i, a in enumerate(arch_of):
+        ws = W.weight_set(a)
+        data = (lambda k, ws=ws: np.zeros(ws.tensors[k].nbytes, dtype=np.uint8)) if zero_weights else None
+        srv.cold_start(f"fn{i}", a, 1000 + i, tensor_data=data)
+    cold_s = time.time() - t0
+    ev_cold = srv.evictions
+    start = time.perf_counter()
+    k = 0
+    n_req = len(times)
+    while k < n_req or srv.busy():
+        now = time.perf_counter() - start
+        while k < n_req and times[k] / speedup <= now:
+            srv.submit(f"fn{int(picks[k])}", now)
+            k += 1
+        srv.poll()
+    wall = time.perf_counter() - start
+    ms = np.array([s["ms"] for s in srv.swaps]) if srv.swaps else np.zeros(1)
+    by = np.array([s["bytes"] for s in srv.swaps], dtype=np.float64) if srv.swaps else np.zeros(1)
+    rel = np.array([s["t"] - start for s in srv.swaps]) if srv.swaps else np.zeros(1)
+    fill = rel < wall * 0.25
+    host = [s for s in srv.swaps if s["src"] < 0]
+    out = {
+        "gpus": n_gpus, "models": n_models, "requests": n_req, "completed": srv.completed, "rate_req_s": rate * speedup,
+        "duration_s": wall, "cap_bytes": cap_bytes, "host_store_bytes": store, "cold_start_s": cold_s,
+        "evictions_at_cold_start": ev_cold, "evictions_in_service": srv.evictions - ev_cold,
+        "local_hits": srv.local_hits, "swaps": len(srv.swaps), "swaps_from_host": len(host),
+        "swaps_from_replica": len(srv.swaps) - len(host),
+        "swapped_bytes": float(by.sum()) if srv.swaps else 0.0,
+        "sustained_swap_gbs": float(by.sum()) / wall / 1e9 if srv.swaps else 0.0,
+        "fill_phase_swap_gbs": float(by[fill].sum()) / max(wall * 0.25, 1e-9) / 1e9 if srv.swaps else 0.0,
+        "steady_swap_gbs": float(by[~fill].sum()) / max(wall * 0.75, 1e-9) / 1e9 if srv.swaps else 0.0,
+        "swap_ms_p50": float(np.percentile(ms, 50)), "swap_ms_p99": float(np.percentile(ms, 99)),
+        "swap_ms_max": float(ms.max()),
+        "per_swap_gbs_p50": float(np.percentile(by / (ms / 1e3) / 1e9, 50)) if srv.swaps else 0.0,
+        "exec_model": "GPU occupancy per request modelled as a constant per architecture (EXEC_MS); inference not run",
+    }
+    srv.close()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--models", type=int, default=64)
+    ap.add_argument("--rate", type=float, default=200.0)
+    ap.add_argument("--duration", type=float, default=120.0)
+    ap.add_argument("--cap-gb", type=float, default=40.0)
+    ap.add_argument("--speedup", type=float, default=1.0)
+    ap.add_argument("--policy", default="LRU")
+    args = ap.parse_args()
+    print(json.dumps(run_stream(args.gpus, args.models, args.rate, args.duration, int(args.cap_gb * (1 << 30)),
+                                speedup=args.speedup, evict_policy=args.policy)), flush=True)
+
+
+if __name__ == "__main__":
+    main()
