@@ -338,7 +338,7 @@ def test_mixed_request_stream_with_eviction(fresh):
     assert out["sustained_swap_gbs"] > 0.1
 
     # the same machinery with real weights: after churn the survivor's bytes are still right
-    srv = serving.SwapServer(2, 300 << 20, devices=[0, 0])
+    srv = serving.SwapServer(2, 190 << 20, devices=[0, 0])
     for i, a in enumerate(["resnet50", "llama_tiny", "resnet50", "llama_tiny"]):
         srv.cold_start(f"fn{i}", a, 50 + i)
     for f in ["fn0", "fn1", "fn2", "fn3", "fn0", "fn2", "fn1"]:
