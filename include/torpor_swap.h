@@ -135,6 +135,14 @@ int tsw_evict(tsw_engine* e, const char* func, int writeback);
  * its readiness flag, as check_param_readiness does (:527-540). */
 int tsw_translate(tsw_engine* e, const char* func, uint64_t vptr, int search_amid,
                   int64_t timeout_ns, uint64_t* out);
+/* Stream-ordered get_cuda_addr: returns the rebound address at once and, when the parameter is
+ * still being swapped in, makes `stream` (a cudaStream_t of the same GPU) wait for it with a
+ * stream memory operation on the device pointer table -- no host blocking, no device spinning --
+ * so the executor can enqueue the kernels of a request before its weights have landed
+ * (replaces the blocking wait of cuda_server.hpp:1265-1268 -> memory_manager.hpp:527-540).
+ * *waited = 1 if a wait was enqueued.  TSW_ERR_STATE if the parameter is neither resident nor
+ * part of a swap in flight (a wait on it could never be satisfied). */
+int tsw_translate_async(tsw_engine* e, const char* func, uint64_t vptr, void* stream, uint64_t* out, int* waited);
 int tsw_is_model_address(tsw_engine* e, const char* func, uint64_t vptr);    /* :286-291; 1/0 */
 int tsw_valid_memory_address(tsw_engine* e, const char* func, uint64_t vptr); /* :293-298; always 0 */
 

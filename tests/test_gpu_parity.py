@@ -353,3 +353,41 @@ def test_mixed_request_stream_with_eviction(fresh):
     assert np.array_equal(eng.checksum_resident("fn1"), sums)
     assert srv.evictions > 0
     srv.close()
+
+
+def test_stream_ordered_translation(fresh):
+    """get_cuda_addr without blocking the host: the address comes back at once, the caller's
+    stream waits on the pointer table's generation word, and work enqueued behind it sees the
+    parameter's bytes -- not what the pool block held before."""
+    import torch
+    from torpor_b200.memory_manager import place_segments_static
+    ws_a, ws_b = W.weight_set("bert_base", seed=101), W.weight_set("bert_base", seed=202)
+    eng = MemoryManager(0, device=0)
+    la = W.cold_start(eng, "A", ws_a)
+    eng.evict("A")
+    lb = W.cold_start(eng, "B", ws_b)
+    last = len(ws_a.tensors) - 2                       # pooler weight: near the end of the access order
+    n = ws_a.tensors[last].nbytes
+    stream = torch.cuda.Stream()
+    scratch = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    waited_any = False
+    for cycle in range(3):
+        eng.evict("B")                                  # B's bytes stay behind in the freed blocks
+        eng.swap_in("A")                                # asynchronous
+        addr, waited = eng.get_cuda_addr_async("A", la.tensor_vaddr[last], stream.cuda_stream)
+        waited_any = waited_any or waited
+        place_segments_static(0, [addr], [scratch.data_ptr()], [n], stream=stream.cuda_stream)
+        stream.synchronize()
+        assert np.array_equal(scratch.cpu().numpy(), W.tensor_bytes(ws_a, last)), f"cycle {cycle}"
+        assert addr == eng.get_cuda_addr("A", la.tensor_vaddr[last])
+        eng.wait_ready("A")
+        eng.evict("A")
+        eng.swap_in("B"); eng.wait_ready("B")
+        addr_b, waited_b = eng.get_cuda_addr_async("B", lb.tensor_vaddr[last], stream.cuda_stream)
+        assert not waited_b                             # already resident: no wait is enqueued
+    assert waited_any, "the last parameter was never still in flight when asked for"
+    eng.evict("B")
+    with pytest.raises(SwapError) as e:                 # nothing in flight: a wait could never be satisfied
+        eng.get_cuda_addr_async("B", lb.tensor_vaddr[last], stream.cuda_stream)
+    assert e.value.code == _cabi.ERR_STATE
+    eng.close()

@@ -97,6 +97,7 @@ SIGNATURES = {
     "tsw_check_alloc": (_i32, [_vp, _cp]),
     "tsw_evict": (_i32, [_vp, _cp, _i32]),
     "tsw_translate": (_i32, [_vp, _cp, _u64, _i32, _i64, _pu64]),
+    "tsw_translate_async": (_i32, [_vp, _cp, _u64, _vp, _pu64, C.POINTER(C.c_int)]),
     "tsw_is_model_address": (_i32, [_vp, _cp, _u64]),
     "tsw_valid_memory_address": (_i32, [_vp, _cp, _u64]),
     "tsw_dump_blocks": (_i32, [_vp, _cp, _i32, _vp, _i32]),

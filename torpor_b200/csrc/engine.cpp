@@ -956,7 +956,9 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
     a.table_flag = pl.d_table_flag;
     a.host_phys = (uint64_t*)pl.phys;
     a.host_flag = (uint32_t*)pl.flag;
-    a.flag_value = TSW_READY_CUDA;
+    pl.epoch += 1;
+    a.flag_value = pl.epoch;
+    a.host_flag_value = TSW_READY_CUDA;
     a.system_scope = (n_helpers > 0) ? 1u : 0u;
     a.status = e->d_status;
 
@@ -1019,15 +1021,14 @@ int tsw_swap_plan(tsw_engine* e, const char* func, tsw_segment* segs, int cap, u
     pub->done_count = (uint64_t)pl.d_done;
     pub->table_phys = (uint64_t)pl.d_table_phys;
     pub->table_flag = (uint64_t)pl.d_table_flag;
-    pub->flag_value = TSW_READY_CUDA;
+    pl.epoch += 1;
+    pub->flag_value = pl.epoch;       // the generation; the host-visible rows are set by tsw_swap_commit
     pub->ticket = (uint64_t)pl.d_ticket;
     pub->ticket_chunk = 1;
     pl.remote_rows.clear();
     for (auto& d : pr.plan.descs) pl.remote_rows.push_back((int)d.row);
     if (n && !e->plan) {
-        // stale flags of earlier swaps must not pass for this one's
-        TSW_CUDA(cudaSetDevice(e->cfg.device));
-        TSW_CUDA(cudaMemsetAsync(pl.d_table_flag, 0, sizeof(uint32_t) * pl.capacity, (cudaStream_t)e->stream));
+            TSW_CUDA(cudaSetDevice(e->cfg.device));
         TSW_CUDA(cudaMemsetAsync(pl.d_ticket, 0, sizeof(uint32_t), (cudaStream_t)e->stream));
         TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
         e->bytes_moved += pr.plan.bytes;
@@ -1057,7 +1058,7 @@ int tsw_swap_commit(tsw_engine* e, const char* func) {
     TSW_CUDA(cudaMemcpy(phys.data(), pl.d_table_phys, sizeof(uint64_t) * pl.capacity, cudaMemcpyDeviceToHost));
     int missing = 0;
     for (int row : pl.remote_rows) {
-        if (flag[row] == TSW_READY_CUDA) set_row(pl, row, TSW_READY_CUDA, phys[row]);
+        if (flag[row] == pl.epoch) set_row(pl, row, TSW_READY_CUDA, phys[row]);
         else ++missing;
     }
     pl.remote_rows.clear();
@@ -1243,6 +1244,57 @@ int tsw_translate(tsw_engine* e, const char* func, uint64_t vptr, int search_ami
     WaitResult w = wait_row(e, *wait_pl, wait_idx, timeout_ns);
     if (w.rc != TSW_OK) return w.rc;
     *out = w.phys;
+    return TSW_OK;
+}
+
+// Stream-ordered form of get_cuda_addr.  The rebound address of a parameter is known as soon
+// as its block is placed; what the executor has to wait for is the bytes.  Instead of blocking
+// the host (check_param_readiness, memory_manager.hpp:527-540) this returns the address at once
+// and, if the parameter is still on its way, makes `stream` wait for it: a stream memory
+// operation on the row's generation word in the device pointer table, which the placement
+// kernel writes when the row's last tile has landed.  Kernels that use the parameter can then
+// be enqueued behind it before the weights have arrived.  Nothing spins on the device.
+int tsw_translate_async(tsw_engine* e, const char* func, uint64_t vptr, void* stream, uint64_t* out, int* waited) {
+    if (!e || !func || !out) return fail(TSW_ERR_INVALID, "null argument");
+    if (waited) *waited = 0;
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine has no streams");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m || m->place.find(e->server_id) == m->place.end()) {
+        *out = vptr;
+        return TSW_OK;
+    }
+    auto pit = m->param_by_vaddr.find(vptr);
+    if (pit == m->param_by_vaddr.end()) {
+        *out = phy_address(e, m, vptr, true);
+        return TSW_OK;
+    }
+    Placement& pl = placement(m, e->server_id);
+    size_placement(m, pl);
+    const int pi = pit->second;
+    if (!pl.readiness_init) {
+        *out = vptr;
+        return TSW_OK;
+    }
+    *out = pl.params[pi].cuda;
+    if (!(e->active_params.count(vptr) && pl.has_row[pi])) return TSW_OK;   // as check_param_readiness: not part of the last swap
+    if (pl.flag[pi] == TSW_READY_CUDA) return TSW_OK;                       // already there
+    if (!pl.in_flight) return fail(TSW_ERR_STATE, "parameter is neither on the device nor on its way: swap the model in first");
+    typedef int (*wait_fn_t)(cudaStream_t, unsigned long long, unsigned int, unsigned int);
+    static wait_fn_t wait_fn = nullptr;
+    if (!wait_fn) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t err = cudaGetDriverEntryPoint("cuStreamWaitValue32", &fn, cudaEnableDefault, &qres);
+        if (err != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+            return fail(TSW_ERR_CUDA, "stream memory operations are not available from this driver");
+        wait_fn = (wait_fn_t)fn;
+    }
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    const int rc = wait_fn((cudaStream_t)stream, (unsigned long long)(uintptr_t)&pl.d_table_flag[pi], pl.epoch, 0x0 /* GEQ */);
+    if (rc != 0) return fail(TSW_ERR_CUDA, "cuStreamWaitValue32 failed with driver error " + std::to_string(rc));
+    if (waited) *waited = 1;
     return TSW_OK;
 }
 
@@ -1624,6 +1676,7 @@ int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t t
         a.host_phys = (uint64_t*)pub->host_phys;
         a.host_flag = (uint32_t*)pub->host_flag;
         a.flag_value = pub->flag_value;
+        a.host_flag_value = pub->flag_value;
         a.ticket = (uint32_t*)pub->ticket;
         a.ticket_chunk = pub->ticket_chunk ? pub->ticket_chunk : 1;
         if (a.done_count && (!a.table_phys || !a.table_flag)) return fail(TSW_ERR_INVALID, "publish block needs both table columns");

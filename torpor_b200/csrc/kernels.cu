@@ -146,7 +146,7 @@ __device__ __forceinline__ void move_tile(const PlaceArgs& a, const uint32_t* s_
                 if (a.host_phys) a.host_phys[d.row] = d.row_dst;
                 __threadfence_system();
                 a.table_flag[d.row] = a.flag_value;
-                if (a.host_flag) a.host_flag[d.row] = a.flag_value;
+                if (a.host_flag) a.host_flag[d.row] = a.host_flag_value;
                 __threadfence_system();
             }
         }
@@ -401,6 +401,7 @@ extern "C" int tsw_place_segments_static(int device, const tsw_segment* segs, in
         a.host_phys = (uint64_t*)pub->host_phys;
         a.host_flag = (uint32_t*)pub->host_flag;
         a.flag_value = pub->flag_value;
+        a.host_flag_value = pub->flag_value;
         a.ticket = (uint32_t*)pub->ticket;
         a.ticket_chunk = pub->ticket_chunk ? pub->ticket_chunk : 1;
     }

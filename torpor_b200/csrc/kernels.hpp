@@ -33,7 +33,8 @@ struct PlaceArgs {
     uint32_t* table_flag;         //                       readiness per param
     uint64_t* host_phys;          // host-mapped mirror of the two columns (may be null)
     uint32_t* host_flag;
-    uint32_t flag_value;          // written to the flag columns when a param completes
+    uint32_t flag_value;          // written to the device flag column when a param completes
+    uint32_t host_flag_value;     // written to the host-mapped flag column
     uint32_t system_scope;        // 1: stores may target a peer GPU / host memory
     // Dynamic dealing: when set, CTAs of every participating GPU draw the next `ticket_chunk`
     // tiles from this counter (on the target GPU) instead of a fixed stride, so that a GPU

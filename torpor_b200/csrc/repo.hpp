@@ -71,6 +71,10 @@ struct Placement {
     void* h_descs = nullptr;
     uint32_t* h_first = nullptr;
     bool in_flight = false;
+    // Swap generation.  The device flag column holds the generation that last completed a row
+    // (never a plain "ready"), so that a stream-ordered wait enqueued for generation g cannot be
+    // satisfied by what an earlier swap left behind.  Starts at 2 and only grows.
+    uint32_t epoch = 1;
     std::vector<tsw_engine*> helpers;   // engines whose kernels still write into these blocks
     std::vector<int> remote_rows;       // rows handed out by a plan and not yet committed
 };

@@ -169,6 +169,13 @@ class MemoryManager:
         check(self.L.tsw_translate(self.h, func.encode(), ptr, 1 if search_amid else 0, timeout_ns, C.byref(out)))
         return out.value
 
+    def get_cuda_addr_async(self, func: str, ptr: int, stream: int):
+        """Stream-ordered ``get_cuda_addr``: (address, waited).  If the parameter is still on its
+        way, ``stream`` is made to wait for it; the host does not block."""
+        out, waited = C.c_uint64(), C.c_int()
+        check(self.L.tsw_translate_async(self.h, func.encode(), ptr, stream, C.byref(out), C.byref(waited)))
+        return out.value, bool(waited.value)
+
     def is_model_address(self, func: str, ptr: int) -> bool:
         return check(self.L.tsw_is_model_address(self.h, func.encode(), ptr)) == 1
 
