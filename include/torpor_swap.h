@@ -269,6 +269,8 @@ int tsw_evictor_unlock(tsw_evictor* ev, int gpu, const char* func);
  * tsw_sched_decide answers gpu = -1 when no GPU is available (the caller queues the request);
  * src_gpu >= 0 asks for a replica swap from that GPU; it reads the replicas of `func` from the
  * process-wide repository (tsw_repo_add_model_info / tsw_repo_remove_model_info). */
+/* Fill the two tables from the machine: peer-access attributes for nvlink, PCI paths for pairs. */
+int tsw_topology_discover(int gpu_count, int* pcie_pairs, int* nvlink);
 int tsw_sched_create(int gpu_count, const char* policy, const int* pcie_pairs, const int* nvlink, tsw_scheduler** out);
 int tsw_sched_destroy(tsw_scheduler* s);
 int tsw_sched_set_status(tsw_scheduler* s, int gpu, int status);

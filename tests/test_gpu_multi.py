@@ -66,6 +66,20 @@ def test_replica_swap_across_nvlink(built, oracle_backend):
     repo_reset(); oracle_backend.reset()
 
 
+@needs2
+def test_topology_discovery_feeds_the_scheduler(built):
+    from torpor_b200.memory_manager import Scheduler, discover_topology
+    n = gpu_count()
+    pairs, nv = discover_topology(n)
+    assert len(pairs) == n and all(0 <= p < n for p in pairs)
+    assert all(nv[i][i] == 0 for i in range(n)) and all(nv[i][j] in (-1, 1, 2) for i in range(n) for j in range(n) if i != j)
+    assert any(nv[0][j] == 2 for j in range(1, n)), "an NVLink machine has at least one fast peer"
+    s = Scheduler(n, "IA", pairs, nv)
+    repo_reset()
+    assert s.decide("f")[0] == 0
+    s.close()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))

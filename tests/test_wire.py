@@ -1,0 +1,152 @@
+"""The remoting surface: the hand-written proto3 codec agrees byte for byte with protobuf on
+the messages of proto/cudarpc.proto and proto/signal.proto that touch memory, and an
+executor fed with serialised QueryLists builds the same tables as direct calls and rewrites
+kernel-argument pointers the way the reference's launch path does."""
+import struct
+
+import numpy as np
+import pytest
+
+from torpor_b200 import wire
+from torpor_b200 import workloads as W
+from torpor_b200.memory_manager import MemoryManager, repo_reset
+
+
+def protobuf_classes():
+    """Message classes built at run time from a hand-made descriptor of the same fields."""
+    from google.protobuf import descriptor_pb2, descriptor_pool, message_factory
+    fdp = descriptor_pb2.FileDescriptorProto(name="swap_subset.proto", package="swapwire", syntax="proto3")
+    T = descriptor_pb2.FieldDescriptorProto
+    kinds = {"u": T.TYPE_UINT64, "b": T.TYPE_BYTES, "s": T.TYPE_STRING}
+    signed = {("cudaMemcpyQuery", "kind"), ("cudaMemcpyAsyncQuery", "kind"), ("cudaMemsetAsyncQuery", "value"),
+              ("genericResponse", "error"), ("cudaMallocResponse", "error"), ("cudaMemcpyResponse", "error"),
+              ("WapperQuery", "client_id"), ("SignalAck", "resp")}
+    for name, fields in wire.SCHEMA.items():
+        m = fdp.message_type.add(name=name)
+        for num, fname, kind in fields:
+            f = m.field.add(name=fname, number=num, label=T.LABEL_OPTIONAL)
+            if kind in kinds:
+                f.type = T.TYPE_INT32 if (name, fname) in signed else kinds[kind]
+            elif kind == "rb":
+                f.type, f.label = T.TYPE_BYTES, T.LABEL_REPEATED
+            else:
+                f.type, f.label, f.type_name = T.TYPE_MESSAGE, T.LABEL_REPEATED, ".swapwire." + kind[3:]
+    pool = descriptor_pool.DescriptorPool()
+    fd = pool.Add(fdp) if hasattr(pool, "Add") and not hasattr(pool, "AddSerializedFile") else pool.AddSerializedFile(fdp.SerializeToString())
+    get = getattr(message_factory, "GetMessageClass", None)
+    return {n: (get(pool.FindMessageTypeByName("swapwire." + n)) if get else
+                message_factory.MessageFactory(pool).GetPrototype(pool.FindMessageTypeByName("swapwire." + n)))
+            for n in wire.SCHEMA}
+
+
+def test_codec_matches_protobuf():
+    cls = protobuf_classes()
+    rng = np.random.default_rng(3)
+    cases = [
+        ("cudaMallocQuery", {"size": 20 << 20}),
+        ("cudaMallocResponse", {"error": 0, "ptr": 0x7F00DEADB000}),
+        ("cudaMemcpyAsyncQuery", {"kind": 1, "src": 0, "dst": 0x7F0012345600, "count": 4096,
+                                  "payload": rng.integers(0, 256, 4096, dtype=np.uint8).tobytes(), "stream": b"\x00" * 8}),
+        ("cudaMemcpyQuery", {"kind": 2, "src": 0x600000000200, "dst": 0, "count": 64, "payload": b""}),
+        ("cudaMemsetAsyncQuery", {"ptr": 1 << 45, "value": -1, "count": 1024, "stream": b""}),
+        ("cudaLaunchKernelQuery", {"function": "_Z6kernelPfS_i", "grid_dim_x": 80, "grid_dim_y": 1, "grid_dim_z": 1,
+                                   "block_dim_x": 256, "block_dim_y": 1, "block_dim_z": 1,
+                                   "args": [struct.pack("<Q", 0x600000200000), struct.pack("<i", 7), b""], "shared_mem": 0,
+                                   "stream": b"\x01\x02"}),
+        ("SignalRequest", {"type": 1, "function": "12", "payload": "3"}),
+        ("SignalAck", {"ack": 0, "resp": -1}),
+        ("genericResponse", {"error": 0}),
+    ]
+    for name, fields in cases:
+        msg = cls[name]()
+        for k, v in fields.items():
+            if isinstance(v, list):
+                getattr(msg, k).extend(v)
+            else:
+                setattr(msg, k, v)
+        want = msg.SerializeToString()
+        assert wire.encode(name, fields) == want, name
+        back = wire.decode(name, want)
+        for k, v in fields.items():
+            got = back[k]
+            if isinstance(v, int) and v < 0:
+                got = wire.int32(got)
+            assert got == v, (name, k)
+    # nesting: QueryList of WapperQuery
+    inner = [{"type": wire.Q_MALLOC, "query": wire.encode("cudaMallocQuery", {"size": 2 << 20}), "client_id": 5, "need_sync": 1},
+             {"type": wire.Q_DEVICE_SYNCHRONIZE, "query": b"", "client_id": 5, "need_sync": 0}]
+    ql = cls["QueryList"]()
+    for it in inner:
+        q = ql.queries.add()
+        q.type, q.query, q.client_id, q.need_sync = it["type"], it["query"], it["client_id"], it["need_sync"]
+    assert wire.encode("QueryList", {"queries": inner}) == ql.SerializeToString()
+    assert [d["type"] for d in wire.decode("QueryList", ql.SerializeToString())["queries"]] == [30, 14]
+
+
+class WireClient:
+    """What the client shim does, as far as memory goes: every call becomes a WapperQuery."""
+
+    def __init__(self, ex):
+        self.ex = ex
+
+    def call(self, qtype, message, fields):
+        ql = wire.encode("QueryList", {"queries": [{"type": qtype, "query": wire.encode(message, fields), "client_id": 1}]})
+        r = self.ex.handle(ql)
+        return r[0] if r else None
+
+    def malloc(self, size):
+        return wire.decode("cudaMallocResponse", self.call(wire.Q_MALLOC, "cudaMallocQuery", {"size": size}))["ptr"]
+
+
+def test_executor_over_the_wire_matches_direct_calls(built):
+    ws = W.weight_set("resnet50")
+    blocks, where = W.pack_blocks(ws)
+    zeros = lambda i: np.zeros(ws.tensors[i].nbytes, dtype=np.uint8)
+
+    repo_reset()
+    direct = MemoryManager(0, device=-1)
+    lm = W.cold_start(direct, "7", ws, tensor_data=zeros)
+    direct.evict("7"); direct.swap_in("7")
+    want_blocks, want_params = direct.dump_blocks("7"), direct.dump_params("7")
+    direct.close()
+
+    repo_reset()
+    eng = MemoryManager(0, device=-1)
+    ex = wire.WireExecutor(eng)
+    cl = WireClient(ex)
+    ex.signal(wire.SIG_STARTUP, "7")
+    bv, tv = {}, {}
+    for c in W.cold_start_stream(ws):
+        if c.op == "malloc":
+            p = cl.malloc(c.size)
+            if c.is_model:
+                bv[c.block] = p
+        elif c.op == "memcpy":
+            tv[c.tensor] = bv[c.block] + c.offset
+            cl.call(wire.Q_MEMCPY_ASYNC, "cudaMemcpyAsyncQuery", {"kind": wire.H2D, "dst": tv[c.tensor], "count": c.size,
+                                                                    "payload": zeros(c.tensor).tobytes()})
+        elif c.op == "sync_done":
+            cl.call(wire.Q_DEVICE_SYNCHRONIZE, "genericResponse", {})
+        elif c.op == "access":
+            # the first inference: one kernel per tensor, weight pointer + an activation pointer + a scalar
+            args = [struct.pack("<Q", tv[c.tensor]), struct.pack("<QQ", 0x1234, tv[c.tensor]), struct.pack("<i", c.tensor)]
+            cl.call(wire.Q_LAUNCH_KERNEL, "cudaLaunchKernelQuery", {"function": f"k{c.tensor % 7}", "grid_dim_x": 1, "args": args})
+    ex.complete()
+    assert [tv[i] for i in range(len(ws.tensors))] == lm.tensor_vaddr     # same client-visible pointers
+    ex.signal(wire.SIG_UNLOAD, "7")
+    ex.signal(wire.SIG_LOAD + 1 - 1, "7")        # Load + 1 + src with src = -1 (controller.hpp:425)
+    ex.signal(wire.SIG_EXECUTE, "7")
+    assert np.array_equal(eng.dump_blocks("7"), want_blocks) and np.array_equal(eng.dump_params("7"), want_params)
+
+    # steady state: recorded pointer words are rewritten, everything else is untouched
+    table = {int(r[0]): int(r[3]) for r in want_params}
+    ex.launched.clear()
+    for t in (0, 5, 160):
+        args = [struct.pack("<Q", tv[t]), struct.pack("<QQ", 0x1234, tv[t]), struct.pack("<i", t)]
+        cl.call(wire.Q_LAUNCH_KERNEL, "cudaLaunchKernelQuery", {"function": f"k{t % 7}", "grid_dim_x": 1, "args": args})
+        name, out = ex.launched[-1]
+        assert struct.unpack("<Q", out[0])[0] == table[tv[t]] != tv[t]
+        assert struct.unpack("<QQ", out[1]) == (0x1234, table[tv[t]])
+        assert out[2] == struct.pack("<i", t)
+    eng.close()
+    repo_reset()

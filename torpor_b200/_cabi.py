@@ -123,6 +123,7 @@ SIGNATURES = {
     "tsw_evictor_force_evict": (_i32, [_vp, _i32, _cp]),
     "tsw_evictor_lock": (_i32, [_vp, _i32, _cp]),
     "tsw_evictor_unlock": (_i32, [_vp, _i32, _cp]),
+    "tsw_topology_discover": (_i32, [_i32, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "tsw_sched_create": (_i32, [_i32, _cp, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(_vp)]),
     "tsw_sched_destroy": (_i32, [_vp]),
     "tsw_sched_set_status": (_i32, [_vp, _i32, _i32]),

@@ -320,3 +320,58 @@ int tsw_sched_decide(tsw_scheduler* s, const char* func, int* gpu, int* src_gpu,
 }
 
 }  // extern "C"
+
+// Topology tables for the scheduler, read from the machine instead of hard-coded
+// (controller.hpp:116-118 has "TODO import function pcie sharing and nvlink topology").
+// nvlink[i*n+j]: 0 self, 2 = peer access at the best performance rank (NVLink / NVSwitch),
+// 1 = peer access at a lower rank, -1 = no peer access.  pcie_pairs[i]: another GPU below the
+// same PCIe root port (they share the uplink to the host), or i itself when it has the port alone.
+#include <cuda_runtime.h>
+#include <climits>
+#include <cstdlib>
+
+extern "C" int tsw_topology_discover(int gpu_count, int* pcie_pairs, int* nvlink) {
+    if (gpu_count <= 0 || !pcie_pairs || !nvlink) return tsw::fail(TSW_ERR_INVALID, "bad topology arguments");
+    int present = 0;
+    cudaError_t err = cudaGetDeviceCount(&present);
+    if (err != cudaSuccess || present < gpu_count) {
+        cudaGetLastError();
+        return tsw::fail(TSW_ERR_NO_DEVICE, "fewer CUDA devices than asked for");
+    }
+    std::vector<std::string> port(gpu_count);
+    for (int i = 0; i < gpu_count; ++i) {
+        char bdf[32] = {0};
+        if (cudaDeviceGetPCIBusId(bdf, sizeof(bdf), i) != cudaSuccess) continue;
+        for (char* c = bdf; *c; ++c) *c = (char)tolower(*c);
+        char resolved[PATH_MAX];
+        const std::string link = std::string("/sys/bus/pci/devices/") + bdf;
+        if (!realpath(link.c_str(), resolved)) continue;
+        // /sys/devices/pci0000:15/0000:15:01.0/...: the first two components after /sys/devices name the root port
+        std::string p(resolved);
+        size_t a = p.find("/pci");
+        if (a == std::string::npos) continue;
+        size_t b = p.find('/', a + 1);
+        size_t c = b == std::string::npos ? b : p.find('/', b + 1);
+        port[i] = p.substr(a, (c == std::string::npos ? p.size() : c) - a);
+        if (c == std::string::npos) port[i].clear();   // the GPU sits directly on the root bus: nothing to share
+    }
+    for (int i = 0; i < gpu_count; ++i) {
+        pcie_pairs[i] = i;
+        for (int j = 0; j < gpu_count; ++j)
+            if (j != i && !port[i].empty() && port[i] == port[j]) {
+                pcie_pairs[i] = j;
+                break;
+            }
+        for (int j = 0; j < gpu_count; ++j) {
+            int v = 0;
+            if (i != j) {
+                int ok = 0, rank = 0;
+                cudaDeviceGetP2PAttribute(&ok, cudaDevP2PAttrAccessSupported, i, j);
+                cudaDeviceGetP2PAttribute(&rank, cudaDevP2PAttrPerformanceRank, i, j);
+                v = !ok ? -1 : (rank == 0 ? 2 : 1);
+            }
+            nvlink[i * gpu_count + j] = v;
+        }
+    }
+    return TSW_OK;
+}

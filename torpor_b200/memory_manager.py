@@ -357,6 +357,14 @@ STATUS_AVAIL, STATUS_RUN_LOCAL, STATUS_RUN_NVLINK = -1, 0, 1
 STATUS_RUN_PCIE_LIGHT, STATUS_RUN_PCIE_MEDIAN, STATUS_RUN_PCIE_HEAVY, STATUS_RUN_COLD_START = 2, 3, 4, 5
 
 
+def discover_topology(gpu_count: int):
+    """(pcie_pairs, nvlink matrix) of this machine, in the form ``Scheduler`` takes."""
+    pairs = (C.c_int * gpu_count)()
+    nv = (C.c_int * (gpu_count * gpu_count))()
+    check(_cabi.lib().tsw_topology_discover(gpu_count, pairs, nv))
+    return list(pairs), [[nv[i * gpu_count + j] for j in range(gpu_count)] for i in range(gpu_count)]
+
+
 class Scheduler:
     """The controller's swap decision (include/server/controller.hpp:296-389) for N GPUs."""
 
