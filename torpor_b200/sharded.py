@@ -123,6 +123,7 @@ class ShardedSwap:
         # without a CUDA engine only planning, sharing and rebasing run (CPU tests)
         self.dry = engine is None or engine.device < 0
         self.dynamic = True         # direct mode: draw tiles from a shared counter instead of t mod N
+        self.staged_tile = 512 * 1024
 
     # ---- control plane
     def _bcast_words(self, words: np.ndarray) -> np.ndarray:
@@ -178,7 +179,6 @@ class ShardedSwap:
             segs, tile, pub = self.engine.swap_plan(func)
             if len(segs) > self.max_segments:
                 raise RuntimeError("raise max_segments")
-            segs = fill_rows(segs, tile)
             bases = [] if self.dry else sorted(b for b, _, _ in self.engine.ipc_regions())
             changed = bases != self.region_bases
             buf[0], buf[1], buf[2], buf[3] = len(segs), tile, 1 if changed else 0, mode
@@ -193,7 +193,11 @@ class ShardedSwap:
         pubw = buf[HEADER_WORDS:HEADER_WORDS + PUB_WORDS]
         w = SEGMENT_DTYPE.itemsize // 8
         segs = buf[HEADER_WORDS + PUB_WORDS:HEADER_WORDS + PUB_WORDS + n * w].copy().view(SEGMENT_DTYPE)
-        return segs, tile, pubw
+        # Tile size of this swap: the target's host tile for moves that cross PCIe; larger tiles
+        # for the staged gather, whose source is HBM.  Every rank derives the same numbering.
+        if mode == 1:
+            tile = self.staged_tile
+        return fill_rows(segs, tile), tile, pubw
 
     def _local_publish(self, pubw, dynamic: bool) -> _cabi.Publish:
         m = self.map
