@@ -40,9 +40,12 @@ def tiles_of(segs: np.ndarray, tile: int) -> np.ndarray:
     return np.concatenate([[0], np.cumsum(n)]).astype(np.int64)
 
 
-def fill_rows(segs: np.ndarray, tile: int) -> np.ndarray:
-    """Make ``row_tiles`` / ``row_dst`` explicit so that every rank launches the same table."""
+def fill_rows(segs: np.ndarray, tile: int, force: bool = False) -> np.ndarray:
+    """Make ``row_tiles`` / ``row_dst`` explicit so that every rank launches the same table.
+    ``force`` recounts rows that already carry a count (made for another tile size)."""
     segs = segs.copy()
+    if force:
+        segs["row_tiles"] = 0
     first = tiles_of(segs, tile)
     per_seg = np.diff(first).astype(np.uint32)
     rows = segs["row"]
@@ -197,7 +200,7 @@ class ShardedSwap:
         # for the staged gather, whose source is HBM.  Every rank derives the same numbering.
         if mode == 1:
             tile = self.staged_tile
-        return fill_rows(segs, tile), tile, pubw
+        return fill_rows(segs, tile, force=True), tile, pubw
 
     def _local_publish(self, pubw, dynamic: bool) -> _cabi.Publish:
         m = self.map
