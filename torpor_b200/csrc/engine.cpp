@@ -136,9 +136,16 @@ int ensure_rows(tsw_engine* e, Model* m, Placement& pl) {
     return TSW_OK;
 }
 
+// The two host-visible columns are written by the placement kernel (through the host mapping)
+// or by the host under the engine lock, and read by waiters without the lock: address first,
+// then the flag with release order; readers take the flag with acquire order.
 void set_row(Placement& pl, int idx, uint32_t flag, uint64_t phys) {
-    pl.phys[idx] = phys;
-    pl.flag[idx] = flag;
+    __atomic_store_n(const_cast<uint64_t*>(&pl.phys[idx]), phys, __ATOMIC_RELAXED);
+    __atomic_store_n(const_cast<uint32_t*>(&pl.flag[idx]), flag, __ATOMIC_RELEASE);
+}
+
+inline uint32_t row_flag(const Placement& pl, int idx) {
+    return __atomic_load_n(const_cast<const uint32_t*>(&pl.flag[idx]), __ATOMIC_ACQUIRE);
 }
 
 // init_model_readiness (memory_manager.hpp:234-238): add a row for every parameter
@@ -220,15 +227,14 @@ struct WaitResult { int rc; uint64_t phys; };
 WaitResult wait_row(tsw_engine* e, Placement& pl, int idx, int64_t timeout_ns) {
     const int64_t deadline = now_ns() + (timeout_ns < 0 ? 0 : timeout_ns);
     int spins = 0;
-    while (pl.flag[idx] != TSW_READY_CUDA) {
+    while (row_flag(pl, idx) != TSW_READY_CUDA) {
         if (e->h_status && *e->h_status) return {fail(TSW_ERR_KERNEL, "placement kernel reported an inconsistent tile table"), 0};
         if ((++spins & 63) == 0) {
             if (now_ns() > deadline) return {fail(TSW_ERR_TIMEOUT, "parameter did not become ready in time"), 0};
             if (spins > 4096) std::this_thread::yield();
         }
     }
-    std::atomic_thread_fence(std::memory_order_acquire);
-    return {TSW_OK, pl.phys[idx]};
+    return {TSW_OK, __atomic_load_n(const_cast<const uint64_t*>(&pl.phys[idx]), __ATOMIC_RELAXED)};
 }
 
 // Map a shared-memory arena at an address far away from where the CUDA driver keeps its own
