@@ -251,6 +251,15 @@ def run_single(args):
     sampler.start()
     wall_v, dev_v, launches_v = timed(1, args.steps, args.warmup)
     wall_e, dev_e, launches_e = timed(-1, args.steps, args.warmup)
+    # swap-out with write-back (no counterpart in the reference, whose swap-out moves nothing):
+    # resident bytes -> host store through the same kernel, PCIe D2H bound
+    wb = []
+    for _ in range(3):
+        target.swap_in("model", 1); target.wait_ready("model")
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        target.evict("model", writeback=True)
+        wb.append(time.perf_counter() - t0)
     clocks = sampler.stop()
 
     # measured DMA peak of this box's link, for context next to the theoretical 63 GB/s
@@ -289,6 +298,9 @@ def run_single(args):
                           "peak": PCIE_GEN5_X16_GBS, "unit": "GB/s", "frac": (B / kern_e / 1e9) / PCIE_GEN5_X16_GBS,
                           "frac_wall": e2e / PCIE_GEN5_X16_GBS, "peak_kind": "theoretical PCIe Gen5 x16, one direction",
                           "cudaMemcpyAsync_pinned_h2d_gbs": best, "kernel": "place_kernel (host store -> HBM, zero-copy)"},
+        "swap_out_writeback": {"value": ws.nbytes / min(wb) / 1e9, "unit": "GB/s", "ms_per_model": min(wb) * 1e3,
+                               "frac_of_pcie": ws.nbytes / min(wb) / 1e9 / PCIE_GEN5_X16_GBS,
+                               "what": "tsw_evict(writeback=1): pool -> host store, D2H over PCIe; the reference's swap-out is metadata only"},
         "cpu_baseline": cpu_baseline,
         "gpu_launches": launches_v, "gpu_launches_e2e": launches_e,
         "clocks": clocks, "host_cores": ncpu, "cold_start_s": cold_s,
