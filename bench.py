@@ -149,7 +149,8 @@ def run_reference(args, quiet=False):
               f"{args.warmup} warm-up + {args.steps} swap-ins with forced evict between; {what}; "
               f"IO_THREAD_NUM={io_threads}")
     line = {
-        "impl": "reference", "metric": "model_swap_in_throughput", "value": gbs, "unit": "GB/s", "n_gpus": 1,
+        # the reference's swap uses one GPU's link whatever N is; n_gpus names the configuration compared
+        "impl": "reference", "metric": "model_swap_in_throughput", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": workload_config(args, args.gpus),
