@@ -40,8 +40,9 @@ import numpy as np  # noqa: E402
 PCIE_GEN5_X16_GBS = 63.0       # 32 GT/s x 16 lanes x 128/130 / 8, one direction, per GPU
 NVLINK5_GBS = 900.0            # per direction per GPU (nominal)
 HBM_FALLBACK_GBS = 6650.0
-# DRAM bytes moved per algorithmic byte by place_kernel with both ends in HBM, from the ncu
-# capture summarised in profiles/place_kernel_hbm_llama_mid.md (read + write sectors).
+# DRAM bytes moved per algorithmic byte by place_kernel with both ends in HBM: dram__bytes_read +
+# dram__bytes_write of one launch in an ncu capture of the llama_mid case, over that launch's
+# 2 x parameter bytes.  The kernel streams, so the ratio carries to the full-size launch.
 DRAM_TRAFFIC_PER_ALGO_BYTE = 0.989
 
 

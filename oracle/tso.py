@@ -16,7 +16,6 @@ from typing import List, Optional
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE_TREE = "/root/reference"
 
 LIBS = {
     "oracle": os.path.join(HERE, "libtorpor_oracle.so"),
