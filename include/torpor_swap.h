@@ -67,6 +67,9 @@ typedef struct {
     int grid_ctas;          /* persistent CTAs of the placement kernel; 0 = default */
     int tile_bytes_host;    /* bytes per tile when the source is host memory; 0 = default */
     int tile_bytes_device;  /* bytes per tile when the source is device memory; 0 = default */
+    int mover;              /* 0 = tiles moved by loads/stores of the SMs' threads (default); 1 = by the bulk
+                               asynchronous copy unit through shared memory where every end is 16-byte
+                               aligned (else falls back to 0).  Env TORPOR_SWAP_MOVER overrides. */
     int shard_static;       /* tsw_swap_in_sharded: 0 = participants draw tiles from a shared counter
                                (default), 1 = tile t is fixed to participant t mod n */
 } tsw_config;

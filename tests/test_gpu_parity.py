@@ -391,3 +391,35 @@ def test_stream_ordered_translation(fresh):
         eng.get_cuda_addr_async("B", lb.tensor_vaddr[last], stream.cuda_stream)
     assert e.value.code == _cabi.ERR_STATE
     eng.close()
+
+
+def test_bulk_copy_mover_is_bit_exact(fresh):
+    """The opt-in bulk-copy mover (cp.async.bulk through shared memory, one thread per CTA)
+    moves the same bytes and publishes the same table as the load/store kernel: swap-in from
+    the host store, replica swap, write-back, and the sharded dealing by tickets."""
+    import torch
+    ws = W.weight_set("llama_tiny")
+    sums = np.array([checksum_host(W.tensor_bytes(ws, i)) for i in range(len(ws.tensors))])
+    tables = []
+    for mover in (0, 1):
+        repo_reset()
+        b = MemoryManager(0, device=0, server_id=1, gpu_count=2, mover=mover)
+        a = MemoryManager(0, device=0, server_id=0, gpu_count=2, mover=mover)
+        lm = W.cold_start(b, "m", ws)
+        ModelRepo.add_model_info("m", 1)
+        for src in (-1, 1):
+            a.swap_in("m", src); a.wait_ready("m")
+            assert np.array_equal(a.checksum_resident("m"), sums), (mover, src)
+            tables.append(a.dump_params("m", canonical=True))
+            a.evict("m")
+        a.swap_in_sharded("m", [b]); a.wait_ready("m")        # two engines draw tiles from one counter
+        assert np.array_equal(a.checksum_resident("m"), sums)
+        new = (np.arange(ws.tensors[3].nbytes) % 199).astype(np.uint8)
+        v = lm.tensor_vaddr[3]
+        assert a.cudaMemcpyAsyncBackendHtoD(v, new, 0, False, "m") == 0
+        torch.cuda.synchronize()
+        a.evict("m", writeback=True)
+        assert np.array_equal(a.read_host_store("m", v, new.size), new)
+        assert a.stats()["kernel_launches"] >= 5
+        a.close(); b.close()
+    assert np.array_equal(tables[0], tables[2]) and np.array_equal(tables[1], tables[3])

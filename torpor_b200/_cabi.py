@@ -45,6 +45,7 @@ class Config(C.Structure):
         ("grid_ctas", C.c_int),
         ("tile_bytes_host", C.c_int),
         ("tile_bytes_device", C.c_int),
+        ("mover", C.c_int),
         ("shard_static", C.c_int),
     ]
 

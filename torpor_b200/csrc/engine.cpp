@@ -228,7 +228,8 @@ WaitResult wait_row(tsw_engine* e, Placement& pl, int idx, int64_t timeout_ns) {
     const int64_t deadline = now_ns() + (timeout_ns < 0 ? 0 : timeout_ns);
     int spins = 0;
     while (row_flag(pl, idx) != TSW_READY_CUDA) {
-        if (e->h_status && *e->h_status) return {fail(TSW_ERR_KERNEL, "placement kernel reported an inconsistent tile table"), 0};
+        if (e->h_status && *e->h_status)
+            return {fail(TSW_ERR_KERNEL, *e->h_status == 2 ? "placement kernel gave up waiting for a bulk copy" : "placement kernel reported an inconsistent tile table"), 0};
         if ((++spins & 63) == 0) {
             if (now_ns() > deadline) return {fail(TSW_ERR_TIMEOUT, "parameter did not become ready in time"), 0};
             if (spins > 4096) std::this_thread::yield();
@@ -328,6 +329,14 @@ int place_blocks(tsw_engine* e, Model* m, Placement& pl) {
 }
 
 uint32_t pick_tile(tsw_engine* e, bool host_side) { return host_side ? e->tile_host : e->tile_dev; }
+
+// The bulk-copy mover needs 16-byte aligned ends; anything else goes to the load/store kernel.
+int pick_mover(const tsw_engine* e, const std::vector<PlaceDesc>& descs) {
+    if (e->mover != 1) return 0;
+    for (auto& d : descs)
+        if ((d.src | d.dst) & 15ull) return 0;
+    return 1;
+}
 
 struct Plan {
     std::vector<PlaceDesc> descs;
@@ -470,6 +479,9 @@ int tsw_engine_create(const tsw_config* cfg, tsw_engine** out) {
         TSW_CUDA(cudaSetDevice(cfg->device));
         e->mem.reset(new CudaMemory(cfg->device));
         e->grid_ctas = cfg->grid_ctas > 0 ? cfg->grid_ctas : default_grid_ctas(cfg->device);
+        e->mover = cfg->mover;
+        if (const char* mv = getenv("TORPOR_SWAP_MOVER")) e->mover = atoi(mv);
+        e->grid_bulk = cfg->grid_ctas > 0 ? cfg->grid_ctas : default_grid_ctas(cfg->device) / 2;
         int lo = 0, hi = 0;
         TSW_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
         cudaStream_t s;
@@ -986,7 +998,7 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
             ar.tile_lo = a.ticket ? 0u : (uint32_t)r;
             TSW_CUDA(cudaSetDevice(w->cfg.device));
             if (r != 0) TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_start, (cudaStream_t)w->stream));
-            cudaError_t le = launch_place(ar, w->grid_ctas, (cudaStream_t)w->stream);
+            cudaError_t le = launch_place(ar, w->mover == 1 ? w->grid_bulk : w->grid_ctas, (cudaStream_t)w->stream, pick_mover(w, plan.descs));
             if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
             if (r != 0) {
                 TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_stop, (cudaStream_t)w->stream));
@@ -997,7 +1009,8 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
         }
         TSW_CUDA(cudaSetDevice(e->cfg.device));
     } else {
-        cudaError_t le = launch_place(a, e->grid_ctas, s);
+        const int mv = pick_mover(e, plan.descs);
+        cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, s, mv);
         if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
         e->kernel_launches++;
     }
@@ -1187,7 +1200,8 @@ int tsw_evict(tsw_engine* e, const char* func, int writeback) {
                 a.tile_stride = 1;
                 a.system_scope = 1;
                 a.status = e->d_status;
-                cudaError_t le = launch_place(a, e->grid_ctas, (cudaStream_t)e->stream);
+                const int mv = pick_mover(e, plan.descs);
+                cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, (cudaStream_t)e->stream, mv);
                 if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("write-back kernel launch: ") + cudaGetErrorString(le));
                 e->kernel_launches++;
                 e->bytes_moved += plan.bytes;
@@ -1707,7 +1721,8 @@ int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t t
             if (rc != TSW_OK) return rc;
         }
     }
-    cudaError_t le = launch_place(a, e->grid_ctas, s);
+    const int mv = pick_mover(e, plan.descs);
+    cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, s, mv);
     if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
     TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_stop, s));
     e->ev_valid = true;

@@ -70,6 +70,8 @@ struct tsw_engine {
     volatile uint32_t* h_status = nullptr;
 
     int grid_ctas = 0;
+    int grid_bulk = 0;   // CTAs of the bulk-copy mover
+    int mover = 0;       // 0 = load/store kernel, 1 = bulk-copy kernel where alignment allows
     uint32_t tile_host = 0, tile_dev = 0;
 
     std::atomic<uint64_t> kernel_launches{0};

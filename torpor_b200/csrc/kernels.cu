@@ -35,7 +35,10 @@ constexpr int kUnroll = 8;
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 v;
-    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+#ifndef TSW_LD16
+#define TSW_LD16 "ld.global.nc.L1::no_allocate.v4.u32"
+#endif
+    asm(TSW_LD16 " {%0,%1,%2,%3}, [%4];"
         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
         : "l"(p));
     return v;
@@ -178,6 +181,169 @@ __global__ void __launch_bounds__(kThreads) place_kernel(const PlaceArgs a) {
     }
 }
 
+// ------------------------------------------------------------------ bulk-copy mover
+//
+// The same placement, moved by the bulk asynchronous copy unit instead of by loads and
+// stores of the SMs' threads: one thread per CTA keeps a ring of shared-memory stages; each
+// 16 KiB chunk of a tile is fetched with cp.async.bulk (global -> shared, completion counted
+// on an mbarrier) and written out with cp.async.bulk (shared -> global, bulk group).  No
+// multicast, no cluster: every CTA fetches its own chunks.  Needs source, destination and
+// chunk sizes to be multiples of 16 bytes; a ragged tail of a tile (< 16 B) is copied by
+// the thread itself.  Every wait is bounded: when an mbarrier does not complete within
+// kSpinLimit polls the CTA records status 2, drains what it has in flight and stops.
+constexpr int kBulkThreads = 32;
+constexpr uint32_t kBulkChunk = 16u * 1024;
+constexpr int kBulkStages = 4;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the barrier did not flip within the limit.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_load(void* smem_dst, uint64_t gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_store(uint64_t gdst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kBulkThreads) place_kernel_bulk(const PlaceArgs a) {
+    extern __shared__ __align__(128) unsigned char bulk_smem[];
+    unsigned char* stage = bulk_smem;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(bulk_smem + kBulkStages * kBulkChunk);
+    uint32_t* s_first = reinterpret_cast<uint32_t*>(bulk_smem + kBulkStages * kBulkChunk + 64);
+    for (uint32_t i = threadIdx.x; i <= a.n_descs; i += kBulkThreads) s_first[i] = a.first_tile[i];
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kBulkStages; ++s) mbar_init(&bar[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_proxy();
+    }
+    __syncwarp();
+    if (threadIdx.x != 0) return;   // one thread drives the copy unit; the warp only loaded the table
+
+    uint32_t parity = 0;            // bit s = phase the next wait on stage s expects
+    bool failed = false;
+    const uint64_t step = (uint64_t)gridDim.x * a.tile_stride;
+    uint64_t next = a.tile_lo + (uint64_t)blockIdx.x * a.tile_stride;
+    uint32_t drawn = 0, drawn_end = 0;
+    for (;;) {
+        uint32_t t;
+        if (a.ticket) {
+            if (drawn == drawn_end) {
+                drawn = atomicAdd_system(a.ticket, a.ticket_chunk);
+                if (drawn >= a.tile_hi) break;
+                drawn_end = (a.tile_hi - drawn < a.ticket_chunk) ? a.tile_hi : drawn + a.ticket_chunk;
+            }
+            t = drawn++;
+        } else {
+            if (next >= a.tile_hi) break;
+            t = (uint32_t)next;
+            next += step;
+        }
+        const uint32_t k = owner_of_tile(s_first, a.n_descs, t);
+        const PlaceDesc d = a.descs[k];
+        const uint64_t off = (uint64_t)(t - s_first[k]) * a.tile_bytes;
+        if (off >= d.bytes) {
+            if (a.status) *reinterpret_cast<volatile uint32_t*>(a.status) = 1u;
+            continue;
+        }
+        const uint64_t left = d.bytes - off;
+        const uint32_t len = left < a.tile_bytes ? (uint32_t)left : a.tile_bytes;
+        const uint32_t body = len & ~15u;
+        const uint32_t n_chunks = (body + kBulkChunk - 1) / kBulkChunk;
+        const uint64_t src = d.src + off, dst = d.dst + off;
+
+        const uint32_t ahead = n_chunks < (uint32_t)kBulkStages ? n_chunks : (uint32_t)kBulkStages;
+        for (uint32_t c = 0; c < ahead; ++c) {
+            const uint32_t bytes = (body - c * kBulkChunk) < kBulkChunk ? (body - c * kBulkChunk) : kBulkChunk;
+            mbar_expect_tx(&bar[c], bytes);
+            bulk_load(stage + c * kBulkChunk, src + (uint64_t)c * kBulkChunk, bytes, &bar[c]);
+        }
+        uint32_t in_flight_lo = 0, in_flight_hi = ahead;   // loads issued and not yet waited for: [lo, hi)
+        for (uint32_t c = 0; c < n_chunks; ++c) {
+            const uint32_t s = c % kBulkStages;
+            const uint32_t bytes = (body - c * kBulkChunk) < kBulkChunk ? (body - c * kBulkChunk) : kBulkChunk;
+            if (!mbar_wait_bounded(&bar[s], (parity >> s) & 1u)) {
+                failed = true;
+                break;
+            }
+            parity ^= 1u << s;
+            in_flight_lo = c + 1;
+            fence_async_proxy();
+            bulk_store(dst + (uint64_t)c * kBulkChunk, stage + s * kBulkChunk, bytes);
+            bulk_commit();
+            const uint32_t n = c + kBulkStages;
+            if (n < n_chunks) {
+                bulk_wait_read_all();   // the stage is free again once the store has read it
+                const uint32_t nb = (body - n * kBulkChunk) < kBulkChunk ? (body - n * kBulkChunk) : kBulkChunk;
+                mbar_expect_tx(&bar[s], nb);
+                bulk_load(stage + s * kBulkChunk, src + (uint64_t)n * kBulkChunk, nb, &bar[s]);
+                in_flight_hi = n + 1;
+            }
+        }
+        if (failed) {
+            // give the loads still in flight one more bounded chance to land, then stop
+            for (uint32_t c = in_flight_lo; c < in_flight_hi; ++c) {
+                const uint32_t s = c % kBulkStages;
+                if (mbar_wait_bounded(&bar[s], (parity >> s) & 1u)) parity ^= 1u << s;
+            }
+            bulk_wait_all();
+            if (a.status) *reinterpret_cast<volatile uint32_t*>(a.status) = 2u;
+            return;
+        }
+        for (uint32_t i = body; i < len; ++i)   // ragged tail, fewer than 16 bytes
+            reinterpret_cast<uint8_t*>(dst)[i] = reinterpret_cast<const uint8_t*>(src)[i];
+        bulk_wait_all();
+        fence_async_proxy();
+
+        if (a.done_count) {
+            __threadfence_system();
+            const uint32_t before = atomicAdd_system(&a.done_count[d.row], 1u);
+            if (before + 1 == d.row_tiles) {
+                a.done_count[d.row] = 0;
+                __threadfence_system();
+                a.table_phys[d.row] = d.row_dst;
+                if (a.host_phys) a.host_phys[d.row] = d.row_dst;
+                __threadfence_system();
+                a.table_flag[d.row] = a.flag_value;
+                if (a.host_flag) a.host_flag[d.row] = a.host_flag_value;
+                __threadfence_system();
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ checksum
 
 __device__ __forceinline__ uint32_t load_word(const uint8_t* base, uint64_t byte_off, uint64_t total, bool aligned) {
@@ -249,10 +415,22 @@ int default_grid_ctas(int device) {
     return sms * 6;
 }
 
-cudaError_t launch_place(const PlaceArgs& a, int grid_ctas, cudaStream_t stream) {
+cudaError_t launch_place(const PlaceArgs& a, int grid_ctas, cudaStream_t stream, int mover) {
     if (a.n_descs == 0 || a.tile_hi <= a.tile_lo) return cudaSuccess;
     if (a.tile_bytes == 0 || (a.tile_bytes & 15u) || a.tile_stride == 0) return cudaErrorInvalidValue;
     if (a.ticket && a.ticket_chunk == 0) return cudaErrorInvalidValue;
+    if (mover == 1) {
+        const uint64_t tiles = a.ticket ? (uint64_t)(a.tile_hi - a.tile_lo)
+                                        : ((uint64_t)(a.tile_hi - a.tile_lo) + a.tile_stride - 1) / a.tile_stride;
+        int g = grid_ctas > 0 ? grid_ctas : 444;
+        if ((uint64_t)g > tiles) g = (int)tiles;
+        const size_t bytes = (size_t)kBulkStages * kBulkChunk + 64 + sizeof(uint32_t) * ((size_t)a.n_descs + 1);
+        if (bytes > 200 * 1024) return cudaErrorInvalidValue;
+        cudaError_t e = cudaFuncSetAttribute(place_kernel_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return e;
+        place_kernel_bulk<<<g, kBulkThreads, bytes, stream>>>(a);
+        return cudaGetLastError();
+    }
     const uint64_t mine = a.ticket ? (uint64_t)(a.tile_hi - a.tile_lo)
                                    : ((uint64_t)(a.tile_hi - a.tile_lo) + a.tile_stride - 1) / a.tile_stride;
     int grid = grid_ctas > 0 ? grid_ctas : 888;

@@ -46,7 +46,9 @@ struct PlaceArgs {
 
 // Descriptor-driven placement copy: host store -> pool blocks (swap-in), pool ->
 // pool across NVLink (replica swap / gather), pool -> host store (write-back).
-cudaError_t launch_place(const PlaceArgs& a, int grid_ctas, cudaStream_t stream);
+// mover: 0 = loads and stores by the SMs' threads (place_kernel), 1 = the bulk asynchronous copy
+// unit through shared memory (place_kernel_bulk; needs 16-byte aligned sources and destinations).
+cudaError_t launch_place(const PlaceArgs& a, int grid_ctas, cudaStream_t stream, int mover = 0);
 
 // Per-parameter checksums of device-resident bytes; out has 2 words per row and must be
 // zeroed by the caller.

@@ -81,7 +81,8 @@ class MemoryManager:
 
     def __init__(self, budget: int = 25 << 30, *, device: int = 0, server_id: int = 0, gpu_count: int = 1,
                  block_manager: str = "Buddy", host_arena_bytes: int = 0, host_arena_shm: Optional[str] = None,
-                 grid_ctas: int = 0, tile_bytes_host: int = 0, tile_bytes_device: int = 0, shard_static: bool = False):
+                 grid_ctas: int = 0, tile_bytes_host: int = 0, tile_bytes_device: int = 0, shard_static: bool = False,
+                 mover: int = 0):
         self.L = _cabi.lib()
         cfg = _cabi.Config()
         self.L.tsw_config_default(C.byref(cfg))
@@ -97,6 +98,7 @@ class MemoryManager:
         cfg.tile_bytes_host = tile_bytes_host
         cfg.tile_bytes_device = tile_bytes_device
         cfg.shard_static = 1 if shard_static else 0
+        cfg.mover = mover
         h = C.c_void_p()
         check(self.L.tsw_engine_create(C.byref(cfg), C.byref(h)))
         self.h = h
