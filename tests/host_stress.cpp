@@ -70,7 +70,11 @@ static void executor(int id, int n_threads, int rounds) {
         // another thread's model: replica swap if it is marked healthy there, else host store
         const int other = (id + 1 + r) % n_threads;
         std::string of = "t" + std::to_string(other) + "_m" + std::to_string(r % 4);
-        int rc = tsw_swap_in(e, of.c_str(), other);
+        // only once its owner has finished loading it (the controller never swaps a model that is
+        // still being cold-started): the owner marks it on the repository after track_end
+        const bool loaded = tsw_repo_model_status(of.c_str(), other) >= 0 && tsw_repo_total_size(of.c_str()) > 0 &&
+                            tsw_repo_model_status(of.c_str(), other) != TSW_MODEL_INCOMPLETE;
+        int rc = loaded ? tsw_swap_in(e, of.c_str(), other) : TSW_ERR_UNKNOWN_MODEL;
         if (rc == TSW_OK) {
             CHECK(tsw_wait_ready(e, of.c_str(), 2000000000ll) == TSW_OK);
             CHECK(tsw_check_alloc(e, of.c_str()) == 1);

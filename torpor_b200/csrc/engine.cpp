@@ -403,11 +403,43 @@ int tsw_repo_reset(void) {
     Lock g(r.mu);
     // Page-locked mirrors belong to the engine that made them; only heap mirrors
     // (plan-only engines) are released here.
-    for (auto& kv : r.models)
+    for (auto& kv : r.models) {
         for (auto& b : kv.second->blocks)
             if (b.mirror && b.mirror_heap) free(b.mirror);
+        for (auto& pk : kv.second->place) {
+            Placement& pl = pk.second;
+            bool plan_rows = false;
+            {
+                std::lock_guard<std::mutex> ge(g_engines_mu);
+                auto it = g_engines.find(pk.first);
+                plan_rows = it == g_engines.end() || it->second->plan;
+            }
+            if (plan_rows && pl.capacity) {   // rows of plan-only engines are heap memory
+                free((void*)pl.flag);
+                free((void*)pl.phys);
+            }
+        }
+    }
     r.models.clear();
     r.active_devices.clear();
+    // With every model gone, what the engines hold for models can be reused: pointer-table
+    // rows, launch descriptors and the host store (blocks still placed in the pools stay
+    // allocated there until their engine goes away).
+    std::lock_guard<std::mutex> ge(g_engines_mu);
+    for (auto& kv : g_engines) {
+        tsw_engine* e = kv.second;
+        Lock g2(e->mu);
+        e->active_params.clear();
+        if (e->plan) continue;
+        cudaSetDevice(e->cfg.device);
+        if (e->stream) cudaStreamSynchronize((cudaStream_t)e->stream);
+        e->dev_slab.used = e->dev_slab_floor;
+        e->host_slab.used = e->host_slab_floor;
+        if (e->dev_slab.base) cudaMemset(e->dev_slab.base + e->dev_slab_floor, 0, e->dev_slab.size - e->dev_slab_floor);
+        e->arena.used = 0;
+        for (void* p : e->loose_host) cudaFreeHost(p);
+        e->loose_host.clear();
+    }
     return TSW_OK;
 }
 
@@ -537,6 +569,8 @@ int tsw_engine_create(const tsw_config* cfg, tsw_engine** out) {
             if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("warm-up launch: ") + cudaGetErrorString(le));
             TSW_CUDA(cudaStreamSynchronize(s));
         }
+        e->dev_slab_floor = e->dev_slab.used;
+        e->host_slab_floor = e->host_slab.used;
         int rc = make_arena(e.get());
         if (rc != TSW_OK) return rc;
         // all-pairs peer access, as the controller does at start-up (controller.hpp:63-75)
@@ -572,7 +606,15 @@ int tsw_engine_destroy(tsw_engine* e) {
         // rows of the pointer table live in this engine's slabs: drop its placements
         Repo& r = repo();
         Lock g(r.mu);
-        for (auto& kv : r.models) kv.second->place.erase(e->server_id);
+        for (auto& kv : r.models) {
+            auto it = kv.second->place.find(e->server_id);
+            if (it == kv.second->place.end()) continue;
+            if (e->plan && it->second.capacity) {
+                free((void*)it->second.flag);
+                free((void*)it->second.phys);
+            }
+            kv.second->place.erase(it);
+        }
     }
     if (!e->plan) {
         cudaSetDevice(e->cfg.device);

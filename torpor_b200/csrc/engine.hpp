@@ -65,6 +65,7 @@ struct tsw_engine {
     void* ev_stop = nullptr;
     bool ev_valid = false;
     tsw::Slab dev_slab, host_slab;
+    uint64_t dev_slab_floor = 0, host_slab_floor = 0;   // what the engine itself took at creation
     tsw::HostArena arena;
     uint32_t* d_status = nullptr;
     volatile uint32_t* h_status = nullptr;
