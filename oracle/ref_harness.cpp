@@ -24,6 +24,14 @@
 #include "block_manager.hpp"
 #include "memory_manager.hpp"
 #include "evictor.hpp"
+#ifdef TORPOR_REF_WITH_CONTROLLER
+// controller.hpp includes "cuda_server.hpp" from its own directory, which no include path can
+// override: the executor stand-in is included first and the real header's guard is pre-defined,
+// so that the real file contributes nothing.  socket_helper.hpp is shadowed by include path.
+#include "ref_shim_ctrl/cuda_server.hpp"
+#define INCLUDE_CUDA_SERVER_HPP_
+#include "controller.hpp"   // the reference's own
+#endif
 #undef private
 #undef protected
 
@@ -351,5 +359,40 @@ int tso_evictor_check_and_add(void* ev, int gpu, const char* func, uint64_t size
 void tso_evictor_force_evict(void* ev, int gpu, const char* func) { string f(func); ((EvictorHandle*)ev)->ev->force_evict(gpu, f); }
 void tso_evictor_lock(void* ev, int gpu, const char* func) { string f(func); ((EvictorHandle*)ev)->ev->lock(gpu, f); }
 void tso_evictor_unlock(void* ev, int gpu, const char* func) { string f(func); ((EvictorHandle*)ev)->ev->unlock(gpu, f); }
+
+// ---------------------------------------------------------------- controller decisions
+#ifdef TORPOR_REF_WITH_CONTROLLER
+// The reference's Controller object itself (include/server/controller.hpp), built on a 4-GPU
+// stand-in: its scheduling functions (:296-389) and its load request (:420-427, with the
+// eviction check :392-400 and the source pin :437-447) run unmodified; sockets are no-ops and
+// executors only record the signals they are sent.
+struct CtrlHandle {
+    zmq::context_t ctx;
+    std::unique_ptr<server::Controller> c;
+};
+
+void* tso_sched_create(int n, const char* policy, const int* pcie_pairs, const int* nvlink) {
+    if (n != 4) return nullptr;   // the reference's tables are hard-coded for 4 GPUs (:116-118)
+    for (int i = 0; i < 4; ++i) {
+        if (pcie_pairs[i] != (int[]){1, 0, 3, 2}[i]) return nullptr;
+    }
+    (void)nvlink;
+    torpor_ref_fake::device_count() = n;
+    if (policy && std::string(policy) == "RAND") setenv("SCHEDULE_POLICY", "RAND", 1);
+    else unsetenv("SCHEDULE_POLICY");
+    setenv("EVICT_POLICY", "LRU", 1);
+    auto* h = new CtrlHandle();
+    h->c.reset(new server::Controller(null_logger(), &h->ctx));
+    return h;
+}
+void tso_sched_destroy(void* s) { delete (CtrlHandle*)s; }
+void tso_sched_set_status(void* s, int gpu, int status) { ((CtrlHandle*)s)->c->executor_status_[gpu].status_ = status; }
+void tso_sched_set_level(void* s, const char* func, int level) { ((CtrlHandle*)s)->c->model_level_map_[func] = level; }
+void tso_sched_decide(void* s, const char* func, int* out3) {
+    string f(func);
+    auto d = ((CtrlHandle*)s)->c->schedule_func_(f);
+    out3[0] = d.gpu_idx_; out3[1] = d.src_swap_gpu_; out3[2] = d.status_;
+}
+#endif
 
 }  // extern "C"

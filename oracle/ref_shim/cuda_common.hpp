@@ -150,6 +150,46 @@ inline cudaError_t cudaDeviceSynchronize() { return cudaSuccess; }
 
 #endif  // TORPOR_REF_FAKE_CUDA
 
+#ifdef TORPOR_REF_WITH_CONTROLLER
+// What include/server/controller.hpp needs beyond the swap-path headers: the signal messages
+// (proto/signal.proto, normally protoc-generated), a cuDNN handle and two peer-access calls.
+namespace signal {
+enum RequestType { ExecuteAfterLoad = 0, Execute = 1, Load = 2, Unload = 3, ExecuteForRecord = 10, Replay = 11 };
+enum AckType { OK = 0, Inavail = 1 };
+inline int format_as(RequestType t) { return (int)t; }   // how the logger prints it
+inline int format_as(AckType t) { return (int)t; }
+struct SignalRequest {
+    RequestType type_ = ExecuteAfterLoad;
+    std::string function_, payload_;
+    bool ParseFromString(const std::string&) { return true; }
+    RequestType type() const { return type_; }
+    const std::string& function() const { return function_; }
+    const std::string& payload() const { return payload_; }
+};
+struct SignalAck {
+    void set_ack(AckType) {}
+    void set_resp(int) {}
+    bool SerializeToString(std::string*) const { return true; }
+};
+}  // namespace signal
+using signal::RequestType;
+using signal::SignalRequest;
+using signal::AckType;
+using signal::SignalAck;
+
+typedef void* cudnnHandle_t;
+typedef int cudnnStatus_t;
+static const cudnnStatus_t CUDNN_STATUS_SUCCESS = 0;
+inline cudnnStatus_t cudnnCreate(cudnnHandle_t* h) { *h = nullptr; return CUDNN_STATUS_SUCCESS; }
+#define cudnnCheck(ans) { (void)(ans); }
+#ifdef TORPOR_REF_FAKE_CUDA
+namespace torpor_ref_fake { inline int& device_count() { static int n = 4; return n; } }
+inline cudaError_t cudaGetDeviceCount(int* n) { *n = torpor_ref_fake::device_count(); return cudaSuccess; }
+inline cudaError_t cudaDeviceCanAccessPeer(int* can, int, int) { *can = 0; return cudaSuccess; }
+inline cudaError_t cudaDeviceEnablePeerAccess(int, unsigned int) { return cudaSuccess; }
+#endif
+#endif  // TORPOR_REF_WITH_CONTROLLER
+
 #define cudaCheck(ans) { cudaAssert((ans), __FILE__, __LINE__); }
 inline void cudaAssert(cudaError_t err, const char* file, int line, bool abort_flag = false) {
     if (err != cudaSuccess) {

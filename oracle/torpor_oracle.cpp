@@ -9,12 +9,11 @@
 //   manager (swap-in / swap-out) include/server/memory_manager.hpp
 //   eviction policy              include/server/evictor.hpp
 //   swap scheduler               include/server/controller.hpp:296-389
-// Parity is PINNED for the first four: tests/golden/ holds tables produced by the
-// reference's own headers compiled against a host-memory CUDA stand-in
-// (ref_harness.cpp); this restatement reproduces them bit for bit
-// (tests/test_oracle_golden.py).  The scheduler section is "parity unpinned":
-// controller.hpp needs zmq and protobuf and cannot be compiled or run here, so
-// that section is a line-by-line restatement with nothing to check it against.
+// Parity is PINNED: tests/golden/ holds tables, victims and scheduling decisions
+// produced by the reference's own headers compiled against a host-memory CUDA
+// stand-in (ref_harness.cpp; controller.hpp with its socket and executor headers
+// shadowed); this restatement reproduces them bit for bit
+// (tests/test_oracle_golden.py, tests/test_scheduler.py).
 //
 // "Device" memory here is a label space: addresses start at the same canonical
 // base as in the stand-in (0x600000000000 + 1 TiB per GPU), bytes live in a
@@ -728,7 +727,7 @@ void tso_evictor_force_evict(void* e, int g, const char* f) { ((EvictorBase*)e)-
 void tso_evictor_lock(void* e, int g, const char* f) { ((EvictorBase*)e)->lock(g, f); }
 void tso_evictor_unlock(void* e, int g, const char* f) { ((EvictorBase*)e)->unlock(g, f); }
 
-// The controller cannot be compiled here (zmq, protobuf); its decision functions are restated above.
+// The controller's decision functions as restated above; any number of GPUs, tables as inputs.
 void* tso_sched_create(int n, const char* policy, const int* pcie_pairs, const int* nvlink) {
     Sched* s = new Sched();
     s->n = n;

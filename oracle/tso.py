@@ -195,6 +195,8 @@ class TsoScheduler:
         pp = (C.c_int * n)(*pcie_pairs)
         nv = (C.c_int * (n * n))(*[v for row in nvlink for v in row])
         self.h = self.L.tso_sched_create(n, policy.encode(), pp, nv)
+        if not self.h:
+            raise ValueError("this checker only knows the reference's hard-coded 4-GPU topology")
 
     def close(self):
         if self.h:

@@ -87,9 +87,10 @@ void tso_evictor_force_evict(void* e, int gpu, const char* func);
 void tso_evictor_lock(void* e, int gpu, const char* func);
 void tso_evictor_unlock(void* e, int gpu, const char* func);
 
-/* Swap decision of the controller (include/server/controller.hpp:296-389).  Exported by the
- * CPU restatement only: controller.hpp itself needs zmq and protobuf and cannot be compiled
- * here, so this part of the checker is NOT pinned against reference output.
+/* Swap decision of the controller (include/server/controller.hpp:296-389).  The reference
+ * checker answers with the reference's own Controller object (controller.hpp compiled where
+ * it lies, zmq / executor headers shadowed) and only accepts the 4-GPU tables hard-coded there
+ * (:116-118), returning NULL otherwise; the restatement takes any tables.
  * out3 = { gpu, src_gpu, status }; replicas are read from tso_set_model_status. */
 void* tso_sched_create(int n, const char* policy, const int* pcie_pairs, const int* nvlink);
 void tso_sched_destroy(void* s);

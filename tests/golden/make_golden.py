@@ -2,9 +2,9 @@
 
 Runs the scenarios of tests/scenarios.py and the eviction-policy sequences of
 tests/evictor_cases.py against oracle/_ref/libtorpor_ref_fake.so -- the reference's
-own headers (include/server/{memory_manager,block_manager,model_repo,evictor}.hpp)
+own headers (include/server/{memory_manager,block_manager,model_repo,evictor,controller}.hpp)
 compiled where they lie against a host-memory CUDA stand-in -- and stores the
-recorded tables.  Needs the reference tree to build that library:
+recorded tables, victims and scheduling decisions.  Needs the reference tree to build that library:
 
     make -C oracle ref && python tests/golden/make_golden.py
 """
@@ -20,6 +20,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 import scenarios  # noqa: E402
 import evictor_cases  # noqa: E402
+import scheduler_cases  # noqa: E402
 
 
 def main():
@@ -34,6 +35,13 @@ def main():
         with open(path, "w") as f:
             json.dump(cases, f)
         print("evictor", kind, len(cases), "sequences,", os.path.getsize(path), "bytes")
+    # the reference's Controller object itself (controller.hpp compiled where it lies)
+    for policy in ("IA", "RAND"):
+        runs = scheduler_cases.record(backend, policy)
+        path = os.path.join(HERE, f"scheduler_{policy}.json")
+        with open(path, "w") as f:
+            json.dump(runs, f)
+        print("scheduler", policy, len(runs), "streams,", sum(len(r) for r in runs), "decisions,", os.path.getsize(path), "bytes")
 
 
 if __name__ == "__main__":

@@ -1,78 +1,65 @@
-"""Swap scheduler of the shipped library against the CPU restatement of the controller's
-decision functions (include/server/controller.hpp:296-389) on seeded request streams, with
-the reference's own 4-GPU tables and with an 8-GPU NVSwitch layout.  (The controller itself
-cannot be compiled without zmq/protobuf, so this row is checked against the restatement
-only.)"""
-import ctypes
+"""Swap scheduler (include/server/controller.hpp:296-389): the shipped library and the CPU
+restatement against decisions recorded from the reference's own Controller object
+(controller.hpp compiled where it lies with its socket and executor headers shadowed;
+tests/golden/scheduler_*.json) on the reference's 4-GPU tables, and against each other on an
+8-GPU NVSwitch layout the reference's hard-coded tables cannot express."""
+import json
+import os
 
-import numpy as np
 import pytest
 
+import scenarios
+import scheduler_cases as SC
 from torpor_b200.memory_manager import ModelRepo, Scheduler, repo_reset
 
-REF_PAIRS = [1, 0, 3, 2]                                               # controller.hpp:117
-REF_NVLINK = [[0, 1, 1, 2], [1, 0, 2, 1], [1, 2, 0, 2], [2, 1, 2, 0]]  # controller.hpp:118
+
+def golden(policy):
+    with open(os.path.join(scenarios.GOLDEN_DIR, f"scheduler_{policy}.json")) as f:
+        return json.load(f)
 
 
-def nvswitch(n):
-    return [i ^ 1 for i in range(n)], [[0 if i == j else 2 for j in range(n)] for i in range(n)]
-
-
-def drive(sched, set_replica, n_gpu, seed, n_ops=600):
-    """A request stream: decisions are applied the way the controller applies them
-    (GPU busy until completion, replica registered on completion, random unloads)."""
-    rng = np.random.default_rng(seed)
-    models = [f"m{i}" for i in range(10)]
-    for m in models:
-        sched.set_level(m, int(rng.integers(0, 4)) - 0)
-    busy = {}
-    homes = {m: set() for m in models}
-    out = []
-    for _ in range(n_ops):
-        r = rng.random()
-        if r < 0.55:
-            m = models[int(rng.integers(0, len(models)))]
-            g, src, st = sched.decide(m)
-            out.append((m, g, src, st))
-            if g >= 0:
-                sched.set_status(g, st)
-                busy[g] = m
-        elif r < 0.9 and busy:
-            g = sorted(busy)[int(rng.integers(0, len(busy)))]
-            m = busy.pop(g)
-            sched.set_status(g, -1)
-            set_replica(m, g, True)
-            homes[m].add(g)
-        else:
-            m = models[int(rng.integers(0, len(models)))]
-            for g in sorted(homes[m]):
-                if g not in busy:
-                    set_replica(m, g, False)
-                    homes[m].discard(g)
-                    break
-    return out
+def engine_stream(n, policy, pairs, nv, seed):
+    repo_reset()
+    SC.reseed_libc()
+    s = Scheduler(n, policy, pairs, nv)
+    got = SC.drive(s, lambda m, g, full: (ModelRepo.add_model_info if full else ModelRepo.remove_model_info)(m, g), n, seed)
+    s.close()
+    repo_reset()
+    return got
 
 
 @pytest.mark.parametrize("policy", ["IA", "RAND"])
-@pytest.mark.parametrize("layout", ["reference_4gpu", "nvswitch_8gpu"])
-def test_decisions_match_the_restatement(built, oracle_backend, policy, layout):
-    n, pairs, nv = (4, REF_PAIRS, REF_NVLINK) if layout == "reference_4gpu" else (8, *nvswitch(8))
-    libc = ctypes.CDLL("libc.so.6")
+def test_engine_decisions_match_the_reference_controller(built, policy):
+    want = golden(policy)
+    assert len(want) == len(SC.SEEDS)
+    for seed, w in zip(SC.SEEDS, want):
+        got = engine_stream(4, policy, SC.REF_PAIRS, SC.REF_NVLINK, seed)
+        assert got == w, f"{policy} seed {seed}"
+        kinds = {d[3] for d in got}
+        assert {-1, 0} <= kinds and (policy == "RAND" or 1 in kinds)   # queued, in place, and replica swaps all occur
+
+
+@pytest.mark.parametrize("policy", ["IA", "RAND"])
+def test_restatement_decisions_match_the_reference_controller(oracle_backend, policy):
+    assert SC.record(oracle_backend, policy) == golden(policy)
+
+
+@pytest.mark.parametrize("policy", ["IA", "RAND"])
+def test_reference_controller_still_matches_its_recordings(ref_backend, policy):
+    assert SC.record(ref_backend, policy) == golden(policy)
+
+
+@pytest.mark.parametrize("policy", ["IA", "RAND"])
+def test_eight_gpu_layout_matches_the_restatement(built, oracle_backend, policy):
+    pairs, nv = SC.nvswitch(8)
     for seed in range(4):
         oracle_backend.reset()
-        libc.srand(1)
-        o = oracle_backend.lib.scheduler(n, policy, pairs, nv)
-        want = drive(o, lambda m, g, full: oracle_backend.lib.set_model_status(m, g, full), n, seed)
+        SC.reseed_libc()
+        o = oracle_backend.lib.scheduler(8, policy, pairs, nv)
+        want = SC.drive(o, lambda m, g, full: oracle_backend.lib.set_model_status(m, g, full), 8, seed)
         o.close()
-        repo_reset()
-        libc.srand(1)
-        s = Scheduler(n, policy, pairs, nv)
-        got = drive(s, lambda m, g, full: (ModelRepo.add_model_info if full else ModelRepo.remove_model_info)(m, g), n, seed)
-        s.close()
-        assert got == want, f"{policy}/{layout} seed {seed}"
-        kinds = {d[3] for d in got}
-        assert {-1, 0} <= kinds and (policy == "RAND" or 1 in kinds)   # queued, local, and replica swaps all occur
-    repo_reset(); oracle_backend.reset()
+        assert engine_stream(8, policy, pairs, nv, seed) == want, f"{policy} seed {seed}"
+    oracle_backend.reset()
 
 
 def test_defaults_describe_an_nvswitch_box(built):
