@@ -46,7 +46,7 @@ def test_sharded_swap_in_process_equals_single_gpu_swap(built, oracle_backend, n
         assert np.array_equal(engines[0].dump_blocks("m", canonical=True), orc.dump_blocks("m"))
         assert np.array_equal(engines[0].checksum_resident("m"), sums)
     for d in range(1, n):
-        assert engines[d].stats()["kernel_launches"] >= 3 + 1   # warm-up + every GPU took part in every cycle
+        assert engines[d].stats()["kernel_launches"] == 3       # every GPU took part in every cycle, one launch each
     for e in engines:
         e.close()
     repo_reset(); oracle_backend.reset()

@@ -1023,8 +1023,9 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
     a.status = e->d_status;
 
     if (n_helpers > 0) {
-        // Deal tiles round-robin over the participating GPUs: GPU r takes tiles r, r + n, ...
-        // so that every link works on the front of the access order at the same time.
+        // Every participating GPU works on the front of the access order at the same time:
+        // by default its CTAs draw the next tile from one counter on the target, so a link
+        // that is fed faster moves more tiles; with shard_static GPU r takes tiles r, r + n, ...
         const int n = n_helpers + 1;
         TSW_CUDA(cudaMemsetAsync(pl.d_ticket, 0, sizeof(uint32_t), s));
         TSW_CUDA(cudaStreamSynchronize(s));  // descriptors and the tile dispenser must be on the target before peers read them
@@ -1040,7 +1041,8 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
             ar.tile_lo = a.ticket ? 0u : (uint32_t)r;
             TSW_CUDA(cudaSetDevice(w->cfg.device));
             if (r != 0) TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_start, (cudaStream_t)w->stream));
-            cudaError_t le = launch_place(ar, w->mover == 1 ? w->grid_bulk : w->grid_ctas, (cudaStream_t)w->stream, pick_mover(w, plan.descs));
+            const int mv = pick_mover(w, plan.descs);
+            cudaError_t le = launch_place(ar, mv ? w->grid_bulk : w->grid_ctas, (cudaStream_t)w->stream, mv);
             if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
             if (r != 0) {
                 TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_stop, (cudaStream_t)w->stream));
