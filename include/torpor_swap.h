@@ -280,6 +280,46 @@ int tsw_sched_set_status(tsw_scheduler* s, int gpu, int status);
 int tsw_sched_set_level(tsw_scheduler* s, const char* func, int level);
 int tsw_sched_decide(tsw_scheduler* s, const char* func, int* gpu, int* src_gpu, int* status);
 
+/* Request handling around a swap: what the controller does with each router request and each
+ * executor completion (controller.hpp:130-262) on top of the scheduler and the eviction
+ * policy above -- round-robin placement of cold starts (:283-294), one request per GPU with a
+ * FIFO for the rest (:176-178,242-262), check_eviction (:392-400), send_exec_req (:402-418),
+ * send_load_req (:420-427) and the pin on a source replica while a GPU copies from it
+ * (:442-453).  No sockets and no executor threads: every signal the reference would send to
+ * an executor (`signal` = ExecutorSignal_* of utils.hpp:70-74; a load is 4 + 1 + src_gpu, so
+ * 4 means "from the host store") and every acknowledgement it would return to the router
+ * (`resp` = the GPU chosen, or -1) goes to a callback, in the reference's order.  Replicas and
+ * model sizes are read from and written to the process-wide repository, as the reference's
+ * controller does with the ModelRepo singleton.
+ * type: TSW_REQ_* (RequestType of proto/signal.proto); payload: the model level "0".."2" for
+ * TSW_REQ_EXECUTE_AFTER_LOAD, an optional GPU index for TSW_REQ_EXECUTE / TSW_REQ_UNLOAD.
+ * Where the reference would spin because nothing can be evicted (evictor.hpp:84-95,211-224):
+ * if pinned replicas are in the way, the request waits in the queue like one that found every
+ * GPU busy (TSW_OK, nothing sent, no acknowledgement yet) and is tried again at the next
+ * completion; a model at or above the limit can never fit, and the call returns TSW_ERR_STATE,
+ * sends nothing and drops the request.  A cold start that has finished is entered even if its
+ * GPU stays over the limit (it is there already); whatever is not pinned is unloaded for it. */
+typedef struct tsw_controller tsw_controller;
+typedef void (*tsw_signal_fn)(void* user, int gpu, int signal, const char* func);
+typedef void (*tsw_ack_fn)(void* user, int ack, int resp);
+#define TSW_REQ_EXECUTE_AFTER_LOAD 0
+#define TSW_REQ_EXECUTE 1
+#define TSW_REQ_LOAD 2
+#define TSW_REQ_UNLOAD 3
+#define TSW_SIGNAL_NOTIFY 0
+#define TSW_SIGNAL_STARTUP 1
+#define TSW_SIGNAL_EXECUTE 2
+#define TSW_SIGNAL_UNLOAD 3
+#define TSW_SIGNAL_LOAD 4
+int tsw_ctrl_create(int gpu_count, uint64_t mem_limit_bytes, const char* schedule_policy, const char* evict_policy,
+                    const int* pcie_pairs, const int* nvlink, tsw_signal_fn on_signal, tsw_ack_fn on_ack, void* user,
+                    tsw_controller** out);
+int tsw_ctrl_destroy(tsw_controller* c);
+int tsw_ctrl_request(tsw_controller* c, int type, const char* func, const char* payload);
+int tsw_ctrl_complete(tsw_controller* c, int executor);    /* the executor's "done" on controller_sync_queue */
+int tsw_ctrl_executor_status(tsw_controller* c, int gpu, int* status, char* func, int cap);
+int tsw_ctrl_queue_depth(tsw_controller* c);
+
 #ifdef __cplusplus
 }
 #endif

@@ -393,6 +393,62 @@ void tso_sched_decide(void* s, const char* func, int* out3) {
     auto d = ((CtrlHandle*)s)->c->schedule_func_(f);
     out3[0] = d.gpu_idx_; out3[1] = d.src_swap_gpu_; out3[2] = d.status_;
 }
+
+// The controller's own loop (Controller::start, :125-264), run for exactly one event: the
+// socket stand-in hands the loop one scripted request -- or puts one executor id on
+// controller_sync_queue, as CUDAExecutor does when it finishes (cuda_server.hpp:298) -- and
+// throws out of the endless loop at the next poll.  The executor threads start() spawns are
+// joined here (the stand-in's executor returns at once).
+void* tso_ctrl_create(int n, uint64_t mem_limit_bytes, const char* sched_policy, const char* evict_policy,
+                      const int* pcie_pairs, const int* nvlink) {
+    const uint64_t GiB = 1ull << 30;
+    if (mem_limit_bytes % GiB != 0 || mem_limit_bytes / GiB < 1 || mem_limit_bytes / GiB > 24) return nullptr;
+    setenv("MEM_LIMIT_IN_GB", std::to_string(mem_limit_bytes / GiB).c_str(), 1);
+    void* h = tso_sched_create(n, sched_policy, pcie_pairs, nvlink);
+    if (!h) return nullptr;
+    // tso_sched_create built the controller with EVICT_POLICY=LRU; rebuild it if the other policy is asked for
+    if (!(evict_policy && std::string(evict_policy) == "LRU")) {
+        delete (CtrlHandle*)h;
+        unsetenv("EVICT_POLICY");
+        auto* fresh = new CtrlHandle();
+        fresh->c.reset(new server::Controller(null_logger(), &fresh->ctx));
+        h = fresh;
+    }
+    unsetenv("MEM_LIMIT_IN_GB");
+    return h;
+}
+void tso_ctrl_destroy(void* c) { delete (CtrlHandle*)c; }
+
+static int run_one_event(CtrlHandle* h, const std::string* request, int executor, char* out, int cap) {
+    auto& st = torpor_ref_script::state();
+    st.trace.clear();
+    int polls = 0;
+    st.next = [&](string* r) -> bool {
+        if (polls++ > 0) throw torpor_ref_script::Stop();
+        if (request) { *r = *request; return true; }
+        server::controller_sync_queue->push(executor);
+        return false;
+    };
+    try {
+        h->c->start();
+    } catch (const torpor_ref_script::Stop&) {
+    }
+    st.next = nullptr;
+    for (auto& t : h->c->thread_vec_) if (t.joinable()) t.join();
+    h->c->thread_vec_.clear();
+    std::string joined;
+    for (size_t i = 0; i < st.trace.size(); ++i) { if (i) joined += "\n"; joined += st.trace[i]; }
+    st.trace.clear();
+    if (out && (int)joined.size() + 1 <= cap) memcpy(out, joined.c_str(), joined.size() + 1);
+    return (int)joined.size() + 1;
+}
+int tso_ctrl_request(void* c, int type, const char* func, const char* payload, char* trace, int cap) {
+    const std::string req = std::to_string(type) + " " + func + " " + (payload ? payload : "");
+    return run_one_event((CtrlHandle*)c, &req, -1, trace, cap);
+}
+int tso_ctrl_complete(void* c, int executor, char* trace, int cap) {
+    return run_one_event((CtrlHandle*)c, nullptr, executor, trace, cap);
+}
 #endif
 
 }  // extern "C"

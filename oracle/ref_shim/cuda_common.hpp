@@ -161,15 +161,26 @@ inline int format_as(AckType t) { return (int)t; }
 struct SignalRequest {
     RequestType type_ = ExecuteAfterLoad;
     std::string function_, payload_;
-    bool ParseFromString(const std::string&) { return true; }
+    // the harness's own encoding of a scripted request: "<type> <function> <payload>"
+    bool ParseFromString(const std::string& s) {
+        size_t a = s.find(' '), b = s.find(' ', a + 1);
+        type_ = (RequestType)atoi(s.substr(0, a).c_str());
+        function_ = s.substr(a + 1, b - a - 1);
+        payload_ = s.substr(b + 1);
+        return true;
+    }
     RequestType type() const { return type_; }
     const std::string& function() const { return function_; }
     const std::string& payload() const { return payload_; }
 };
 struct SignalAck {
-    void set_ack(AckType) {}
-    void set_resp(int) {}
-    bool SerializeToString(std::string*) const { return true; }
+    int ack_ = 0, resp_ = 0;
+    void set_ack(AckType a) { ack_ = (int)a; }
+    void set_resp(int r) { resp_ = r; }
+    bool SerializeToString(std::string* out) const {
+        *out = std::to_string(ack_) + " " + std::to_string(resp_);
+        return true;
+    }
 };
 }  // namespace signal
 using signal::RequestType;

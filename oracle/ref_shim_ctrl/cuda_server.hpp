@@ -11,23 +11,15 @@
 
 namespace server {
 
-struct SentSignal {
-    int gpu;
-    int signal;
-    string func;
-};
-inline vector<SentSignal>& sent_signals() {
-    static vector<SentSignal> v;
-    return v;
-}
-
 static sf::safe_ptr<queue<int>> controller_sync_queue;
 
 class CUDAExecutor {
 public:
     CUDAExecutor(int id, size_t, zmq::context_t*) : id_(id) {}
     void start() {}
-    void sig_exec_from_controller(int signal, string& func) { sent_signals().push_back({id_, signal, func}); }
+    void sig_exec_from_controller(int signal, string& func) {
+        torpor_ref_script::state().trace.push_back("S " + std::to_string(id_) + " " + std::to_string(signal) + " " + func);
+    }
 private:
     int id_;
 };

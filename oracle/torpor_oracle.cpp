@@ -594,6 +594,117 @@ struct Sched {
     }
 };
 
+// ---------------------------------------------------------------- request handling (controller.hpp)
+// The controller's loop body (:130-262) with its helpers (:271-294, :392-453), one event per
+// call.  Signals to executors and acknowledgements to the router become lines of a trace:
+// "S <gpu> <signal> <func>" and "A <ack> <resp>".
+struct Ctrl {
+    Sched sched;                                           // executor_status_, model_level_map_, schedule_func_
+    std::unique_ptr<EvictorBase> ev;
+    std::vector<string> running;                           // executor_status_[i].function_
+    std::unordered_map<int, std::pair<int, string>> demand;   // executor_gpu_demand_ (:460)
+    std::list<std::pair<string, bool>> waiting;            // req_queue_ (:466)
+    int cur_id = 0;
+    std::vector<string> trace;
+
+    void send(const string& f, int gpu, int sig) { trace.push_back("S " + std::to_string(gpu) + " " + std::to_string(sig) + " " + f); }
+    void ack(int gpu) { trace.push_back("A 0 " + std::to_string(gpu)); }                    // :432-440
+    void add_info(const string& f, int gpu) { g_repo.dev[gpu][f].status = 0; g_repo.active[f].insert(gpu); }      // model_repo.hpp:82-85
+    void remove_info(const string& f, int gpu) { g_repo.dev[gpu][f].status = 3; g_repo.active[f].erase(gpu); }    // model_repo.hpp:87-90
+
+    int naive() {                                                                            // :271-281
+        for (int i = 0; i < sched.n; ++i) if (sched.status[i] == -1) return i;
+        return -1;
+    }
+    int placement() {                                                                        // :283-294
+        int g = -1;
+        if (sched.status[cur_id] == -1) { g = cur_id; cur_id = (cur_id + 1) % sched.n; }
+        if (g == -1) g = naive();
+        return g;
+    }
+    void check_eviction(int gpu, const string& f) {                                          // :392-400
+        std::vector<string> out = ev->add(gpu, f, g_repo.host[f].total, sched.level);
+        for (auto& v : out) { remove_info(v, gpu); send(v, gpu, 3); }
+    }
+    void send_exec(const string& f, int gpu, int status) {                                   // :402-418
+        if (status == 5) {
+            for (int i = 0; i < sched.n; ++i) {
+                if (i == gpu) { sched.status[i] = 5; running[i] = f; send(f, i, 1); }
+                else send(f, i, 0);
+            }
+        } else {
+            sched.status[gpu] = status; running[gpu] = f; send(f, gpu, 2);
+        }
+    }
+    void send_load(const string& f, int dst, int src) {                                      // :420-427
+        if (src >= 0) { demand.insert({dst, {src, f}}); ev->lock(src, f); }                 // :442-445
+        check_eviction(dst, f);
+        send(f, dst, 4 + 1 + src);
+    }
+    void unlock_src(int dst) {                                                               // :447-453
+        auto it = demand.find(dst);
+        if (it == demand.end()) return;
+        ev->unlock(it->second.first, it->second.second);
+        demand.erase(it);
+    }
+
+    void request(int type, const string& f, const string& payload) {
+        if (type == 0) {                                                                     // ExecuteAfterLoad :141-162
+            sched.level[f] = 1;
+            if (!payload.empty()) { int lv = std::stoi(payload); if (lv >= 0 && lv <= 2) sched.level[f] = lv; }
+            int g = placement();
+            if (g == -1) waiting.push_back({f, true});
+            else { send_exec(f, g, 5); ack(g); }
+        } else if (type == 1) {                                                              // Execute :163-185
+            if (!payload.empty()) {
+                int g = std::stoi(payload);
+                send_load(f, g, -1); send_exec(f, g, Sched::level_to_status(sched.level[f])); ack(g);
+            } else {
+                int d[3]; sched.decide(f, d);
+                if (d[0] == -1) waiting.push_back({f, false});
+                else { send_load(f, d[0], d[1]); send_exec(f, d[0], d[2]); ack(d[0]); }
+            }
+        } else if (type == 3) {                                                              // Unload :186-206
+            if (!payload.empty()) {
+                int g = std::stoi(payload);
+                if (g_repo.active[f].count(g)) { ev->force(g, f); remove_info(f, g); send(f, g, 3); }
+            } else {
+                std::vector<int> gpus(g_repo.active[f].begin(), g_repo.active[f].end());
+                for (int g : gpus) { ev->force(g, f); remove_info(f, g); send(f, g, 3); }
+            }
+            ack(-1);
+        } else if (type == 2) {                                                              // Load :207-214
+            for (int i = 0; i < sched.n; ++i) { send_load(f, i, -1); add_info(f, i); }
+            ack(-1);
+        }
+    }
+    void complete(int id) {                                                                  // :217-262
+        if (sched.status[id] == 5) { add_info(running[id], id); check_eviction(id, running[id]); }
+        else if (sched.status[id] > -1 && sched.status[id] < 5) add_info(running[id], id);
+        unlock_src(id);
+        sched.status[id] = -1;
+        if (!waiting.empty()) {
+            auto next = waiting.front();
+            waiting.pop_front();
+            if (next.second) send_exec(next.first, id, 5);
+            else {
+                int d[3]; sched.decide(next.first, d);
+                if (d[0] != id) { send_load(next.first, id, -1); send_exec(next.first, id, Sched::level_to_status(sched.level[next.first])); }
+                else { send_load(next.first, d[0], d[1]); send_exec(next.first, d[0], d[2]); }
+            }
+            ack(id);
+        }
+    }
+};
+
+int write_trace(std::vector<string>& trace, char* out, int cap) {
+    string joined;
+    for (size_t i = 0; i < trace.size(); ++i) { if (i) joined += "\n"; joined += trace[i]; }
+    trace.clear();
+    if (out && (int)joined.size() + 1 <= cap) memcpy(out, joined.c_str(), joined.size() + 1);
+    return (int)joined.size() + 1;
+}
+
 }  // namespace
 
 // ================================================================= scenario ABI
@@ -742,5 +853,30 @@ void tso_sched_destroy(void* s) { delete (Sched*)s; }
 void tso_sched_set_status(void* s, int gpu, int status) { ((Sched*)s)->status[gpu] = status; }
 void tso_sched_set_level(void* s, const char* f, int level) { ((Sched*)s)->level[f] = level; }
 void tso_sched_decide(void* s, const char* f, int* out3) { ((Sched*)s)->decide(f, out3); }
+
+void* tso_ctrl_create(int n, uint64_t mem_limit_bytes, const char* sched_policy, const char* evict_policy,
+                      const int* pcie_pairs, const int* nvlink) {
+    Ctrl* c = new Ctrl();
+    c->sched.n = n;
+    c->sched.random_policy = sched_policy && string(sched_policy) == "RAND";
+    c->sched.status.assign(n, -1);
+    c->sched.pcie_pairs.assign(pcie_pairs, pcie_pairs + n);
+    c->sched.nvlink.assign(n, std::vector<int>(n, 0));
+    for (int i = 0; i < n; ++i) for (int j = 0; j < n; ++j) c->sched.nvlink[i][j] = nvlink[i * n + j];
+    c->ev.reset((EvictorBase*)tso_evictor_create(evict_policy, n, mem_limit_bytes));
+    c->running.assign(n, string());
+    return c;
+}
+void tso_ctrl_destroy(void* c) { delete (Ctrl*)c; }
+int tso_ctrl_request(void* h, int type, const char* f, const char* payload, char* trace, int cap) {
+    Ctrl* c = (Ctrl*)h;
+    c->request(type, f, payload ? payload : "");
+    return write_trace(c->trace, trace, cap);
+}
+int tso_ctrl_complete(void* h, int executor, char* trace, int cap) {
+    Ctrl* c = (Ctrl*)h;
+    c->complete(executor);
+    return write_trace(c->trace, trace, cap);
+}
 
 }  // extern "C"

@@ -89,6 +89,10 @@ class TsoLib:
             "tso_sched_set_status": (None, [vp, i32, i32]),
             "tso_sched_set_level": (None, [vp, cp, i32]),
             "tso_sched_decide": (None, [vp, cp, C.POINTER(C.c_int)]),
+            "tso_ctrl_create": (vp, [i32, u64, cp, cp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+            "tso_ctrl_destroy": (None, [vp]),
+            "tso_ctrl_request": (i32, [vp, i32, cp, cp, C.c_char_p, i32]),
+            "tso_ctrl_complete": (i32, [vp, i32, C.c_char_p, i32]),
         }
         self.has_scheduler = hasattr(L, "tso_sched_create")   # the restatement only
         if self.has_scheduler:
@@ -114,6 +118,9 @@ class TsoLib:
 
     def scheduler(self, n, policy, pcie_pairs, nvlink) -> "TsoScheduler":
         return TsoScheduler(self, n, policy, pcie_pairs, nvlink)
+
+    def controller(self, n, mem_limit_bytes, sched_policy, evict_policy, pcie_pairs, nvlink) -> "TsoController":
+        return TsoController(self, n, mem_limit_bytes, sched_policy, evict_policy, pcie_pairs, nvlink)
 
     def set_model_status(self, func: str, gpu: int, full: bool) -> None:
         self.lib.tso_set_model_status(func.encode(), gpu, 1 if full else 0)
@@ -210,6 +217,36 @@ class TsoScheduler:
         out = (C.c_int * 3)()
         self.L.tso_sched_decide(self.h, func.encode(), out)
         return out[0], out[1], out[2]
+
+
+class TsoController:
+    """One controller of a checker; ``request`` / ``complete`` return the trace lines of that event."""
+
+    def __init__(self, lib: TsoLib, n, mem_limit_bytes, sched_policy, evict_policy, pcie_pairs, nvlink):
+        self.L = lib.lib
+        pp = (C.c_int * n)(*pcie_pairs)
+        nv = (C.c_int * (n * n))(*[v for row in nvlink for v in row])
+        self.h = self.L.tso_ctrl_create(n, mem_limit_bytes, sched_policy.encode(), evict_policy.encode(), pp, nv)
+        if not self.h:
+            raise ValueError("this checker only knows the reference's 4-GPU topology and whole-GiB limits below 25")
+        self.buf = C.create_string_buffer(1 << 16)
+
+    def close(self):
+        if self.h:
+            self.L.tso_ctrl_destroy(self.h)
+            self.h = None
+
+    def _lines(self, need):
+        if need > len(self.buf):
+            raise RuntimeError("controller trace larger than the buffer")
+        text = self.buf.value.decode()
+        return text.split("\n") if text else []
+
+    def request(self, kind, func, payload=""):
+        return self._lines(self.L.tso_ctrl_request(self.h, kind, func.encode(), payload.encode(), self.buf, len(self.buf)))
+
+    def complete(self, executor):
+        return self._lines(self.L.tso_ctrl_complete(self.h, executor, self.buf, len(self.buf)))
 
 
 class TsoEvictor:

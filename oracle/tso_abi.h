@@ -98,6 +98,22 @@ void tso_sched_set_status(void* s, int gpu, int status);
 void tso_sched_set_level(void* s, const char* func, int level);
 void tso_sched_decide(void* s, const char* func, int* out3);
 
+/* The controller's handling of one router request or one executor completion
+ * (include/server/controller.hpp:130-262).  The reference checker runs the reference's own loop
+ * for exactly one event on its Controller object (the socket stand-in feeds the event and ends
+ * the loop); it accepts 4 GPUs with the tables of :116-118 and a whole number of GiB below 25
+ * (MEM_LIMIT_IN_GB, :84-91), else NULL.  `trace` receives what was sent while handling the
+ * event, one line each, in order: "S <gpu> <signal> <func>" for a signal to an executor and
+ * "A <ack> <resp>" for the acknowledgement to the router; the return value is the size the text
+ * needs including its terminator.  Model sizes and replicas are those of the checker's
+ * repository (tso_malloc under tso_track_begin; tso_set_model_status).  Function names must not
+ * contain blanks. */
+void* tso_ctrl_create(int n, uint64_t mem_limit_bytes, const char* sched_policy, const char* evict_policy,
+                      const int* pcie_pairs, const int* nvlink);
+void tso_ctrl_destroy(void* c);
+int tso_ctrl_request(void* c, int type, const char* func, const char* payload, char* trace, int cap);
+int tso_ctrl_complete(void* c, int executor, char* trace, int cap);
+
 const char* tso_impl_name(void);
 
 #ifdef __cplusplus

@@ -67,6 +67,8 @@ class IpcRegion(C.Structure):
 
 # Every symbol include/torpor_swap.h declares: name -> (restype, argtypes)
 _u64, _i32, _i64, _vp, _cp = C.c_uint64, C.c_int, C.c_int64, C.c_void_p, C.c_char_p
+SIGNAL_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_int, C.c_int, C.c_char_p)    # tsw_signal_fn
+ACK_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_int, C.c_int)                    # tsw_ack_fn
 _pu64 = C.POINTER(C.c_uint64)
 SIGNATURES = {
     "tsw_config_default": (None, [C.POINTER(Config)]),
@@ -130,6 +132,13 @@ SIGNATURES = {
     "tsw_sched_set_status": (_i32, [_vp, _i32, _i32]),
     "tsw_sched_set_level": (_i32, [_vp, _cp, _i32]),
     "tsw_sched_decide": (_i32, [_vp, _cp, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "tsw_ctrl_create": (_i32, [_i32, _u64, _cp, _cp, C.POINTER(C.c_int), C.POINTER(C.c_int), SIGNAL_FN, ACK_FN, _vp,
+                               C.POINTER(_vp)]),
+    "tsw_ctrl_destroy": (_i32, [_vp]),
+    "tsw_ctrl_request": (_i32, [_vp, _i32, _cp, _cp]),
+    "tsw_ctrl_complete": (_i32, [_vp, _i32]),
+    "tsw_ctrl_executor_status": (_i32, [_vp, _i32, C.POINTER(C.c_int), C.c_char_p, _i32]),
+    "tsw_ctrl_queue_depth": (_i32, [_vp]),
 }
 
 _lib = None

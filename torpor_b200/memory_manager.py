@@ -392,6 +392,60 @@ class Scheduler:
         return g.value, s.value, st.value
 
 
+# RequestType (proto/signal.proto) and ExecutorSignal_* (common/include/utils.hpp:70-74)
+REQ_EXECUTE_AFTER_LOAD, REQ_EXECUTE, REQ_LOAD, REQ_UNLOAD = 0, 1, 2, 3
+SIGNAL_NOTIFY, SIGNAL_STARTUP, SIGNAL_EXECUTE, SIGNAL_UNLOAD, SIGNAL_LOAD = 0, 1, 2, 3, 4
+
+
+class Controller:
+    """Request and completion handling of the controller (include/server/controller.hpp:130-262,
+    392-453) over the library's scheduler and eviction policy.
+
+    ``request`` and ``complete`` return what the reference would have sent while handling that
+    event, in its order: ``("S", gpu, signal, func)`` for a signal to an executor (a load is
+    ``SIGNAL_LOAD + 1 + src_gpu``) and ``("A", ack, resp)`` for the acknowledgement to the router.
+    """
+
+    def __init__(self, gpu_count: int, mem_limit_bytes: int, schedule_policy: str = "IA", evict_policy: str = "IA",
+                 pcie_pairs=None, nvlink=None):
+        self.L = _cabi.lib()
+        self.n = gpu_count
+        self._events: List[tuple] = []
+        self._on_signal = _cabi.SIGNAL_FN(lambda user, gpu, sig, func: self._events.append(("S", gpu, sig, func.decode())))
+        self._on_ack = _cabi.ACK_FN(lambda user, ack, resp: self._events.append(("A", ack, resp)))
+        pp = (C.c_int * gpu_count)(*pcie_pairs) if pcie_pairs is not None else None
+        nv = (C.c_int * (gpu_count * gpu_count))(*[v for row in nvlink for v in row]) if nvlink is not None else None
+        h = C.c_void_p()
+        check(self.L.tsw_ctrl_create(gpu_count, mem_limit_bytes, schedule_policy.encode(), evict_policy.encode(), pp, nv,
+                                     self._on_signal, self._on_ack, None, C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if self.h:
+            self.L.tsw_ctrl_destroy(self.h)
+            self.h = None
+
+    def _drain(self, rc: int) -> List[tuple]:
+        out, self._events = self._events, []
+        check(rc)
+        return out
+
+    def request(self, kind: int, func: str, payload: str = "") -> List[tuple]:
+        return self._drain(self.L.tsw_ctrl_request(self.h, kind, func.encode(), payload.encode()))
+
+    def complete(self, executor: int) -> List[tuple]:
+        return self._drain(self.L.tsw_ctrl_complete(self.h, executor))
+
+    def executor_status(self, gpu: int):
+        st = C.c_int()
+        buf = C.create_string_buffer(512)
+        check(self.L.tsw_ctrl_executor_status(self.h, gpu, C.byref(st), buf, 512))
+        return st.value, buf.value.decode()
+
+    def queue_depth(self) -> int:
+        return check(self.L.tsw_ctrl_queue_depth(self.h))
+
+
 def checksum_host(data: np.ndarray) -> np.ndarray:
     """The checksum of ``tsw_checksum_resident`` computed with numpy on host bytes."""
     b = np.ascontiguousarray(data).view(np.uint8).reshape(-1)

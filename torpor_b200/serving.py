@@ -1,9 +1,10 @@
 """Controller-level replay of a serverless request stream over the swap engines.
 
-Drives the swap path the way Torpor's controller does for every request
-(include/server/controller.hpp:163-262,392-453): ask the scheduler for a GPU and a source,
-pin the source replica, let the eviction policy make room (victims are unloaded first),
-signal the load, run, and on completion register the new replica and release the pin.
+Every request goes through the library's controller (``tsw_ctrl_*``, the request handling of
+include/server/controller.hpp:130-262,392-453): it asks the scheduler for a GPU and a source,
+pins the source replica, lets the eviction policy make room (victims are unloaded first) and
+signals the load; on completion it registers the new replica, releases the pin and serves its
+queue.  This module is the executor side: it carries those signals out on real engines.
 Swap-ins are asynchronous (``tsw_swap_in`` returns once the kernel is enqueued), so swaps on
 different GPUs overlap for real and compete for PCIe / NVLink as they would in service.
 Requests arrive on the wall clock (optionally compressed by ``speedup``); the client's
@@ -24,8 +25,8 @@ from typing import Dict, List, Optional
 import numpy as np
 
 from . import workloads as W
-from .memory_manager import (Evictor, MemoryManager, ModelRepo, Scheduler, SwapError, repo_reset,
-                             STATUS_AVAIL, STATUS_RUN_COLD_START, STATUS_RUN_LOCAL, STATUS_RUN_NVLINK)
+from .memory_manager import (Controller, MemoryManager, repo_reset, REQ_EXECUTE, REQ_EXECUTE_AFTER_LOAD,
+                             SIGNAL_EXECUTE, SIGNAL_LOAD, SIGNAL_STARTUP, SIGNAL_UNLOAD)
 
 # GPU occupancy per request once the weights are there (ms).  Stand-ins for the client's
 # inference, in the range the reference's own node simulator uses (misc/tools/node_simu.py:98-99).
@@ -36,78 +37,78 @@ LEVEL = {"resnet50": 0, "bert_tiny": 0, "bert_base": 1, "vgg19": 1, "llama_tiny"
 
 
 class SwapServer:
+    """N engines under the library's controller (``tsw_ctrl_*``): this class only carries out the
+    signals the controller sends -- unload, load (from the host store or a replica), execute -- on
+    real engines, and reports completions back, as the reference's executors do
+    (include/server/cuda_server.hpp:243-300)."""
+
     def __init__(self, n_gpus: int, cap_bytes: int, evict_policy: str = "LRU", sched_policy: str = "IA",
-                 devices: Optional[List[int]] = None, host_arena_bytes: int = 0):
+                 devices: Optional[List[int]] = None, host_arena_bytes: int = 0, pcie_pairs=None, nvlink=None):
         self.n = n_gpus
         self.devices = devices or list(range(n_gpus))
         self.engines = [MemoryManager(cap_bytes, device=self.devices[g], server_id=g, gpu_count=n_gpus,
                                       host_arena_bytes=host_arena_bytes if g == 0 else 0)
                         for g in range(n_gpus)]
-        self.evictor = Evictor(evict_policy, n_gpus, cap_bytes)
-        self.sched = Scheduler(n_gpus, sched_policy)
+        self.ctrl = Controller(n_gpus, cap_bytes, sched_policy, evict_policy, pcie_pairs, nvlink)
         self.arch: Dict[str, str] = {}
         self.nbytes: Dict[str, int] = {}
         self.state = [dict(kind="idle") for _ in range(n_gpus)]
-        self.demand: Dict[int, tuple] = {}          # dst gpu -> (src gpu, func): executor_gpu_demand_
-        self.queue = collections.deque()
+        self.pending = [None] * n_gpus              # a load signalled to GPU g, waiting for its execute signal
+        self.arrivals = collections.deque()         # arrival times of queued requests, in the controller's FIFO order
         self.swaps: List[dict] = []
         self.evictions = 0
         self.local_hits = 0
         self.completed = 0
-        self.next_cold = 0
 
     def close(self):
         for e in self.engines:
             e.close()
-        self.evictor.close()
-        self.sched.close()
+        self.ctrl.close()
         repo_reset()
 
-    # ---- ExecuteAfterLoad (controller.hpp:141-162, 223-227): load once, anywhere
+    # ---- ExecuteAfterLoad (controller.hpp:141-162, 223-227): round-robin placement, load once
     def cold_start(self, func: str, arch: str, seed: int, tensor_data=None):
         ws = W.weight_set(arch, seed=seed)
-        g = self.next_cold % self.n                                   # round-robin placement (:283-294)
-        self.next_cold += 1
         self.arch[func], self.nbytes[func] = arch, ws.nbytes
-        self.sched.set_level(func, LEVEL.get(arch, 1))
+        events = self.ctrl.request(REQ_EXECUTE_AFTER_LOAD, func, str(LEVEL.get(arch, 1)))
+        g = next(e[1] for e in events if e[0] == "S" and e[2] == SIGNAL_STARTUP)   # every GPU is idle at this point
         W.cold_start(self.engines[g], func, ws, tensor_data=tensor_data)
-        ModelRepo.add_model_info(func, g)
-        for v in self._make_room(g, func):
-            self._unload(v, g)
+        self._carry_out(self.ctrl.complete(g), time.perf_counter())      # registers the replica; may unload others
 
-    def _make_room(self, g: int, func: str) -> List[str]:               # check_eviction (:392-400)
-        return self.evictor.check_and_add(g, func, ModelRepo.total_size(func), LEVEL.get(self.arch[func], 1))
-
-    def _unload(self, func: str, g: int):
-        ModelRepo.remove_model_info(func, g)
-        self.engines[g].evict(func)
-        self.evictions += 1
+    def _carry_out(self, events, t_arrival):
+        """Executor side of the signals of one controller event."""
+        for e in events:
+            if e[0] != "S":
+                continue
+            _, g, sig, func = e
+            if sig == SIGNAL_UNLOAD:
+                self.engines[g].evict(func)
+                self.evictions += 1
+            elif sig >= SIGNAL_LOAD:
+                src = sig - SIGNAL_LOAD - 1
+                if self.engines[g].check_alloc(func):                    # resident: nothing to move (cuda_server.hpp:246)
+                    self.pending[g] = None
+                else:
+                    self.pending[g] = dict(src=src, t_signal=time.perf_counter())
+                    self.engines[g].swap_in(func, src)                   # asynchronous: kernel enqueued
+            elif sig == SIGNAL_EXECUTE:
+                st = dict(func=func, t_arrival=t_arrival)
+                if self.pending[g] is None:
+                    self.local_hits += 1
+                    st.update(kind="exec", until=time.perf_counter() + EXEC_MS.get(self.arch[func], 10.0) / 1e3)
+                else:
+                    st.update(kind="swap", **self.pending[g])
+                    self.pending[g] = None
+                self.state[g] = st
 
     # ---- Execute (controller.hpp:163-185)
     def submit(self, func: str, now: float) -> bool:
-        g, src, status = self.sched.decide(func)
-        if g < 0:
-            self.queue.append((func, now))
+        events = self.ctrl.request(REQ_EXECUTE, func)
+        if not events:                                   # every GPU busy, or pinned replicas in the way: the controller queued it
+            self.arrivals.append(now)
             return False
-        self._start(func, g, src, status, now)
+        self._carry_out(events, now)
         return True
-
-    def _start(self, func: str, g: int, src: int, status: int, t_arrival: float):
-        self.sched.set_status(g, status)
-        st = dict(kind="exec", func=func, t_arrival=t_arrival)
-        if status == STATUS_RUN_LOCAL:
-            self.local_hits += 1
-            self.evictor.check_and_add(g, func, ModelRepo.total_size(func), LEVEL.get(self.arch[func], 1))  # refresh recency
-            st["until"] = time.perf_counter() + EXEC_MS.get(self.arch[func], 10.0) / 1e3
-        else:
-            if src >= 0:                                               # lock_src_func (:437-440)
-                self.demand[g] = (src, func)
-                self.evictor.lock(src, func)
-            for v in self._make_room(g, func):                         # victims go first (:394-399)
-                self._unload(v, g)
-            st.update(kind="swap", t_signal=time.perf_counter(), src=src)
-            self.engines[g].swap_in(func, src)                         # asynchronous: kernel enqueued
-        self.state[g] = st
 
     def poll(self):
         """Advance every GPU: finished swaps start executing, finished executions complete."""
@@ -120,25 +121,14 @@ class SwapServer:
                 st["kind"] = "exec"
                 st["until"] = now + EXEC_MS.get(self.arch[st["func"]], 10.0) / 1e3
             if st["kind"] == "exec" and now >= st["until"]:
-                func = st["func"]
-                ModelRepo.add_model_info(func, g)                      # completion (:223-230)
-                if g in self.demand:                                   # unlock_src_func (:442-447)
-                    s, f = self.demand.pop(g)
-                    self.evictor.unlock(s, f)
-                self.sched.set_status(g, STATUS_AVAIL)
                 self.state[g] = dict(kind="idle")
                 self.completed += 1
-                if self.queue:                                         # queued request takes the freed GPU (:242-262)
-                    qf, qt = self.queue.popleft()
-                    g2, src, status = self.sched.decide(qf)
-                    if g2 != g:
-                        src, status = -1, 2 + LEVEL.get(self.arch[qf], 1)
-                        if g in ModelRepo.active_devices(qf):
-                            status = STATUS_RUN_LOCAL
-                    self._start(qf, g, src, status, qt)
+                events = self.ctrl.complete(g)                           # replica registered, pin released, queue served
+                started = any(e[0] == "S" and e[2] == SIGNAL_EXECUTE for e in events)
+                self._carry_out(events, self.arrivals.popleft() if started and self.arrivals else now)
 
     def busy(self) -> bool:
-        return any(st["kind"] != "idle" for st in self.state) or bool(self.queue)
+        return any(st["kind"] != "idle" for st in self.state) or self.ctrl.queue_depth() > 0
 
 
 def run_stream(n_gpus: int, n_models: int, rate: float, duration_s: float, cap_bytes: int, seed: int = 4,
