@@ -124,25 +124,41 @@ def run_reference(args, quiet=False):
     except Exception:
         pass
     if tso.available("ref_cuda") and have_gpu:
-        kind, lib, io_threads = "reference", tso.load("ref_cuda"), max(1, ncpu)
+        kind, lib, io_threads = "reference", tso.load("ref_cuda"), (args.ref_io_threads or max(1, ncpu))
         what = "reference headers (memory_manager.hpp:213-449) + CUDA runtime"
     else:
         kind, lib, io_threads = "port", tso.load("oracle"), 1
         what = "CPU restatement (oracle/torpor_oracle.cpp), host memcpy into the block layout"
     ws = W.weight_set(args.ref_sample)
     lib.reset_world()
-    m = lib.manager(budget=0, io_threads=io_threads)
+    src = args.ref_src_gpu
     pool, data = generate_tensors(ws, min(ncpu, 16))
-    W.cold_start(m, "ref", ws, tensor_data=data)
+    if src >= 0:
+        # the reference's replica swap (memory_manager.hpp:394-396): the model is resident on GPU `src`,
+        # GPU 0 copies it parameter by parameter with cudaMemcpyPeerAsync
+        if kind != "reference":
+            return {"impl": "reference", "unavailable": "the replica-swap baseline needs the reference library and two GPUs"}
+        pairs = lib.enable_peer_access(src + 1)          # as the controller does at start-up (controller.hpp:63-75)
+        what += f"; peer access enabled for {pairs} directed pairs"
+        holder = lib.manager(server_id=src, budget=0, gpu_count=src + 1, io_threads=io_threads)
+        m = lib.manager(server_id=0, budget=0, gpu_count=src + 1, io_threads=io_threads)
+        W.cold_start(holder, "ref", ws, tensor_data=data)
+        lib.set_model_status("ref", src, True)
+        what += f"; replica swap from GPU {src} (cudaMemcpyPeerAsync per parameter)"
+    else:
+        m = lib.manager(budget=0, io_threads=io_threads)
+        W.cold_start(m, "ref", ws, tensor_data=data)
+        m.evict("ref")
     pool.shutdown()
-    m.evict("ref")
     for _ in range(args.warmup):
-        m.swap_in_timed("ref"); m.evict("ref")
-    t_sig = []
+        m.swap_in_timed("ref", src); m.evict("ref")
+    t_sig, t_evict = [], []
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        t_sig.append(m.swap_in_timed("ref"))
+        t_sig.append(m.swap_in_timed("ref", src))
+        te = time.perf_counter()
         m.evict("ref")
+        t_evict.append((time.perf_counter() - te) * 1e6)
     wall = time.perf_counter() - t0
     gbs = ws.nbytes * args.steps / wall / 1e9
     cores = io_threads + 1 if kind == "reference" else 1
@@ -156,10 +172,84 @@ def run_reference(args, quiet=False):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": workload_config(args, args.gpus),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample,
-                         "host_cores": ncpu, "signal_to_ready_ms_median": statistics.median(t_sig) / 1e3},
+                         "host_cores": ncpu, "signal_to_ready_ms_median": statistics.median(t_sig) / 1e3,
+                         "signal_to_ready_gbs": ws.nbytes / (statistics.median(t_sig) / 1e6) / 1e9,
+                         "swap_out_metadata_only_us_median": statistics.median(t_evict)},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     return line
+
+
+def run_baselines(args):
+    """Reported baselines around the path, each reference run in its own process (the reference's
+    threads cannot be joined): swap-in with the reference's default IO_THREAD_NUM=4 and with one
+    staging thread per host core, its replica swap over cudaMemcpyPeerAsync when a second GPU is
+    there, its metadata-only swap-out, and plain copy-engine rates of this box."""
+    import torch
+    ncpu = os.cpu_count() or 1
+    me = os.path.abspath(__file__)
+
+    def ref(*extra):
+        r = subprocess.run([sys.executable, me, "--impl", "reference", "--steps", str(args.steps), "--warmup",
+                            str(args.warmup), "--ref-sample", args.ref_sample, "--workload", args.workload, *extra],
+                           stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)
+        for ln in r.stdout.splitlines():
+            if ln.startswith("{"):
+                d = json.loads(ln)
+                return d.get("cpu_baseline", d)
+        return {"failed": r.stderr[-300:]}
+
+    out = {"host_cores": ncpu, "gpus": torch.cuda.device_count(), "sample": args.ref_sample,
+           "reference_swap_in_io4": ref("--ref-io-threads", "4"),
+           "reference_swap_in_io_all": ref("--ref-io-threads", str(ncpu))}
+    nbytes = 1 << 30
+    host = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    dev0 = torch.empty(nbytes, dtype=torch.uint8, device="cuda:0")
+
+    def timed(fn, dev=0, reps=5):
+        torch.cuda.synchronize(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()
+        with torch.cuda.device(dev):
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+        torch.cuda.synchronize(dev)
+        return nbytes * reps / (a.elapsed_time(b) / 1e3) / 1e9
+
+    out["copy_engine_h2d_pinned_gbs"] = timed(lambda: dev0.copy_(host, non_blocking=True))
+    out["copy_engine_d2h_pinned_gbs"] = timed(lambda: host.copy_(dev0, non_blocking=True))
+    if torch.cuda.device_count() >= 2:
+        out["reference_replica_swap"] = ref("--ref-src-gpu", "1")
+        dev1 = torch.empty(nbytes, dtype=torch.uint8, device="cuda:1")
+        out["copy_engine_peer_gbs"] = timed(lambda: dev0.copy_(dev1, non_blocking=True))
+        del dev1
+        # the same replica swap through this library: GPU 0 places the model from GPU 1's pool over NVLink
+        from torpor_b200 import workloads as W
+        from torpor_b200.memory_manager import MemoryManager, ModelRepo, repo_reset
+        ws = W.weight_set(args.ref_sample)
+        repo_reset()
+        holder = MemoryManager(W.pool_budget_for(ws), device=1, server_id=1, gpu_count=2, host_arena_bytes=W.host_store_bytes(ws))
+        target = MemoryManager(W.pool_budget_for(ws), device=0, server_id=0, gpu_count=2)
+        pool, data = generate_tensors(ws, min(ncpu, 16))
+        W.cold_start(holder, "m", ws, tensor_data=data)
+        pool.shutdown()
+        ModelRepo.add_model_info("m", 1)
+        wall, dev = [], []
+        for it in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            target.swap_in("m", 1); target.wait_ready("m")
+            if it >= args.warmup:
+                wall.append(time.perf_counter() - t0)
+                dev.append(target.stats()["last_swap_device_ns"] / 1e9)
+            target.evict("m")
+        out["ours_replica_swap"] = {"signal_to_ready_gbs": ws.nbytes / statistics.median(wall) / 1e9,
+                                    "signal_to_ready_ms_median": statistics.median(wall) * 1e3,
+                                    "kernel_gbs": ws.nbytes / statistics.median(dev) / 1e9,
+                                    "what": "tsw_swap_in(func, src_gpu=1) + tsw_wait_ready on GPU 0: place_kernel reads GPU 1's pool over NVLink"}
+        target.close(); holder.close(); repo_reset()
+    return {"baselines": out}
 
 
 def workload_config(args, n):
@@ -320,10 +410,20 @@ def main():
     ap.add_argument("--workload", default="llama2_7b")
     ap.add_argument("--ref-sample", default="llama_mid")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ref-io-threads", type=int, default=0, help="IO_THREAD_NUM of the reference arm (0 = host cores)")
+    ap.add_argument("--ref-src-gpu", type=int, default=-1, help="reference arm: swap from a replica on this GPU instead of the host store")
+    ap.add_argument("--baselines", action="store_true",
+                    help="print the reported baselines around the path (reference with its default 4 and with all "
+                         "staging threads, its replica swap, copy-engine rates) as one JSON line; not the contract line")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.baselines:
+        if rank == 0:
+            print(json.dumps(run_baselines(args)), flush=True)
+        return 0
 
     if args.impl == "reference":
         if rank != 0:

@@ -360,6 +360,31 @@ void tso_evictor_force_evict(void* ev, int gpu, const char* func) { string f(fun
 void tso_evictor_lock(void* ev, int gpu, const char* func) { string f(func); ((EvictorHandle*)ev)->ev->lock(gpu, f); }
 void tso_evictor_unlock(void* ev, int gpu, const char* func) { string f(func); ((EvictorHandle*)ev)->ev->unlock(gpu, f); }
 
+// All-pairs peer access, which the reference's controller switches on at start-up for the process
+// that holds every manager (controller.hpp:63-75); without it a peer copy is staged through the host.
+int tso_enable_peer_access(int gpu_count) {
+#ifdef TORPOR_REF_FAKE_CUDA
+    (void)gpu_count;
+    return 0;
+#else
+    int enabled = 0;
+    for (int i = 0; i < gpu_count; ++i) {
+        cudaSetDevice(i);
+        for (int j = 0; j < gpu_count; ++j) {
+            if (i == j) continue;
+            int able = 0;
+            cudaDeviceCanAccessPeer(&able, i, j);
+            if (able) {
+                cudaError_t err = cudaDeviceEnablePeerAccess(j, 0);
+                if (err == cudaSuccess || err == cudaErrorPeerAccessAlreadyEnabled) ++enabled;
+                cudaGetLastError();
+            }
+        }
+    }
+    return enabled;
+#endif
+}
+
 // ---------------------------------------------------------------- controller decisions
 #ifdef TORPOR_REF_WITH_CONTROLLER
 // The reference's Controller object itself (include/server/controller.hpp), built on a 4-GPU

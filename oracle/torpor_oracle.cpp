@@ -838,6 +838,8 @@ void tso_evictor_force_evict(void* e, int g, const char* f) { ((EvictorBase*)e)-
 void tso_evictor_lock(void* e, int g, const char* f) { ((EvictorBase*)e)->lock(g, f); }
 void tso_evictor_unlock(void* e, int g, const char* f) { ((EvictorBase*)e)->unlock(g, f); }
 
+int tso_enable_peer_access(int) { return 0; }   // no devices here
+
 // The controller's decision functions as restated above; any number of GPUs, tables as inputs.
 void* tso_sched_create(int n, const char* policy, const int* pcie_pairs, const int* nvlink) {
     Sched* s = new Sched();

@@ -82,6 +82,7 @@ class TsoLib:
             "tso_evictor_lock": (None, [vp, i32, cp]),
             "tso_evictor_unlock": (None, [vp, i32, cp]),
             "tso_impl_name": (cp, []),
+            "tso_enable_peer_access": (i32, [i32]),
         }
         sched = {
             "tso_sched_create": (vp, [i32, cp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
@@ -121,6 +122,9 @@ class TsoLib:
 
     def controller(self, n, mem_limit_bytes, sched_policy, evict_policy, pcie_pairs, nvlink) -> "TsoController":
         return TsoController(self, n, mem_limit_bytes, sched_policy, evict_policy, pcie_pairs, nvlink)
+
+    def enable_peer_access(self, gpu_count: int) -> int:
+        return self.lib.tso_enable_peer_access(gpu_count)
 
     def set_model_status(self, func: str, gpu: int, full: bool) -> None:
         self.lib.tso_set_model_status(func.encode(), gpu, 1 if full else 0)

@@ -87,6 +87,10 @@ void tso_evictor_force_evict(void* e, int gpu, const char* func);
 void tso_evictor_lock(void* e, int gpu, const char* func);
 void tso_evictor_unlock(void* e, int gpu, const char* func);
 
+/* All-pairs peer access as the controller enables it at start-up (controller.hpp:63-75); returns the
+ * number of directed pairs enabled (0 without real devices). */
+int tso_enable_peer_access(int gpu_count);
+
 /* Swap decision of the controller (include/server/controller.hpp:296-389).  The reference
  * checker answers with the reference's own Controller object (controller.hpp compiled where
  * it lies, zmq / executor headers shadowed) and only accepts the 4-GPU tables hard-coded there
