@@ -279,6 +279,13 @@ int tsw_sched_destroy(tsw_scheduler* s);
 int tsw_sched_set_status(tsw_scheduler* s, int gpu, int status);
 int tsw_sched_set_level(tsw_scheduler* s, const char* func, int level);
 int tsw_sched_decide(tsw_scheduler* s, const char* func, int* gpu, int* src_gpu, int* status);
+/* 1-link or k-link swap-in: the GPUs that can lend their PCIe link to a swap-in of `dst` from the
+ * host store right now (helpers for tsw_swap_in_sharded); returns their number.  Read from the same
+ * occupancy signal the reference's scheduler uses to pick a GPU (status RunPcie* / RunColdStart =
+ * link busy, :379-385): available GPUs (with include_running, also GPUs that run in place or swap
+ * over NVLink), minus those whose uplink sibling (pcie_pairs) is dst, is loading, or already lends.
+ * No reference counterpart: the reference always uses one link per swap. */
+int tsw_sched_helpers(tsw_scheduler* s, int dst, int include_running, int* helpers, int cap);
 
 /* Request handling around a swap: what the controller does with each router request and each
  * executor completion (controller.hpp:130-262) on top of the scheduler and the eviction
@@ -319,6 +326,7 @@ int tsw_ctrl_request(tsw_controller* c, int type, const char* func, const char* 
 int tsw_ctrl_complete(tsw_controller* c, int executor);    /* the executor's "done" on controller_sync_queue */
 int tsw_ctrl_executor_status(tsw_controller* c, int gpu, int* status, char* func, int cap);
 int tsw_ctrl_queue_depth(tsw_controller* c);
+int tsw_ctrl_helpers(tsw_controller* c, int dst, int include_running, int* helpers, int cap);  /* tsw_sched_helpers on its scheduler */
 
 #ifdef __cplusplus
 }

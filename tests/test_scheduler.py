@@ -10,6 +10,7 @@ import pytest
 
 import scenarios
 import scheduler_cases as SC
+from scheduler_cases import nvswitch
 from torpor_b200.memory_manager import ModelRepo, Scheduler, repo_reset
 
 
@@ -77,4 +78,23 @@ def test_defaults_describe_an_nvswitch_box(built):
     for g in range(8):
         s.set_status(g, 3)
     assert s.decide("f") == (-1, -1, -1)                # nothing available: the caller queues
+    s.close(); repo_reset()
+
+
+def test_link_lending_reads_the_same_occupancy_signal(built):
+    """Helpers for a swap-in over several PCIe links: available GPUs whose uplink is not shared with
+    the target, with a loading GPU or with another helper."""
+    repo_reset()
+    s = Scheduler(8)                                     # default table: GPU i shares its uplink with i^1
+    assert s.helpers(0) == [2, 4, 6]                     # 1 shares the target's uplink; 3, 5, 7 share a helper's
+    s.set_status(3, 3)                                   # GPU 3 loads over PCIe: its sibling 2 would add nothing
+    assert s.helpers(0) == [4, 6]
+    s.set_status(4, 0)                                   # GPU 4 runs in place: busy, but its link is idle
+    assert s.helpers(0) == [5, 6] and s.helpers(0, include_running=True) == [4, 6]
+    s.close()
+    own = list(range(8))                                 # every GPU has its uplink alone
+    s = Scheduler(8, "IA", own, nvswitch(8)[1])
+    assert s.helpers(2) == [0, 1, 3, 4, 5, 6, 7]
+    s.set_status(5, 4); s.set_status(6, 1)
+    assert s.helpers(2) == [0, 1, 3, 4, 7] and s.helpers(2, include_running=True) == [0, 1, 3, 4, 6, 7]
     s.close(); repo_reset()

@@ -42,3 +42,15 @@ def test_engines_and_repository_agree_after_churn(built):
         for g in range(3):
             assert srv.engines[g].check_alloc(f"fn{i}") == (g in homes), (i, g, homes)
     srv.close()
+
+
+def test_large_host_swaps_borrow_idle_links(built):
+    repo_reset()
+    kw = dict(n_gpus=4, n_models=10, rate=300.0, duration_s=1.0, cap_bytes=300 << 20, seed=4,
+              archs=("bert_tiny", "llama_tiny", "resnet50"), devices=[-1] * 4, zero_weights=True,
+              pcie_pairs=[0, 1, 2, 3], nvlink=[[0 if i == j else 2 for j in range(4)] for i in range(4)])
+    one = serving.run_stream(**kw)
+    many = serving.run_stream(shard_min_bytes=50 << 20, **kw)
+    assert one["host_swaps_over_several_links"] == 0 and one["links_per_host_swap_mean"] == 1.0
+    assert many["completed"] == many["requests"] == one["requests"]
+    assert many["host_swaps_over_several_links"] > 5 and 1.0 < many["links_per_host_swap_mean"] <= 4.0

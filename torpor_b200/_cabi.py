@@ -132,6 +132,8 @@ SIGNATURES = {
     "tsw_sched_set_status": (_i32, [_vp, _i32, _i32]),
     "tsw_sched_set_level": (_i32, [_vp, _cp, _i32]),
     "tsw_sched_decide": (_i32, [_vp, _cp, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "tsw_sched_helpers": (_i32, [_vp, _i32, _i32, C.POINTER(C.c_int), _i32]),
+    "tsw_ctrl_helpers": (_i32, [_vp, _i32, _i32, C.POINTER(C.c_int), _i32]),
     "tsw_ctrl_create": (_i32, [_i32, _u64, _cp, _cp, C.POINTER(C.c_int), C.POINTER(C.c_int), SIGNAL_FN, ACK_FN, _vp,
                                C.POINTER(_vp)]),
     "tsw_ctrl_destroy": (_i32, [_vp]),

@@ -352,6 +352,30 @@ int tsw_sched_decide(tsw_scheduler* s, const char* func, int* gpu, int* src_gpu,
     return TSW_OK;
 }
 
+// GPUs whose PCIe link carries no swap right now and could lend it to a swap-in of `dst` from
+// the host store (tsw_swap_in_sharded).  The signal is the one interference_aware_schedule reads
+// (:379-385): an executor status of RunPcie* or RunColdStart means "link busy".  A GPU is left
+// out when the GPU it shares an uplink with (pcie_pairs) is `dst`, is loading over PCIe itself,
+// or has already been picked -- two GPUs behind one uplink move no more than one.
+int tsw_sched_helpers(tsw_scheduler* s, int dst, int include_running, int* helpers, int cap) {
+    if (!s || dst < 0 || dst >= s->n || (cap > 0 && !helpers)) return tsw::fail(TSW_ERR_INVALID, "bad scheduler arguments");
+    auto link_busy = [&](int g) { return s->status[g] >= kRunPcieLight; };
+    std::vector<char> taken(s->n, 0);
+    taken[dst] = 1;
+    int n = 0;
+    for (int g = 0; g < s->n; ++g) {
+        if (g == dst) continue;
+        const bool idle = s->status[g] == kAvail || (include_running && !link_busy(g));
+        if (!idle) continue;
+        const int sib = s->pcie_pair[g];
+        if (sib != g && (taken[sib] || link_busy(sib))) continue;
+        taken[g] = 1;
+        if (n < cap) helpers[n] = g;
+        ++n;
+    }
+    return n;
+}
+
 }  // extern "C"
 
 // =====================================================================================
@@ -624,6 +648,11 @@ int tsw_ctrl_executor_status(tsw_controller* c, int gpu, int* status, char* func
         memcpy(func, f.c_str(), f.size() + 1);
     }
     return TSW_OK;
+}
+
+int tsw_ctrl_helpers(tsw_controller* c, int dst, int include_running, int* helpers, int cap) {
+    if (!c) return tsw::fail(TSW_ERR_INVALID, "bad controller arguments");
+    return tsw_sched_helpers(c->sched, dst, include_running, helpers, cap);
 }
 
 int tsw_ctrl_queue_depth(tsw_controller* c) {

@@ -386,6 +386,12 @@ class Scheduler:
     def set_status(self, gpu: int, status: int): check(self.L.tsw_sched_set_status(self.h, gpu, status))
     def set_level(self, func: str, level: int): check(self.L.tsw_sched_set_level(self.h, func.encode(), level))
 
+    def helpers(self, dst: int, include_running: bool = False) -> List[int]:
+        """GPUs whose PCIe link is free to help a swap-in of ``dst`` from the host store."""
+        buf = (C.c_int * 64)()
+        n = check(self.L.tsw_sched_helpers(self.h, dst, 1 if include_running else 0, buf, 64))
+        return list(buf[:min(n, 64)])
+
     def decide(self, func: str):
         g, s, st = C.c_int(), C.c_int(), C.c_int()
         check(self.L.tsw_sched_decide(self.h, func.encode(), C.byref(g), C.byref(s), C.byref(st)))
@@ -444,6 +450,12 @@ class Controller:
 
     def queue_depth(self) -> int:
         return check(self.L.tsw_ctrl_queue_depth(self.h))
+
+    def helpers(self, dst: int, include_running: bool = False) -> List[int]:
+        """GPUs whose PCIe link is free to help a swap-in of ``dst`` from the host store."""
+        buf = (C.c_int * 64)()
+        n = check(self.L.tsw_ctrl_helpers(self.h, dst, 1 if include_running else 0, buf, 64))
+        return list(buf[:min(n, 64)])
 
 
 def checksum_host(data: np.ndarray) -> np.ndarray:

@@ -43,7 +43,8 @@ class SwapServer:
     (include/server/cuda_server.hpp:243-300)."""
 
     def __init__(self, n_gpus: int, cap_bytes: int, evict_policy: str = "LRU", sched_policy: str = "IA",
-                 devices: Optional[List[int]] = None, host_arena_bytes: int = 0, pcie_pairs=None, nvlink=None):
+                 devices: Optional[List[int]] = None, host_arena_bytes: int = 0, pcie_pairs=None, nvlink=None,
+                 shard_min_bytes: int = 0):
         self.n = n_gpus
         self.devices = devices or list(range(n_gpus))
         self.engines = [MemoryManager(cap_bytes, device=self.devices[g], server_id=g, gpu_count=n_gpus,
@@ -55,6 +56,9 @@ class SwapServer:
         self.state = [dict(kind="idle") for _ in range(n_gpus)]
         self.pending = [None] * n_gpus              # a load signalled to GPU g, waiting for its execute signal
         self.arrivals = collections.deque()         # arrival times of queued requests, in the controller's FIFO order
+        # 1-link or k-link: a swap-in from the host store of at least this many bytes borrows the PCIe links
+        # of the GPUs the scheduler reports free (tsw_sched_helpers); 0 = always one link, as the reference
+        self.shard_min_bytes = shard_min_bytes
         self.swaps: List[dict] = []
         self.evictions = 0
         self.local_hits = 0
@@ -89,8 +93,14 @@ class SwapServer:
                 if self.engines[g].check_alloc(func):                    # resident: nothing to move (cuda_server.hpp:246)
                     self.pending[g] = None
                 else:
-                    self.pending[g] = dict(src=src, t_signal=time.perf_counter())
-                    self.engines[g].swap_in(func, src)                   # asynchronous: kernel enqueued
+                    helpers = []
+                    if src < 0 and self.shard_min_bytes and self.nbytes[func] >= self.shard_min_bytes:
+                        helpers = [h for h in self.ctrl.helpers(g) if self.state[h]["kind"] == "idle"]
+                    self.pending[g] = dict(src=src, t_signal=time.perf_counter(), links=1 + len(helpers))
+                    if helpers:                                          # asynchronous either way: kernels enqueued
+                        self.engines[g].swap_in_sharded(func, [self.engines[h] for h in helpers])
+                    else:
+                        self.engines[g].swap_in(func, src)
             elif sig == SIGNAL_EXECUTE:
                 st = dict(func=func, t_arrival=t_arrival)
                 if self.pending[g] is None:
@@ -117,7 +127,7 @@ class SwapServer:
             st = self.state[g]
             if st["kind"] == "swap" and self.engines[g].poll_ready(st["func"]) == 0:
                 self.swaps.append(dict(func=st["func"], gpu=g, src=st["src"], bytes=self.nbytes[st["func"]],
-                                       ms=(now - st["t_signal"]) * 1e3, t=st["t_signal"]))
+                                       ms=(now - st["t_signal"]) * 1e3, t=st["t_signal"], links=st["links"]))
                 st["kind"] = "exec"
                 st["until"] = now + EXEC_MS.get(self.arch[st["func"]], 10.0) / 1e3
             if st["kind"] == "exec" and now >= st["until"]:
@@ -133,11 +143,13 @@ class SwapServer:
 
 def run_stream(n_gpus: int, n_models: int, rate: float, duration_s: float, cap_bytes: int, seed: int = 4,
                speedup: float = 1.0, archs=("resnet50", "bert_base", "bert_large", "vgg19"),
-               evict_policy: str = "LRU", zero_weights: bool = True, devices: Optional[List[int]] = None) -> dict:
+               evict_policy: str = "LRU", zero_weights: bool = True, devices: Optional[List[int]] = None,
+               shard_min_bytes: int = 0, pcie_pairs=None, nvlink=None) -> dict:
     """The mixed serverless stream: ``n_models`` functions, Zipf popularity, Poisson arrivals."""
     arch_of, times, picks = W.mixed_stream(seed=seed, n_models=n_models, rate=rate, duration_s=duration_s, archs=archs)
     store = sum(W.host_store_bytes(W.weight_set(a)) for a in arch_of)
-    srv = SwapServer(n_gpus, cap_bytes, evict_policy=evict_policy, host_arena_bytes=0, devices=devices)
+    srv = SwapServer(n_gpus, cap_bytes, evict_policy=evict_policy, host_arena_bytes=0, devices=devices,
+                     shard_min_bytes=shard_min_bytes, pcie_pairs=pcie_pairs, nvlink=nvlink)
     t0 = time.time()
     for i, a in enumerate(arch_of):
         ws = W.weight_set(a)
@@ -160,12 +172,19 @@ def run_stream(n_gpus: int, n_models: int, rate: float, duration_s: float, cap_b
     rel = np.array([s["t"] - start for s in srv.swaps]) if srv.swaps else np.zeros(1)
     fill = rel < wall * 0.25
     host = [s for s in srv.swaps if s["src"] < 0]
+    multi = [s for s in host if s["links"] > 1]
+    host_ms = np.array([s["ms"] for s in host]) if host else np.zeros(1)
+    host_by = np.array([s["bytes"] for s in host], dtype=np.float64) if host else np.zeros(1)
     out = {
         "gpus": n_gpus, "models": n_models, "requests": n_req, "completed": srv.completed, "rate_req_s": rate * speedup,
         "duration_s": wall, "cap_bytes": cap_bytes, "host_store_bytes": store, "cold_start_s": cold_s,
         "evictions_at_cold_start": ev_cold, "evictions_in_service": srv.evictions - ev_cold,
         "local_hits": srv.local_hits, "swaps": len(srv.swaps), "swaps_from_host": len(host),
         "swaps_from_replica": len(srv.swaps) - len(host),
+        "host_swaps_over_several_links": len(multi),
+        "links_per_host_swap_mean": float(np.mean([s["links"] for s in host])) if host else 0.0,
+        "host_swap_ms_p50": float(np.percentile(host_ms, 50)), "host_swap_ms_p99": float(np.percentile(host_ms, 99)),
+        "host_swap_gbs_p50": float(np.percentile(host_by / (host_ms / 1e3) / 1e9, 50)) if host else 0.0,
         "swapped_bytes": float(by.sum()) if srv.swaps else 0.0,
         "sustained_swap_gbs": float(by.sum()) / wall / 1e9 if srv.swaps else 0.0,
         "fill_phase_swap_gbs": float(by[fill].sum()) / max(wall * 0.25, 1e-9) / 1e9 if srv.swaps else 0.0,
@@ -188,9 +207,19 @@ def main():
     ap.add_argument("--cap-gb", type=float, default=40.0)
     ap.add_argument("--speedup", type=float, default=1.0)
     ap.add_argument("--policy", default="LRU")
+    ap.add_argument("--archs", default="resnet50,bert_base,bert_large,vgg19")
+    ap.add_argument("--shard-min-mb", type=float, default=0.0,
+                    help="swap-ins from the host store of at least this size borrow idle GPUs' PCIe links (0 = one link)")
+    ap.add_argument("--seed", type=int, default=4)
     args = ap.parse_args()
+    pairs = nvl = None
+    if args.gpus > 1:
+        from .memory_manager import discover_topology
+        pairs, nvl = discover_topology(args.gpus)        # which GPUs share an uplink, which pairs are NVLink peers
     print(json.dumps(run_stream(args.gpus, args.models, args.rate, args.duration, int(args.cap_gb * (1 << 30)),
-                                speedup=args.speedup, evict_policy=args.policy)), flush=True)
+                                seed=args.seed, speedup=args.speedup, evict_policy=args.policy,
+                                archs=tuple(args.archs.split(",")), shard_min_bytes=int(args.shard_min_mb * (1 << 20)),
+                                pcie_pairs=pairs, nvlink=nvl)), flush=True)
 
 
 if __name__ == "__main__":
