@@ -129,3 +129,50 @@ def test_unknown_model_and_bad_arguments(built):
     m.evict("f") if False else None
     m.close()
     repo_reset()
+
+
+def test_swap_in_that_does_not_fit_leaves_nothing_behind():
+    """Where the reference exits (block_manager.hpp:343-352) the engine refuses the swap-in: blocks it
+    had taken go back to the pool, the model's table is what it was, and the pool serves the next
+    swap-in as if the attempt had never been made."""
+    from torpor_b200.memory_manager import MemoryManager, SwapError, repo_reset
+    MiB = 1 << 20
+    repo_reset()
+    m = MemoryManager(0, device=-1, server_id=0, gpu_count=1)          # 40 chunks of 128 MiB
+
+    def cold(f, n, size):
+        m.track_begin(f)
+        ptrs = [m.malloc(f, size, True) for _ in range(n)]
+        for p in ptrs:
+            m.memcpy_h2d_model(f, p, np.zeros(16, dtype=np.uint8))
+        m.sync_done(f)
+        for p in ptrs:
+            m.mark_access(p)
+        m.track_end(f)
+
+    def spans(f):
+        return {(int(r[4]), int(r[4] + r[1])) for r in m.dump_blocks(f, canonical=True) if r[3]}
+
+    cold("A", 16, 128 * MiB); cold("B", 10, 128 * MiB); cold("S", 6, 2 * MiB)
+    m.evict("A"); m.evict("B")
+    cold("C", 16, 128 * MiB)
+    m.swap_in("A")                                                      # 16 + 16 + 1 chunks in use, 7 free
+    before_b, before_s = m.dump_blocks("B", canonical=True).copy(), spans("S")
+    with pytest.raises(SwapError) as err:
+        m.swap_in("B")                                                  # needs 10
+    assert "POOL_EXHAUSTED" in str(err.value)
+    assert np.array_equal(m.dump_blocks("B", canonical=True), before_b) and not m.check_alloc("B")
+    m.evict("C")
+    m.swap_in("B")                                                      # fits now
+    assert m.check_alloc("B") and len(spans("B")) == 10
+    live = [spans(f) for f in ("A", "B", "S")]
+    assert spans("S") == before_s
+    flat = sorted(x for s in live for x in s)
+    assert all(flat[i][1] <= flat[i + 1][0] for i in range(len(flat) - 1)), "two live blocks overlap"
+    with pytest.raises(SwapError):
+        m.swap_in("C")                                                  # A 16 + B 10 + S 1 = 27 in use; C's 16 do not fit
+    assert [spans(f) for f in ("A", "B", "S")] == live and not m.check_alloc("C")
+    m.evict("A")
+    m.swap_in("C")
+    assert m.check_alloc("C") and len(spans("C")) == 16
+    m.close(); repo_reset()

@@ -116,6 +116,15 @@ int ensure_rows(tsw_engine* e, Model* m, Placement& pl) {
             return fail(TSW_ERR_POOL_EXHAUSTED, "pointer-table slab exhausted");
         memset((void*)flag, 0, sizeof(uint32_t) * cap);
         memset((void*)phys, 0, sizeof(uint64_t) * cap);
+        if (pl.capacity) {
+            // a model that gained parameters after its first placement: the rows published so far
+            // move to the larger device table as well (the old arrays stay in the slab until a reset)
+            cudaStream_t s = (cudaStream_t)e->stream;
+            if (cudaSetDevice(e->cfg.device) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess ||
+                cudaMemcpy(dp, pl.d_table_phys, sizeof(uint64_t) * pl.capacity, cudaMemcpyDeviceToDevice) != cudaSuccess ||
+                cudaMemcpy(df, pl.d_table_flag, sizeof(uint32_t) * pl.capacity, cudaMemcpyDeviceToDevice) != cudaSuccess)
+                return fail(TSW_ERR_CUDA, "moving the device pointer table to a larger one failed");
+        }
         pl.h_descs = hd;
         pl.h_first = (uint32_t*)hf;
         pl.d_table_phys = (uint64_t*)dp;
@@ -129,6 +138,10 @@ int ensure_rows(tsw_engine* e, Model* m, Placement& pl) {
     for (uint32_t i = 0; i < pl.capacity; ++i) {
         flag[i] = pl.flag[i];
         phys[i] = pl.phys[i];
+    }
+    if (e->plan && pl.capacity) {
+        free((void*)pl.flag);
+        free((void*)pl.phys);
     }
     pl.flag = flag;
     pl.phys = phys;
@@ -243,14 +256,18 @@ WaitResult wait_row(tsw_engine* e, Placement& pl, int idx, int64_t timeout_ns) {
 // the process on the first kernel launch that followed (the driver re-maps ranges it considers
 // its own), which left the registered store unmapped under a running kernel.
 void* map_shared_far(int fd, uint64_t size, int slot) {
-    static std::atomic<uint64_t> next{0};
-    const uint64_t stride = 1ull << 40;
-    for (int attempt = 0; attempt < 64; ++attempt) {
-        const uint64_t hint = 0x200000000000ull + (uint64_t)((slot + 64 * (int)(next++ % 1024)) % 4096) * stride;
-        void* p = mmap((void*)hint, size, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED_NOREPLACE, fd, 0);
-        if (p != MAP_FAILED) {
+    // 1 TiB apart from 32 TiB up to 95 TiB: inside the 47-bit user address space, above the heap and
+    // below the stacks and libraries, and clear of the driver's zone.  Each process starts probing at
+    // its own slot so that the arenas of one job do not compete for the same hint.
+    const uint64_t base = 0x200000000000ull, stride = 1ull << 40;
+    const int slots = 64;
+    if (size <= stride) {
+        for (int j = 0; j < slots; ++j) {
+            const uint64_t hint = base + (uint64_t)(((slot % slots) + slots + j) % slots) * stride;
+            void* p = mmap((void*)hint, size, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED_NOREPLACE, fd, 0);
+            if (p == MAP_FAILED) continue;   // taken
             if ((uint64_t)p == hint) return p;
-            munmap(p, size);  // an old kernel ignored the flag and placed it elsewhere
+            munmap(p, size);                 // an old kernel ignored the flag and placed it elsewhere
         }
     }
     return mmap(nullptr, size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
@@ -297,7 +314,8 @@ tsw_engine* engine_of_block_mirror(const uint8_t* p) {
 // check_and_malloc_model (memory_manager.hpp:451-507): place every block that is not
 // resident, in the reference's block order, and rebind the parameters inside it.
 int place_blocks(tsw_engine* e, Model* m, Placement& pl) {
-    std::vector<std::pair<uint64_t, uint64_t>> taken;  // for roll-back
+    struct Taken { int block; uint64_t phys; Placement::B before; };
+    std::vector<Taken> taken;  // for roll-back
     for (auto& kv : m->block_order) {
         const int bi = kv.second;
         VBlock& vb = m->blocks[bi];
@@ -305,11 +323,18 @@ int place_blocks(tsw_engine* e, Model* m, Placement& pl) {
         if (b.known && b.in_cuda) continue;
         DevAddr a;
         if (e->pool->acquire(vb.size, false, &a) != 0) {
-            for (auto& t : taken) e->pool->evict(t.first, t.second, false);
+            // Nothing of a swap-in that does not fit stays behind: the blocks taken so far go back to
+            // the pool and their table entries return to what they were (parameters of a block that is
+            // not resident are never read, so their rebound addresses need no undoing).
+            e->pool->finish_block_alloc();   // the chunks this attempt opened return to the heaps first
+            for (auto& t : taken) {
+                e->pool->evict(t.phys, m->blocks[t.block].size, false);
+                pl.blocks[t.block] = t.before;
+            }
             e->pool->finish_release_block();
             return fail(TSW_ERR_POOL_EXHAUSTED, "pool exhausted while placing " + m->name + ": " + e->pool->last_warning);
         }
-        taken.emplace_back(a.phys, vb.size);
+        taken.push_back({bi, a.phys, b});
         b.known = true;
         b.in_cuda = true;
         b.cuda = a.phys;
@@ -491,9 +516,8 @@ int tsw_repo_active_devices(const char* func, int* gpus, int cap) {
     return n;
 }
 
-int tsw_engine_create(const tsw_config* cfg, tsw_engine** out) {
-    if (!cfg || !out) return fail(TSW_ERR_INVALID, "null argument");
-    std::unique_ptr<tsw_engine> e(new tsw_engine());
+// Everything tsw_engine_create sets up; on failure the caller releases what was made so far.
+static int engine_setup(const tsw_config* cfg, tsw_engine* e) {
     e->cfg = *cfg;
     e->plan = cfg->device < 0;
     e->server_id = cfg->server_id;
@@ -571,7 +595,7 @@ int tsw_engine_create(const tsw_config* cfg, tsw_engine** out) {
         }
         e->dev_slab_floor = e->dev_slab.used;
         e->host_slab_floor = e->host_slab.used;
-        int rc = make_arena(e.get());
+        int rc = make_arena(e);
         if (rc != TSW_OK) return rc;
         // all-pairs peer access, as the controller does at start-up (controller.hpp:63-75)
         for (int j = 0; j < n; ++j) {
@@ -589,20 +613,36 @@ int tsw_engine_create(const tsw_config* cfg, tsw_engine** out) {
     if (e->pool->init() != 0) return fail(TSW_ERR_CUDA, "pool allocation failed: " + tsw::last_error());
     {
         std::lock_guard<std::mutex> g(g_engines_mu);
-        g_engines[cfg->server_id] = e.get();
+        g_engines[cfg->server_id] = e;
     }
-    *out = e.release();
+    return TSW_OK;
+}
+
+int tsw_engine_create(const tsw_config* cfg, tsw_engine** out) {
+    if (!cfg || !out) return fail(TSW_ERR_INVALID, "null argument");
+    tsw_engine* e = new tsw_engine();
+    const int rc = engine_setup(cfg, e);
+    if (rc != TSW_OK) {
+        const std::string why = tsw::last_error();
+        tsw_engine_destroy(e);   // streams, slabs, pool chunks and the arena made before the failure
+        return fail(rc, why);
+    }
+    *out = e;
     return TSW_OK;
 }
 
 int tsw_engine_destroy(tsw_engine* e) {
     if (!e) return TSW_ERR_INVALID;
+    bool registered = false;
     {
         std::lock_guard<std::mutex> g(g_engines_mu);
         auto it = g_engines.find(e->server_id);
-        if (it != g_engines.end() && it->second == e) g_engines.erase(it);
+        if (it != g_engines.end() && it->second == e) {
+            g_engines.erase(it);
+            registered = true;
+        }
     }
-    {
+    if (registered) {   // (an engine whose creation failed never owned the placements of its server id)
         // rows of the pointer table live in this engine's slabs: drop its placements
         Repo& r = repo();
         Lock g(r.mu);
@@ -701,8 +741,12 @@ int tsw_malloc(tsw_engine* e, const char* func, uint64_t size, int load_model_fl
         b.mirror = alloc_mirror(e, size);
         b.mirror_heap = e->plan;
         b.params.clear();
-        if (!b.mirror) {
+        if (!b.mirror) {   // no page-locked memory for the host copy: the block is given back, the model forgets it
+            e->pool->finish_block_alloc();
             e->pool->evict(a.phys, size, false);
+            e->pool->finish_release_block();
+            b.alive = false;
+            m->block_by_vaddr.erase(a.phys);
             return TSW_ERR_CUDA;
         }
     }
@@ -1091,7 +1135,7 @@ int tsw_swap_plan(tsw_engine* e, const char* func, tsw_segment* segs, int cap, u
     pl.remote_rows.clear();
     for (auto& d : pr.plan.descs) pl.remote_rows.push_back((int)d.row);
     if (n && !e->plan) {
-            TSW_CUDA(cudaSetDevice(e->cfg.device));
+        TSW_CUDA(cudaSetDevice(e->cfg.device));
         TSW_CUDA(cudaMemsetAsync(pl.d_ticket, 0, sizeof(uint32_t), (cudaStream_t)e->stream));
         TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
         e->bytes_moved += pr.plan.bytes;
