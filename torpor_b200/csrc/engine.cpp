@@ -139,9 +139,9 @@ int ensure_rows(tsw_engine* e, Model* m, Placement& pl) {
         flag[i] = pl.flag[i];
         phys[i] = pl.phys[i];
     }
-    if (e->plan && pl.capacity) {
-        free((void*)pl.flag);
-        free((void*)pl.phys);
+    if (e->plan && pl.capacity) {   // freed with the placement: a waiter outside the lock may still be reading them
+        pl.retired_rows.push_back((void*)pl.flag);
+        pl.retired_rows.push_back((void*)pl.phys);
     }
     pl.flag = flag;
     pl.phys = phys;
@@ -442,6 +442,7 @@ int tsw_repo_reset(void) {
             if (plan_rows && pl.capacity) {   // rows of plan-only engines are heap memory
                 free((void*)pl.flag);
                 free((void*)pl.phys);
+                for (void* p : pl.retired_rows) free(p);
             }
         }
     }
@@ -652,6 +653,7 @@ int tsw_engine_destroy(tsw_engine* e) {
             if (e->plan && it->second.capacity) {
                 free((void*)it->second.flag);
                 free((void*)it->second.phys);
+                for (void* p : it->second.retired_rows) free(p);
             }
             kv.second->place.erase(it);
         }
