@@ -9,7 +9,7 @@ import pytest
 
 from torpor_b200 import wire
 from torpor_b200 import workloads as W
-from torpor_b200.memory_manager import MemoryManager, repo_reset
+from torpor_b200.memory_manager import MemoryManager, ModelRepo, repo_reset
 
 
 def protobuf_classes():
@@ -149,4 +149,75 @@ def test_executor_over_the_wire_matches_direct_calls(built):
         assert struct.unpack("<QQ", out[1]) == (0x1234, table[tv[t]])
         assert out[2] == struct.pack("<i", t)
     eng.close()
+    repo_reset()
+
+
+def test_server_at_both_wire_surfaces(built):
+    """Router requests in (SignalRequest), acknowledgements out (SignalAck), client streams to the GPU the
+    acknowledgement names: two functions are cold-started, run again, copied between GPUs and unloaded,
+    all through serialised messages, on two plan-only engines."""
+    repo_reset()
+    engines = [MemoryManager(0, device=-1, server_id=g, gpu_count=2) for g in range(2)]
+    srv = wire.WireServer(engines, 1 << 30, "IA", "LRU")
+    ws = W.weight_set("bert_tiny")
+    zeros = lambda i: np.zeros(ws.tensors[i].nbytes, dtype=np.uint8)
+
+    def router(kind, func, payload=""):
+        acks = srv.request(wire.encode("SignalRequest", {"type": kind, "function": func, "payload": payload}))
+        return [wire.int32(wire.decode("SignalAck", a).get("resp", 0)) for a in acks]
+
+    def cold_start(func):
+        (gpu,) = router(wire.REQ_EXECUTE_AFTER_LOAD, func, "1")
+        cl = WireClient(srv.executors[gpu])
+        bv, tv = {}, {}
+        for c in W.cold_start_stream(ws):
+            if c.op == "malloc":
+                p = cl.malloc(c.size)
+                if c.is_model:
+                    bv[c.block] = p
+            elif c.op == "memcpy":
+                tv[c.tensor] = bv[c.block] + c.offset
+                cl.call(wire.Q_MEMCPY_ASYNC, "cudaMemcpyAsyncQuery", {"kind": wire.H2D, "dst": tv[c.tensor], "count": c.size,
+                                                                        "payload": zeros(c.tensor).tobytes()})
+            elif c.op == "sync_done":
+                cl.call(wire.Q_DEVICE_SYNCHRONIZE, "genericResponse", {})
+            elif c.op == "access":
+                cl.call(wire.Q_LAUNCH_KERNEL, "cudaLaunchKernelQuery",
+                        {"function": "k", "grid_dim_x": 1, "args": [struct.pack("<Q", tv[c.tensor])]})
+        assert srv.complete(gpu) == []
+        return gpu, tv
+
+    g_a, tv_a = cold_start("a")
+    g_b, tv_b = cold_start("b")
+    assert (g_a, g_b) == (0, 1)                                   # round-robin placement
+    assert ModelRepo.active_devices("a") == [0] and ModelRepo.active_devices("b") == [1]
+
+    assert router(wire.REQ_EXECUTE, "a") == [0]                   # resident and idle: runs in place
+    assert router(wire.REQ_EXECUTE, "a") == [1]                   # GPU 0 busy: GPU 1 copies it from GPU 0
+    assert srv.sent[-2:] == [(1, wire.SIG_LOAD + 1 + 0, "a"), (1, wire.SIG_EXECUTE, "a")]
+    assert engines[1].check_alloc("a")                            # the executor carried the load out
+    assert router(wire.REQ_EXECUTE, "b") == []                    # both busy: queued, acknowledged later
+    acks = srv.complete(0)                                        # ... when GPU 0 completes
+    assert [wire.int32(wire.decode("SignalAck", a).get("resp", 0)) for a in acks] == [0]
+    # "b" lives on GPU 1, which is busy: GPU 0 copies it from there
+    assert srv.sent[-2:] == [(0, wire.SIG_LOAD + 1 + 1, "b"), (0, wire.SIG_EXECUTE, "b")] and engines[0].check_alloc("b")
+    srv.complete(1); srv.complete(0)
+    assert sorted(ModelRepo.active_devices("a")) == [0, 1] and sorted(ModelRepo.active_devices("b")) == [0, 1]
+
+    # steady state on GPU 1: the pointer words recorded at a's first run on GPU 0 are rewritten there as well
+    assert router(wire.REQ_EXECUTE, "a") in ([0], [1])
+    g = srv.sent[-1][0]
+    ex = srv.executors[g]
+    ex.access_loc = srv.executors[g_a].access_loc                 # kernel_model_access_loc is process-wide in the reference
+    WireClient(ex).call(wire.Q_LAUNCH_KERNEL, "cudaLaunchKernelQuery",
+                        {"function": "k", "grid_dim_x": 1, "args": [struct.pack("<Q", tv_a[3])]})
+    table = {int(r[0]): int(r[3]) for r in engines[g].dump_params("a")}
+    assert struct.unpack("<Q", ex.launched[-1][1][0])[0] == table[tv_a[3]]
+    srv.complete(g)
+
+    assert router(wire.REQ_UNLOAD, "a") == [-1]                   # from every GPU
+    assert ModelRepo.active_devices("a") == [] and not engines[0].check_alloc("a") and not engines[1].check_alloc("a")
+    srv.close()
+    for e in engines:
+        e.close()
     repo_reset()

@@ -256,3 +256,42 @@ class WireExecutor:
             for i, j in sorted(loc):
                 words[i][j] = self.mm.get_cuda_addr(f, words[i][j])
         return [struct.pack(f"<{len(w)}Q", *w) if w is not None else a for w, a in zip(words, args)]
+
+
+class WireServer:
+    """The GPU server at its two wire surfaces: the router's ``SignalRequest`` / ``SignalAck``
+    (proto/signal.proto) handled by the library's controller, whose signals go to one
+    ``WireExecutor`` per GPU, and the clients' ``QueryList`` streams handled by those executors
+    (include/server/controller.hpp:125-264 with cuda_server.hpp:212-300).  An executor that ends a
+    request reports it here, as the reference's does through ``controller_sync_queue``."""
+
+    def __init__(self, managers, mem_limit_bytes: int, schedule_policy: str = "IA", evict_policy: str = "IA",
+                 pcie_pairs=None, nvlink=None):
+        from .memory_manager import Controller
+        self.executors = [WireExecutor(m) for m in managers]
+        self.ctrl = Controller(len(managers), mem_limit_bytes, schedule_policy, evict_policy, pcie_pairs, nvlink)
+        self.sent: List[Tuple[int, int, str]] = []       # (gpu, signal, func) in the order they were sent
+
+    def close(self):
+        self.ctrl.close()
+
+    def _carry_out(self, events) -> List[bytes]:
+        acks = []
+        for e in events:
+            if e[0] == "S":
+                self.sent.append((e[1], e[2], e[3]))
+                self.executors[e[1]].signal(e[2], e[3])
+            else:
+                acks.append(encode("SignalAck", {"ack": e[1], "resp": e[2] & 0xFFFFFFFFFFFFFFFF}))
+        return acks
+
+    def request(self, signal_request: bytes) -> List[bytes]:
+        """One serialised SignalRequest from the router; returns the serialised SignalAck, if one is due now
+        (a request that has to wait for a GPU is acknowledged when it starts)."""
+        r = decode("SignalRequest", signal_request)
+        return self._carry_out(self.ctrl.request(r.get("type", 0), r.get("function", ""), r.get("payload", "")))
+
+    def complete(self, gpu: int) -> List[bytes]:
+        """Executor ``gpu`` finished its request: completion bookkeeping, then the next queued request."""
+        self.executors[gpu].complete()
+        return self._carry_out(self.ctrl.complete(gpu))
