@@ -4,6 +4,9 @@
 #include "memory_manager.hpp"
 #include "evictor.hpp"
 #include "spdlog/sinks/null_sink.h"
+#include "spdlog/sinks/ostream_sink.h"
+
+#include <sstream>
 
 #include <cstdio>
 #include <cstring>
@@ -51,6 +54,44 @@ int main() {
     void (MemoryManager::*h2d_fn)(void*, const string&, cudaStream_t, bool, string&) = &MemoryManager::cudaMemcpyAsyncBackendHtoD;
     (void)malloc_fn; (void)sig_fn; (void)addr_fn; (void)h2d_fn;
 
+    // ... and run as the executor runs it (cuda_server.hpp:73-74,223-253,951-978), on a plan-only engine, with
+    // a logger that keeps the text: the reference's three timing lines must come out under their own names
+    tsw_engine_destroy(e);
+    e = nullptr;
+    tsw_repo_reset();
+    {
+        std::ostringstream text;
+        auto keep = std::make_shared<spdlog::logger>("probe2", std::make_shared<spdlog::sinks::ostream_sink_mt>(text));
+        setenv("TORPOR_SWAP_DEVICE", "-1", 1);
+        MemoryManager m2(0);
+        m2.set_logger(keep);
+        m2.set_server_id(0);
+        m2.start_trans_thread(1);
+        if (!m2.engine()) return 10;
+        string g = "fn2";
+        m2.set_track_model_memory(g);
+        void* block = m2.cudaMallocBackend(2 << 20, true, g);
+        if (!block) return 11;
+        m2.cudaMemcpyAsyncBackendHtoD((char*)block + 1024, payload, nullptr, true, g);
+        m2.init_model_readiness(g);
+        if (!m2.try_insert_model_access((char*)block + 1024)) return 12;
+        m2.unset_track_model_memory(g);
+        m2.evict_model(g);
+        if (m2.check_model_alloc_status(g)) return 13;
+        m2.sig_trans_thread(g, -1);
+        if (!m2.check_model_alloc_status(g)) return 14;
+        if (m2.get_cuda_addr(g, (char*)block + 1024) == nullptr) return 15;
+        keep->flush();
+        const std::string logged = text.str();
+        for (const char* want : {"Evict model fn2 elasped ", "CheckMalloc model fn2 elasped ", "Start transfering model fn2 from GPU -1",
+                                 "Transfer model fn2 from -1 wait count 0 pinned elasped 0 overall elasped "})
+            if (logged.find(want) == std::string::npos) {
+                printf("missing log line: %s\n--- log ---\n%s\n", want, logged.c_str());
+                return 16;
+            }
+        m2.destroy_trans_thread();
+    }
+
     std::shared_ptr<Evictor> ev = std::make_shared<LRUEvictor>(2, 1000);
     map<string, int> levels;
     string a = "a", b = "b", c = "c";
@@ -59,7 +100,6 @@ int main() {
     auto victims = ev->check_and_add(0, c, 400, levels);
     if (victims.size() != 1 || victims[0] != "a") return 7;
 
-    tsw_engine_destroy(e);
     printf("adapter probe ok\n");
     return 0;
 }
