@@ -213,6 +213,9 @@ int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t t
  * a shared-memory arena (config host_arena_shm on the target, tsw_arena_attach elsewhere), and
  * rebase the addresses accordingly; when all are done the target calls tsw_swap_commit, which
  * takes the rows the kernels published on the device over into its host-visible table.
+ * If a participant went away, tsw_swap_commit returns TSW_ERR_STATE and keeps the unfinished rows
+ * listed: commit again later, or call tsw_swap_in, which moves what is missing by itself (the tile
+ * counters of the abandoned rows are cleared first).
  * No counterpart in the reference (one process, one GPU per swap). */
 typedef struct {
     uint64_t base, size;

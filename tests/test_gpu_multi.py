@@ -138,3 +138,63 @@ def test_sharded_swap_one_process_per_gpu(built, tmp_path):
     res = [np.load(os.path.join(str(tmp_path), f"r{r}.npy")) for r in range(world)]
     assert res[0][0] == 1, "resident bytes or pointer table wrong after a sharded swap"
     assert res[1][1] >= 4, "the helper rank launched no kernels"
+
+
+def _rank_losing_helper(rank, world, port, shm, out_dir):
+    sys.path.insert(0, ROOT)
+    import datetime
+    import torch
+    import torch.distributed as dist
+    from torpor_b200 import sharded
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=5))
+    ws = W.weight_set("llama_tiny")
+    repo_reset()
+    if rank == 0:
+        eng = MemoryManager(0, device=0, server_id=0, gpu_count=world, host_arena_bytes=W.host_store_bytes(ws), host_arena_shm=shm)
+        W.cold_start(eng, "m", ws)
+        eng.evict("m")
+    else:
+        eng = MemoryManager(0, device=rank, server_id=rank, gpu_count=world, block_manager="Fixed")
+    dist.barrier()
+    sw = sharded.ShardedSwap(eng, rank, world, None, shm_name=shm, max_segments=256)
+    sw.attach_arena(); sw.share_regions()
+    sw.swap_in("m", "direct"); sw.evict("m")
+    sw.swap_in("m", "staged"); sw.evict("m")
+    if rank != 0:
+        # leave between two swaps: place_segments ran synchronously, nothing of this rank is in flight
+        torch.cuda.synchronize()
+        os._exit(0)
+    sums = np.array([checksum_host(W.tensor_bytes(ws, i)) for i in range(len(ws.tensors))])
+    ok = not sw.alone
+    for mode in ("direct", "staged", "direct"):
+        sw.swap_in("m", mode)                       # the first of these finds the helper gone
+        ok = ok and sw.alone and np.array_equal(eng.checksum_resident("m"), sums)
+        tab = eng.dump_params("m", canonical=True)
+        ok = ok and bool((tab[:, 4] == _cabi.READY_CUDA).all()) and bool((tab[:, 3] == tab[:, 5]).all())
+        sw.evict("m")
+    eng.swap_in("m"); eng.wait_ready("m")           # and the engine's ordinary path is intact afterwards
+    ok = ok and np.array_equal(eng.checksum_resident("m"), sums)
+    np.save(os.path.join(out_dir, "r0.npy"), np.array([int(ok)]))
+    eng.close()
+    os._exit(0)
+
+
+@needs2
+@pytest.mark.timeout(600)
+def test_target_swaps_alone_after_its_helper_process_is_gone(built, tmp_path):
+    """Failure made on the host: the helper process exits between two swaps (no kernel in flight, no
+    collective library on the data path).  The target's next control message fails, it stops asking for
+    help, and every later swap-in is bit-exact, moved by the target alone."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    shm = f"/torpor_swap_lost_{os.getpid()}"
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_losing_helper, args=(r, 2, port, shm, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    assert np.load(os.path.join(str(tmp_path), "r0.npy"))[0] == 1

@@ -110,3 +110,65 @@ def test_shares_and_rebasing():
         m.rebase(np.array([0x1100], dtype=np.uint64))
     with pytest.raises(ValueError):
         m.rebase(np.array([0x10], dtype=np.uint64))
+
+
+def _worker_losing_a_helper(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    import datetime
+    import torch.distributed as dist
+    from torpor_b200 import sharded, workloads as W
+    from torpor_b200.memory_manager import MemoryManager, repo_reset
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=5))
+    ws = W.weight_set("resnet50")
+    eng = None
+    if rank == 0:
+        repo_reset()
+        eng = MemoryManager(0, device=-1)
+        W.cold_start(eng, "m", ws, tensor_data=lambda i: np.zeros(ws.tensors[i].nbytes, dtype=np.uint8))
+        eng.evict("m")
+    sw = sharded.ShardedSwap(eng, rank, world, None, shm_name=None, max_segments=512)
+    sw.attach_arena()
+    sw.share_regions()
+    sw.swap_in("m", "direct")
+    sw.evict("m")
+    if rank != 0:
+        os._exit(0)                      # the helper goes away between two swaps, without a word
+    res = {"alone_before": sw.alone}
+    for mode in ("direct", "staged", "direct"):
+        sw.swap_in("m", mode)
+        res.setdefault("tiles", []).append((len(sw.my_tiles), sw.last["tiles"]))
+        res.setdefault("params", []).append(eng.dump_params("m", canonical=True).tolist())
+        res.setdefault("alloc", []).append(eng.check_alloc("m"))
+        sw.evict("m")
+    res["alone_after"], res["reason"] = sw.alone, sw.lost_reason
+    eng.swap_in("m"); eng.wait_ready("m")
+    res["plain"] = eng.dump_params("m", canonical=True).tolist()
+    eng.close()
+    repo_reset()
+    np.save(os.path.join(out_dir, "r0.npy"), np.array([res], dtype=object), allow_pickle=True)
+    os._exit(0)                          # no orderly shutdown of a group whose other member is gone
+
+
+@pytest.mark.timeout(300)
+def test_target_carries_on_alone_when_its_helper_goes_away(built, tmp_path):
+    """Failure made on the host: the helper rank exits between two swaps.  The target's next control
+    message fails (at once or at the group's 5 s timeout); it stops asking for help and moves every
+    tile itself, and the tables it ends up with are those of an ordinary swap-in."""
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_losing_a_helper, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    res = np.load(os.path.join(str(tmp_path), "r0.npy"), allow_pickle=True)[0]
+    assert res["alone_before"] is False and res["alone_after"] is True and res["reason"]
+    for mine, total in res["tiles"]:
+        assert mine == total > 161                                       # the target took every tile
+    assert all(res["alloc"])
+    plain = np.array(res["plain"], dtype=np.uint64)
+    for params in res["params"]:
+        p = np.array(params, dtype=np.uint64)
+        assert (p[:, 4] == 2).all() and np.array_equal(p[:, [0, 1, 2, 4, 6]], plain[:, [0, 1, 2, 4, 6]])

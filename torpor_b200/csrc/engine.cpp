@@ -1002,6 +1002,17 @@ static int prepare_swap(tsw_engine* e, const char* func, int src_gpu, Prepared& 
     }
     rc = drain_placement(e, pl);
     if (rc != TSW_OK) return rc;
+    if (pl.counters_dirty) {
+        // The last swap was abandoned with parameters half moved (a participant went away): their
+        // tile counters were never re-armed by a last finisher.  Start this swap from zero.
+        if (!e->plan) {
+            TSW_CUDA(cudaSetDevice(e->cfg.device));
+            TSW_CUDA(cudaMemsetAsync(pl.d_done, 0, sizeof(uint32_t) * pl.capacity, (cudaStream_t)e->stream));
+            TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+        }
+        pl.counters_dirty = false;
+        pl.remote_rows.clear();
+    }
     rc = place_blocks(e, m, pl);
     if (rc != TSW_OK) return rc;
 
@@ -1165,13 +1176,19 @@ int tsw_swap_commit(tsw_engine* e, const char* func) {
     TSW_CUDA(cudaSetDevice(e->cfg.device));
     TSW_CUDA(cudaMemcpy(flag.data(), pl.d_table_flag, sizeof(uint32_t) * pl.capacity, cudaMemcpyDeviceToHost));
     TSW_CUDA(cudaMemcpy(phys.data(), pl.d_table_phys, sizeof(uint64_t) * pl.capacity, cudaMemcpyDeviceToHost));
-    int missing = 0;
+    std::vector<int> missing;
     for (int row : pl.remote_rows) {
         if (flag[row] == pl.epoch) set_row(pl, row, TSW_READY_CUDA, phys[row]);
-        else ++missing;
+        else missing.push_back(row);
     }
-    pl.remote_rows.clear();
-    if (missing) return fail(TSW_ERR_STATE, std::to_string(missing) + " parameters were not completed by the participants");
+    // Rows still on their way stay listed: the caller may commit again once the participants have
+    // finished, or give up and swap the model in by itself (which starts the counters afresh).
+    pl.remote_rows.swap(missing);
+    if (!pl.remote_rows.empty()) {
+        pl.counters_dirty = true;
+        return fail(TSW_ERR_STATE, std::to_string(pl.remote_rows.size()) + " parameters were not completed by the participants");
+    }
+    pl.counters_dirty = false;
     return TSW_OK;
 }
 

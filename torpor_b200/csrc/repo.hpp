@@ -58,6 +58,7 @@ struct Placement {
     // host-mapped page-locked arrays written by the placement kernel; on a plan-only
     // engine plain memory written by the planner.
     uint32_t capacity = 0;
+    bool counters_dirty = false;         // a swap ended with rows incomplete: their tile counters hold partial counts
     std::vector<void*> retired_rows;     // plan-only: smaller tables replaced by growth; a waiter may still read them
     volatile uint32_t* flag = nullptr;   // TSW_READY_*
     volatile uint64_t* phys = nullptr;   // readiness address (0 = none)

@@ -127,24 +127,50 @@ class ShardedSwap:
         self.dry = engine is None or engine.device < 0
         self.dynamic = True         # direct mode: draw tiles from a shared counter instead of t mod N
         self.staged_tile = 512 * 1024
+        # Helpers only lend bandwidth.  When a control message to them fails (a helper process is gone,
+        # or the group's timeout ran out) the target stops asking and from then on swaps by itself.
+        self.alone = world == 1
+        self.lost_reason = ""
+        self.settle_s = 2.0         # how long the target waits for helpers still at work before it takes over
 
     # ---- control plane
+    def _collective(self, fn, mine):
+        """Run one control-plane collective; ``mine`` is the answer when this rank is on its own."""
+        if self.alone:
+            return mine
+        try:
+            return fn()
+        except RuntimeError as ex:              # gloo reports a lost peer or a timeout this way
+            if self.rank != 0:
+                raise
+            self.alone = True
+            self.lost_reason = str(ex).splitlines()[0][:200] if str(ex) else type(ex).__name__
+            return mine
+
     def _bcast_words(self, words: np.ndarray) -> np.ndarray:
         import torch
-        t = torch.from_numpy(words.view(np.int64))
-        self.dist.broadcast(t, src=0, group=self.group)
-        return t.numpy().view(np.uint64)
+
+        def run():
+            t = torch.from_numpy(words.view(np.int64))
+            self.dist.broadcast(t, src=0, group=self.group)
+            return t.numpy().view(np.uint64)
+        return self._collective(run, words)
 
     def _bcast_obj(self, obj):
-        box = [obj]
-        self.dist.broadcast_object_list(box, src=0, group=self.group)
-        return box[0]
+        def run():
+            box = [obj]
+            self.dist.broadcast_object_list(box, src=0, group=self.group)
+            return box[0]
+        return self._collective(run, obj)
 
     def _max_over_ranks(self, value: float) -> float:
         import torch
-        t = torch.tensor([value], dtype=torch.float64)
-        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX, group=self.group)
-        return float(t[0])
+
+        def run():
+            t = torch.tensor([value], dtype=torch.float64)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX, group=self.group)
+            return float(t[0])
+        return self._collective(run, value)
 
     def attach_arena(self):
         """Map the target's host store into every rank (once)."""
@@ -226,10 +252,15 @@ class ShardedSwap:
         else:
             self.my_tiles = range(*contiguous_share(n_tiles, self.rank, self.world))
         self.last_plan = (segs, tile)
+        if self.alone and self.rank == 0:
+            self.my_tiles = range(n_tiles)
         if len(segs) and not self.dry:
             local = self.localize(segs)
-            pub = self._local_publish(pubw, dynamic=(mode == "direct" and self.dynamic))
-            if mode == "direct" and self.dynamic:
+            pub = self._local_publish(pubw, dynamic=(mode == "direct" and self.dynamic and not self.alone))
+            if self.alone:
+                # nobody to share with (any more): the target moves every tile itself, from the host store
+                self.engine.place_segment_array(local, tile, 0, 1, 0, pub, sync=True)
+            elif mode == "direct" and self.dynamic:
                 # every rank draws tiles from the counter on the target: faster links move more
                 self.engine.place_segment_array(local, tile, 0, 1, 0, pub, sync=True)
             elif mode == "direct":
@@ -243,12 +274,31 @@ class ShardedSwap:
                     self.engine.place_segment_array(local, tile, lo, 1, hi, pub, sync=True)
             dev_ns = float(self.engine.stats()["last_swap_device_ns"])
         t_done = time.perf_counter()
+        was_alone = self.alone
         dev_max = self._max_over_ranks(dev_ns)          # doubles as the completion barrier
         if self.rank == 0 and self.engine is not None:
-            self.engine.swap_commit(func)
+            self._commit(func, lost_now=self.alone and not was_alone)
         self.last = {"tiles": n_tiles, "segments": len(segs), "tile_bytes": tile, "device_ns": dev_ns,
                      "device_ns_max": dev_max, "local_wall_s": t_done - t0, "wall_s": time.perf_counter() - t0}
         return self.last
+
+    def _commit(self, func: str, lost_now: bool):
+        """Take the published rows over.  If the helpers were lost during this very swap, those still alive
+        may be finishing their tiles: give them ``settle_s``, then move what is missing alone."""
+        from ._cabi import SwapError
+        deadline = time.perf_counter() + (self.settle_s if lost_now else 0.0)
+        while True:
+            try:
+                self.engine.swap_commit(func)
+                return
+            except SwapError:
+                if not lost_now:
+                    raise
+                if time.perf_counter() >= deadline:
+                    break
+                time.sleep(0.01)
+        self.engine.swap_in(func)           # clears the abandoned tile counters, moves the unfinished parameters
+        self.engine.wait_ready(func)
 
     def _staging(self, func, segs, tile, lo, hi):
         """This rank's contiguous share of the swap, resident in local HBM."""
