@@ -308,7 +308,9 @@ int tsw_sched_helpers(tsw_scheduler* s, int dst, int include_running, int* helpe
  * GPU busy (TSW_OK, nothing sent, no acknowledgement yet) and is tried again at the next
  * completion; a model at or above the limit can never fit, and the call returns TSW_ERR_STATE,
  * sends nothing and drops the request.  A cold start that has finished is entered even if its
- * GPU stays over the limit (it is there already); whatever is not pinned is unloaded for it. */
+ * GPU stays over the limit (it is there already); whatever is not pinned is unloaded for it.
+ * A controller, a scheduler and an eviction policy are each driven from one thread, as the
+ * reference's controller loop drives them; they take no lock of their own. */
 typedef struct tsw_controller tsw_controller;
 typedef void (*tsw_signal_fn)(void* user, int gpu, int signal, const char* func);
 typedef void (*tsw_ack_fn)(void* user, int ack, int resp);
