@@ -225,6 +225,28 @@ def run_baselines(args):
         dev1 = torch.empty(nbytes, dtype=torch.uint8, device="cuda:1")
         out["copy_engine_peer_gbs"] = timed(lambda: dev0.copy_(dev1, non_blocking=True))
         del dev1
+        n = torch.cuda.device_count()
+        if n > 2:
+            # every other GPU's copy engine pushes 1 GiB into GPU 0 at once: the (n-1) -> 1 gather ceiling
+            dst = [torch.empty(nbytes, dtype=torch.uint8, device="cuda:0") for _ in range(n - 1)]
+            src = [torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{i}") for i in range(1, n)]
+            streams = [torch.cuda.Stream(device=i) for i in range(1, n)]
+
+            def gather():
+                for d, s_, st in zip(dst, src, streams):
+                    with torch.cuda.stream(st):
+                        d.copy_(s_, non_blocking=True)
+            best = 0.0
+            for _ in range(4):
+                for i in range(n):
+                    torch.cuda.synchronize(i)
+                t0 = time.perf_counter()
+                gather()
+                for i in range(n):
+                    torch.cuda.synchronize(i)
+                best = max(best, nbytes * (n - 1) / (time.perf_counter() - t0) / 1e9)
+            out["copy_engine_gather_gbs"] = {"value": best, "what": f"{n - 1} -> 1 concurrent peer copies of 1 GiB each, wall clock, best of 4"}
+            del dst, src
         # the same replica swap through this library: GPU 0 places the model from GPU 1's pool over NVLink
         from torpor_b200 import workloads as W
         from torpor_b200.memory_manager import MemoryManager, ModelRepo, repo_reset
