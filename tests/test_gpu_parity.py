@@ -269,6 +269,31 @@ def test_tiles_dealt_to_several_launches_publish_once(fresh):
     eng.close()
 
 
+def test_more_segments_than_the_launch_scratch_holds_at_first(fresh):
+    """A raw segment list longer than the engine's initial launch scratch (4096 entries) makes the
+    scratch grow; the host store and the rest of the engine must come through that untouched."""
+    import torch
+    ws = W.weight_set("bert_tiny")
+    eng = MemoryManager(0, device=0)
+    lm = W.cold_start(eng, "m", ws)
+    n, piece = 6000, 1040                                  # 16-byte multiples, not a power of two
+    rng = np.random.default_rng(8)
+    src = torch.from_numpy(rng.integers(0, 256, size=n * piece, dtype=np.uint8)).cuda()
+    dst = torch.zeros(n * piece, dtype=torch.uint8, device="cuda")
+    order = rng.permutation(n)
+    s_list = [src.data_ptr() + int(i) * piece for i in order]
+    d_list = [dst.data_ptr() + int(k) * piece for k in range(n)]
+    eng.place_segments(s_list, d_list, [piece] * n, tile_bytes=4096)
+    want = src.cpu().numpy().reshape(n, piece)[order].reshape(-1)
+    assert np.array_equal(dst.cpu().numpy(), want)
+    eng.place_segments(s_list[:10], d_list[:10], [piece] * 10, tile_bytes=4096)      # and the grown scratch is reused
+    # the model the engine holds still swaps in bit-exact afterwards
+    eng.evict("m"); eng.swap_in("m"); eng.wait_ready("m")
+    sums = np.array([checksum_host(W.tensor_bytes(ws, i)) for i in range(len(ws.tensors))])
+    assert np.array_equal(eng.checksum_resident("m"), sums)
+    eng.close()
+
+
 # ---------------------------------------------------------------- bounded waits, errors
 
 def test_waits_are_bounded(fresh):

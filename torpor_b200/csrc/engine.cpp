@@ -1762,14 +1762,10 @@ int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t t
     const uint64_t need_d = sizeof(PlaceDesc) * (uint64_t)n, need_f = sizeof(uint32_t) * ((uint64_t)n + 1);
     if (e->raw_cap < (uint64_t)n) {
         TSW_CUDA(cudaStreamSynchronize(s));
-        for (auto& kv : e->ipc_open) cudaIpcCloseMemHandle((void*)kv.second);
-        for (auto& a : e->attached) {
-            cudaHostUnregister(a.host);
-            munmap(a.host, a.size);
-        }
         if (e->raw_d_descs) cudaFree(e->raw_d_descs);
         if (e->raw_d_first) cudaFree(e->raw_d_first);
         if (e->raw_h) cudaFreeHost(e->raw_h);
+        e->raw_d_descs = e->raw_d_first = e->raw_h = nullptr;
         e->raw_cap = 0;
         const uint64_t cap = std::max<uint64_t>((uint64_t)n, 1024);
         TSW_CUDA(cudaMalloc(&e->raw_d_descs, sizeof(PlaceDesc) * cap));
