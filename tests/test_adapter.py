@@ -11,7 +11,7 @@ import pytest
 from torpor_b200 import _cabi
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = "/root/reference"
+REF = os.environ.get("TORPOR_REFERENCE", "/root/reference")   # same default as oracle/Makefile's REF
 
 
 def test_adapter_compiles_against_reference_headers_and_runs(built, tmp_path):
