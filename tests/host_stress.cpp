@@ -1,8 +1,8 @@
 // Host-side stress of the swap library under sanitizers (no GPU): several executor threads,
 // each with its own plan-only engine, hammer the shared repository concurrently -- cold
 // starts, evictions, swap-ins from the host store and from another engine's replica,
-// pointer translation with bounded waits, frees and re-mallocs, the eviction policy and the
-// scheduler.  Built by tests/test_sanitizers.py from the library's host sources with
+// pointer translation with bounded waits, frees and re-mallocs, the eviction policy, the
+// scheduler and the controller's request handling.  Built by tests/test_sanitizers.py from the library's host sources with
 // -fsanitize=address,undefined or -fsanitize=thread; the kernels' launchers are stubbed.
 #include <atomic>
 #include <cstdio>
@@ -119,11 +119,74 @@ static void policy(int rounds) {
     tsw_sched_destroy(s);
 }
 
+// The controller's request handling, closed-loop, on its own thread (a controller is driven from one
+// thread; what it shares with the executors is the repository, which has its lock).
+struct CtrlSink {
+    std::vector<int> busy = std::vector<int>(4, 0);
+    long signals = 0, acks = 0;
+};
+static void on_signal(void* user, int gpu, int signal, const char* func) {
+    CtrlSink* k = (CtrlSink*)user;
+    k->signals++;
+    if (gpu < 0 || gpu >= 4 || !func) g_fail++;
+    if (signal == TSW_SIGNAL_STARTUP || signal == TSW_SIGNAL_EXECUTE) k->busy[gpu] = 1;
+}
+static void on_ack(void* user, int, int) { ((CtrlSink*)user)->acks++; }
+
+static void controller(int rounds) {
+    tsw_config cfg;
+    tsw_config_default(&cfg);
+    cfg.device = -1;
+    cfg.server_id = 8;
+    cfg.gpu_count = 4;
+    cfg.budget_bytes = 0;
+    tsw_engine* e = nullptr;
+    CHECK(tsw_engine_create(&cfg, &e) == TSW_OK);
+    for (int i = 0; i < 9; ++i) {            // sizes for the eviction policy: 16..144 MiB of blocks per model
+        std::string f = "c" + std::to_string(i);
+        uint64_t p;
+        tsw_track_begin(e, f.c_str());
+        for (int b = 0; b <= i; ++b) CHECK(tsw_malloc(e, f.c_str(), 16ull << 20, 1, &p) == TSW_OK);
+        tsw_track_end(e, f.c_str());
+    }
+    CtrlSink sink;
+    tsw_controller* c = nullptr;
+    CHECK(tsw_ctrl_create(4, 400ull << 20, "IA", "IA", nullptr, nullptr, on_signal, on_ack, &sink, &c) == TSW_OK);
+    unsigned x = 12345;
+    auto rnd = [&x]() { x = x * 1664525u + 1013904223u; return x >> 8; };
+    for (int r = 0; r < rounds * 40; ++r) {
+        std::string f = "c" + std::to_string(rnd() % 9);
+        const unsigned pick = rnd() % 100;
+        int rc = TSW_OK;
+        if (r < 9) rc = tsw_ctrl_request(c, TSW_REQ_EXECUTE_AFTER_LOAD, ("c" + std::to_string(r)).c_str(), std::to_string(r % 4).c_str());
+        else if (pick < 50) rc = tsw_ctrl_request(c, TSW_REQ_EXECUTE, f.c_str(), "");
+        else if (pick < 88) {
+            const int g = (int)(rnd() % 4);
+            if (sink.busy[g]) { sink.busy[g] = 0; rc = tsw_ctrl_complete(c, g); }
+        } else if (pick < 94) rc = tsw_ctrl_request(c, TSW_REQ_UNLOAD, f.c_str(), pick % 2 ? "" : std::to_string(rnd() % 4).c_str());
+        else if (pick < 97) rc = tsw_ctrl_request(c, TSW_REQ_EXECUTE, f.c_str(), std::to_string(rnd() % 4).c_str());
+        else rc = tsw_ctrl_request(c, 11 /* Replay: not the controller's */, f.c_str(), "x");
+        CHECK(rc == TSW_OK || rc == TSW_ERR_STATE);
+        int st;
+        char name[64];
+        CHECK(tsw_ctrl_executor_status(c, (int)(rnd() % 4), &st, name, sizeof(name)) == TSW_OK);
+        int helpers[8];
+        CHECK(tsw_ctrl_helpers(c, (int)(rnd() % 4), r % 2, helpers, 8) >= 0);
+    }
+    for (int g = 0; g < 4; ++g)
+        while (sink.busy[g]) { sink.busy[g] = 0; tsw_ctrl_complete(c, g); }
+    CHECK(sink.signals > 0 && sink.acks > 0);
+    CHECK(tsw_ctrl_queue_depth(c) >= 0);
+    tsw_ctrl_destroy(c);
+    CHECK(tsw_engine_destroy(e) == TSW_OK);
+}
+
 int main(int argc, char** argv) {
     const int n_threads = 4, rounds = argc > 1 ? atoi(argv[1]) : 40;
     std::vector<std::thread> th;
     for (int i = 0; i < n_threads; ++i) th.emplace_back(executor, i, n_threads, rounds);
     th.emplace_back(policy, rounds);
+    th.emplace_back(controller, rounds);
     for (auto& t : th) t.join();
     tsw_repo_reset();
     if (g_fail.load()) {

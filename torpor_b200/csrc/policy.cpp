@@ -529,7 +529,8 @@ int tsw_ctrl_request(tsw_controller* c, int type, const char* func_c, const char
     const std::string func(func_c);
     const bool has_payload = payload && payload[0];
     int hint = 0;
-    if (has_payload && type != kReqLoad && !parse_int(payload, &hint)) return tsw::fail(TSW_ERR_INVALID, "request payload is not a number");
+    const bool reads_payload = type == kReqExecuteAfterLoad || type == kReqExecute || type == kReqUnload;
+    if (has_payload && reads_payload && !parse_int(payload, &hint)) return tsw::fail(TSW_ERR_INVALID, "request payload is not a number");
 
     if (type == kReqExecuteAfterLoad) {                               // :141-162
         int level = kLevelMedian;
