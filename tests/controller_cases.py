@@ -103,10 +103,10 @@ def drive(ctrl, seed, n_gpu=4, n_ops=400):
     return out
 
 
-def record(tso_backend, sched_policy, evict_policy):
+def record(tso_backend, sched_policy, evict_policy, seeds=SEEDS):
     """Traces of a checker library on the reference's 4-GPU tables, one per seed."""
     runs = []
-    for seed in SEEDS:
+    for seed in seeds:
         tso_backend.reset()
         reseed_libc()
         register_sizes(tso_backend.manager(server_id=0, budget=0, gpu_count=4), model_blocks(seed))

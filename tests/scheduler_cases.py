@@ -53,10 +53,10 @@ def drive(sched, set_replica, n_gpu, seed, n_ops=600):
     return out
 
 
-def record(tso_backend, policy):
+def record(tso_backend, policy, seeds=SEEDS):
     """Decision lists of a checker library on the reference's 4-GPU tables, one per seed."""
     runs = []
-    for seed in SEEDS:
+    for seed in seeds:
         tso_backend.reset()
         reseed_libc()
         s = tso_backend.lib.scheduler(4, policy, REF_PAIRS, REF_NVLINK)

@@ -79,6 +79,15 @@ def test_reference_controller_loop_still_matches_its_recordings(ref_backend, sp,
 
 
 @pytest.mark.parametrize("sp,ep", CC.COMBOS)
+def test_live_differential_against_the_reference_controller_loop(built, ref_backend, sp, ep):
+    """Beyond the recordings: twelve more seeded streams per policy pair, the reference's loop run now."""
+    seeds = range(100, 112)
+    want = CC.record(ref_backend, sp, ep, seeds)
+    for seed, w in zip(seeds, want):
+        assert engine_run(4, sp, ep, CC.REF_PAIRS, CC.REF_NVLINK, seed) == w, f"{sp}/{ep} seed {seed}"
+
+
+@pytest.mark.parametrize("sp,ep", CC.COMBOS)
 def test_eight_gpu_layout_matches_the_restatement(built, oracle_backend, sp, ep):
     pairs, nv = nvswitch(8)
     for seed in range(3):

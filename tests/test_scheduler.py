@@ -51,6 +51,15 @@ def test_reference_controller_still_matches_its_recordings(ref_backend, policy):
 
 
 @pytest.mark.parametrize("policy", ["IA", "RAND"])
+def test_live_differential_against_the_reference_controller(built, ref_backend, policy):
+    """Beyond the recordings: twenty more seeded streams, decided by the reference's Controller now."""
+    seeds = range(50, 70)
+    want = SC.record(ref_backend, policy, seeds)
+    for seed, w in zip(seeds, want):
+        assert engine_stream(4, policy, SC.REF_PAIRS, SC.REF_NVLINK, seed) == w, f"{policy} seed {seed}"
+
+
+@pytest.mark.parametrize("policy", ["IA", "RAND"])
 def test_eight_gpu_layout_matches_the_restatement(built, oracle_backend, policy):
     pairs, nv = SC.nvswitch(8)
     for seed in range(4):
