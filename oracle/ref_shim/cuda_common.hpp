@@ -147,6 +147,7 @@ inline cudaError_t cudaEventCreate(cudaEvent_t* e) { *e = nullptr; return cudaSu
 inline cudaError_t cudaEventRecord(cudaEvent_t, cudaStream_t = nullptr) { return cudaSuccess; }
 inline cudaError_t cudaEventSynchronize(cudaEvent_t) { return cudaSuccess; }
 inline cudaError_t cudaDeviceSynchronize() { return cudaSuccess; }
+inline cudaError_t cudaStreamSynchronize(cudaStream_t) { return cudaSuccess; }
 
 #endif  // TORPOR_REF_FAKE_CUDA
 

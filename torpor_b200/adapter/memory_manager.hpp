@@ -1,7 +1,9 @@
 // Drop-in for include/server/memory_manager.hpp: the same class, constructor and public
 // methods (memory_manager.hpp:36-298), implemented over the C ABI of libtorpor_swap.so.
-// Put this directory ahead of include/server on the include path and link the server with
-// -ltorpor_swap; include/server/cuda_server.hpp and controller.hpp compile unchanged.
+// Force-include this header and evictor.hpp ahead of the server's sources (-include) and link
+// with -ltorpor_swap: the headers carry the reference's include guards, so the quoted includes of
+// the neighbouring originals inside include/server/cuda_server.hpp and controller.hpp (which an
+// include path cannot redirect) find nothing left to add, and both compile unchanged.
 //
 // Error behaviour follows the reference: nothing is returned or thrown on this surface;
 // a failed call prints one line and execution continues (cuda_common.hpp:108-114), except
