@@ -17,6 +17,8 @@
 #include <map>
 #include <thread>
 #include <chrono>
+#include <deque>
+#include <mutex>
 
 #define private public
 #define protected public
@@ -31,6 +33,19 @@
 #include "ref_shim_ctrl/cuda_server.hpp"
 #define INCLUDE_CUDA_SERVER_HPP_
 #include "controller.hpp"   // the reference's own
+#endif
+#ifdef TORPOR_REF_WITH_EXECUTOR
+// The reference's executor (include/server/cuda_server.hpp), unmodified.  Its constructor opens a
+// log file per executor (cuda_server.hpp:57-59); inside that header the call is redirected to a
+// logger without a file, so that tests leave nothing behind and can make an executor twice.
+namespace spdlog {
+inline std::shared_ptr<logger> torpor_fileless_logger(const std::string& name, const std::string&, bool = false) {
+    return std::make_shared<logger>(name, std::make_shared<sinks::null_sink_mt>());
+}
+}  // namespace spdlog
+#define basic_logger_mt torpor_fileless_logger
+#include "cuda_server.hpp"   // the reference's own; socket_helper.hpp is shadowed by ref_shim_exec/
+#undef basic_logger_mt
 #endif
 #undef private
 #undef protected
@@ -473,6 +488,196 @@ int tso_ctrl_request(void* c, int type, const char* func, const char* payload, c
 }
 int tso_ctrl_complete(void* c, int executor, char* trace, int cap) {
     return run_one_event((CtrlHandle*)c, nullptr, executor, trace, cap);
+}
+#endif
+
+// ---------------------------------------------------------------- executor
+#ifdef TORPOR_REF_WITH_EXECUTOR
+}  // extern "C"
+
+// src/server/kernel_lookup.cpp fills this table from the CUDA fat binaries the server links; here
+// the harness registers kernel names (tso_exec_register_kernel).
+map<string, const void*>& lookup() {
+    static map<string, const void*> table;
+    return table;
+}
+map<string, KernelAccessLoc>& kernel_model_access_loc() {
+    static map<string, KernelAccessLoc> table;
+    return table;
+}
+
+namespace {
+struct Launch {
+    std::string kernel;
+    std::vector<std::string> args;
+};
+std::mutex g_launch_mu;
+std::deque<std::vector<size_t>> g_expected_arg_sizes;   // byte length of every argument of the launches to come
+std::vector<Launch> g_launches;
+
+struct ExecHandle {
+    zmq::context_t ctx;
+    server::CUDAExecutor* ex = nullptr;   // never destroyed: the manager inside it cannot be torn down (see tso_destroy)
+    std::thread loop;
+    Handle view;                          // the executor's own manager, for the table dumps (not owned)
+    torpor_ref_exec::Channel* channel = nullptr;
+};
+}  // namespace
+
+namespace torpor_ref_fake {
+void record_launch(const void* func, void** args) {
+    std::lock_guard<std::mutex> g(g_launch_mu);
+    Launch l;
+    for (auto& kv : lookup()) if (kv.second == func) l.kernel = kv.first;
+    if (!g_expected_arg_sizes.empty()) {
+        std::vector<size_t> sizes = g_expected_arg_sizes.front();
+        g_expected_arg_sizes.pop_front();
+        for (size_t i = 0; i < sizes.size(); ++i) l.args.emplace_back((const char*)args[i], sizes[i]);
+    }
+    g_launches.push_back(l);
+}
+}  // namespace torpor_ref_fake
+
+extern "C" {
+
+void tso_exec_register_kernel(const char* name) {
+    static char anchors[4096];
+    auto& t = lookup();
+    if (!t.count(name) && t.size() < sizeof(anchors)) t[name] = &anchors[t.size()];
+}
+
+void* tso_exec_create(int id, uint64_t budget_bytes, int gpu_count) {
+    torpor_ref_fake::device_count() = gpu_count;
+    unsetenv("BLOCK_MANAGER");
+    setenv("IO_THREAD_NUM", "2", 1);
+    auto* h = new ExecHandle();
+    h->ex = new server::CUDAExecutor(id, (size_t)budget_bytes, &h->ctx);
+    h->channel = &torpor_ref_exec::channel_of((void*)&h->ex->srv_pull_handler_);
+    server::CUDAExecutor* ex = h->ex;
+    h->loop = std::thread([ex] {
+        try {
+            ex->start();
+        } catch (const torpor_ref_exec::Stop&) {
+        }
+    });
+    {   // until the loop has set itself up (pool, streams) and polls for the first time
+        std::unique_lock<std::mutex> lk(h->channel->mu);
+        h->channel->cv.wait(lk, [&] { return h->channel->polls > 0; });
+    }
+    h->view.mm.reset(&h->ex->mem_manager_);
+    h->view.server_id = id;
+    h->view.started = false;
+    return h;
+}
+
+void* tso_exec_manager(void* hv) { return &((ExecHandle*)hv)->view; }
+
+void tso_exec_destroy(void* hv) {
+    auto* h = (ExecHandle*)hv;
+    {
+        std::lock_guard<std::mutex> g(h->channel->mu);
+        h->channel->stop = true;
+        h->channel->cv.notify_all();
+    }
+    if (h->loop.joinable()) h->loop.join();
+    {
+        std::lock_guard<std::mutex> g(h->channel->mu);
+        h->channel->stop = false;
+        h->channel->polls = 0;
+        h->channel->inbox.clear();
+        h->channel->sent.clear();
+    }
+    h->view.mm.release();
+    // the executor object stays (its manager's staging threads cannot be stopped); the handle with it
+}
+
+// What the controller does to an executor (controller.hpp:429-431 -> cuda_server.hpp:282-285):
+// returns when the executor's loop has acted on the signal.
+void tso_exec_signal(void* hv, int signal, const char* func) {
+    string f(func);
+    ((ExecHandle*)hv)->ex->sig_exec_from_controller(signal, f);
+}
+
+// One serialised QueryList, as the client's sender pushes it (cuda_server.hpp:199-209).  Returns
+// when the executor is back at its poll; `out` receives what it sent to its clients meanwhile as
+// records of a 4-byte little-endian length followed by the serialised response.  The return value
+// is the size the records need.
+int tso_exec_queries(void* hv, const void* bytes, int n, void* out, int cap) {
+    auto* h = (ExecHandle*)hv;
+    std::string msg((const char*)bytes, (size_t)n);
+    {   // argument sizes of the launches inside, for the launch recorder
+        QueryList ql;
+        ql.ParseFromString(msg);
+        std::lock_guard<std::mutex> g(g_launch_mu);
+        for (auto& q : ql.queries()) {
+            if (q.type() != QueryType::cudaLaunchKernel) continue;
+            cudaLaunchKernelQuery lq;
+            lq.ParseFromString(q.query());
+            if (!lookup().count(lq.function())) continue;     // the executor will not launch it
+            std::vector<size_t> sizes;
+            for (int i = 0; i < lq.args_size(); ++i) sizes.push_back(lq.args(i).length());
+            g_expected_arg_sizes.push_back(sizes);
+        }
+    }
+    std::vector<std::string> sent;
+    {
+        std::unique_lock<std::mutex> lk(h->channel->mu);
+        h->channel->inbox.push_back(msg);
+        h->channel->cv.notify_all();
+        h->channel->cv.wait(lk, [&] { return h->channel->inbox.empty() && !h->channel->busy; });
+        sent.swap(h->channel->sent);
+    }
+    std::string records;
+    for (auto& s : sent) {
+        uint32_t len = (uint32_t)s.size();
+        records.append((const char*)&len, 4);
+        records.append(s);
+    }
+    if (out && (int)records.size() <= cap) memcpy(out, records.data(), records.size());
+    return (int)records.size();
+}
+
+// Kernel launches the executor made since the last call: one line each, the kernel's name and the
+// argument bytes it passed (after its pointer rewrite) in hex.
+int tso_exec_launches(char* out, int cap) {
+    std::lock_guard<std::mutex> g(g_launch_mu);
+    std::string text;
+    static const char* hex = "0123456789abcdef";
+    for (auto& l : g_launches) {
+        text += l.kernel;
+        for (auto& a : l.args) {
+            text += ' ';
+            for (unsigned char c : a) { text += hex[c >> 4]; text += hex[c & 15]; }
+            if (a.empty()) text += '-';
+        }
+        text += '\n';
+    }
+    const int need = (int)text.size() + 1;
+    if (out && need <= cap) {
+        memcpy(out, text.c_str(), need);
+        g_launches.clear();
+    }
+    return need;
+}
+
+// Executor ids that have reported a finished request to the controller (controller_sync_queue).
+int tso_exec_completions(int* out, int cap) {
+    int n = 0;
+    while (!server::controller_sync_queue->empty()) {
+        int id = server::controller_sync_queue->front();
+        server::controller_sync_queue->pop();
+        if (out && n < cap) out[n] = id;
+        ++n;
+    }
+    return n;
+}
+
+void tso_exec_reset(void) {
+    std::lock_guard<std::mutex> g(g_launch_mu);
+    g_expected_arg_sizes.clear();
+    g_launches.clear();
+    kernel_model_access_loc().clear();
+    while (!server::controller_sync_queue->empty()) server::controller_sync_queue->pop();
 }
 #endif
 

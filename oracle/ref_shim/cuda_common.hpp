@@ -57,6 +57,7 @@ enum cudaMemcpyKind {
     cudaMemcpyDefault = 4
 };
 static const unsigned int cudaStreamNonBlocking = 1;
+inline int format_as(cudaMemcpyKind k) { return (int)k; }   // how the reference's logger prints it
 
 namespace torpor_ref_fake {
 
@@ -201,6 +202,72 @@ inline cudaError_t cudaDeviceCanAccessPeer(int* can, int, int) { *can = 0; retur
 inline cudaError_t cudaDeviceEnablePeerAccess(int, unsigned int) { return cudaSuccess; }
 #endif
 #endif  // TORPOR_REF_WITH_CONTROLLER
+
+#ifdef TORPOR_REF_WITH_EXECUTOR
+// What include/server/cuda_server.hpp (the executor) needs beyond the swap-path headers: the
+// message classes (stand-ins generated from the reference's .proto files by gen_pb_shim.py),
+// cuDNN / cuBLAS names, and the rest of the CUDA calls its services make.  Only the memory
+// services and the kernel launch are exercised; everything else merely has to compile.
+#include "cudarpc.pb.h"
+#include "signal.pb.h"
+#include "cudarpc.using.h"
+#include "signal.using.h"
+#include <set>
+
+typedef void* cudnnHandle_t;
+typedef void* cudnnTensorDescriptor_t;
+typedef void* cudnnFilterDescriptor_t;
+typedef void* cudnnConvolutionDescriptor_t;
+typedef int cudnnStatus_t;
+typedef int cudnnDataType_t;
+typedef int cudnnTensorFormat_t;
+typedef int cudnnMathType_t;
+typedef int cudnnConvolutionMode_t;
+typedef int cudnnConvolutionFwdAlgo_t;
+typedef int cudnnBatchNormMode_t;
+struct cudnnConvolutionFwdAlgoPerf_t { int algo = 0; int status = 0; float time = 0; size_t memory = 0; int determinism = 0; int mathType = 0; int reserved[3] = {0, 0, 0}; };
+static const cudnnStatus_t CUDNN_STATUS_SUCCESS = 0;
+typedef void* cublasHandle_t;
+typedef int cublasStatus_t;
+typedef int cublasOperation_t;
+typedef int cublasMath_t;
+#define TORPOR_STUB(name) inline int name(...) { return 0; }   /* C variadic: some calls pass variable-length arrays */
+TORPOR_STUB(cudnnCreate) TORPOR_STUB(cudnnDestroy) TORPOR_STUB(cudnnSetStream)
+TORPOR_STUB(cudnnCreateTensorDescriptor) TORPOR_STUB(cudnnSetTensorNdDescriptor) TORPOR_STUB(cudnnDestroyTensorDescriptor)
+TORPOR_STUB(cudnnCreateFilterDescriptor) TORPOR_STUB(cudnnSetFilterNdDescriptor) TORPOR_STUB(cudnnDestroyFilterDescriptor)
+TORPOR_STUB(cudnnCreateConvolutionDescriptor) TORPOR_STUB(cudnnSetConvolutionNdDescriptor) TORPOR_STUB(cudnnDestroyConvolutionDescriptor)
+TORPOR_STUB(cudnnSetConvolutionGroupCount) TORPOR_STUB(cudnnSetConvolutionMathType) TORPOR_STUB(cudnnGetConvolutionForwardAlgorithm_v7)
+TORPOR_STUB(cudnnConvolutionForward) TORPOR_STUB(cudnnBatchNormalizationForwardInference)
+TORPOR_STUB(cublasCreate) TORPOR_STUB(cublasDestroy) TORPOR_STUB(cublasSetStream) TORPOR_STUB(cublasSetMathMode)
+TORPOR_STUB(cublasGetMathMode) TORPOR_STUB(cublasSgemm) TORPOR_STUB(cublasSgemmStridedBatched)
+#define cudnnCheck(ans) { (void)(ans); }
+
+#ifdef TORPOR_REF_FAKE_CUDA
+typedef int CUresult;
+typedef int CUdevice;
+typedef int cudaDeviceAttr;
+typedef int cudaStreamCaptureStatus;
+static const unsigned int cudaStreamDefault = 0;
+struct cudaDeviceProp { char name[256]; size_t totalGlobalMem; int major, minor, multiProcessorCount; };
+struct dim3 { unsigned int x, y, z; dim3(unsigned int a = 1, unsigned int b = 1, unsigned int c = 1) : x(a), y(b), z(c) {} };
+TORPOR_STUB(cuInit) TORPOR_STUB(cuDriverGetVersion) TORPOR_STUB(cuDevicePrimaryCtxGetState)
+TORPOR_STUB(cudaDriverGetVersion) TORPOR_STUB(cudaRuntimeGetVersion) TORPOR_STUB(cudaGetLastError)
+TORPOR_STUB(cudaDeviceGetAttribute) TORPOR_STUB(cudaStreamCreate) TORPOR_STUB(cudaStreamCreateWithFlags)
+TORPOR_STUB(cudaStreamIsCapturing) TORPOR_STUB(cudaStreamGetCaptureInfo) TORPOR_STUB(cudaGetSymbolAddress)
+TORPOR_STUB(cudaEventCreateWithFlags) TORPOR_STUB(cudaEventQuery)
+inline cudaError_t cudaGetDeviceProperties(cudaDeviceProp* p, int) { memset(p, 0, sizeof(*p)); return cudaSuccess; }
+namespace torpor_ref_fake { inline int& device_count() { static int n = 4; return n; } }
+inline cudaError_t cudaGetDeviceCount(int* n) { *n = torpor_ref_fake::device_count(); return cudaSuccess; }
+inline cudaError_t cudaDeviceCanAccessPeer(int* can, int, int) { *can = 0; return cudaSuccess; }
+inline cudaError_t cudaDeviceEnablePeerAccess(int, unsigned int) { return cudaSuccess; }
+// A launch is not run: the harness keeps the kernel and the argument words the executor passed.
+namespace torpor_ref_fake { void record_launch(const void* func, void** args); }
+inline cudaError_t cudaLaunchKernel(const void* func, dim3, dim3, void** args, size_t, cudaStream_t) {
+    torpor_ref_fake::record_launch(func, args);
+    return cudaSuccess;
+}
+#endif
+#endif  // TORPOR_REF_WITH_EXECUTOR
 
 #define cudaCheck(ans) { cudaAssert((ans), __FILE__, __LINE__); }
 inline void cudaAssert(cudaError_t err, const char* file, int line, bool abort_flag = false) {

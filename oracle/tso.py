@@ -21,6 +21,7 @@ LIBS = {
     "oracle": os.path.join(HERE, "libtorpor_oracle.so"),
     "ref_fake": os.path.join(HERE, "_ref", "libtorpor_ref_fake.so"),
     "ref_cuda": os.path.join(HERE, "_ref", "libtorpor_ref_cuda.so"),
+    "ref_exec": os.path.join(HERE, "_ref", "libtorpor_ref_exec.so"),   # ref_fake's contents plus the reference's executor
 }
 
 
@@ -95,6 +96,20 @@ class TsoLib:
             "tso_ctrl_request": (i32, [vp, i32, cp, cp, C.c_char_p, i32]),
             "tso_ctrl_complete": (i32, [vp, i32, C.c_char_p, i32]),
         }
+        executor = {
+            "tso_exec_register_kernel": (None, [cp]),
+            "tso_exec_create": (vp, [i32, u64, i32]),
+            "tso_exec_manager": (vp, [vp]),
+            "tso_exec_destroy": (None, [vp]),
+            "tso_exec_signal": (None, [vp, i32, cp]),
+            "tso_exec_queries": (i32, [vp, vp, i32, vp, i32]),
+            "tso_exec_launches": (i32, [C.c_char_p, i32]),
+            "tso_exec_completions": (i32, [C.POINTER(C.c_int), i32]),
+            "tso_exec_reset": (None, []),
+        }
+        self.has_executor = hasattr(L, "tso_exec_create")
+        if self.has_executor:
+            sig.update(executor)
         self.has_scheduler = hasattr(L, "tso_sched_create")   # the restatement only
         if self.has_scheduler:
             sig.update(sched)
@@ -119,6 +134,9 @@ class TsoLib:
 
     def scheduler(self, n, policy, pcie_pairs, nvlink) -> "TsoScheduler":
         return TsoScheduler(self, n, policy, pcie_pairs, nvlink)
+
+    def executor(self, server_id=0, budget=0, gpu_count=1) -> "TsoExecutor":
+        return TsoExecutor(self, server_id, budget, gpu_count)
 
     def controller(self, n, mem_limit_bytes, sched_policy, evict_policy, pcie_pairs, nvlink) -> "TsoController":
         return TsoController(self, n, mem_limit_bytes, sched_policy, evict_policy, pcie_pairs, nvlink)
@@ -221,6 +239,63 @@ class TsoScheduler:
         out = (C.c_int * 3)()
         self.L.tso_sched_decide(self.h, func.encode(), out)
         return out[0], out[1], out[2]
+
+
+class TsoExecutor:
+    """The reference's CUDAExecutor (include/server/cuda_server.hpp) with its loop running on a thread:
+    signals as the controller sends them, serialised QueryLists as the clients send them."""
+
+    def __init__(self, lib: TsoLib, server_id, budget, gpu_count):
+        self.lib, self.L = lib, lib.lib
+        self.server_id = server_id
+        self.h = self.L.tso_exec_create(server_id, budget, gpu_count)
+        if not self.h:
+            raise RuntimeError("tso_exec_create failed")
+        # the executor's own memory manager, for the table dumps (a view: never closed through it)
+        self.manager = TsoManager.__new__(TsoManager)
+        self.manager.L, self.manager.server_id, self.manager.h = self.L, server_id, self.L.tso_exec_manager(self.h)
+        self.buf = C.create_string_buffer(1 << 20)
+
+    def close(self):
+        if self.h:
+            self.manager.h = None
+            self.L.tso_exec_destroy(self.h)
+            self.h = None
+
+    def register_kernel(self, name: str):
+        self.L.tso_exec_register_kernel(name.encode())
+
+    def signal(self, sig: int, func: str):
+        self.L.tso_exec_signal(self.h, sig, func.encode())
+
+    def handle(self, query_list: bytes) -> List[bytes]:
+        """One serialised QueryList in, the serialised responses the executor sent while handling it out."""
+        src = C.create_string_buffer(query_list, len(query_list))
+        need = self.L.tso_exec_queries(self.h, src, len(query_list), self.buf, len(self.buf))
+        if need > len(self.buf):
+            raise RuntimeError("responses larger than the buffer")
+        raw, out, pos = self.buf.raw[:need], [], 0
+        while pos < need:
+            n = int.from_bytes(raw[pos:pos + 4], "little")
+            out.append(raw[pos + 4:pos + 4 + n])
+            pos += 4 + n
+        return out
+
+    def launches(self):
+        """[(kernel name, [argument bytes, ...])] since the last call, as passed to cudaLaunchKernel."""
+        need = self.L.tso_exec_launches(self.buf, len(self.buf))
+        if need > len(self.buf):
+            raise RuntimeError("launch list larger than the buffer")
+        out = []
+        for ln in self.buf.value.decode().splitlines():
+            parts = ln.split(" ")
+            out.append((parts[0], [b"" if a == "-" else bytes.fromhex(a) for a in parts[1:]]))
+        return out
+
+    def completions(self) -> List[int]:
+        arr = (C.c_int * 64)()
+        n = self.L.tso_exec_completions(arr, 64)
+        return list(arr[:min(n, 64)])
 
 
 class TsoController:

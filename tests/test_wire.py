@@ -221,3 +221,100 @@ def test_server_at_both_wire_surfaces(built):
     for e in engines:
         e.close()
     repo_reset()
+
+
+def _ref_exec():
+    from oracle import tso
+    if not tso.available("ref_exec"):
+        pytest.skip("oracle/_ref/libtorpor_ref_exec.so not built (reference tree absent)")
+    lib = tso.load("ref_exec")
+    lib.reset_world()
+    lib.lib.tso_exec_reset()
+    return lib
+
+
+@pytest.mark.parametrize("name", ["bert_tiny", "resnet50"])
+def test_executor_matches_the_reference_executor(built, name):
+    """The same serialised client stream and controller signals through the reference's own
+    CUDAExecutor (include/server/cuda_server.hpp compiled where it lies, its loop running on a thread
+    over the reference's MemoryManager on the host-memory CUDA stand-in) and through WireExecutor on a
+    plan-only engine: every response is byte-identical, every kernel launch receives the same argument
+    bytes after the pointer rewrite, and the tables end up word for word the same."""
+    lib = _ref_exec()
+    ws = W.weight_set(name)
+    zeros = lambda i: np.zeros(ws.tensors[i].nbytes, dtype=np.uint8)
+    func = "7"                                        # executors derive the client's address from the name (cuda_server.hpp:223)
+    ref = lib.executor(0, 0, 1)
+    repo_reset()
+    eng = MemoryManager(0, device=-1)
+    mine = wire.WireExecutor(eng)
+    kernels = [f"k{i}" for i in range(7)]
+    for k in kernels:
+        ref.register_kernel(k)
+
+    def both(queries):
+        """One QueryList with these (type, message, fields) entries to both executors; responses must agree."""
+        ql = wire.encode("QueryList", {"queries": [{"type": t, "query": wire.encode(m, f), "client_id": 1} for t, m, f in queries]})
+        a, b = ref.handle(ql), mine.handle(ql)
+        assert a == b, (queries[0][1], a, b)
+        return a
+
+    def launches_agree():
+        got = mine.launched[:]
+        mine.launched.clear()
+        assert ref.launches() == [(k, list(args)) for k, args in got]
+        return got
+
+    ref.signal(wire.SIG_STARTUP, func); mine.signal(wire.SIG_STARTUP, func)
+    bv, tv, batch = {}, {}, []
+    for c in W.cold_start_stream(ws):
+        if c.op == "malloc":
+            if batch:                                  # uploads travel in batches of up to 30, as the client's sender makes them
+                both(batch); batch = []
+            r = both([(wire.Q_MALLOC, "cudaMallocQuery", {"size": c.size})])
+            if c.is_model:
+                bv[c.block] = wire.decode("cudaMallocResponse", r[0])["ptr"]
+        elif c.op == "memcpy":
+            tv[c.tensor] = bv[c.block] + c.offset
+            batch.append((wire.Q_MEMCPY_ASYNC, "cudaMemcpyAsyncQuery", {"kind": wire.H2D, "dst": tv[c.tensor], "count": c.size,
+                                                                        "payload": zeros(c.tensor).tobytes(), "stream": bytes(8)}))
+            if len(batch) == 30:
+                both(batch); batch = []
+        elif c.op == "sync_done":
+            if batch:
+                both(batch); batch = []
+            both([(wire.Q_DEVICE_SYNCHRONIZE, "genericResponse", {})])
+        elif c.op == "access":
+            args = [struct.pack("<Q", tv[c.tensor]), struct.pack("<QQ", 0x1234, tv[c.tensor]), struct.pack("<i", c.tensor)]
+            both([(wire.Q_LAUNCH_KERNEL, "cudaLaunchKernelQuery", {"function": kernels[c.tensor % 7], "grid_dim_x": 1, "args": args,
+                                                                  "stream": bytes(8)})])
+    first_run = launches_agree()
+    assert len(first_run) == len(ws.tensors)
+    # the request ends: the reference's executor ends it when the result is copied back (cuda_server.hpp:1043-1049)
+    ref.handle(wire.encode("QueryList", {"queries": [{"type": wire.Q_MEMCPY_ASYNC, "client_id": 1, "query": wire.encode(
+        "cudaMemcpyAsyncQuery", {"kind": wire.D2H, "src": tv[0], "dst": 0x7000, "count": 16, "stream": bytes(8)})}]}))
+    assert ref.completions() == [0]
+    mine.complete()
+
+    def tables_agree():
+        assert np.array_equal(ref.manager.dump_blocks(func), eng.dump_blocks(func))
+        assert np.array_equal(ref.manager.dump_params(func), eng.dump_params(func))
+
+    tables_agree()
+    for cycle in range(2):
+        for sig in (wire.SIG_UNLOAD, wire.SIG_LOAD, wire.SIG_EXECUTE):
+            ref.signal(sig, func); mine.signal(sig, func)
+        ref.manager.wait_ready(func)
+        tables_agree()
+        moved = {int(r[0]): int(r[3]) for r in eng.dump_params(func)}
+        for t in (0, len(ws.tensors) // 2, len(ws.tensors) - 1):
+            args = [struct.pack("<Q", tv[t]), struct.pack("<QQ", 0x1234, tv[t]), struct.pack("<i", t)]
+            both([(wire.Q_LAUNCH_KERNEL, "cudaLaunchKernelQuery", {"function": kernels[t % 7], "grid_dim_x": 1, "args": args, "stream": bytes(8)})])
+        steady = launches_agree()
+        assert [struct.unpack("<Q", a[0])[0] for _, a in steady] == [moved[tv[t]] for t in (0, len(ws.tensors) // 2, len(ws.tensors) - 1)]
+        ref.handle(wire.encode("QueryList", {"queries": [{"type": wire.Q_MEMCPY_ASYNC, "client_id": 1, "query": wire.encode(
+            "cudaMemcpyAsyncQuery", {"kind": wire.D2H, "src": tv[0], "dst": 0x7000, "count": 16, "stream": bytes(8)})}]}))
+        assert ref.completions() == [0]
+        mine.complete()
+    ref.close(); eng.close()
+    repo_reset(); lib.reset_world(); lib.lib.tso_exec_reset()
