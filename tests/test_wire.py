@@ -318,3 +318,58 @@ def test_executor_matches_the_reference_executor(built, name):
         mine.complete()
     ref.close(); eng.close()
     repo_reset(); lib.reset_world(); lib.lib.tso_exec_reset()
+
+
+def test_replica_load_signal_through_both_executors(built):
+    """Two executors each: a model cold-started on GPU 0 is loaded on GPU 1 by the controller's signal
+    `Load + 1 + 0` (copy from GPU 0's replica), then by `Load + 1 + 1` (its own id: from the host store,
+    cuda_server.hpp:246-252); GPU 1's tables agree with the reference executor's after each."""
+    lib = _ref_exec()
+    ws = W.weight_set("bert_tiny")
+    func = "3"
+    refs = [lib.executor(g, 0, 2) for g in range(2)]
+    repo_reset()
+    engines = [MemoryManager(0, device=-1, server_id=g, gpu_count=2) for g in range(2)]
+    mines = [wire.WireExecutor(e) for e in engines]
+    for r in refs:
+        r.register_kernel("k")
+
+    def both(g, queries):
+        ql = wire.encode("QueryList", {"queries": [{"type": t, "query": wire.encode(m, f), "client_id": 1} for t, m, f in queries]})
+        a, b = refs[g].handle(ql), mines[g].handle(ql)
+        assert a == b
+        return a
+
+    refs[0].signal(wire.SIG_STARTUP, func); mines[0].signal(wire.SIG_STARTUP, func)
+    bv, tv = {}, {}
+    for c in W.cold_start_stream(ws):
+        if c.op == "malloc":
+            r = both(0, [(wire.Q_MALLOC, "cudaMallocQuery", {"size": c.size})])
+            if c.is_model:
+                bv[c.block] = wire.decode("cudaMallocResponse", r[0])["ptr"]
+        elif c.op == "memcpy":
+            tv[c.tensor] = bv[c.block] + c.offset
+            both(0, [(wire.Q_MEMCPY_ASYNC, "cudaMemcpyAsyncQuery", {"kind": wire.H2D, "dst": tv[c.tensor], "count": c.size,
+                                                                    "payload": bytes(c.size), "stream": bytes(8)})])
+        elif c.op == "sync_done":
+            both(0, [(wire.Q_DEVICE_SYNCHRONIZE, "genericResponse", {})])
+        elif c.op == "access":
+            both(0, [(wire.Q_LAUNCH_KERNEL, "cudaLaunchKernelQuery", {"function": "k", "grid_dim_x": 1, "stream": bytes(8),
+                                                                     "args": [struct.pack("<Q", tv[c.tensor])]})])
+    refs[0].handle(wire.encode("QueryList", {"queries": [{"type": wire.Q_MEMCPY_ASYNC, "client_id": 1, "query": wire.encode(
+        "cudaMemcpyAsyncQuery", {"kind": wire.D2H, "src": tv[0], "dst": 0x7000, "count": 16, "stream": bytes(8)})}]}))
+    mines[0].complete()
+    lib.set_model_status(func, 0, True); ModelRepo.add_model_info(func, 0)       # the controller registers the replica
+
+    for sig in (wire.SIG_LOAD + 1 + 0, wire.SIG_UNLOAD, wire.SIG_LOAD + 1 + 1):
+        refs[1].signal(sig, func); mines[1].signal(sig, func)
+        if sig != wire.SIG_UNLOAD:
+            refs[1].manager.wait_ready(func)
+        assert np.array_equal(refs[1].manager.dump_blocks(func), engines[1].dump_blocks(func))
+        assert np.array_equal(refs[1].manager.dump_params(func), engines[1].dump_params(func))
+        assert engines[1].check_alloc(func) == (sig != wire.SIG_UNLOAD)
+    for r in refs:
+        r.close()
+    for e in engines:
+        e.close()
+    repo_reset(); lib.reset_world(); lib.lib.tso_exec_reset()
