@@ -274,6 +274,8 @@ def test_executor_matches_the_reference_executor(built, name):
             r = both([(wire.Q_MALLOC, "cudaMallocQuery", {"size": c.size})])
             if c.is_model:
                 bv[c.block] = wire.decode("cudaMallocResponse", r[0])["ptr"]
+            else:
+                work = wire.decode("cudaMallocResponse", r[0])["ptr"]       # the activations' block
         elif c.op == "memcpy":
             tv[c.tensor] = bv[c.block] + c.offset
             batch.append((wire.Q_MEMCPY_ASYNC, "cudaMemcpyAsyncQuery", {"kind": wire.H2D, "dst": tv[c.tensor], "count": c.size,
@@ -285,7 +287,9 @@ def test_executor_matches_the_reference_executor(built, name):
                 both(batch); batch = []
             both([(wire.Q_DEVICE_SYNCHRONIZE, "genericResponse", {})])
         elif c.op == "access":
-            args = [struct.pack("<Q", tv[c.tensor]), struct.pack("<QQ", 0x1234, tv[c.tensor]), struct.pack("<i", c.tensor)]
+            # weight pointer; a scalar-looking word and the weight again; the activations' block and a pointer into it; an int
+            args = [struct.pack("<Q", tv[c.tensor]), struct.pack("<QQ", 0x1234, tv[c.tensor]),
+                    struct.pack("<QQ", work, work + 4096 + 8 * c.tensor), struct.pack("<i", c.tensor)]
             both([(wire.Q_LAUNCH_KERNEL, "cudaLaunchKernelQuery", {"function": kernels[c.tensor % 7], "grid_dim_x": 1, "args": args,
                                                                   "stream": bytes(8)})])
     first_run = launches_agree()
@@ -307,10 +311,16 @@ def test_executor_matches_the_reference_executor(built, name):
         ref.manager.wait_ready(func)
         tables_agree()
         moved = {int(r[0]): int(r[3]) for r in eng.dump_params(func)}
+        # a request's own workspace: allocated, used (block and interior pointers), freed, as a client's allocator does
+        scratch = [wire.decode("cudaMallocResponse", both([(wire.Q_MALLOC, "cudaMallocQuery", {"size": sz})])[0])["ptr"]
+                   for sz in (2 << 20, 20 << 20, 48 << 20)]
         for t in (0, len(ws.tensors) // 2, len(ws.tensors) - 1):
-            args = [struct.pack("<Q", tv[t]), struct.pack("<QQ", 0x1234, tv[t]), struct.pack("<i", t)]
+            args = [struct.pack("<Q", tv[t]), struct.pack("<QQ", 0x1234, tv[t]),
+                    struct.pack("<QQ", work, scratch[t % 3] + 512), struct.pack("<i", t)]
             both([(wire.Q_LAUNCH_KERNEL, "cudaLaunchKernelQuery", {"function": kernels[t % 7], "grid_dim_x": 1, "args": args, "stream": bytes(8)})])
         steady = launches_agree()
+        both([(wire.Q_FREE, "cudaFreeQuery", {"ptr": p}) for p in scratch[:2]])
+        tables_agree()
         assert [struct.unpack("<Q", a[0])[0] for _, a in steady] == [moved[tv[t]] for t in (0, len(ws.tensors) // 2, len(ws.tensors) - 1)]
         ref.handle(wire.encode("QueryList", {"queries": [{"type": wire.Q_MEMCPY_ASYNC, "client_id": 1, "query": wire.encode(
             "cudaMemcpyAsyncQuery", {"kind": wire.D2H, "src": tv[0], "dst": 0x7000, "count": 16, "stream": bytes(8)})}]}))
