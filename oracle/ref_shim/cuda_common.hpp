@@ -102,6 +102,14 @@ inline void* dev_alloc(size_t size) {
         void* got = mmap(want, grow_to - s.mapped_end, PROT_READ | PROT_WRITE,
                          MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE | MAP_FIXED_NOREPLACE, -1, 0);
         if (got != want) {
+            // Another checker library of this process (each has its own copy of this stand-in) may
+            // have left the range mapped, e.g. after a test that failed half way: its contents are
+            // stale by then, so the range is taken over.
+            if (got != MAP_FAILED) munmap(got, grow_to - s.mapped_end);
+            got = mmap(want, grow_to - s.mapped_end, PROT_READ | PROT_WRITE,
+                       MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE | MAP_FIXED, -1, 0);
+        }
+        if (got != want) {
             fprintf(stderr, "torpor_ref_fake: cannot map canonical device range at %p\n", want);
             abort();
         }

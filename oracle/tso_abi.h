@@ -118,6 +118,27 @@ void tso_ctrl_destroy(void* c);
 int tso_ctrl_request(void* c, int type, const char* func, const char* payload, char* trace, int cap);
 int tso_ctrl_complete(void* c, int executor, char* trace, int cap);
 
+/* The reference's executor (include/server/cuda_server.hpp), exported by libtorpor_ref_exec.so only.
+ * tso_exec_create builds a CUDAExecutor on the fake GPU `id` and runs its loop (cuda_server.hpp:99-262)
+ * on a thread; tso_exec_signal is what the controller does to it (controller.hpp:429-431), and
+ * tso_exec_queries hands it one serialised QueryList as a client's sender would, returning what it
+ * sent back (records of a 4-byte little-endian length + serialised response; the return value is the
+ * size the records need).  Kernels are looked up by name in a table the caller fills
+ * (tso_exec_register_kernel; the reference fills it from the fat binaries it links); a launch is
+ * recorded, not run: tso_exec_launches returns one line per launch, the kernel's name and each
+ * argument's bytes in hex as the executor passed them to cudaLaunchKernel.  tso_exec_manager is the
+ * executor's own MemoryManager as a handle for the tso_dump_* / tso_wait_ready calls above (never
+ * pass it to tso_destroy).  tso_exec_completions drains controller_sync_queue. */
+void tso_exec_register_kernel(const char* name);
+void* tso_exec_create(int id, uint64_t budget_bytes, int gpu_count);
+void* tso_exec_manager(void* exec);
+void tso_exec_destroy(void* exec);
+void tso_exec_signal(void* exec, int signal, const char* func);
+int tso_exec_queries(void* exec, const void* query_list, int n, void* out, int cap);
+int tso_exec_launches(char* out, int cap);
+int tso_exec_completions(int* out, int cap);
+void tso_exec_reset(void);
+
 const char* tso_impl_name(void);
 
 #ifdef __cplusplus
