@@ -548,8 +548,7 @@ void tso_exec_register_kernel(const char* name) {
 
 void* tso_exec_create(int id, uint64_t budget_bytes, int gpu_count) {
     torpor_ref_fake::device_count() = gpu_count;
-    unsetenv("BLOCK_MANAGER");
-    setenv("IO_THREAD_NUM", "2", 1);
+    setenv("IO_THREAD_NUM", "2", 1);            // BLOCK_MANAGER is the caller's to set, as for the server itself
     auto* h = new ExecHandle();
     h->ex = new server::CUDAExecutor(id, (size_t)budget_bytes, &h->ctx);
     h->channel = &torpor_ref_exec::channel_of((void*)&h->ex->srv_pull_handler_);

@@ -40,7 +40,9 @@ def random_stream(seed, block_manager):
         if r < 0.08:
             ops.append(("free_ws", f))
         elif r < 0.14:
-            ops.append(("malloc_ws", f, int(BLOCK_SIZES[int(rng.integers(0, len(BLOCK_SIZES)))])))
+            # a later request's workspace: half of them arrive outside any tracking (an ordinary request through
+            # the executor), so the pool's active-chunk lists are not closed after them (block_manager.hpp:275-286)
+            ops.append(("malloc_ws", f, int(BLOCK_SIZES[int(rng.integers(0, len(BLOCK_SIZES)))]), bool(rng.random() < 0.5)))
         elif resident[f]:
             ops.append(("evict", f)); resident[f] = False
         else:
@@ -79,9 +81,12 @@ def replay(backend, ops):
                     m.free(op[1], ws_ptrs[op[1]].pop(0))
                 rec.snap(m, op[1], "free")
             elif op[0] == "malloc_ws":
-                m.track_begin(op[1])      # later mallocs arrive while the function is active
-                ws_ptrs[op[1]].append(m.malloc(op[1], op[2], False))
-                m.track_end(op[1])
+                if op[3]:
+                    m.track_begin(op[1])  # during the function's first run
+                    ws_ptrs[op[1]].append(m.malloc(op[1], op[2], False))
+                    m.track_end(op[1])
+                else:
+                    ws_ptrs[op[1]].append(m.malloc(op[1], op[2], False))
                 rec.snap(m, op[1], "malloc")
             elif op[0] == "evict":
                 m.evict(op[1]); rec.snap(m, op[1], "evict")

@@ -2,6 +2,7 @@
 the messages of proto/cudarpc.proto and proto/signal.proto that touch memory, and an
 executor fed with serialised QueryLists builds the same tables as direct calls and rewrites
 kernel-argument pointers the way the reference's launch path does."""
+import os
 import struct
 
 import numpy as np
@@ -230,6 +231,7 @@ def _ref_exec():
     lib = tso.load("ref_exec")
     lib.reset_world()
     lib.lib.tso_exec_reset()
+    os.environ["BLOCK_MANAGER"] = "Buddy"     # written, not removed: other checkers set it with setenv behind Python's back
     return lib
 
 

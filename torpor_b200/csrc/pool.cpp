@@ -66,8 +66,16 @@ struct Chunk {
         uint64_t round;
         int step;
         shape(regular, size, &round, &step);
-        if (step == 0) { step = 1; round = slot_bytes(); }
         if (ptr < base || ptr >= base + kChunkBytes || (ptr - base) % slot_bytes() != 0) return false;
+        if (!regular && size == kRegular2MiB) {
+            // A 2 MiB block is never taken from an irregular chunk; it can only be released into one
+            // when the same address has been granted by two chunk objects over one 128 MiB and the
+            // later grant owns the map entry.  The reference's zero step then flips no slot and only
+            // adds the 2 MiB to the chunk's free bytes (:108-120); so does this.
+            avail += size;
+            return true;
+        }
+        if (step == 0) { step = 1; round = slot_bytes(); }
         int s = (int)((ptr - base) / slot_bytes());
         for (int i = 0; i < step && s + i < slots; ++i) free_mask |= 1ull << (s + i);
         avail += round;
@@ -91,8 +99,13 @@ struct ChunkHeap {
         std::pop_heap(c.begin(), c.end(), [this](int a, int b) { return less(a, b); });
         c.pop_back();
     }
+    // The reference removes the first entry that *equals* the chunk, and its chunks compare by base
+    // address (block_manager.hpp:124,155-161).  That matters when a retired chunk object is still
+    // listed somewhere and a new one has since been made over the same 128 MiB: the entry removed is
+    // the first with that base, not necessarily the object asked for.
     void remove(int id) {
-        auto it = std::find(c.begin(), c.end(), id);
+        const uint64_t base = (*chunks)[id].base;
+        auto it = std::find_if(c.begin(), c.end(), [&](int other) { return (*chunks)[other].base == base; });
         if (it != c.end()) {
             c.erase(it);
             std::make_heap(c.begin(), c.end(), [this](int a, int b) { return less(a, b); });
@@ -194,6 +207,7 @@ public:
                     irregular_heap_.remove(id);
                 }
             }
+            held_[id]--;
             owner_.erase(it);
             return 0;
         }
@@ -261,32 +275,41 @@ private:
     }
 
     int granted(uint64_t p, int id, DevAddr* out) {
+        auto prev = owner_.find(p);
+        if (prev != owner_.end()) held_[prev->second]--;   // the same address granted again: the entry changes hands
         owner_[p] = id;
+        held_[id]++;
         out->phys = p;
         out->canon = canon_base_ + (p - base_);
         return 0;
     }
 
+    // Chunk objects live as long as anything refers to them, as the reference's shared pointers do:
+    // a list, a heap, or an address that was granted from them and has not been released yet.
+    bool referenced(int id) const {
+        auto in = [id](const std::vector<int>& v) { return std::find(v.begin(), v.end(), id) != v.end(); };
+        return held_[id] > 0 || in(active_regular_) || in(active_irregular_) || in(deactive_regular_) ||
+               in(deactive_irregular_) || in(regular_heap_.c) || in(irregular_heap_.c);
+    }
+
     int new_chunk(uint64_t base, bool regular) {
-        if (!spare_ids_.empty()) {
-            int id = spare_ids_.back();
-            spare_ids_.pop_back();
-            chunks_[id] = Chunk(base, regular);
-            return id;
+        // ids of retired chunks are reused once nothing refers to them any more
+        for (size_t k = 0; k < retired_.size(); ++k) {
+            const int id = retired_[k];
+            if (!referenced(id)) {
+                retired_.erase(retired_.begin() + (long)k);
+                chunks_[id] = Chunk(base, regular);
+                return id;
+            }
         }
         chunks_.emplace_back(base, regular);
+        held_.push_back(0);
         return (int)chunks_.size() - 1;
     }
 
     void retire(int id) {
         free_chunks_.push_back(chunks_[id].base);
-        // The id may still sit in an active list if a block was freed during
-        // tracking; only recycle ids that nothing refers to.
-        bool referenced = std::find(active_regular_.begin(), active_regular_.end(), id) != active_regular_.end() ||
-                          std::find(active_irregular_.begin(), active_irregular_.end(), id) != active_irregular_.end() ||
-                          std::find(regular_heap_.c.begin(), regular_heap_.c.end(), id) != regular_heap_.c.end() ||
-                          std::find(irregular_heap_.c.begin(), irregular_heap_.c.end(), id) != irregular_heap_.c.end();
-        if (!referenced) spare_ids_.push_back(id);
+        if (std::find(retired_.begin(), retired_.end(), id) == retired_.end()) retired_.push_back(id);
     }
 
     uint64_t budget_;
@@ -296,7 +319,8 @@ private:
 
     std::vector<uint64_t> free_chunks_;  // LIFO: back() is taken first
     std::vector<Chunk> chunks_;
-    std::vector<int> spare_ids_;
+    std::vector<int> retired_;           // ids whose 128 MiB went back to the free list; reusable once unreferenced
+    std::vector<int> held_;              // per chunk id: granted addresses that still map to it in owner_
     std::vector<int> active_regular_, deactive_regular_, active_irregular_, deactive_irregular_;
     ChunkHeap regular_heap_, irregular_heap_;
     std::unordered_map<uint64_t, int> owner_;  // granted address -> chunk id (requested_to_block_map_)
