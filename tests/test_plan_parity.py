@@ -176,3 +176,44 @@ def test_swap_in_that_does_not_fit_leaves_nothing_behind():
     m.swap_in("C")
     assert m.check_alloc("C") and len(spans("C")) == 16
     m.close(); repo_reset()
+
+
+def test_guard_against_granting_a_blocks_name_again(monkeypatch):
+    """A block is named by the first address it was given.  After an eviction that address is free, and
+    the pool's LIFO order hands it straight to the function's next malloc: the reference then replaces
+    the old block's entry with the new block (model_repo.hpp:133-141) and the model has lost a block.
+    The engine does the same by default (the reference's decisions, one for one) and keeps both
+    blocks with TORPOR_SWAP_GUARD_NAMES=1."""
+    from torpor_b200.memory_manager import MemoryManager, repo_reset
+    MiB = 1 << 20
+
+    def run():
+        repo_reset()
+        m = MemoryManager(0, device=-1)
+        m.track_begin("f")
+        blocks = [m.malloc("f", 32 * MiB, True), m.malloc("f", 48 * MiB, True)]
+        for b in blocks:
+            m.memcpy_h2d_model("f", b + 4096, np.zeros(64, dtype=np.uint8))
+        m.sync_done("f")
+        for b in blocks:
+            m.mark_access(b + 4096)
+        m.track_end("f")
+        m.evict("f")
+        extra = m.malloc("f", 32 * MiB, False)          # a later request's workspace
+        m.swap_in("f")
+        table = m.dump_blocks("f")
+        moved = [m.translate("f", b + 4096) for b in blocks]
+        m.close(); repo_reset()
+        return blocks, extra, table, moved
+
+    monkeypatch.delenv("TORPOR_SWAP_GUARD_NAMES", raising=False)
+    blocks, extra, table, moved = run()
+    assert extra in blocks and len(table) == 2           # as the reference: the new block took a model block's place
+
+    monkeypatch.setenv("TORPOR_SWAP_GUARD_NAMES", "1")
+    blocks, extra, table, moved = run()
+    assert extra not in blocks and len(table) == 3
+    assert sorted(int(r[0]) for r in table) == sorted(blocks + [extra])
+    spans = sorted((int(r[4]), int(r[4] + r[1])) for r in table if r[3])
+    assert len(spans) == 3 and all(spans[i][1] <= spans[i + 1][0] for i in range(2))     # three live, disjoint blocks
+    assert all(a != 0 for a in moved)

@@ -98,6 +98,48 @@ def replay(backend, ops):
     return rec.out
 
 
+def reuses_a_block_name(ops):
+    """True if somewhere in the stream a new block of a function is granted an address that already
+    names another live block of that function (its first address, free again since an eviction).  The
+    reference then overwrites the old block's entry and goes on with corrupted tables -- with real
+    bytes behind them it may crash -- so such streams are compared on the plan-only engine and the
+    restatement only.  Found by replaying on the plan-only engine, whose placement is the reference's."""
+    from torpor_b200.memory_manager import MemoryManager, repo_reset
+    repo_reset()
+    m, ws_ptrs, found = None, {}, False
+    try:
+        for op in ops:
+            if op[0] == "manager":
+                m = MemoryManager(0, device=-1, block_manager=op[1])
+            elif op[0] == "cold":
+                _, f, blocks, ws, access, seed = op
+                m.track_begin(f)
+                for size, pars in blocks:
+                    b = m.malloc(f, size, True)
+                    for off, n in pars:
+                        m.memcpy_h2d_model(f, b + off, np.zeros(n, dtype=np.uint8))
+                m.sync_done(f)
+                ws_ptrs[f] = [m.malloc(f, s, False) for s in ws]
+                m.track_end(f)
+            elif op[0] == "free_ws":
+                if ws_ptrs[op[1]]:
+                    m.free(op[1], ws_ptrs[op[1]].pop(0))
+            elif op[0] == "malloc_ws":
+                names = {int(r[0]) for r in m.dump_blocks(op[1])}
+                p = m.malloc(op[1], op[2], False)
+                found = found or p in names
+                ws_ptrs[op[1]].append(p)
+            elif op[0] == "evict":
+                m.evict(op[1])
+            elif op[0] == "swap_in":
+                m.swap_in(op[1])
+    finally:
+        if m:
+            m.close()
+        repo_reset()
+    return found
+
+
 @pytest.mark.parametrize("block_manager", ["Buddy", "Fixed"])
 @pytest.mark.parametrize("seed", range(12))
 def test_random_streams_agree_with_the_restatement(built, oracle_backend, seed, block_manager):
@@ -109,9 +151,11 @@ def test_random_streams_agree_with_the_restatement(built, oracle_backend, seed, 
 
 
 @pytest.mark.parametrize("block_manager", ["Buddy", "Fixed"])
-@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("seed", range(10))
 def test_restatement_agrees_with_the_reference_on_random_streams(built, oracle_backend, ref_backend, seed, block_manager):
     """Where the reference's own headers are built: the restatement follows them on the random
     streams too, not only on the recorded scenarios."""
     ops = random_stream(seed, block_manager)
+    if reuses_a_block_name(ops):
+        pytest.skip("a block's name is granted again in this stream: the reference corrupts its own tables there")
     scenarios.assert_same(replay(oracle_backend, ops), replay(ref_backend, ops), f"oracle vs reference, seed {seed} / {block_manager}")

@@ -522,6 +522,7 @@ static int engine_setup(const tsw_config* cfg, tsw_engine* e) {
     e->cfg = *cfg;
     e->plan = cfg->device < 0;
     e->server_id = cfg->server_id;
+    if (const char* g = getenv("TORPOR_SWAP_GUARD_NAMES")) e->guard_names = g[0] == '1';
     e->tile_host = cfg->tile_bytes_host > 0 ? (uint32_t)cfg->tile_bytes_host : 64u * 1024;
     e->tile_dev = cfg->tile_bytes_device > 0 ? (uint32_t)cfg->tile_bytes_device : 512u * 1024;
     if ((e->tile_host & 15u) || (e->tile_dev & 15u)) return fail(TSW_ERR_INVALID, "tile sizes must be multiples of 16 bytes");
@@ -722,6 +723,30 @@ int tsw_malloc(tsw_engine* e, const char* func, uint64_t size, int load_model_fl
     if (e->pool->acquire(size, true, &a) != 0)
         return fail(TSW_ERR_POOL_EXHAUSTED, "pool exhausted in malloc: " + e->pool->last_warning);
     Model* m = repo().get_or_create(func);
+    if (e->guard_names) {
+        // A block is named, for good, by the first address it was given (memory_manager.hpp:88-93).  Once
+        // the model has been evicted or has come back elsewhere, that address is free again, and the pool
+        // can grant it to a new block of the same model: in the reference the new block then replaces the
+        // old one's entry (model_repo.hpp:133-141) and the old block's parameters are lost.  With the
+        // guard on, such an address is set aside and another one is asked for.
+        std::vector<DevAddr> aside;
+        for (;;) {
+            auto clash = m->block_by_vaddr.find(a.phys);
+            if (clash == m->block_by_vaddr.end() || !m->blocks[clash->second].alive) break;
+            aside.push_back(a);
+            if (aside.size() > 64 || e->pool->acquire(size, true, &a) != 0) {
+                e->pool->finish_block_alloc();
+                for (auto& h : aside) e->pool->evict(h.phys, size, false);
+                e->pool->finish_release_block();
+                return fail(TSW_ERR_POOL_EXHAUSTED, "no address left that does not name another block of " + m->name);
+            }
+        }
+        if (!aside.empty()) {
+            e->pool->finish_block_alloc();      // close the lists before handing the set-aside addresses back
+            for (auto& h : aside) e->pool->evict(h.phys, size, false);
+            e->pool->finish_release_block();
+        }
+    }
     // malloc_block_for_model (model_repo.hpp:133-141)
     int bi;
     auto known = m->block_by_vaddr.find(a.phys);

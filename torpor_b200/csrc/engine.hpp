@@ -73,6 +73,7 @@ struct tsw_engine {
     int grid_ctas = 0;
     int grid_bulk = 0;   // CTAs of the bulk-copy mover
     int mover = 0;       // 0 = load/store kernel, 1 = bulk-copy kernel where alignment allows
+    bool guard_names = false;   // TORPOR_SWAP_GUARD_NAMES=1: never grant an address that names another live block of the model
     uint32_t tile_host = 0, tile_dev = 0;
 
     std::atomic<uint64_t> kernel_launches{0};
