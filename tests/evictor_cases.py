@@ -15,9 +15,9 @@ GPU_COUNT = 4
 BUDGET = 1000
 
 
-def sequences(kind: str, n_seq: int = 12, n_ops: int = 160) -> List[List[list]]:
+def sequences(kind: str, n_seq: int = 12, n_ops: int = 160, first: int = 0) -> List[List[list]]:
     out = []
-    for s in range(n_seq):
+    for s in range(first, first + n_seq):
         rng = np.random.default_rng([31, s, 0 if kind == "LRU" else 1])
         n_models = int(rng.integers(6, 20))
         sizes = {f"m{i}": int(rng.integers(40, 420)) for i in range(n_models)}
