@@ -20,8 +20,16 @@
 #include "torpor_swap.h"
 
 #include <chrono>
+#include <cstdio>
 #include <cstdlib>
 #include <iostream>
+
+// The executor checks try_insert_model_access with this (cuda_server.hpp:515,726,757-760,1255); the
+// reference defines it next to its manager (memory_manager.hpp:12-17), so the drop-in has to as well.
+#define memoryCheck(ans) { memoryAssert((ans), __FILE__, __LINE__); }
+inline void memoryAssert(bool ok, const char* file, int line) {
+    if (!ok) fprintf(stderr, "Memory access error: %s %d\n", file, line);
+}
 
 namespace server {
 namespace manager {
