@@ -1,22 +1,9 @@
-// Swap engine + C ABI.  See include/torpor_swap.h for the contract of every
-// entry point and the reference method it stands for.
+// Swap engine + C ABI, first part: process-wide state, helpers shared with engine_swap.cpp and
+// engine_share.cpp, the model repository, engine set-up and tear-down, and the cold-start
+// recorders.  See include/torpor_swap.h for the contract of every entry point and the reference
+// method it stands for.
 
-#include "engine.hpp"
-#include "kernels.hpp"
-
-#include <fcntl.h>
-#include <sys/mman.h>
-#include <sys/stat.h>
-#include <unistd.h>
-
-#include <algorithm>
-#include <chrono>
-#include <cstdio>
-#include <cstdlib>
-#include <cstring>
-#include <thread>
-
-#include <cuda_runtime.h>
+#include "engine_internal.hpp"
 
 namespace tsw {
 
@@ -32,15 +19,8 @@ Repo& repo() {
     return r;
 }
 
-static std::mutex g_engines_mu;
-static std::map<int, tsw_engine*> g_engines;  // server id -> engine of this process
-
-#define TSW_CUDA(call)                                                                             \
-    do {                                                                                           \
-        cudaError_t _e = (call);                                                                   \
-        if (_e != cudaSuccess)                                                                     \
-            return fail(TSW_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(_e));         \
-    } while (0)
+std::mutex g_engines_mu;
+std::map<int, tsw_engine*> g_engines;  // server id -> engine of this process
 
 namespace {
 
@@ -74,7 +54,7 @@ public:
     bool plan_only() const override { return true; }
 };
 
-using Lock = std::lock_guard<std::recursive_mutex>;
+}  // namespace
 
 int64_t now_ns() {
     return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch())
@@ -157,10 +137,6 @@ void set_row(Placement& pl, int idx, uint32_t flag, uint64_t phys) {
     __atomic_store_n(const_cast<uint32_t*>(&pl.flag[idx]), flag, __ATOMIC_RELEASE);
 }
 
-inline uint32_t row_flag(const Placement& pl, int idx) {
-    return __atomic_load_n(const_cast<const uint32_t*>(&pl.flag[idx]), __ATOMIC_ACQUIRE);
-}
-
 // init_model_readiness (memory_manager.hpp:234-238): add a row for every parameter
 // that has none yet; existing rows keep their state.
 int init_readiness(tsw_engine* e, Model* m, Placement& pl, uint32_t flag) {
@@ -234,8 +210,6 @@ uint64_t phy_address(tsw_engine* e, Model* m, uint64_t ptr, bool search_amid) {
     if (b.in_cuda && b.cuda != 0) return ptr - m->blocks[it->second].vaddr + b.cuda;
     return ptr;
 }
-
-struct WaitResult { int rc; uint64_t phys; };
 
 WaitResult wait_row(tsw_engine* e, Placement& pl, int idx, int64_t timeout_ns) {
     const int64_t deadline = now_ns() + (timeout_ns < 0 ? 0 : timeout_ns);
@@ -363,12 +337,6 @@ int pick_mover(const tsw_engine* e, const std::vector<PlaceDesc>& descs) {
     return 1;
 }
 
-struct Plan {
-    std::vector<PlaceDesc> descs;
-    std::vector<uint32_t> first;  // n + 1
-    uint64_t bytes = 0;
-};
-
 // Number the tiles; where a segment does not say how many tiles complete its row, count
 // them over the segments of this list and publish the first segment's destination.
 void finish_plan(Plan& p, uint32_t tile) {
@@ -402,7 +370,6 @@ int upload_plan(tsw_engine* e, Placement& pl, const Plan& p) {
     return TSW_OK;
 }
 
-}  // namespace
 }  // namespace tsw
 
 using namespace tsw;
@@ -962,920 +929,6 @@ int tsw_memset(tsw_engine* e, const char* func, uint64_t vptr, int value, uint64
     }
     TSW_CUDA(cudaSetDevice(e->cfg.device));
     TSW_CUDA(cudaMemsetAsync((void*)phys, value, size, (cudaStream_t)stream));
-    return TSW_OK;
-}
-
-// --------------------------------------------------------------- swap-in
-
-struct Prepared {
-    Model* m = nullptr;
-    Placement* pl = nullptr;
-    Plan plan;
-    uint32_t tile = 0;
-};
-
-// Wait for whatever still writes into this placement's blocks: the engine's own stream and
-// the streams of helper engines of a sharded swap.
-static int drain_placement(tsw_engine* e, Placement& pl) {
-    if (e->plan || !pl.in_flight) return TSW_OK;
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
-    for (tsw_engine* h : pl.helpers) {
-        TSW_CUDA(cudaSetDevice(h->cfg.device));
-        TSW_CUDA(cudaStreamSynchronize((cudaStream_t)h->stream));
-    }
-    pl.helpers.clear();
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    pl.in_flight = false;
-    return TSW_OK;
-}
-
-// Everything of a swap-in that precedes the data movement: source health check, block
-// placement with rebind, and the list of moves in access order.  Caller holds both locks.
-static int prepare_swap(tsw_engine* e, const char* func, int src_gpu, Prepared& out, bool defer = false) {
-    Model* m = repo().find(func);
-    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, std::string("model ") + func + " not found in model repo");
-
-    // sig_trans_thread (memory_manager.hpp:213-227): an unhealthy source replica falls back to the host store
-    Placement* src_pl = nullptr;
-    tsw_engine* src_engine = nullptr;
-    if (src_gpu >= 0) {
-        auto it = m->place.find(src_gpu);
-        if (it != m->place.end() && it->second.status == TSW_MODEL_FULL) {
-            src_pl = &it->second;
-            std::lock_guard<std::mutex> g(g_engines_mu);
-            auto eit = g_engines.find(src_gpu);
-            if (eit != g_engines.end()) src_engine = eit->second;
-        }
-        if (!src_pl || (!e->plan && !src_engine)) {
-            src_pl = nullptr;
-            src_gpu = -1;
-        }
-    }
-
-    const bool first_time_here = m->place.find(e->server_id) == m->place.end();
-    Placement& pl = placement(m, e->server_id);
-    if (first_time_here) pl.status = TSW_MODEL_NODATA;  // init_device_model_info (model_repo.hpp:78-80)
-    size_placement(m, pl);
-    int rc;
-    if (!pl.readiness_init) {
-        rc = init_readiness(e, m, pl, TSW_READY_HOST);
-        if (rc != TSW_OK) return rc;
-    } else {
-        rc = ensure_rows(e, m, pl);
-        if (rc != TSW_OK) return rc;
-    }
-    rc = drain_placement(e, pl);
-    if (rc != TSW_OK) return rc;
-    if (pl.counters_dirty) {
-        // The last swap was abandoned with parameters half moved (a participant went away): their
-        // tile counters were never re-armed by a last finisher.  Start this swap from zero.
-        if (!e->plan) {
-            TSW_CUDA(cudaSetDevice(e->cfg.device));
-            TSW_CUDA(cudaMemsetAsync(pl.d_done, 0, sizeof(uint32_t) * pl.capacity, (cudaStream_t)e->stream));
-            TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
-        }
-        pl.counters_dirty = false;
-        pl.remote_rows.clear();
-    }
-    rc = place_blocks(e, m, pl);
-    if (rc != TSW_OK) return rc;
-
-    // transfer_model (:331-438): every accessed parameter that is not on the device yet, in access order
-    const bool from_host = src_gpu < 0;
-    out.tile = pick_tile(e, from_host);
-    for (int pi : m->access_order) {
-        if (!pl.has_row[pi] || pl.flag[pi] == TSW_READY_CUDA) continue;
-        const VParam& p = m->params[pi];
-        const uint64_t dst = pl.params[pi].cuda;
-        if ((e->plan && !defer) || p.size == 0) {
-            set_row(pl, pi, TSW_READY_CUDA, dst);
-            continue;
-        }
-        PlaceDesc d;
-        d.src = from_host ? host_dev_addr(engine_of_block_mirror(p.host), p.host) : src_pl->params[pi].cuda;
-        d.dst = dst;
-        d.bytes = p.size;
-        d.row_dst = dst;
-        d.row = (uint32_t)pi;
-        d.row_tiles = 0;
-        out.plan.descs.push_back(d);
-    }
-    if (!out.plan.descs.empty()) finish_plan(out.plan, out.tile);
-    out.m = m;
-    out.pl = &pl;
-    return TSW_OK;
-}
-
-static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine* const* helpers, int n_helpers) {
-    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Lock g2(e->mu);
-    Prepared pr;
-    int rc = prepare_swap(e, func, src_gpu, pr);
-    if (rc != TSW_OK) return rc;
-    Placement& pl = *pr.pl;
-    Plan& plan = pr.plan;
-    if (e->plan || plan.descs.empty()) return TSW_OK;
-
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    cudaStream_t s = (cudaStream_t)e->stream;
-    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_start, s));
-    rc = upload_plan(e, pl, plan);
-    if (rc != TSW_OK) return rc;
-
-    PlaceArgs a;
-    memset(&a, 0, sizeof(a));
-    a.descs = (const PlaceDesc*)pl.d_descs;
-    a.first_tile = pl.d_first;
-    a.n_descs = (uint32_t)plan.descs.size();
-    a.tile_bytes = pr.tile;
-    a.tile_lo = 0;
-    a.tile_hi = plan.first.back();
-    a.tile_stride = 1;
-    a.done_count = pl.d_done;
-    a.table_phys = pl.d_table_phys;
-    a.table_flag = pl.d_table_flag;
-    a.host_phys = (uint64_t*)pl.phys;
-    a.host_flag = (uint32_t*)pl.flag;
-    pl.epoch += 1;
-    a.flag_value = pl.epoch;
-    a.host_flag_value = TSW_READY_CUDA;
-    a.system_scope = (n_helpers > 0) ? 1u : 0u;
-    a.status = e->d_status;
-
-    if (n_helpers > 0) {
-        // Every participating GPU works on the front of the access order at the same time:
-        // by default its CTAs draw the next tile from one counter on the target, so a link
-        // that is fed faster moves more tiles; with shard_static GPU r takes tiles r, r + n, ...
-        const int n = n_helpers + 1;
-        TSW_CUDA(cudaMemsetAsync(pl.d_ticket, 0, sizeof(uint32_t), s));
-        TSW_CUDA(cudaStreamSynchronize(s));  // descriptors and the tile dispenser must be on the target before peers read them
-        a.tile_stride = (uint32_t)n;
-        if (e->cfg.shard_static == 0) {
-            a.ticket = pl.d_ticket;   // tiles are drawn, not dealt: faster links take more
-            a.ticket_chunk = 1;
-        }
-        for (int r = n - 1; r >= 0; --r) {
-            tsw_engine* w = r == 0 ? e : helpers[r - 1];
-            if (!w || w->plan) return fail(TSW_ERR_INVALID, "sharded swap needs CUDA engines as helpers");
-            PlaceArgs ar = a;
-            ar.tile_lo = a.ticket ? 0u : (uint32_t)r;
-            TSW_CUDA(cudaSetDevice(w->cfg.device));
-            if (r != 0) TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_start, (cudaStream_t)w->stream));
-            const int mv = pick_mover(w, plan.descs);
-            cudaError_t le = launch_place(ar, mv ? w->grid_bulk : w->grid_ctas, (cudaStream_t)w->stream, mv);
-            if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
-            if (r != 0) {
-                TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_stop, (cudaStream_t)w->stream));
-                w->ev_valid = true;
-                pl.helpers.push_back(w);
-            }
-            w->kernel_launches++;
-        }
-        TSW_CUDA(cudaSetDevice(e->cfg.device));
-    } else {
-        const int mv = pick_mover(e, plan.descs);
-        cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, s, mv);
-        if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
-        e->kernel_launches++;
-    }
-    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_stop, s));
-    e->ev_valid = true;
-    e->bytes_moved += plan.bytes;
-    pl.in_flight = true;
-    return TSW_OK;
-}
-
-// Swap-in whose data movement is carried out by other parties (one process per GPU): this
-// engine places the blocks and rebinds exactly as tsw_swap_in does, then hands out the moves.
-int tsw_swap_plan(tsw_engine* e, const char* func, tsw_segment* segs, int cap, uint32_t* tile_bytes, tsw_publish* pub) {
-    if (!e || !func || !tile_bytes || !pub) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Lock g2(e->mu);
-    Prepared pr;
-    int rc = prepare_swap(e, func, -1, pr, true);
-    if (rc != TSW_OK) return rc;
-    Placement& pl = *pr.pl;
-    const int n = (int)pr.plan.descs.size();
-    if (n > cap || (n > 0 && !segs)) return fail(TSW_ERR_BUFFER, "segment buffer too small: need " + std::to_string(n));
-    static_assert(sizeof(tsw_segment) == sizeof(PlaceDesc), "segment layout");
-    if (n) memcpy(segs, pr.plan.descs.data(), sizeof(PlaceDesc) * n);
-    *tile_bytes = pr.tile;
-    memset(pub, 0, sizeof(*pub));
-    pub->done_count = (uint64_t)pl.d_done;
-    pub->table_phys = (uint64_t)pl.d_table_phys;
-    pub->table_flag = (uint64_t)pl.d_table_flag;
-    pl.epoch += 1;
-    pub->flag_value = pl.epoch;       // the generation; the host-visible rows are set by tsw_swap_commit
-    pub->ticket = (uint64_t)pl.d_ticket;
-    pub->ticket_chunk = 1;
-    pl.remote_rows.clear();
-    for (auto& d : pr.plan.descs) pl.remote_rows.push_back((int)d.row);
-    if (n && !e->plan) {
-        TSW_CUDA(cudaSetDevice(e->cfg.device));
-        TSW_CUDA(cudaMemsetAsync(pl.d_ticket, 0, sizeof(uint32_t), (cudaStream_t)e->stream));
-        TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
-        e->bytes_moved += pr.plan.bytes;
-    }
-    return n;
-}
-
-// After every party has finished its share of a tsw_swap_plan: take the rows the kernels
-// published on the device over into the host-visible table.
-int tsw_swap_commit(tsw_engine* e, const char* func) {
-    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Lock g2(e->mu);
-    Model* m = repo().find(func);
-    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
-    Placement& pl = placement(m, e->server_id);
-    if (pl.remote_rows.empty()) return TSW_OK;
-    if (e->plan) {  // nothing moved, nothing to read back: the plan is the result
-        for (int row : pl.remote_rows) set_row(pl, row, TSW_READY_CUDA, pl.params[row].cuda);
-        pl.remote_rows.clear();
-        return TSW_OK;
-    }
-    std::vector<uint32_t> flag(pl.capacity);
-    std::vector<uint64_t> phys(pl.capacity);
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    TSW_CUDA(cudaMemcpy(flag.data(), pl.d_table_flag, sizeof(uint32_t) * pl.capacity, cudaMemcpyDeviceToHost));
-    TSW_CUDA(cudaMemcpy(phys.data(), pl.d_table_phys, sizeof(uint64_t) * pl.capacity, cudaMemcpyDeviceToHost));
-    std::vector<int> missing;
-    for (int row : pl.remote_rows) {
-        if (flag[row] == pl.epoch) set_row(pl, row, TSW_READY_CUDA, phys[row]);
-        else missing.push_back(row);
-    }
-    // Rows still on their way stay listed: the caller may commit again once the participants have
-    // finished, or give up and swap the model in by itself (which starts the counters afresh).
-    pl.remote_rows.swap(missing);
-    if (!pl.remote_rows.empty()) {
-        pl.counters_dirty = true;
-        return fail(TSW_ERR_STATE, std::to_string(pl.remote_rows.size()) + " parameters were not completed by the participants");
-    }
-    pl.counters_dirty = false;
-    return TSW_OK;
-}
-
-int tsw_swap_in(tsw_engine* e, const char* func, int src_gpu) { return swap_in_impl(e, func, src_gpu, nullptr, 0); }
-
-int tsw_swap_in_sharded(tsw_engine* e, const char* func, tsw_engine* const* helpers, int n_helpers) {
-    if (n_helpers < 0 || (n_helpers > 0 && !helpers)) return fail(TSW_ERR_INVALID, "bad helper list");
-    return swap_in_impl(e, func, -1, helpers, n_helpers);
-}
-
-int tsw_wait_ready(tsw_engine* e, const char* func, int64_t timeout_ns) {
-    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
-    Placement* pl;
-    std::vector<int> order;
-    {
-        Lock g1(repo().mu);
-        Lock g2(e->mu);
-        Model* m = repo().find(func);
-        if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
-        pl = &placement(m, e->server_id);
-        if (!pl->readiness_init) return fail(TSW_ERR_STATE, "model has no readiness rows on this engine");
-        for (int pi : m->access_order)
-            if (pl->has_row[pi]) order.push_back(pi);
-    }
-    const int64_t deadline = now_ns() + timeout_ns;
-    // the kernel completes parameters roughly in access order: wait from the back
-    for (auto it = order.rbegin(); it != order.rend(); ++it) {
-        int64_t left = deadline - now_ns();
-        WaitResult w = wait_row(e, *pl, *it, left > 0 ? left : 0);
-        if (w.rc != TSW_OK) return w.rc;
-    }
-    return TSW_OK;
-}
-
-int tsw_poll_ready(tsw_engine* e, const char* func) {
-    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Lock g2(e->mu);
-    Model* m = repo().find(func);
-    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
-    auto it = m->place.find(e->server_id);
-    if (it == m->place.end() || !it->second.readiness_init) return fail(TSW_ERR_STATE, "model has no readiness rows on this engine");
-    if (e->h_status && *e->h_status) return fail(TSW_ERR_KERNEL, "placement kernel reported an inconsistent tile table");
-    int waiting = 0;
-    for (int pi : m->access_order)
-        if (it->second.has_row[pi] && it->second.flag[pi] != TSW_READY_CUDA) ++waiting;
-    return waiting;
-}
-
-int tsw_check_alloc(tsw_engine* e, const char* func) {
-    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Lock g2(e->mu);
-    Model* m = repo().find(func);
-    if (!m) return 0;
-    auto it = m->place.find(e->server_id);
-    if (it == m->place.end()) return 0;
-    Placement& pl = it->second;
-    size_placement(m, pl);
-    for (auto& kv : m->block_order) {
-        const Placement::B& b = pl.blocks[kv.second];
-        if (!b.known || !b.in_cuda) return 0;
-    }
-    return 1;
-}
-
-// --------------------------------------------------------------- swap-out
-
-int tsw_evict(tsw_engine* e, const char* func, int writeback) {
-    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Lock g2(e->mu);
-    Model* m = repo().find(func);
-    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "try to evict unrecognized model");
-    auto pit = m->place.find(e->server_id);
-    if (pit == m->place.end() || !pit->second.readiness_init)
-        return fail(TSW_ERR_UNKNOWN_MODEL, "try to evict unrecognized model");  // memory_manager.hpp:241-244
-    Placement& pl = pit->second;
-    size_placement(m, pl);
-
-    if (!e->plan) {
-        int drc = drain_placement(e, pl);
-        if (drc != TSW_OK) return drc;
-        TSW_CUDA(cudaSetDevice(e->cfg.device));
-        if (writeback) {
-            // Eviction write-back: resident parameter bytes -> host store, through the same kernel.
-            Plan plan;
-            for (size_t pi = 0; pi < m->params.size(); ++pi) {
-                if (!pl.has_row[pi] || pl.flag[pi] != TSW_READY_CUDA) continue;
-                const VParam& p = m->params[pi];
-                const Placement::B& b = pl.blocks[p.block];
-                if (!b.in_cuda || p.size == 0) continue;
-                PlaceDesc d;
-                d.src = pl.params[pi].cuda;
-                d.dst = host_dev_addr(engine_of_block_mirror(p.host), p.host);
-                d.bytes = p.size;
-                d.row_dst = d.dst;
-                d.row = (uint32_t)pi;
-                d.row_tiles = 0;
-                plan.descs.push_back(d);
-            }
-            if (!plan.descs.empty()) {
-                int rc = ensure_rows(e, m, pl);
-                if (rc != TSW_OK) return rc;
-                finish_plan(plan, e->tile_host);
-                rc = upload_plan(e, pl, plan);
-                if (rc != TSW_OK) return rc;
-                PlaceArgs a;
-                memset(&a, 0, sizeof(a));
-                a.descs = (const PlaceDesc*)pl.d_descs;
-                a.first_tile = pl.d_first;
-                a.n_descs = (uint32_t)plan.descs.size();
-                a.tile_bytes = e->tile_host;
-                a.tile_lo = 0;
-                a.tile_hi = plan.first.back();
-                a.tile_stride = 1;
-                a.system_scope = 1;
-                a.status = e->d_status;
-                const int mv = pick_mover(e, plan.descs);
-                cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, (cudaStream_t)e->stream, mv);
-                if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("write-back kernel launch: ") + cudaGetErrorString(le));
-                e->kernel_launches++;
-                e->bytes_moved += plan.bytes;
-                TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
-            }
-        }
-    }
-
-    // evict_model (:247-256): release every resident block, in the reference's block order
-    for (auto& kv : m->block_order) {
-        const int bi = kv.second;
-        Placement::B& b = pl.blocks[bi];
-        if (!b.in_cuda) continue;
-        b.in_cuda = false;
-        e->pool->evict(b.cuda, m->blocks[bi].size, false);
-        if (m->blocks[bi].is_model) {
-            for (int pi : m->blocks[bi].params)  // reset_model_readiness (:301-309)
-                if (pl.has_row[pi]) set_row(pl, pi, TSW_READY_HOST, 0);
-        }
-    }
-    e->pool->finish_release_block();
-    return TSW_OK;
-}
-
-// --------------------------------------------------------------- translation
-
-int tsw_translate(tsw_engine* e, const char* func, uint64_t vptr, int search_amid, int64_t timeout_ns, uint64_t* out) {
-    if (!e || !func || !out) return fail(TSW_ERR_INVALID, "null argument");
-    Placement* wait_pl = nullptr;
-    int wait_idx = -1;
-    {
-        Lock g1(repo().mu);
-        Lock g2(e->mu);
-        Model* m = repo().find(func);
-        if (!m || m->place.find(e->server_id) == m->place.end()) {
-            *out = vptr;  // memory_manager.hpp:270
-            return TSW_OK;
-        }
-        auto pit = m->param_by_vaddr.find(vptr);
-        if (pit == m->param_by_vaddr.end()) {
-            *out = phy_address(e, m, vptr, search_amid != 0);
-            return TSW_OK;
-        }
-        // check_param_readiness (:527-540)
-        Placement& pl = placement(m, e->server_id);
-        size_placement(m, pl);
-        const int pi = pit->second;
-        if (!pl.readiness_init) {
-            *out = vptr;
-            return TSW_OK;
-        }
-        if (e->active_params.count(vptr) && pl.has_row[pi]) {
-            wait_pl = &pl;
-            wait_idx = pi;
-        } else {
-            *out = pl.params[pi].cuda;
-            return TSW_OK;
-        }
-    }
-    WaitResult w = wait_row(e, *wait_pl, wait_idx, timeout_ns);
-    if (w.rc != TSW_OK) return w.rc;
-    *out = w.phys;
-    return TSW_OK;
-}
-
-// Stream-ordered form of get_cuda_addr.  The rebound address of a parameter is known as soon
-// as its block is placed; what the executor has to wait for is the bytes.  Instead of blocking
-// the host (check_param_readiness, memory_manager.hpp:527-540) this returns the address at once
-// and, if the parameter is still on its way, makes `stream` wait for it: a stream memory
-// operation on the row's generation word in the device pointer table, which the placement
-// kernel writes when the row's last tile has landed.  Kernels that use the parameter can then
-// be enqueued behind it before the weights have arrived.  Nothing spins on the device.
-int tsw_translate_async(tsw_engine* e, const char* func, uint64_t vptr, void* stream, uint64_t* out, int* waited) {
-    if (!e || !func || !out) return fail(TSW_ERR_INVALID, "null argument");
-    if (waited) *waited = 0;
-    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine has no streams");
-    Lock g1(repo().mu);
-    Lock g2(e->mu);
-    Model* m = repo().find(func);
-    if (!m || m->place.find(e->server_id) == m->place.end()) {
-        *out = vptr;
-        return TSW_OK;
-    }
-    auto pit = m->param_by_vaddr.find(vptr);
-    if (pit == m->param_by_vaddr.end()) {
-        *out = phy_address(e, m, vptr, true);
-        return TSW_OK;
-    }
-    Placement& pl = placement(m, e->server_id);
-    size_placement(m, pl);
-    const int pi = pit->second;
-    if (!pl.readiness_init) {
-        *out = vptr;
-        return TSW_OK;
-    }
-    *out = pl.params[pi].cuda;
-    if (!(e->active_params.count(vptr) && pl.has_row[pi])) return TSW_OK;   // as check_param_readiness: not part of the last swap
-    if (pl.flag[pi] == TSW_READY_CUDA) return TSW_OK;                       // already there
-    if (!pl.in_flight) return fail(TSW_ERR_STATE, "parameter is neither on the device nor on its way: swap the model in first");
-    typedef int (*wait_fn_t)(cudaStream_t, unsigned long long, unsigned int, unsigned int);
-    static wait_fn_t wait_fn = nullptr;
-    if (!wait_fn) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        cudaError_t err = cudaGetDriverEntryPoint("cuStreamWaitValue32", &fn, cudaEnableDefault, &qres);
-        if (err != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
-            return fail(TSW_ERR_CUDA, "stream memory operations are not available from this driver");
-        wait_fn = (wait_fn_t)fn;
-    }
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    const int rc = wait_fn((cudaStream_t)stream, (unsigned long long)(uintptr_t)&pl.d_table_flag[pi], pl.epoch, 0x0 /* GEQ */);
-    if (rc != 0) return fail(TSW_ERR_CUDA, "cuStreamWaitValue32 failed with driver error " + std::to_string(rc));
-    if (waited) *waited = 1;
-    return TSW_OK;
-}
-
-int tsw_is_model_address(tsw_engine* e, const char* func, uint64_t vptr) {
-    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Model* m = repo().find(func);
-    return (m && m->param_by_vaddr.count(vptr)) ? 1 : 0;
-}
-
-int tsw_valid_memory_address(tsw_engine* e, const char* func, uint64_t vptr) {
-    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Model* m = repo().find(func);
-    if (m) cache_interior_pointer(m, vptr);
-    return 0;
-}
-
-// --------------------------------------------------------------- introspection
-
-int tsw_dump_blocks(tsw_engine* e, const char* func, int canonical, uint64_t* out, int cap) {
-    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Lock g2(e->mu);
-    Model* m = repo().find(func);
-    if (!m) return 0;
-    auto pit = m->place.find(e->server_id);
-    int n = 0;
-    for (auto& kv : m->block_order) {
-        if (out && n < cap) {
-            const VBlock& b = m->blocks[kv.second];
-            uint64_t* o = out + 6 * n;
-            o[0] = canonical ? b.canon : b.vaddr;
-            o[1] = b.size;
-            o[2] = b.is_model;
-            o[3] = o[4] = o[5] = 0;
-            if (pit != m->place.end() && (size_t)kv.second < pit->second.blocks.size() && pit->second.blocks[kv.second].known) {
-                const Placement::B& pb = pit->second.blocks[kv.second];
-                o[3] = pb.in_cuda;
-                o[4] = canonical ? pb.canon : pb.cuda;
-            }
-        }
-        ++n;
-    }
-    return n;
-}
-
-static std::vector<int> dump_order(Model* m) {
-    std::vector<int> order = m->access_order;
-    std::vector<int> rest;
-    for (size_t i = 0; i < m->params.size(); ++i)
-        if (!m->params[i].accessed) rest.push_back((int)i);
-    std::sort(rest.begin(), rest.end(), [m](int a, int b) { return m->params[a].vaddr < m->params[b].vaddr; });
-    order.insert(order.end(), rest.begin(), rest.end());
-    return order;
-}
-
-int tsw_dump_params(tsw_engine* e, const char* func, int canonical, uint64_t* out, int cap) {
-    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Lock g2(e->mu);
-    Model* m = repo().find(func);
-    if (!m) return 0;
-    auto pit = m->place.find(e->server_id);
-    std::vector<int> order = dump_order(m);
-    int n = 0;
-    for (int pi : order) {
-        if (out && n < cap) {
-            const VParam& p = m->params[pi];
-            uint64_t* o = out + 7 * n;
-            o[0] = canonical ? p.canon : p.vaddr;
-            o[1] = p.size;
-            o[2] = canonical ? m->blocks[p.block].canon : m->blocks[p.block].vaddr;
-            o[3] = 0;
-            o[4] = (uint64_t)-1;
-            o[5] = 0;
-            if (pit != m->place.end()) {
-                const Placement& pl = pit->second;
-                const bool known = (size_t)pi < pl.params.size() && pl.params[pi].known;
-                if (known) o[3] = canonical ? pl.params[pi].canon : pl.params[pi].cuda;
-                if ((size_t)pi < pl.has_row.size() && pl.has_row[pi]) {
-                    o[4] = pl.flag[pi];
-                    uint64_t r = pl.phys[pi];
-                    if (canonical && r != 0) {
-                        if (known && r == pl.params[pi].cuda) r = pl.params[pi].canon;
-                        else if (r == p.vaddr) r = p.canon;
-                    }
-                    o[5] = r;
-                }
-            }
-            o[6] = p.accessed ? 1 : 0;
-        }
-        ++n;
-    }
-    return n;
-}
-
-int tsw_pool_info(tsw_engine* e, uint64_t* pool_base, uint64_t* n_chunks, uint64_t* canon_base) {
-    if (!e) return fail(TSW_ERR_INVALID, "null argument");
-    if (pool_base) *pool_base = e->pool->pool_base();
-    if (n_chunks) *n_chunks = e->pool->pool_chunks();
-    if (canon_base) *canon_base = kCanonBase + (uint64_t)e->server_id * kCanonStride;
-    return TSW_OK;
-}
-
-int tsw_canonical_address(tsw_engine* e, const char* func, uint64_t addr, uint64_t* out) {
-    if (!e || !out) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Lock g2(e->mu);
-    uint64_t c = e->pool->canon_inside(addr);
-    if (!c && func) {
-        Model* m = repo().find(func);
-        if (m)
-            for (auto& b : m->blocks)
-                if (b.alive && addr >= b.vaddr && addr < b.vaddr + b.size) {
-                    c = b.canon + (addr - b.vaddr);
-                    break;
-                }
-    }
-    *out = c ? c : addr;
-    return TSW_OK;
-}
-
-int tsw_read_phys(tsw_engine* e, uint64_t addr, void* out, uint64_t size) {
-    if (!e || !out) return fail(TSW_ERR_INVALID, "null argument");
-    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine holds no bytes");
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    TSW_CUDA(cudaMemcpy(out, (void*)addr, size, cudaMemcpyDeviceToHost));
-    return TSW_OK;
-}
-
-int tsw_read_host_store(tsw_engine* e, const char* func, uint64_t vptr, void* out, uint64_t size) {
-    if (!e || !func || !out) return fail(TSW_ERR_INVALID, "null argument");
-    Lock g1(repo().mu);
-    Model* m = repo().find(func);
-    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
-    auto it = m->param_by_vaddr.find(vptr);
-    if (it == m->param_by_vaddr.end() || m->params[it->second].size < size) return fail(TSW_ERR_NOT_FOUND, "no such parameter");
-    memcpy(out, m->params[it->second].host, size);
-    return TSW_OK;
-}
-
-int tsw_checksum_resident(tsw_engine* e, const char* func, uint64_t* out, int cap) {
-    if (!e || !func || !out) return fail(TSW_ERR_INVALID, "null argument");
-    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine holds no bytes");
-    std::vector<SumDesc> descs;
-    int n_rows = 0;
-    const uint32_t tile = 256u * 1024;
-    {
-        Lock g1(repo().mu);
-        Lock g2(e->mu);
-        Model* m = repo().find(func);
-        if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
-        Placement& pl = placement(m, e->server_id);
-        size_placement(m, pl);
-        std::vector<int> order = dump_order(m);
-        n_rows = (int)order.size();
-        if (n_rows > cap) return fail(TSW_ERR_BUFFER, "checksum buffer too small");
-        uint64_t t = 0;
-        for (int row = 0; row < n_rows; ++row) {
-            const int pi = order[row];
-            const VParam& p = m->params[pi];
-            if (!pl.params[pi].known || !pl.blocks[p.block].in_cuda || p.size == 0) continue;
-            SumDesc d;
-            d.addr = pl.params[pi].cuda;
-            d.bytes = p.size;
-            d.first_tile = (uint32_t)t;
-            d.row = (uint32_t)row;
-            descs.push_back(d);
-            t += (p.size + tile - 1) / tile;
-        }
-        memset(out, 0, sizeof(uint64_t) * 2 * n_rows);
-        if (descs.empty()) return n_rows;
-        TSW_CUDA(cudaSetDevice(e->cfg.device));
-        cudaStream_t s = (cudaStream_t)e->stream;
-        TSW_CUDA(cudaStreamSynchronize(s));
-        void* d_descs = nullptr;
-        void* d_out = nullptr;
-        TSW_CUDA(cudaMalloc(&d_descs, sizeof(SumDesc) * descs.size()));
-        TSW_CUDA(cudaMalloc(&d_out, sizeof(uint64_t) * 2 * n_rows));
-        TSW_CUDA(cudaMemcpyAsync(d_descs, descs.data(), sizeof(SumDesc) * descs.size(), cudaMemcpyHostToDevice, s));
-        TSW_CUDA(cudaMemsetAsync(d_out, 0, sizeof(uint64_t) * 2 * n_rows, s));
-        cudaError_t le = launch_checksum((const SumDesc*)d_descs, (uint32_t)descs.size(), (uint32_t)t, tile,
-                                         (unsigned long long*)d_out, e->grid_ctas, s);
-        if (le == cudaSuccess) le = cudaMemcpyAsync(out, d_out, sizeof(uint64_t) * 2 * n_rows, cudaMemcpyDeviceToHost, s);
-        if (le == cudaSuccess) le = cudaStreamSynchronize(s);
-        cudaFree(d_descs);
-        cudaFree(d_out);
-        if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("checksum: ") + cudaGetErrorString(le));
-        e->kernel_launches++;
-    }
-    return n_rows;
-}
-
-// --------------------------------------------------------------- sharing with other processes
-
-int tsw_ipc_regions(tsw_engine* e, tsw_ipc_region* out, int cap) {
-    if (!e) return fail(TSW_ERR_INVALID, "null argument");
-    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine has no device memory");
-    Lock g2(e->mu);
-    std::vector<std::pair<uint64_t, uint64_t>> regs;
-    e->pool->regions(&regs);
-    regs.emplace_back((uint64_t)e->dev_slab.base, e->dev_slab.size);
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    int n = 0;
-    for (auto& r : regs) {
-        if (out && n < cap) {
-            out[n].base = r.first;
-            out[n].size = r.second;
-            cudaIpcMemHandle_t h;
-            TSW_CUDA(cudaIpcGetMemHandle(&h, (void*)r.first));
-            static_assert(sizeof(h) == sizeof(out[n].handle), "IPC handle size");
-            memcpy(out[n].handle, &h, sizeof(h));
-        }
-        ++n;
-    }
-    return n;
-}
-
-int tsw_ipc_open(tsw_engine* e, const void* handle, uint64_t* mapped_base) {
-    if (!e || !handle || !mapped_base) return fail(TSW_ERR_INVALID, "null argument");
-    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine has no device");
-    Lock g2(e->mu);
-    std::string key((const char*)handle, sizeof(cudaIpcMemHandle_t));
-    auto it = e->ipc_open.find(key);
-    if (it != e->ipc_open.end()) {
-        *mapped_base = it->second;
-        return TSW_OK;
-    }
-    cudaIpcMemHandle_t h;
-    memcpy(&h, handle, sizeof(h));
-    void* p = nullptr;
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    TSW_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
-    e->ipc_open[key] = (uint64_t)p;
-    *mapped_base = (uint64_t)p;
-    return TSW_OK;
-}
-
-int tsw_pointer_info(tsw_engine* e, uint64_t addr, int* type, int* device, uint64_t* device_pointer, uint64_t* host_pointer) {
-    if (!e) return fail(TSW_ERR_INVALID, "null argument");
-    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine has no device");
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    cudaPointerAttributes at;
-    cudaError_t err = cudaPointerGetAttributes(&at, (const void*)addr);
-    if (err != cudaSuccess) {
-        cudaGetLastError();
-        return fail(TSW_ERR_CUDA, std::string("cudaPointerGetAttributes: ") + cudaGetErrorString(err));
-    }
-    if (type) *type = (int)at.type;
-    if (device) *device = at.device;
-    if (device_pointer) *device_pointer = (uint64_t)at.devicePointer;
-    if (host_pointer) *host_pointer = (uint64_t)at.hostPointer;
-    return TSW_OK;
-}
-
-int tsw_arena_info(tsw_engine* e, uint64_t* host_base, uint64_t* dev_base, uint64_t* size, uint64_t* used) {
-    if (!e) return fail(TSW_ERR_INVALID, "null argument");
-    if (host_base) *host_base = (uint64_t)e->arena.base;
-    if (dev_base) *dev_base = e->arena.base ? (uint64_t)((int64_t)(uint64_t)e->arena.base + e->arena.dev_delta) : 0;
-    if (size) *size = e->arena.size;
-    if (used) *used = e->arena.used;
-    return TSW_OK;
-}
-
-int tsw_arena_attach(tsw_engine* e, const char* shm_name, uint64_t size, uint64_t* dev_base) {
-    if (!e || !shm_name || !dev_base || size == 0) return fail(TSW_ERR_INVALID, "bad arguments");
-    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine has no device");
-    Lock g2(e->mu);
-    int fd = shm_open(shm_name, O_RDWR, 0600);
-    if (fd < 0) return fail(TSW_ERR_NOT_FOUND, std::string("shm_open(") + shm_name + ") failed");
-    void* p = map_shared_far(fd, size, e->server_id);
-    close(fd);
-    if (p == MAP_FAILED) return fail(TSW_ERR_INVALID, "mmap of the shared host arena failed");
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    cudaError_t err = cudaHostRegister(p, size, cudaHostRegisterPortable | cudaHostRegisterMapped);
-    if (err != cudaSuccess) {
-        munmap(p, size);
-        return fail(TSW_ERR_CUDA, std::string("cudaHostRegister(shared arena): ") + cudaGetErrorString(err));
-    }
-    void* dp = nullptr;
-    TSW_CUDA(cudaHostGetDevicePointer(&dp, p, 0));
-    e->attached.push_back({p, size, (uint64_t)dp});
-    *dev_base = (uint64_t)dp;
-    return TSW_OK;
-}
-
-// Ask the driver what every address of a launch is before the kernel touches it.  Used when
-// TORPOR_SWAP_VALIDATE=1: a pointer the driver does not know (a stale IPC mapping, an
-// unregistered host range, an address of another process) is reported as an error instead
-// of faulting the GPU.
-static int validate_address(tsw_engine* e, const char* what, int index, uint64_t addr, uint64_t bytes) {
-    if (bytes == 0) return TSW_OK;
-    // Device-side aliases of registered host memory (where the device address differs from the
-    // host address) are not reported by the driver; the engine knows the ones it made.
-    if (e->arena.base) {
-        const uint64_t lo = (uint64_t)((int64_t)(uint64_t)e->arena.base + e->arena.dev_delta);
-        if (addr >= lo && addr + bytes <= lo + e->arena.size) return TSW_OK;
-    }
-    for (auto& a : e->attached)
-        if (addr >= a.dev && addr + bytes <= a.dev + a.size) return TSW_OK;
-    for (uint64_t probe : {addr, addr + bytes - 1}) {
-        cudaPointerAttributes at;
-        cudaError_t err = cudaPointerGetAttributes(&at, (const void*)probe);
-        if (err != cudaSuccess) {
-            cudaGetLastError();
-            return fail(TSW_ERR_INVALID, std::string(what) + " " + std::to_string(index) + ": cudaPointerGetAttributes failed for " +
-                                             std::to_string(probe) + ": " + cudaGetErrorString(err));
-        }
-        if (at.type == cudaMemoryTypeUnregistered)
-            return fail(TSW_ERR_INVALID, std::string(what) + " " + std::to_string(index) + ": address " + std::to_string(probe) +
-                                             " is not known to the CUDA driver in this process");
-    }
-    return TSW_OK;
-}
-
-static bool validation_on() {
-    static const bool on = [] { const char* v = getenv("TORPOR_SWAP_VALIDATE"); return v && v[0] == '1'; }();
-    return on;
-}
-
-int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
-                       uint32_t tile_stride, uint32_t tile_end, const tsw_publish* pub, int sync) {
-    if (!e || (n > 0 && !segs) || n < 0) return fail(TSW_ERR_INVALID, "bad segment list");
-    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine moves no bytes");
-    if (n == 0) return TSW_OK;
-    if (tile_bytes == 0) tile_bytes = e->tile_host;
-    if ((tile_bytes & 15u) || tile_stride == 0) return fail(TSW_ERR_INVALID, "tile size must be a multiple of 16 and stride positive");
-    static_assert(sizeof(tsw_segment) == sizeof(PlaceDesc), "segment layout");
-    Lock g2(e->mu);
-    Plan plan;
-    plan.descs.resize(n);
-    memcpy(plan.descs.data(), segs, sizeof(PlaceDesc) * n);
-    finish_plan(plan, tile_bytes);
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    cudaStream_t s = (cudaStream_t)e->stream;
-    // launch scratch: grown on demand, reused by the next call once the stream has drained
-    const uint64_t need_d = sizeof(PlaceDesc) * (uint64_t)n, need_f = sizeof(uint32_t) * ((uint64_t)n + 1);
-    if (e->raw_cap < (uint64_t)n) {
-        TSW_CUDA(cudaStreamSynchronize(s));
-        if (e->raw_d_descs) cudaFree(e->raw_d_descs);
-        if (e->raw_d_first) cudaFree(e->raw_d_first);
-        if (e->raw_h) cudaFreeHost(e->raw_h);
-        e->raw_d_descs = e->raw_d_first = e->raw_h = nullptr;
-        e->raw_cap = 0;
-        const uint64_t cap = std::max<uint64_t>((uint64_t)n, 1024);
-        TSW_CUDA(cudaMalloc(&e->raw_d_descs, sizeof(PlaceDesc) * cap));
-        TSW_CUDA(cudaMalloc(&e->raw_d_first, sizeof(uint32_t) * (cap + 1)));
-        TSW_CUDA(cudaHostAlloc(&e->raw_h, sizeof(PlaceDesc) * cap + sizeof(uint32_t) * (cap + 1), cudaHostAllocDefault));
-        e->raw_cap = cap;
-    } else {
-        TSW_CUDA(cudaStreamSynchronize(s));  // the staging buffer may still feed the previous launch
-    }
-    uint8_t* hs = (uint8_t*)e->raw_h;
-    memcpy(hs, plan.descs.data(), need_d);
-    memcpy(hs + sizeof(PlaceDesc) * e->raw_cap, plan.first.data(), need_f);
-    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_start, s));
-    TSW_CUDA(cudaMemcpyAsync(e->raw_d_descs, hs, need_d, cudaMemcpyHostToDevice, s));
-    TSW_CUDA(cudaMemcpyAsync(e->raw_d_first, hs + sizeof(PlaceDesc) * e->raw_cap, need_f, cudaMemcpyHostToDevice, s));
-    PlaceArgs a;
-    memset(&a, 0, sizeof(a));
-    a.descs = (const PlaceDesc*)e->raw_d_descs;
-    a.first_tile = (const uint32_t*)e->raw_d_first;
-    a.n_descs = (uint32_t)n;
-    a.tile_bytes = tile_bytes;
-    a.tile_lo = tile_first;
-    a.tile_hi = (tile_end != 0 && tile_end < plan.first.back()) ? tile_end : plan.first.back();
-    a.tile_stride = tile_stride;
-    a.system_scope = 1;
-    a.status = e->d_status;
-    if (pub) {
-        a.done_count = (uint32_t*)pub->done_count;
-        a.table_phys = (uint64_t*)pub->table_phys;
-        a.table_flag = (uint32_t*)pub->table_flag;
-        a.host_phys = (uint64_t*)pub->host_phys;
-        a.host_flag = (uint32_t*)pub->host_flag;
-        a.flag_value = pub->flag_value;
-        a.host_flag_value = pub->flag_value;
-        a.ticket = (uint32_t*)pub->ticket;
-        a.ticket_chunk = pub->ticket_chunk ? pub->ticket_chunk : 1;
-        if (a.done_count && (!a.table_phys || !a.table_flag)) return fail(TSW_ERR_INVALID, "publish block needs both table columns");
-    }
-    if (validation_on()) {
-        uint32_t max_row = 0;
-        for (int i = 0; i < n; ++i) {
-            // only the part of the segment whose tiles this launch can touch
-            const uint64_t t0 = std::max<uint64_t>(plan.first[i], a.tile_lo), t1 = std::min<uint64_t>(plan.first[i + 1], a.tile_hi);
-            if (t0 >= t1) continue;
-            const uint64_t off = (t0 - plan.first[i]) * tile_bytes;
-            const uint64_t end = std::min<uint64_t>((t1 - plan.first[i]) * tile_bytes, plan.descs[i].bytes);
-            int rc = validate_address(e, "segment source", i, plan.descs[i].src + off, end - off);
-            if (rc == TSW_OK) rc = validate_address(e, "segment destination", i, plan.descs[i].dst + off, end - off);
-            if (rc != TSW_OK) return rc;
-            max_row = std::max(max_row, plan.descs[i].row);
-        }
-        if (a.done_count) {
-            int rc = validate_address(e, "tile counters", 0, (uint64_t)a.done_count, 4ull * (max_row + 1));
-            if (rc == TSW_OK) rc = validate_address(e, "table column phys", 0, (uint64_t)a.table_phys, 8ull * (max_row + 1));
-            if (rc == TSW_OK) rc = validate_address(e, "table column flag", 0, (uint64_t)a.table_flag, 4ull * (max_row + 1));
-            if (rc != TSW_OK) return rc;
-        }
-    }
-    const int mv = pick_mover(e, plan.descs);
-    cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, s, mv);
-    if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
-    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_stop, s));
-    e->ev_valid = true;
-    if (a.tile_hi > a.tile_lo) e->kernel_launches++;
-    if (a.tile_hi > a.tile_lo)
-        e->bytes_moved += (uint64_t)((double)plan.bytes * (double)(a.tile_hi - a.tile_lo) / (double)plan.first.back() / tile_stride);
-    if (sync) TSW_CUDA(cudaStreamSynchronize(s));
-    return TSW_OK;
-}
-
-int tsw_stats(tsw_engine* e, uint64_t* kernel_launches, uint64_t* bytes_moved, uint64_t* last_swap_device_ns) {
-    if (!e) return fail(TSW_ERR_INVALID, "null argument");
-    if (kernel_launches) *kernel_launches = e->kernel_launches.load();
-    if (bytes_moved) *bytes_moved = e->bytes_moved.load();
-    if (last_swap_device_ns) {
-        *last_swap_device_ns = 0;
-        if (!e->plan && e->ev_valid) {
-            cudaSetDevice(e->cfg.device);
-            if (cudaEventSynchronize((cudaEvent_t)e->ev_stop) == cudaSuccess) {
-                float ms = 0;
-                if (cudaEventElapsedTime(&ms, (cudaEvent_t)e->ev_start, (cudaEvent_t)e->ev_stop) == cudaSuccess)
-                    *last_swap_device_ns = (uint64_t)(ms * 1e6);
-            }
-        }
-    }
     return TSW_OK;
 }
 

@@ -1,0 +1,509 @@
+// Swap-in, swap-out and pointer translation of the swap engine (C ABI, second part).
+
+#include "engine_internal.hpp"
+
+using namespace tsw;
+
+extern "C" {
+
+// --------------------------------------------------------------- swap-in
+
+struct Prepared {
+    Model* m = nullptr;
+    Placement* pl = nullptr;
+    Plan plan;
+    uint32_t tile = 0;
+};
+
+// Wait for whatever still writes into this placement's blocks: the engine's own stream and
+// the streams of helper engines of a sharded swap.
+static int drain_placement(tsw_engine* e, Placement& pl) {
+    if (e->plan || !pl.in_flight) return TSW_OK;
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+    for (tsw_engine* h : pl.helpers) {
+        TSW_CUDA(cudaSetDevice(h->cfg.device));
+        TSW_CUDA(cudaStreamSynchronize((cudaStream_t)h->stream));
+    }
+    pl.helpers.clear();
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    pl.in_flight = false;
+    return TSW_OK;
+}
+
+// Everything of a swap-in that precedes the data movement: source health check, block
+// placement with rebind, and the list of moves in access order.  Caller holds both locks.
+static int prepare_swap(tsw_engine* e, const char* func, int src_gpu, Prepared& out, bool defer = false) {
+    Model* m = repo().find(func);
+    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, std::string("model ") + func + " not found in model repo");
+
+    // sig_trans_thread (memory_manager.hpp:213-227): an unhealthy source replica falls back to the host store
+    Placement* src_pl = nullptr;
+    tsw_engine* src_engine = nullptr;
+    if (src_gpu >= 0) {
+        auto it = m->place.find(src_gpu);
+        if (it != m->place.end() && it->second.status == TSW_MODEL_FULL) {
+            src_pl = &it->second;
+            std::lock_guard<std::mutex> g(g_engines_mu);
+            auto eit = g_engines.find(src_gpu);
+            if (eit != g_engines.end()) src_engine = eit->second;
+        }
+        if (!src_pl || (!e->plan && !src_engine)) {
+            src_pl = nullptr;
+            src_gpu = -1;
+        }
+    }
+
+    const bool first_time_here = m->place.find(e->server_id) == m->place.end();
+    Placement& pl = placement(m, e->server_id);
+    if (first_time_here) pl.status = TSW_MODEL_NODATA;  // init_device_model_info (model_repo.hpp:78-80)
+    size_placement(m, pl);
+    int rc;
+    if (!pl.readiness_init) {
+        rc = init_readiness(e, m, pl, TSW_READY_HOST);
+        if (rc != TSW_OK) return rc;
+    } else {
+        rc = ensure_rows(e, m, pl);
+        if (rc != TSW_OK) return rc;
+    }
+    rc = drain_placement(e, pl);
+    if (rc != TSW_OK) return rc;
+    if (pl.counters_dirty) {
+        // The last swap was abandoned with parameters half moved (a participant went away): their
+        // tile counters were never re-armed by a last finisher.  Start this swap from zero.
+        if (!e->plan) {
+            TSW_CUDA(cudaSetDevice(e->cfg.device));
+            TSW_CUDA(cudaMemsetAsync(pl.d_done, 0, sizeof(uint32_t) * pl.capacity, (cudaStream_t)e->stream));
+            TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+        }
+        pl.counters_dirty = false;
+        pl.remote_rows.clear();
+    }
+    rc = place_blocks(e, m, pl);
+    if (rc != TSW_OK) return rc;
+
+    // transfer_model (:331-438): every accessed parameter that is not on the device yet, in access order
+    const bool from_host = src_gpu < 0;
+    out.tile = pick_tile(e, from_host);
+    for (int pi : m->access_order) {
+        if (!pl.has_row[pi] || pl.flag[pi] == TSW_READY_CUDA) continue;
+        const VParam& p = m->params[pi];
+        const uint64_t dst = pl.params[pi].cuda;
+        if ((e->plan && !defer) || p.size == 0) {
+            set_row(pl, pi, TSW_READY_CUDA, dst);
+            continue;
+        }
+        PlaceDesc d;
+        d.src = from_host ? host_dev_addr(engine_of_block_mirror(p.host), p.host) : src_pl->params[pi].cuda;
+        d.dst = dst;
+        d.bytes = p.size;
+        d.row_dst = dst;
+        d.row = (uint32_t)pi;
+        d.row_tiles = 0;
+        out.plan.descs.push_back(d);
+    }
+    if (!out.plan.descs.empty()) finish_plan(out.plan, out.tile);
+    out.m = m;
+    out.pl = &pl;
+    return TSW_OK;
+}
+
+static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine* const* helpers, int n_helpers) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Prepared pr;
+    int rc = prepare_swap(e, func, src_gpu, pr);
+    if (rc != TSW_OK) return rc;
+    Placement& pl = *pr.pl;
+    Plan& plan = pr.plan;
+    if (e->plan || plan.descs.empty()) return TSW_OK;
+
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    cudaStream_t s = (cudaStream_t)e->stream;
+    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_start, s));
+    rc = upload_plan(e, pl, plan);
+    if (rc != TSW_OK) return rc;
+
+    PlaceArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = (const PlaceDesc*)pl.d_descs;
+    a.first_tile = pl.d_first;
+    a.n_descs = (uint32_t)plan.descs.size();
+    a.tile_bytes = pr.tile;
+    a.tile_lo = 0;
+    a.tile_hi = plan.first.back();
+    a.tile_stride = 1;
+    a.done_count = pl.d_done;
+    a.table_phys = pl.d_table_phys;
+    a.table_flag = pl.d_table_flag;
+    a.host_phys = (uint64_t*)pl.phys;
+    a.host_flag = (uint32_t*)pl.flag;
+    pl.epoch += 1;
+    a.flag_value = pl.epoch;
+    a.host_flag_value = TSW_READY_CUDA;
+    a.system_scope = (n_helpers > 0) ? 1u : 0u;
+    a.status = e->d_status;
+
+    if (n_helpers > 0) {
+        // Every participating GPU works on the front of the access order at the same time:
+        // by default its CTAs draw the next tile from one counter on the target, so a link
+        // that is fed faster moves more tiles; with shard_static GPU r takes tiles r, r + n, ...
+        const int n = n_helpers + 1;
+        TSW_CUDA(cudaMemsetAsync(pl.d_ticket, 0, sizeof(uint32_t), s));
+        TSW_CUDA(cudaStreamSynchronize(s));  // descriptors and the tile dispenser must be on the target before peers read them
+        a.tile_stride = (uint32_t)n;
+        if (e->cfg.shard_static == 0) {
+            a.ticket = pl.d_ticket;   // tiles are drawn, not dealt: faster links take more
+            a.ticket_chunk = 1;
+        }
+        for (int r = n - 1; r >= 0; --r) {
+            tsw_engine* w = r == 0 ? e : helpers[r - 1];
+            if (!w || w->plan) return fail(TSW_ERR_INVALID, "sharded swap needs CUDA engines as helpers");
+            PlaceArgs ar = a;
+            ar.tile_lo = a.ticket ? 0u : (uint32_t)r;
+            TSW_CUDA(cudaSetDevice(w->cfg.device));
+            if (r != 0) TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_start, (cudaStream_t)w->stream));
+            const int mv = pick_mover(w, plan.descs);
+            cudaError_t le = launch_place(ar, mv ? w->grid_bulk : w->grid_ctas, (cudaStream_t)w->stream, mv);
+            if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
+            if (r != 0) {
+                TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_stop, (cudaStream_t)w->stream));
+                w->ev_valid = true;
+                pl.helpers.push_back(w);
+            }
+            w->kernel_launches++;
+        }
+        TSW_CUDA(cudaSetDevice(e->cfg.device));
+    } else {
+        const int mv = pick_mover(e, plan.descs);
+        cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, s, mv);
+        if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
+        e->kernel_launches++;
+    }
+    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_stop, s));
+    e->ev_valid = true;
+    e->bytes_moved += plan.bytes;
+    pl.in_flight = true;
+    return TSW_OK;
+}
+
+// Swap-in whose data movement is carried out by other parties (one process per GPU): this
+// engine places the blocks and rebinds exactly as tsw_swap_in does, then hands out the moves.
+int tsw_swap_plan(tsw_engine* e, const char* func, tsw_segment* segs, int cap, uint32_t* tile_bytes, tsw_publish* pub) {
+    if (!e || !func || !tile_bytes || !pub) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Prepared pr;
+    int rc = prepare_swap(e, func, -1, pr, true);
+    if (rc != TSW_OK) return rc;
+    Placement& pl = *pr.pl;
+    const int n = (int)pr.plan.descs.size();
+    if (n > cap || (n > 0 && !segs)) return fail(TSW_ERR_BUFFER, "segment buffer too small: need " + std::to_string(n));
+    static_assert(sizeof(tsw_segment) == sizeof(PlaceDesc), "segment layout");
+    if (n) memcpy(segs, pr.plan.descs.data(), sizeof(PlaceDesc) * n);
+    *tile_bytes = pr.tile;
+    memset(pub, 0, sizeof(*pub));
+    pub->done_count = (uint64_t)pl.d_done;
+    pub->table_phys = (uint64_t)pl.d_table_phys;
+    pub->table_flag = (uint64_t)pl.d_table_flag;
+    pl.epoch += 1;
+    pub->flag_value = pl.epoch;       // the generation; the host-visible rows are set by tsw_swap_commit
+    pub->ticket = (uint64_t)pl.d_ticket;
+    pub->ticket_chunk = 1;
+    pl.remote_rows.clear();
+    for (auto& d : pr.plan.descs) pl.remote_rows.push_back((int)d.row);
+    if (n && !e->plan) {
+        TSW_CUDA(cudaSetDevice(e->cfg.device));
+        TSW_CUDA(cudaMemsetAsync(pl.d_ticket, 0, sizeof(uint32_t), (cudaStream_t)e->stream));
+        TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+        e->bytes_moved += pr.plan.bytes;
+    }
+    return n;
+}
+
+// After every party has finished its share of a tsw_swap_plan: take the rows the kernels
+// published on the device over into the host-visible table.
+int tsw_swap_commit(tsw_engine* e, const char* func) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
+    Placement& pl = placement(m, e->server_id);
+    if (pl.remote_rows.empty()) return TSW_OK;
+    if (e->plan) {  // nothing moved, nothing to read back: the plan is the result
+        for (int row : pl.remote_rows) set_row(pl, row, TSW_READY_CUDA, pl.params[row].cuda);
+        pl.remote_rows.clear();
+        return TSW_OK;
+    }
+    std::vector<uint32_t> flag(pl.capacity);
+    std::vector<uint64_t> phys(pl.capacity);
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    TSW_CUDA(cudaMemcpy(flag.data(), pl.d_table_flag, sizeof(uint32_t) * pl.capacity, cudaMemcpyDeviceToHost));
+    TSW_CUDA(cudaMemcpy(phys.data(), pl.d_table_phys, sizeof(uint64_t) * pl.capacity, cudaMemcpyDeviceToHost));
+    std::vector<int> missing;
+    for (int row : pl.remote_rows) {
+        if (flag[row] == pl.epoch) set_row(pl, row, TSW_READY_CUDA, phys[row]);
+        else missing.push_back(row);
+    }
+    // Rows still on their way stay listed: the caller may commit again once the participants have
+    // finished, or give up and swap the model in by itself (which starts the counters afresh).
+    pl.remote_rows.swap(missing);
+    if (!pl.remote_rows.empty()) {
+        pl.counters_dirty = true;
+        return fail(TSW_ERR_STATE, std::to_string(pl.remote_rows.size()) + " parameters were not completed by the participants");
+    }
+    pl.counters_dirty = false;
+    return TSW_OK;
+}
+
+int tsw_swap_in(tsw_engine* e, const char* func, int src_gpu) { return swap_in_impl(e, func, src_gpu, nullptr, 0); }
+
+int tsw_swap_in_sharded(tsw_engine* e, const char* func, tsw_engine* const* helpers, int n_helpers) {
+    if (n_helpers < 0 || (n_helpers > 0 && !helpers)) return fail(TSW_ERR_INVALID, "bad helper list");
+    return swap_in_impl(e, func, -1, helpers, n_helpers);
+}
+
+int tsw_wait_ready(tsw_engine* e, const char* func, int64_t timeout_ns) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Placement* pl;
+    std::vector<int> order;
+    {
+        Lock g1(repo().mu);
+        Lock g2(e->mu);
+        Model* m = repo().find(func);
+        if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
+        pl = &placement(m, e->server_id);
+        if (!pl->readiness_init) return fail(TSW_ERR_STATE, "model has no readiness rows on this engine");
+        for (int pi : m->access_order)
+            if (pl->has_row[pi]) order.push_back(pi);
+    }
+    const int64_t deadline = now_ns() + timeout_ns;
+    // the kernel completes parameters roughly in access order: wait from the back
+    for (auto it = order.rbegin(); it != order.rend(); ++it) {
+        int64_t left = deadline - now_ns();
+        WaitResult w = wait_row(e, *pl, *it, left > 0 ? left : 0);
+        if (w.rc != TSW_OK) return w.rc;
+    }
+    return TSW_OK;
+}
+
+int tsw_poll_ready(tsw_engine* e, const char* func) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
+    auto it = m->place.find(e->server_id);
+    if (it == m->place.end() || !it->second.readiness_init) return fail(TSW_ERR_STATE, "model has no readiness rows on this engine");
+    if (e->h_status && *e->h_status) return fail(TSW_ERR_KERNEL, "placement kernel reported an inconsistent tile table");
+    int waiting = 0;
+    for (int pi : m->access_order)
+        if (it->second.has_row[pi] && it->second.flag[pi] != TSW_READY_CUDA) ++waiting;
+    return waiting;
+}
+
+int tsw_check_alloc(tsw_engine* e, const char* func) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return 0;
+    auto it = m->place.find(e->server_id);
+    if (it == m->place.end()) return 0;
+    Placement& pl = it->second;
+    size_placement(m, pl);
+    for (auto& kv : m->block_order) {
+        const Placement::B& b = pl.blocks[kv.second];
+        if (!b.known || !b.in_cuda) return 0;
+    }
+    return 1;
+}
+
+// --------------------------------------------------------------- swap-out
+
+int tsw_evict(tsw_engine* e, const char* func, int writeback) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "try to evict unrecognized model");
+    auto pit = m->place.find(e->server_id);
+    if (pit == m->place.end() || !pit->second.readiness_init)
+        return fail(TSW_ERR_UNKNOWN_MODEL, "try to evict unrecognized model");  // memory_manager.hpp:241-244
+    Placement& pl = pit->second;
+    size_placement(m, pl);
+
+    if (!e->plan) {
+        int drc = drain_placement(e, pl);
+        if (drc != TSW_OK) return drc;
+        TSW_CUDA(cudaSetDevice(e->cfg.device));
+        if (writeback) {
+            // Eviction write-back: resident parameter bytes -> host store, through the same kernel.
+            Plan plan;
+            for (size_t pi = 0; pi < m->params.size(); ++pi) {
+                if (!pl.has_row[pi] || pl.flag[pi] != TSW_READY_CUDA) continue;
+                const VParam& p = m->params[pi];
+                const Placement::B& b = pl.blocks[p.block];
+                if (!b.in_cuda || p.size == 0) continue;
+                PlaceDesc d;
+                d.src = pl.params[pi].cuda;
+                d.dst = host_dev_addr(engine_of_block_mirror(p.host), p.host);
+                d.bytes = p.size;
+                d.row_dst = d.dst;
+                d.row = (uint32_t)pi;
+                d.row_tiles = 0;
+                plan.descs.push_back(d);
+            }
+            if (!plan.descs.empty()) {
+                int rc = ensure_rows(e, m, pl);
+                if (rc != TSW_OK) return rc;
+                finish_plan(plan, e->tile_host);
+                rc = upload_plan(e, pl, plan);
+                if (rc != TSW_OK) return rc;
+                PlaceArgs a;
+                memset(&a, 0, sizeof(a));
+                a.descs = (const PlaceDesc*)pl.d_descs;
+                a.first_tile = pl.d_first;
+                a.n_descs = (uint32_t)plan.descs.size();
+                a.tile_bytes = e->tile_host;
+                a.tile_lo = 0;
+                a.tile_hi = plan.first.back();
+                a.tile_stride = 1;
+                a.system_scope = 1;
+                a.status = e->d_status;
+                const int mv = pick_mover(e, plan.descs);
+                cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, (cudaStream_t)e->stream, mv);
+                if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("write-back kernel launch: ") + cudaGetErrorString(le));
+                e->kernel_launches++;
+                e->bytes_moved += plan.bytes;
+                TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+            }
+        }
+    }
+
+    // evict_model (:247-256): release every resident block, in the reference's block order
+    for (auto& kv : m->block_order) {
+        const int bi = kv.second;
+        Placement::B& b = pl.blocks[bi];
+        if (!b.in_cuda) continue;
+        b.in_cuda = false;
+        e->pool->evict(b.cuda, m->blocks[bi].size, false);
+        if (m->blocks[bi].is_model) {
+            for (int pi : m->blocks[bi].params)  // reset_model_readiness (:301-309)
+                if (pl.has_row[pi]) set_row(pl, pi, TSW_READY_HOST, 0);
+        }
+    }
+    e->pool->finish_release_block();
+    return TSW_OK;
+}
+
+// --------------------------------------------------------------- translation
+
+int tsw_translate(tsw_engine* e, const char* func, uint64_t vptr, int search_amid, int64_t timeout_ns, uint64_t* out) {
+    if (!e || !func || !out) return fail(TSW_ERR_INVALID, "null argument");
+    Placement* wait_pl = nullptr;
+    int wait_idx = -1;
+    {
+        Lock g1(repo().mu);
+        Lock g2(e->mu);
+        Model* m = repo().find(func);
+        if (!m || m->place.find(e->server_id) == m->place.end()) {
+            *out = vptr;  // memory_manager.hpp:270
+            return TSW_OK;
+        }
+        auto pit = m->param_by_vaddr.find(vptr);
+        if (pit == m->param_by_vaddr.end()) {
+            *out = phy_address(e, m, vptr, search_amid != 0);
+            return TSW_OK;
+        }
+        // check_param_readiness (:527-540)
+        Placement& pl = placement(m, e->server_id);
+        size_placement(m, pl);
+        const int pi = pit->second;
+        if (!pl.readiness_init) {
+            *out = vptr;
+            return TSW_OK;
+        }
+        if (e->active_params.count(vptr) && pl.has_row[pi]) {
+            wait_pl = &pl;
+            wait_idx = pi;
+        } else {
+            *out = pl.params[pi].cuda;
+            return TSW_OK;
+        }
+    }
+    WaitResult w = wait_row(e, *wait_pl, wait_idx, timeout_ns);
+    if (w.rc != TSW_OK) return w.rc;
+    *out = w.phys;
+    return TSW_OK;
+}
+
+// Stream-ordered form of get_cuda_addr.  The rebound address of a parameter is known as soon
+// as its block is placed; what the executor has to wait for is the bytes.  Instead of blocking
+// the host (check_param_readiness, memory_manager.hpp:527-540) this returns the address at once
+// and, if the parameter is still on its way, makes `stream` wait for it: a stream memory
+// operation on the row's generation word in the device pointer table, which the placement
+// kernel writes when the row's last tile has landed.  Kernels that use the parameter can then
+// be enqueued behind it before the weights have arrived.  Nothing spins on the device.
+int tsw_translate_async(tsw_engine* e, const char* func, uint64_t vptr, void* stream, uint64_t* out, int* waited) {
+    if (!e || !func || !out) return fail(TSW_ERR_INVALID, "null argument");
+    if (waited) *waited = 0;
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine has no streams");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m || m->place.find(e->server_id) == m->place.end()) {
+        *out = vptr;
+        return TSW_OK;
+    }
+    auto pit = m->param_by_vaddr.find(vptr);
+    if (pit == m->param_by_vaddr.end()) {
+        *out = phy_address(e, m, vptr, true);
+        return TSW_OK;
+    }
+    Placement& pl = placement(m, e->server_id);
+    size_placement(m, pl);
+    const int pi = pit->second;
+    if (!pl.readiness_init) {
+        *out = vptr;
+        return TSW_OK;
+    }
+    *out = pl.params[pi].cuda;
+    if (!(e->active_params.count(vptr) && pl.has_row[pi])) return TSW_OK;   // as check_param_readiness: not part of the last swap
+    if (pl.flag[pi] == TSW_READY_CUDA) return TSW_OK;                       // already there
+    if (!pl.in_flight) return fail(TSW_ERR_STATE, "parameter is neither on the device nor on its way: swap the model in first");
+    typedef int (*wait_fn_t)(cudaStream_t, unsigned long long, unsigned int, unsigned int);
+    static wait_fn_t wait_fn = nullptr;
+    if (!wait_fn) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t err = cudaGetDriverEntryPoint("cuStreamWaitValue32", &fn, cudaEnableDefault, &qres);
+        if (err != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+            return fail(TSW_ERR_CUDA, "stream memory operations are not available from this driver");
+        wait_fn = (wait_fn_t)fn;
+    }
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    const int rc = wait_fn((cudaStream_t)stream, (unsigned long long)(uintptr_t)&pl.d_table_flag[pi], pl.epoch, 0x0 /* GEQ */);
+    if (rc != 0) return fail(TSW_ERR_CUDA, "cuStreamWaitValue32 failed with driver error " + std::to_string(rc));
+    if (waited) *waited = 1;
+    return TSW_OK;
+}
+
+int tsw_is_model_address(tsw_engine* e, const char* func, uint64_t vptr) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Model* m = repo().find(func);
+    return (m && m->param_by_vaddr.count(vptr)) ? 1 : 0;
+}
+
+int tsw_valid_memory_address(tsw_engine* e, const char* func, uint64_t vptr) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Model* m = repo().find(func);
+    if (m) cache_interior_pointer(m, vptr);
+    return 0;
+}
+
+}  // extern "C"
