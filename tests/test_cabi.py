@@ -56,3 +56,32 @@ def test_cuda_engine_without_a_device_fails_loudly(built):
     with pytest.raises(SwapError) as e:
         MemoryManager(0, device=0)
     assert e.value.code in (_cabi.ERR_NO_DEVICE, _cabi.ERR_CUDA)
+
+
+def test_null_arguments_are_refused_not_dereferenced(built):
+    """Every entry point, called with null for every pointer and zero for every number, answers with an
+    error (or does nothing) -- in a child process, so that a crash would be seen and not end the run."""
+    import subprocess
+    import sys
+    child = r'''
+import ctypes as C, sys
+sys.path.insert(0, sys.argv[1])
+from torpor_b200 import _cabi
+L = _cabi.lib()
+noop = {"signal": _cabi.SIGNAL_FN(lambda *a: None), "ack": _cabi.ACK_FN(lambda *a: None)}
+for name, (res, args) in _cabi.SIGNATURES.items():
+    vals = []
+    for a in args:
+        if a is _cabi.SIGNAL_FN: vals.append(noop["signal"])
+        elif a is _cabi.ACK_FN: vals.append(noop["ack"])
+        elif a in (C.c_void_p, C.c_char_p) or (isinstance(a, type) and issubclass(a, C._Pointer)): vals.append(None)
+        else: vals.append(0)
+    r = getattr(L, name)(*vals)
+    if name in ("tsw_last_error", "tsw_version"):
+        assert isinstance(r, bytes)
+    elif res is not None:
+        assert r <= 0, (name, r)
+print("all refused")
+'''
+    r = subprocess.run([sys.executable, "-c", child, ROOT], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+    assert r.returncode == 0 and "all refused" in r.stdout, (r.returncode, r.stdout[-500:], r.stderr[-1500:])

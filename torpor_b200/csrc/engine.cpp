@@ -382,6 +382,7 @@ const char* tsw_last_error(void) { return tsw::last_error().c_str(); }
 const char* tsw_version(void) { return "torpor-swap-b200 0.1 (sm_100a)"; }
 
 void tsw_config_default(tsw_config* c) {
+    if (!c) return;
     memset(c, 0, sizeof(*c));
     c->device = 0;
     c->server_id = 0;
@@ -437,6 +438,7 @@ int tsw_repo_reset(void) {
 }
 
 int tsw_repo_add_model_info(const char* func, int gpu) {
+    if (!func) return fail(TSW_ERR_INVALID, "null argument");
     Repo& r = repo();
     Lock g(r.mu);
     Model* m = r.get_or_create(func);
@@ -446,6 +448,7 @@ int tsw_repo_add_model_info(const char* func, int gpu) {
 }
 
 int tsw_repo_remove_model_info(const char* func, int gpu) {
+    if (!func) return fail(TSW_ERR_INVALID, "null argument");
     Repo& r = repo();
     Lock g(r.mu);
     Model* m = r.get_or_create(func);
@@ -455,6 +458,7 @@ int tsw_repo_remove_model_info(const char* func, int gpu) {
 }
 
 int tsw_repo_model_status(const char* func, int gpu) {
+    if (!func) return fail(TSW_ERR_INVALID, "null argument");
     Repo& r = repo();
     Lock g(r.mu);
     Model* m = r.find(func);
@@ -465,6 +469,7 @@ int tsw_repo_model_status(const char* func, int gpu) {
 }
 
 uint64_t tsw_repo_total_size(const char* func) {
+    if (!func) return 0;
     Repo& r = repo();
     Lock g(r.mu);
     Model* m = r.find(func);
@@ -472,6 +477,7 @@ uint64_t tsw_repo_total_size(const char* func) {
 }
 
 int tsw_repo_active_devices(const char* func, int* gpus, int cap) {
+    if (!func) return fail(TSW_ERR_INVALID, "null argument");
     Repo& r = repo();
     Lock g(r.mu);
     auto it = r.active_devices.find(func);
