@@ -85,3 +85,53 @@ print("all refused")
 '''
     r = subprocess.run([sys.executable, "-c", child, ROOT], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
     assert r.returncode == 0 and "all refused" in r.stdout, (r.returncode, r.stdout[-500:], r.stderr[-1500:])
+
+
+def test_random_calls_with_wild_values_never_crash(built):
+    """Random calls on two plan-only engines with unknown functions, wild pointers and sizes, calls out of
+    order: errors are fine, a crash is not.  Run in child processes (six seeds)."""
+    import subprocess
+    import sys
+    child = r'''
+import sys, ctypes as C, random
+sys.path.insert(0, sys.argv[2])
+import numpy as np
+from torpor_b200 import _cabi
+from torpor_b200.memory_manager import MemoryManager, repo_reset, SwapError, Evictor, Scheduler, Controller
+seed = int(sys.argv[1]); rnd = random.Random(seed)
+repo_reset()
+ms = [MemoryManager(0, device=-1, server_id=g, gpu_count=2, block_manager=rnd.choice(["Buddy", "Fixed"])) for g in range(2)]
+funcs = ["a", "b", "c", "", "zz"]
+ptrs = [0, 1, 0x600000000000, 0x600138000000, 2**63, 2**64 - 1]
+sizes = [0, 1, 512, 2 << 20, 20 << 20, 48 << 20, 130 << 20, (1 << 40), 2**63]
+def pick(xs): return rnd.choice(xs)
+for step in range(600):
+    m = pick(ms); f = pick(funcs)
+    op = rnd.randrange(16)
+    try:
+        if op == 0: m.track_begin(f)
+        elif op == 1: m.track_end(f)
+        elif op == 2:
+            p = m.malloc(f, pick(sizes[:7]), rnd.random() < 0.5); ptrs.append(p); ptrs.append(p + pick([0, 8, 512, 4096]))
+        elif op == 3: m.free(f, pick(ptrs))
+        elif op == 4: m.memcpy_h2d_model(f, pick(ptrs), np.zeros(pick([0, 1, 64, 4096]), dtype=np.uint8))
+        elif op == 5: m.sync_done(f)
+        elif op == 6: m.mark_access(pick(ptrs))
+        elif op == 7: m.swap_in(f, pick([-1, 0, 1, 5, -7]))
+        elif op == 8: m.evict(f)
+        elif op == 9: m.get_cuda_addr(f, pick(ptrs), timeout_ns=1000000) if hasattr(m, "get_cuda_addr") else None
+        elif op == 10: m.dump_blocks(f); m.dump_params(f, canonical=True)
+        elif op == 11: m.check_alloc(f); m.is_model_address(f, pick(ptrs)); m.valid_memory_address(f, pick(ptrs))
+        elif op == 12: m.poll_ready(f)
+        elif op == 13: m.swap_in_sharded(f, [x for x in ms if x is not m])
+        elif op == 14: m.swap_plan(f); m.swap_commit(f)
+        elif op == 15: m.canonical_address(f, pick(ptrs))
+    except (SwapError, RuntimeError, ValueError, OverflowError, C.ArgumentError):
+        pass
+for m in ms: m.close()
+repo_reset()
+print("ok", seed)
+'''
+    for seed in range(6):
+        r = subprocess.run([sys.executable, "-c", child, str(seed), ROOT], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=300)
+        assert r.returncode == 0 and f"ok {seed}" in r.stdout, (seed, r.returncode, r.stderr[-1500:])
