@@ -385,3 +385,27 @@ def test_replica_load_signal_through_both_executors(built):
     for e in engines:
         e.close()
     repo_reset(); lib.reset_world(); lib.lib.tso_exec_reset()
+
+
+def test_decoder_refuses_malformed_bytes_cleanly():
+    """Random bytes either parse (unknown fields skipped) or raise ValueError -- nothing else."""
+    import random
+    rnd = random.Random(7)
+    parsed = 0
+    for _ in range(20000):
+        buf = bytes(rnd.randrange(256) for _ in range(rnd.randrange(0, 40)))
+        msg = rnd.choice(list(wire.SCHEMA))
+        try:
+            wire.decode(msg, buf)
+            parsed += 1
+        except ValueError:
+            pass
+    assert parsed > 100
+    # and what protobuf itself would call a truncated message is one here as well
+    good = wire.encode("cudaMemcpyAsyncQuery", {"kind": wire.H2D, "dst": 1 << 40, "count": 64, "payload": bytes(64)})
+    for cut in range(1, len(good)):
+        try:
+            wire.decode("cudaMemcpyAsyncQuery", good[:cut])
+        except ValueError:
+            continue
+    assert wire.decode("cudaMemcpyAsyncQuery", good)["payload"] == bytes(64)

@@ -65,6 +65,8 @@ def _varint(v: int) -> bytes:
 def _read_varint(buf: bytes, pos: int) -> Tuple[int, int]:
     shift = val = 0
     while True:
+        if pos >= len(buf):
+            raise ValueError("truncated varint")
         b = buf[pos]
         pos += 1
         val |= (b & 0x7F) << shift
@@ -113,25 +115,31 @@ def decode(message: str, buf: bytes) -> dict:
             val, pos = _read_varint(buf, pos)
         elif wt == LEN:
             n, pos = _read_varint(buf, pos)
-            val = buf[pos:pos + n]
-            if len(val) != n:
+            if n > len(buf) - pos:
                 raise ValueError("truncated message")
+            val = buf[pos:pos + n]
             pos += n
-        elif wt == 1:
-            val, pos = buf[pos:pos + 8], pos + 8
-        elif wt == 5:
-            val, pos = buf[pos:pos + 4], pos + 4
+        elif wt in (1, 5):
+            n = 8 if wt == 1 else 4
+            if n > len(buf) - pos:
+                raise ValueError("truncated message")
+            val, pos = buf[pos:pos + n], pos + n
         else:
             raise ValueError(f"unsupported wire type {wt}")
         if num not in spec:
             continue                # unknown fields are skipped, as protobuf does
         name, kind = spec[num]
+        if (kind == "u") != (wt == VARINT) or (kind != "u" and wt != LEN):
+            continue                # a known number with another wire type is an unknown field to protobuf, too
         if kind == "u":
             out[name] = val
         elif kind == "b":
             out[name] = bytes(val)
         elif kind == "s":
-            out[name] = bytes(val).decode()
+            try:
+                out[name] = bytes(val).decode()
+            except UnicodeDecodeError:
+                raise ValueError(f"field {num} of {message} is not valid UTF-8") from None
         elif kind == "rb":
             out[name].append(bytes(val))
         else:
