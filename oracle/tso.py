@@ -11,7 +11,7 @@ from __future__ import annotations
 import ctypes as C
 import os
 import subprocess
-from typing import List, Optional
+from typing import List
 
 import numpy as np
 

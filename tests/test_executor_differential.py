@@ -7,7 +7,6 @@ must be identical, and so must every response on the way."""
 import os
 import struct
 
-import numpy as np
 import pytest
 
 import scenarios

@@ -18,7 +18,6 @@ from __future__ import annotations
 import argparse
 import collections
 import json
-import os
 import time
 from typing import Dict, List, Optional
 

@@ -329,7 +329,7 @@ def bench_main(args, bench):
     import torch
     import torch.distributed as dist
     from . import workloads as W
-    from .memory_manager import ModelRepo, checksum_host, repo_reset
+    from .memory_manager import checksum_host, repo_reset
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
