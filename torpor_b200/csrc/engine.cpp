@@ -555,16 +555,16 @@ static int engine_setup(const tsw_config* cfg, tsw_engine* e) {
             const uint32_t first[2] = {0, 1};
             TSW_CUDA(cudaMemcpy(e->raw_d_descs, &d, sizeof(d), cudaMemcpyHostToDevice));
             TSW_CUDA(cudaMemcpy(e->raw_d_first, first, sizeof(first), cudaMemcpyHostToDevice));
-            PlaceArgs a;
-            memset(&a, 0, sizeof(a));
-            a.descs = (const PlaceDesc*)e->raw_d_descs;
-            a.first_tile = (const uint32_t*)e->raw_d_first;
-            a.n_descs = 1;
-            a.tile_bytes = 64;
-            a.tile_hi = 1;
-            a.tile_stride = 1;
-            a.status = e->d_status;
-            cudaError_t le = launch_place(a, 1, s);
+            PlaceArgs warm_up;
+            memset(&warm_up, 0, sizeof(warm_up));
+            warm_up.descs = (const PlaceDesc*)e->raw_d_descs;
+            warm_up.first_tile = (const uint32_t*)e->raw_d_first;
+            warm_up.n_descs = 1;
+            warm_up.tile_bytes = 64;
+            warm_up.tile_hi = 1;
+            warm_up.tile_stride = 1;
+            warm_up.status = e->d_status;
+            cudaError_t le = launch_place(warm_up, 1, s);
             if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("warm-up launch: ") + cudaGetErrorString(le));
             TSW_CUDA(cudaStreamSynchronize(s));
         }
