@@ -409,3 +409,50 @@ def test_decoder_refuses_malformed_bytes_cleanly():
         except ValueError:
             continue
     assert wire.decode("cudaMemcpyAsyncQuery", good)["payload"] == bytes(64)
+
+
+def test_result_copy_and_stream_synchronise_follow_the_reference_protocol(built):
+    """The result copy of a request (cudaMemcpyAsync device-to-host) is not answered at once: it ends the
+    request, and its bytes travel back in one AsyncResponse when the client synchronises the stream
+    (cuda_server.hpp:1038-1049,1131-1148).  Same bytes from the reference's executor (uploaded data read
+    back from its stand-in device memory) and from WireExecutor over a manager that returns those data."""
+    lib = _ref_exec()
+    ref = lib.executor(0, 0, 1)
+    data = bytes(range(200))
+
+    class Manager:                                   # what WireExecutor needs of a manager for this exchange
+        device, server_id = -1, 0
+        store = {}
+        def set_track_model_memory(self, f): pass
+        def unset_track_model_memory(self, f): pass
+        def cudaMallocBackend(self, size, flag, f): return self.ptr
+        def cudaMemcpyAsyncBackendHtoD(self, dst, payload, stream, flag, f): self.store[dst] = bytes(payload); return 0
+        def cudaMemcpyAsyncBackendDtoH(self, src, count, stream, f): return np.frombuffer(self.store[src][:count], dtype=np.uint8)
+        def init_model_readiness(self, f): pass
+
+    mine = wire.WireExecutor(Manager())
+
+    def ql(queries):
+        return wire.encode("QueryList", {"queries": [{"type": t, "query": (wire.encode(m, f) if m else f), "client_id": 1}
+                                                     for t, m, f in queries]})
+
+    ref.signal(wire.SIG_STARTUP, "5"); mine.signal(wire.SIG_STARTUP, "5")
+    r = ref.handle(ql([(wire.Q_MALLOC, "cudaMallocQuery", {"size": 2 << 20})]))
+    Manager.ptr = wire.decode("cudaMallocResponse", r[0])["ptr"]
+    assert mine.handle(ql([(wire.Q_MALLOC, "cudaMallocQuery", {"size": 2 << 20})])) == r
+    up = ql([(wire.Q_MEMCPY_ASYNC, "cudaMemcpyAsyncQuery", {"kind": wire.H2D, "dst": Manager.ptr, "count": len(data),
+                                                            "payload": data, "stream": bytes(8)}),
+             (wire.Q_DEVICE_SYNCHRONIZE, "genericResponse", {})])
+    assert ref.handle(up) == mine.handle(up)
+    back = ql([(wire.Q_MEMCPY_ASYNC, "cudaMemcpyAsyncQuery", {"kind": wire.D2H, "src": Manager.ptr, "dst": 0x7f0000001000,
+                                                              "count": 100, "stream": bytes(8)})])
+    assert ref.handle(back) == mine.handle(back) == []            # no answer yet; the request is over
+    assert ref.completions() == [0] and mine.active_func == ""
+    sync = ql([(wire.Q_STREAM_SYNCHRONIZE, None, bytes(8))])
+    a, b = ref.handle(sync), mine.handle(sync)
+    assert a == b and len(a) == 1
+    got = wire.decode("AsyncResponse", a[0])
+    assert got["responses"] == [{"ptr": 0x7f0000001000, "payload": data[:100]}]
+    assert ref.handle(sync) == mine.handle(sync)                   # nothing pending any more: an empty AsyncResponse
+    ref.close()
+    lib.reset_world(); lib.lib.tso_exec_reset()

@@ -19,6 +19,7 @@ from typing import Dict, List, Tuple
 
 # QueryType values (proto/cudarpc.proto:7-50)
 Q_DEVICE_SYNCHRONIZE, Q_MALLOC, Q_FREE, Q_MEMCPY, Q_MEMCPY_ASYNC, Q_MEMSET_ASYNC, Q_LAUNCH_KERNEL = 14, 30, 31, 32, 33, 34, 50
+Q_STREAM_SYNCHRONIZE = 23
 # cudaMemcpyKind
 H2D, D2H, D2D = 1, 2, 3
 # signal.RequestType (proto/signal.proto:5-13) and executor signals (common/include/utils.hpp:70-74)
@@ -40,6 +41,8 @@ SCHEMA: Dict[str, List[Tuple[int, str, str]]] = {
     "cudaMemcpyResponse": [(1, "error", "u"), (2, "payload", "b")],
     "cudaMemcpyAsyncQuery": [(1, "kind", "u"), (2, "src", "u"), (3, "dst", "u"), (4, "count", "u"), (5, "payload", "b"),
                              (6, "stream", "b")],
+    "cudaMemcpyAsyncResponse": [(1, "ptr", "u"), (2, "payload", "b")],
+    "AsyncResponse": [(1, "error", "u"), (2, "responses", "rm:cudaMemcpyAsyncResponse")],
     "cudaMemsetAsyncQuery": [(1, "ptr", "u"), (2, "value", "u"), (3, "count", "u"), (4, "stream", "b")],
     "cudaLaunchKernelQuery": [(1, "function", "s"), (2, "grid_dim_x", "u"), (3, "grid_dim_y", "u"), (4, "grid_dim_z", "u"),
                               (5, "block_dim_x", "u"), (6, "block_dim_y", "u"), (7, "block_dim_z", "u"), (8, "args", "rb"),
@@ -166,6 +169,7 @@ class WireExecutor:
         # kernel_model_access_loc (src/server/kernel_lookup.cpp): func -> kernel -> {(arg, word)}
         self.access_loc: Dict[str, Dict[str, set]] = {}
         self.launched: List[Tuple[str, List[bytes]]] = []
+        self.async_results: list = []        # stream_async_msg_: (client's destination, array being read into)
 
     # ---- signals from the controller (cuda_server.hpp:212-255)
     def signal(self, sig: int, func: str):
@@ -216,9 +220,13 @@ class WireExecutor:
                 return encode("cudaMemcpyResponse", {"error": 0 if rc == 0 else 1}) if qtype == Q_MEMCPY else None
             if kind == D2H:
                 data = self.mm.cudaMemcpyAsyncBackendDtoH(q["src"], q["count"], 0, f)
-                self._device_sync()
                 if qtype == Q_MEMCPY_ASYNC:
-                    self.complete()          # the result copy ends a request (cuda_server.hpp:1043-1049)
+                    # the result copy: kept until the client synchronises the stream, and it ends the
+                    # request (cuda_server.hpp:1038-1049); nothing is answered now
+                    self.async_results.append((q["dst"], data))      # read after the synchronise
+                    self.complete()
+                    return None
+                self._device_sync()
                 return encode("cudaMemcpyResponse", {"error": 0, "payload": data.tobytes()})
             if kind == D2D:
                 self.mm.cudaMemcpyAsyncBackendDtoD(q["dst"], q["src"], q["count"], 0, f)
@@ -234,6 +242,12 @@ class WireExecutor:
             self.flag = LOAD_TRACK
             self.mm.init_model_readiness(f)
             return encode("genericResponse", {"error": 0})
+        if qtype == Q_STREAM_SYNCHRONIZE:
+            # the body is the stream handle itself, not a message (cuda_server.hpp:1131-1148): every result
+            # copy issued since the last synchronise travels back in one AsyncResponse
+            self._device_sync()
+            pending, self.async_results = self.async_results, []
+            return encode("AsyncResponse", {"error": 0, "responses": [{"ptr": p, "payload": b.tobytes()} for p, b in pending]})
         if qtype == Q_LAUNCH_KERNEL:
             q = decode("cudaLaunchKernelQuery", body)
             self.launched.append((q["function"], self.rewrite_args(q["function"], q["args"])))
