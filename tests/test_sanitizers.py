@@ -9,7 +9,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SRC = [os.path.join(ROOT, "tests", "host_stress.cpp")] + [os.path.join(ROOT, "torpor_b200", "csrc", f)
-                                                            for f in ("engine.cpp", "engine_swap.cpp", "engine_share.cpp", "pool.cpp", "policy.cpp")]
+                                                            for f in ("engine.cpp", "engine_swap.cpp", "engine_share.cpp", "pool.cpp", "evictor.cpp", "scheduler.cpp", "controller.cpp")]
 
 
 @pytest.mark.parametrize("name,flags", [("asan_ubsan", "-fsanitize=address,undefined"), ("tsan", "-fsanitize=thread")])
