@@ -72,7 +72,17 @@ typedef struct {
                                aligned (else falls back to 0).  Env TORPOR_SWAP_MOVER overrides. */
     int shard_static;       /* tsw_swap_in_sharded: 0 = participants draw tiles from a shared counter
                                (default), 1 = tile t is fixed to participant t mod n */
+    int host_store_mode;    /* how the host model store is made page-locked (model_repo.hpp:124-141,173-177
+                               keeps it pageable): 0 = cudaHostAlloc, portable + device-mapped (default);
+                               TSW_STORE_WRITE_COMBINED = the same, write-combined (no CPU-cache snoop on
+                               device reads; slow to read back on the CPU); TSW_STORE_HUGE_PAGES = an
+                               anonymous mapping (the shm arena when host_arena_shm is set) advised to
+                               transparent huge pages, then registered.  Env TORPOR_SWAP_HOST_STORE
+                               overrides.  Huge pages apply to the arena only (host_arena_bytes > 0). */
+    int ticket_chunk;       /* sharded swaps that draw tiles from the shared counter: tiles taken per
+                               draw; 0 = 1 */
 } tsw_config;
+enum { TSW_STORE_DEFAULT = 0, TSW_STORE_WRITE_COMBINED = 1, TSW_STORE_HUGE_PAGES = 2 };
 
 void tsw_config_default(tsw_config* cfg);
 
@@ -144,8 +154,22 @@ int tsw_translate(tsw_engine* e, const char* func, uint64_t vptr, int search_ami
  * so the executor can enqueue the kernels of a request before its weights have landed
  * (replaces the blocking wait of cuda_server.hpp:1265-1268 -> memory_manager.hpp:527-540).
  * *waited = 1 if a wait was enqueued.  TSW_ERR_STATE if the parameter is neither resident nor
- * part of a swap in flight (a wait on it could never be satisfied). */
+ * part of a swap in flight (a wait on it could never be satisfied).
+ * The wait is bounded from the host.  The rows waited for are remembered; they are let go -- the
+ * host writes the generation word they wait for, the stream runs on WITHOUT the bytes, and the
+ * row is marked failed -- when the whole-model wait gives up (tsw_wait_ready times out or sees a
+ * kernel error), when a kernel error is taken note of at the next swap or eviction on the engine,
+ * when the model is evicted or its swap-in cannot be placed, when the engine is destroyed, or on
+ * request (tsw_release_waiters).  After synchronising a stream that waited, check tsw_poll_ready
+ * or tsw_translate: both answer TSW_ERR_KERNEL for a failed row until the model is swapped in
+ * again or evicted.  A swap that is repeated (tsw_swap_in after an abandoned plan) releases the
+ * waiters of the earlier attempt with the real bytes: generations only grow and a wait is for
+ * "at least this generation". */
 int tsw_translate_async(tsw_engine* e, const char* func, uint64_t vptr, void* stream, uint64_t* out, int* waited);
+/* Let go of every stream still waiting for a parameter of func on this engine (see above);
+ * returns how many rows were released without their bytes.  No counterpart in the reference,
+ * whose wait (memory_manager.hpp:527-540) has no way out. */
+int tsw_release_waiters(tsw_engine* e, const char* func);
 int tsw_is_model_address(tsw_engine* e, const char* func, uint64_t vptr);    /* :286-291; 1/0 */
 int tsw_valid_memory_address(tsw_engine* e, const char* func, uint64_t vptr); /* :293-298; always 0 */
 
@@ -250,6 +274,12 @@ int tsw_arena_attach(tsw_engine* e, const char* shm_name, uint64_t size, uint64_
  * (rows are not summed over the list), and no device timing is recorded. */
 int tsw_place_segments_static(int device, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
                               uint32_t tile_stride, const tsw_publish* pub, void* stream);
+/* The word in which the kernel of tsw_place_segments_static reports a table that does not fit its
+ * tile numbering -- what overlapping calls on one device produce -- read back after `stream` has
+ * drained (this call synchronises it); 0 = nothing reported.  clear != 0 resets a non-zero word.
+ * Allocates nothing either.  The cached array addresses do not survive a cudaDeviceReset; the
+ * caller's current device is unchanged by both calls.  No counterpart in the reference. */
+int tsw_place_segments_static_status(int device, void* stream, uint32_t* status, int clear);
 
 /* Counters: kernels launched by this engine, bytes they were asked to move, and device
  * time of the last swap on the transfer stream (CUDA events), in nanoseconds. */

@@ -15,6 +15,8 @@ int main() {
     using namespace server;
     using namespace server::manager;
     setenv("TORPOR_SWAP_ADAPTER_PROBE", "1", 1);
+    setenv("TORPOR_SWAP_WAIT_PERIODS", "2", 1);   // bound the repeated wait (unbounded by default, as the reference)
+    setenv("TORPOR_SWAP_WAIT_MS", "20", 1);
     auto log = std::make_shared<spdlog::logger>("probe", std::make_shared<spdlog::sinks::null_sink_mt>());
     // the probe drives a plan-only engine directly; start_trans_thread would need a GPU
     tsw_config cfg;
@@ -89,6 +91,22 @@ int main() {
                 printf("missing log line: %s\n--- log ---\n%s\n", want, logged.c_str());
                 return 16;
             }
+        // The wait that runs out: a planned swap whose moves nobody carries out leaves the rows
+        // unready.  The reference would block; the adapter repeats the wait a bounded number of
+        // periods here and must then answer null -- never the client's own pointer, which names
+        // pool memory that may belong to another function by now.
+        m2.evict_model(g);
+        tsw_segment segs[4];
+        tsw_publish pub;
+        uint32_t tile = 0;
+        if (tsw_swap_plan(m2.engine(), g.c_str(), segs, 4, &tile, &pub) != 1) return 17;
+        void* got = m2.get_cuda_addr(g, (char*)block + 1024);
+        if (got != nullptr) {
+            printf("timed-out translation returned %p (client pointer %p)\n", got, (char*)block + 1024);
+            return 18;
+        }
+        if (tsw_swap_commit(m2.engine(), g.c_str()) != TSW_OK) return 19;
+        if (m2.get_cuda_addr(g, (char*)block + 1024) == nullptr) return 20;
         m2.destroy_trans_thread();
     }
 

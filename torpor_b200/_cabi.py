@@ -19,6 +19,7 @@ ERR_TIMEOUT, ERR_NOT_FOUND, ERR_BUFFER, ERR_STATE, ERR_KERNEL = -6, -7, -8, -9, 
 READY_HOST, READY_PINNED, READY_CUDA = 0, 1, 2
 MODEL_FULL, MODEL_INCOMPLETE, MODEL_PARTIAL, MODEL_NODATA = 0, 1, 2, 3
 POOL_BUDDY, POOL_FIXED = 0, 1
+STORE_DEFAULT, STORE_WRITE_COMBINED, STORE_HUGE_PAGES = 0, 1, 2
 
 _ERR_NAMES = {
     -1: "TSW_ERR_INVALID", -2: "TSW_ERR_NO_DEVICE", -3: "TSW_ERR_CUDA", -4: "TSW_ERR_POOL_EXHAUSTED",
@@ -47,6 +48,8 @@ class Config(C.Structure):
         ("tile_bytes_device", C.c_int),
         ("mover", C.c_int),
         ("shard_static", C.c_int),
+        ("host_store_mode", C.c_int),
+        ("ticket_chunk", C.c_int),
     ]
 
 
@@ -101,6 +104,7 @@ SIGNATURES = {
     "tsw_evict": (_i32, [_vp, _cp, _i32]),
     "tsw_translate": (_i32, [_vp, _cp, _u64, _i32, _i64, _pu64]),
     "tsw_translate_async": (_i32, [_vp, _cp, _u64, _vp, _pu64, C.POINTER(C.c_int)]),
+    "tsw_release_waiters": (_i32, [_vp, _cp]),
     "tsw_is_model_address": (_i32, [_vp, _cp, _u64]),
     "tsw_valid_memory_address": (_i32, [_vp, _cp, _u64]),
     "tsw_dump_blocks": (_i32, [_vp, _cp, _i32, _vp, _i32]),
@@ -119,6 +123,7 @@ SIGNATURES = {
     "tsw_arena_info": (_i32, [_vp, _pu64, _pu64, _pu64, _pu64]),
     "tsw_arena_attach": (_i32, [_vp, _cp, _u64, _pu64]),
     "tsw_place_segments_static": (_i32, [_i32, _vp, _i32, C.c_uint32, C.c_uint32, C.c_uint32, _vp, _vp]),
+    "tsw_place_segments_static_status": (_i32, [_i32, _vp, C.POINTER(C.c_uint32), _i32]),
     "tsw_stats": (_i32, [_vp, _pu64, _pu64, _pu64]),
     "tsw_evictor_create": (_i32, [_cp, _i32, _u64, C.POINTER(_vp)]),
     "tsw_evictor_destroy": (_i32, [_vp]),

@@ -193,15 +193,32 @@ public:
                              std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::system_clock::now() - evict_start).count());
     }
 
+    // The reference blocks here until the parameter has landed (memory_manager.hpp:527-540) and never
+    // hands the executor an untranslated parameter pointer: a client pointer names cold-start pool
+    // memory that may by now belong to another function.  Same here: a wait that runs out is
+    // repeated (with a warning per period, TORPOR_SWAP_WAIT_PERIODS bounds the number, default
+    // unbounded as in the reference); a parameter whose swap failed (kernel error, abandoned swap)
+    // is moved again, up to three times.  Only when that fails too does the call give up, and then
+    // with a null pointer -- never with the client's own pointer.
     inline void* get_cuda_addr(string& function, void* ptr, bool search_amid = true) {
         uint64_t out = (uint64_t)ptr;
         if (!pending_func_.empty()) log_finished_transfer();
-        int rc = tsw_translate(engine_, function.c_str(), (uint64_t)ptr, search_amid ? 1 : 0, wait_ns_, &out);
-        if (rc != TSW_OK) {
+        static const long max_periods = [] {
+            auto v = get_env_var("TORPOR_SWAP_WAIT_PERIODS");
+            return v.empty() ? -1l : std::stol(v);
+        }();
+        long periods = 0;
+        int repairs = 0;
+        for (;;) {
+            int rc = tsw_translate(engine_, function.c_str(), (uint64_t)ptr, search_amid ? 1 : 0, wait_ns_, &out);
+            if (rc == TSW_OK) return (void*)out;
             report(rc, "get_cuda_addr");
-            return ptr;
+            if (rc == TSW_ERR_TIMEOUT && (max_periods < 0 || ++periods < max_periods)) continue;
+            if (rc == TSW_ERR_KERNEL && repairs++ < 3 && tsw_swap_in(engine_, function.c_str(), -1) == TSW_OK) continue;
+            std::cout << "Server " << server_id_ << " -- error: parameter " << (uint64_t)ptr << " of " << function
+                      << " is not on the device; returning a null pointer" << std::endl;
+            return nullptr;
         }
-        return (void*)out;
     }
 
     inline bool try_insert_model_access(void* dev_ptr) {

@@ -67,6 +67,7 @@ void size_placement(Model* m, Placement& pl) {
     if (pl.blocks.size() < m->blocks.size()) pl.blocks.resize(m->blocks.size());
     if (pl.params.size() < m->params.size()) pl.params.resize(m->params.size());
     if (pl.has_row.size() < m->params.size()) pl.has_row.resize(m->params.size(), false);
+    if (pl.failed.size() < m->params.size()) pl.failed.resize(m->params.size(), false);
 }
 
 // Make room for one pointer-table row per parameter.
@@ -163,7 +164,9 @@ uint8_t* alloc_mirror(tsw_engine* e, uint64_t size) {
     }
     void* p = nullptr;
     cudaSetDevice(e->cfg.device);
-    cudaError_t err = cudaHostAlloc(&p, size ? size : 1, cudaHostAllocPortable | cudaHostAllocMapped);
+    unsigned flags = cudaHostAllocPortable | cudaHostAllocMapped;
+    if (e->host_store_mode & TSW_STORE_WRITE_COMBINED) flags |= cudaHostAllocWriteCombined;
+    cudaError_t err = cudaHostAlloc(&p, size ? size : 1, flags);
     if (err != cudaSuccess) {
         fail(TSW_ERR_CUDA, std::string("cudaHostAlloc(model store): ") + cudaGetErrorString(err));
         return nullptr;
@@ -261,13 +264,43 @@ int make_arena(tsw_engine* e) {
         a.base = (uint8_t*)p;
         a.size = size;
         a.owner = true;
+        if (e->host_store_mode & TSW_STORE_HUGE_PAGES) a.huge = madvise(p, size, MADV_HUGEPAGE) == 0;
         TSW_CUDA(cudaHostRegister(p, size, cudaHostRegisterPortable | cudaHostRegisterMapped));
+        void* dp = nullptr;
+        TSW_CUDA(cudaHostGetDevicePointer(&dp, p, 0));
+        a.dev_delta = (int64_t)(uint64_t)dp - (int64_t)(uint64_t)p;
+    } else if (e->host_store_mode & TSW_STORE_HUGE_PAGES) {
+        // An anonymous mapping on 2 MiB boundaries, advised to transparent huge pages before the
+        // driver pins it: fewer, larger translations for the links to walk.  Whether the kernel
+        // honours the advice is up to the machine (a.huge says whether it accepted the call).
+        const uint64_t two_mb = 2ull << 20;
+        const uint64_t len = (size + two_mb - 1) / two_mb * two_mb;
+        void* raw = mmap(nullptr, len + two_mb, PROT_READ | PROT_WRITE, MAP_PRIVATE | MAP_ANONYMOUS, -1, 0);
+        if (raw == MAP_FAILED) return fail(TSW_ERR_INVALID, "mmap failed for the huge-page host arena");
+        const uint64_t lo = ((uint64_t)raw + two_mb - 1) / two_mb * two_mb;
+        if (lo > (uint64_t)raw) munmap(raw, lo - (uint64_t)raw);
+        const uint64_t tail = (uint64_t)raw + len + two_mb - (lo + len);
+        if (tail) munmap((void*)(lo + len), tail);
+        void* p = (void*)lo;
+        a.huge = madvise(p, len, MADV_HUGEPAGE) == 0;
+        a.base = (uint8_t*)p;
+        a.size = len;
+        a.owner = true;
+        a.anon = true;
+        cudaError_t err = cudaHostRegister(p, len, cudaHostRegisterPortable | cudaHostRegisterMapped);
+        if (err != cudaSuccess) {
+            munmap(p, len);
+            a.base = nullptr;
+            return fail(TSW_ERR_CUDA, std::string("cudaHostRegister(huge-page arena): ") + cudaGetErrorString(err));
+        }
         void* dp = nullptr;
         TSW_CUDA(cudaHostGetDevicePointer(&dp, p, 0));
         a.dev_delta = (int64_t)(uint64_t)dp - (int64_t)(uint64_t)p;
     } else {
         void* p = nullptr;
-        TSW_CUDA(cudaHostAlloc(&p, size, cudaHostAllocPortable | cudaHostAllocMapped));
+        unsigned flags = cudaHostAllocPortable | cudaHostAllocMapped;
+        if (e->host_store_mode & TSW_STORE_WRITE_COMBINED) flags |= cudaHostAllocWriteCombined;
+        TSW_CUDA(cudaHostAlloc(&p, size, flags));
         a.base = (uint8_t*)p;
         a.size = size;
         a.owner = true;
@@ -324,6 +357,23 @@ int place_blocks(tsw_engine* e, Model* m, Placement& pl) {
     e->active_params.clear();
     for (int pi : m->access_order) e->active_params.insert(m->params[pi].vaddr);
     e->pool->finish_block_alloc();
+    return TSW_OK;
+}
+
+// Peer access from this engine's GPU to `to_device`, enabled the first time a swap needs it (a
+// replica source, or the target of a sharded swap this engine helps with) instead of for every
+// pair of GPUs in the machine at start-up (controller.hpp:63-75): an engine opens no context on
+// a GPU it never exchanges bytes with.
+int ensure_peer(tsw_engine* e, int to_device) {
+    if (e->plan || to_device == e->cfg.device || e->peers.count(to_device)) return TSW_OK;
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    int can = 0;
+    TSW_CUDA(cudaDeviceCanAccessPeer(&can, e->cfg.device, to_device));
+    if (!can) return fail(TSW_ERR_CUDA, "GPU " + std::to_string(e->cfg.device) + " has no peer access to GPU " + std::to_string(to_device));
+    cudaError_t pe = cudaDeviceEnablePeerAccess(to_device, 0);
+    if (pe == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+    else if (pe != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("cudaDeviceEnablePeerAccess: ") + cudaGetErrorString(pe));
+    e->peers.insert(to_device);
     return TSW_OK;
 }
 
@@ -498,6 +548,9 @@ static int engine_setup(const tsw_config* cfg, tsw_engine* e) {
     if (const char* g = getenv("TORPOR_SWAP_GUARD_NAMES")) e->guard_names = g[0] == '1';
     e->tile_host = cfg->tile_bytes_host > 0 ? (uint32_t)cfg->tile_bytes_host : 64u * 1024;
     e->tile_dev = cfg->tile_bytes_device > 0 ? (uint32_t)cfg->tile_bytes_device : 512u * 1024;
+    e->host_store_mode = cfg->host_store_mode;
+    if (const char* hs = getenv("TORPOR_SWAP_HOST_STORE")) e->host_store_mode = atoi(hs);
+    e->ticket_chunk = cfg->ticket_chunk > 0 ? (uint32_t)cfg->ticket_chunk : 1u;
     if ((e->tile_host & 15u) || (e->tile_dev & 15u)) return fail(TSW_ERR_INVALID, "tile sizes must be multiples of 16 bytes");
     if (e->plan) {
         e->mem.reset(new PlanMemory());
@@ -572,15 +625,6 @@ static int engine_setup(const tsw_config* cfg, tsw_engine* e) {
         e->host_slab_floor = e->host_slab.used;
         int rc = make_arena(e);
         if (rc != TSW_OK) return rc;
-        // all-pairs peer access, as the controller does at start-up (controller.hpp:63-75)
-        for (int j = 0; j < n; ++j) {
-            if (j == cfg->device) continue;
-            int can = 0;
-            if (cudaDeviceCanAccessPeer(&can, cfg->device, j) == cudaSuccess && can) {
-                cudaError_t pe = cudaDeviceEnablePeerAccess(j, 0);
-                if (pe != cudaSuccess) cudaGetLastError();  // already enabled is fine
-            }
-        }
     }
     const uint64_t total = cfg->budget_bytes + kHiddenBudget;  // memory_manager.hpp:43-44
     e->pool = cfg->pool_policy == TSW_POOL_FIXED ? make_fixed_pool(total, cfg->server_id, e->mem.get())
@@ -624,6 +668,8 @@ int tsw_engine_destroy(tsw_engine* e) {
         for (auto& kv : r.models) {
             auto it = kv.second->place.find(e->server_id);
             if (it == kv.second->place.end()) continue;
+            if (!e->plan && !it->second.waited_rows.empty())
+                tsw_release_waiters(e, kv.first.c_str());   // no stream may be left waiting on a table that goes away
             if (e->plan && it->second.capacity) {
                 free((void*)it->second.flag);
                 free((void*)it->second.phys);
@@ -657,6 +703,9 @@ int tsw_engine_destroy(tsw_engine* e) {
                 munmap(e->arena.base, e->arena.size);
                 close(e->arena.shm_fd);
                 if (e->arena.owner) shm_unlink(e->arena.shm_name.c_str());
+            } else if (e->arena.anon) {
+                cudaHostUnregister(e->arena.base);
+                munmap(e->arena.base, e->arena.size);
             } else {
                 cudaFreeHost(e->arena.base);
             }

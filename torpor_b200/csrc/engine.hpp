@@ -42,6 +42,8 @@ struct HostArena {
     std::string shm_name;
     int shm_fd = -1;
     bool owner = false;
+    bool anon = false;            // anonymous mapping registered with the driver (huge-page mode)
+    bool huge = false;            // the kernel accepted the transparent-huge-page advice
 };
 
 }  // namespace tsw
@@ -75,6 +77,10 @@ struct tsw_engine {
     int mover = 0;       // 0 = load/store kernel, 1 = bulk-copy kernel where alignment allows
     bool guard_names = false;   // TORPOR_SWAP_GUARD_NAMES=1: never grant an address that names another live block of the model
     uint32_t tile_host = 0, tile_dev = 0;
+    int host_store_mode = 0;     // TSW_STORE_*
+    uint32_t ticket_chunk = 1;   // tiles per draw from the shared counter of a sharded swap
+    std::unordered_set<int> peers;   // devices this engine's device has been given peer access to
+    uint32_t last_kernel_status = 0; // last non-zero status word a kernel of this engine reported
 
     std::atomic<uint64_t> kernel_launches{0};
     std::atomic<uint64_t> bytes_moved{0};

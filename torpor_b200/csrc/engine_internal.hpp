@@ -56,6 +56,7 @@ void* map_shared_far(int fd, uint64_t size, int slot);
 int make_arena(tsw_engine* e);
 tsw_engine* engine_of_block_mirror(const uint8_t* p);
 int place_blocks(tsw_engine* e, Model* m, Placement& pl);
+int ensure_peer(tsw_engine* e, int to_device);
 uint32_t pick_tile(tsw_engine* e, bool host_side);
 int pick_mover(const tsw_engine* e, const std::vector<PlaceDesc>& descs);
 

@@ -13,6 +13,7 @@ struct Prepared {
     Placement* pl = nullptr;
     Plan plan;
     uint32_t tile = 0;
+    int src_device = -1;   // device ordinal of the replica the swap reads, if any
 };
 
 // Wait for whatever still writes into this placement's blocks: the engine's own stream and
@@ -28,6 +29,57 @@ static int drain_placement(tsw_engine* e, Placement& pl) {
     pl.helpers.clear();
     TSW_CUDA(cudaSetDevice(e->cfg.device));
     pl.in_flight = false;
+    return TSW_OK;
+}
+
+// Let go of every stream that waits (tsw_translate_async) for a row of this placement that has
+// not arrived, and remember those rows as failed: the generation word each of them waits for is
+// written by the host, on the engine's own stream (non-blocking, so it cannot queue up behind a
+// waiting stream).  The released streams run on WITHOUT the parameter's bytes; tsw_translate and
+// tsw_poll_ready answer TSW_ERR_KERNEL for such rows until the model is swapped in again or
+// evicted, and callers check one of them after synchronising.  Returns the number of rows let go.
+static int release_waiters(tsw_engine* e, Placement& pl) {
+    std::vector<int> stuck;
+    for (int row : pl.waited_rows)
+        if (row >= 0 && (uint32_t)row < pl.capacity && pl.flag[row] != TSW_READY_CUDA) stuck.push_back(row);
+    pl.waited_rows.clear();
+    if (e->plan || stuck.empty()) return 0;
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    cudaStream_t s = (cudaStream_t)e->stream;
+    const uint32_t generation = pl.epoch;
+    for (int row : stuck) {
+        if ((size_t)row < pl.failed.size()) pl.failed[row] = true;
+        TSW_CUDA(cudaMemcpyAsync(&pl.d_table_flag[row], &generation, sizeof(uint32_t), cudaMemcpyHostToDevice, s));
+    }
+    TSW_CUDA(cudaStreamSynchronize(s));
+    return (int)stuck.size();
+}
+
+// A kernel of this engine reported an error status (inconsistent tile table, or a bulk copy that
+// never completed): it moved nothing for the tiles concerned and published nothing.  Taken note of
+// once, at the start of the next swap or eviction on the engine: rows that were on their way are
+// marked failed, their waiters are let go, their tile counters are started afresh by the next
+// swap, and the status word is cleared so that later swaps are not failed by an old report.
+// Caller holds the repository lock and the engine lock.
+static int absorb_kernel_status(tsw_engine* e) {
+    if (e->plan || !e->h_status || *e->h_status == 0) return TSW_OK;
+    e->last_kernel_status = *e->h_status;
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+    for (auto& kv : repo().models) {
+        Model* m = kv.second.get();
+        auto it = m->place.find(e->server_id);
+        if (it == m->place.end()) continue;
+        Placement& pl = it->second;
+        if (!pl.in_flight && pl.waited_rows.empty()) continue;
+        size_placement(m, pl);
+        for (int pi : m->access_order)
+            if (pl.has_row[pi] && pl.flag[pi] != TSW_READY_CUDA) pl.failed[pi] = true;
+        int rc = release_waiters(e, pl);
+        if (rc < 0) return rc;
+        pl.counters_dirty = true;
+    }
+    *e->h_status = 0;
     return TSW_OK;
 }
 
@@ -66,8 +118,11 @@ static int prepare_swap(tsw_engine* e, const char* func, int src_gpu, Prepared& 
         rc = ensure_rows(e, m, pl);
         if (rc != TSW_OK) return rc;
     }
+    rc = absorb_kernel_status(e);
+    if (rc != TSW_OK) return rc;
     rc = drain_placement(e, pl);
     if (rc != TSW_OK) return rc;
+    std::fill(pl.failed.begin(), pl.failed.end(), false);
     if (pl.counters_dirty) {
         // The last swap was abandoned with parameters half moved (a participant went away): their
         // tile counters were never re-armed by a last finisher.  Start this swap from zero.
@@ -80,10 +135,18 @@ static int prepare_swap(tsw_engine* e, const char* func, int src_gpu, Prepared& 
         pl.remote_rows.clear();
     }
     rc = place_blocks(e, m, pl);
-    if (rc != TSW_OK) return rc;
+    if (rc != TSW_OK) {
+        const std::string why = tsw::last_error();
+        release_waiters(e, pl);   // nothing of this generation will be published
+        return fail(rc, why);
+    }
+    // A new generation starts.  Waits enqueued for the old one need no release: the generation
+    // word only grows and they wait for "at least", so this generation's rows satisfy them.
+    pl.waited_rows.clear();
 
     // transfer_model (:331-438): every accessed parameter that is not on the device yet, in access order
     const bool from_host = src_gpu < 0;
+    if (!from_host && src_engine && !src_engine->plan) out.src_device = src_engine->cfg.device;
     out.tile = pick_tile(e, from_host);
     for (int pi : m->access_order) {
         if (!pl.has_row[pi] || pl.flag[pi] == TSW_READY_CUDA) continue;
@@ -118,6 +181,10 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
     Placement& pl = *pr.pl;
     Plan& plan = pr.plan;
     if (e->plan || plan.descs.empty()) return TSW_OK;
+    if (pr.src_device >= 0) {
+        rc = ensure_peer(e, pr.src_device);   // the kernel reads the replica in the source GPU's pool
+        if (rc != TSW_OK) return rc;
+    }
 
     TSW_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = (cudaStream_t)e->stream;
@@ -145,32 +212,45 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
     a.system_scope = (n_helpers > 0) ? 1u : 0u;
     a.status = e->d_status;
 
+    // From here on kernels may be writing into the placement's blocks and counters.  Should a launch
+    // fail half way, the placement stays marked: the next swap or eviction drains every stream that
+    // was used and starts the tile counters afresh.
+    pl.in_flight = true;
+    pl.counters_dirty = true;
     if (n_helpers > 0) {
         // Every participating GPU works on the front of the access order at the same time:
         // by default its CTAs draw the next tile from one counter on the target, so a link
         // that is fed faster moves more tiles; with shard_static GPU r takes tiles r, r + n, ...
         const int n = n_helpers + 1;
+        for (int r = 1; r < n; ++r) {
+            tsw_engine* w = helpers[r - 1];
+            if (!w || w->plan) return fail(TSW_ERR_INVALID, "sharded swap needs CUDA engines as helpers");
+            rc = ensure_peer(w, e->cfg.device);   // a helper stores into the target's pool and reads its tables
+            if (rc != TSW_OK) return rc;
+        }
+        TSW_CUDA(cudaSetDevice(e->cfg.device));
         TSW_CUDA(cudaMemsetAsync(pl.d_ticket, 0, sizeof(uint32_t), s));
         TSW_CUDA(cudaStreamSynchronize(s));  // descriptors and the tile dispenser must be on the target before peers read them
         a.tile_stride = (uint32_t)n;
         if (e->cfg.shard_static == 0) {
             a.ticket = pl.d_ticket;   // tiles are drawn, not dealt: faster links take more
-            a.ticket_chunk = 1;
+            a.ticket_chunk = e->ticket_chunk;
         }
         for (int r = n - 1; r >= 0; --r) {
             tsw_engine* w = r == 0 ? e : helpers[r - 1];
-            if (!w || w->plan) return fail(TSW_ERR_INVALID, "sharded swap needs CUDA engines as helpers");
             PlaceArgs ar = a;
             ar.tile_lo = a.ticket ? 0u : (uint32_t)r;
             TSW_CUDA(cudaSetDevice(w->cfg.device));
-            if (r != 0) TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_start, (cudaStream_t)w->stream));
+            if (r != 0) {
+                pl.helpers.push_back(w);
+                TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_start, (cudaStream_t)w->stream));
+            }
             const int mv = pick_mover(w, plan.descs);
             cudaError_t le = launch_place(ar, mv ? w->grid_bulk : w->grid_ctas, (cudaStream_t)w->stream, mv);
             if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
             if (r != 0) {
                 TSW_CUDA(cudaEventRecord((cudaEvent_t)w->ev_stop, (cudaStream_t)w->stream));
                 w->ev_valid = true;
-                pl.helpers.push_back(w);
             }
             w->kernel_launches++;
         }
@@ -181,10 +261,10 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
         if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
         e->kernel_launches++;
     }
+    pl.counters_dirty = false;
     TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_stop, s));
     e->ev_valid = true;
     e->bytes_moved += plan.bytes;
-    pl.in_flight = true;
     return TSW_OK;
 }
 
@@ -210,7 +290,7 @@ int tsw_swap_plan(tsw_engine* e, const char* func, tsw_segment* segs, int cap, u
     pl.epoch += 1;
     pub->flag_value = pl.epoch;       // the generation; the host-visible rows are set by tsw_swap_commit
     pub->ticket = (uint64_t)pl.d_ticket;
-    pub->ticket_chunk = 1;
+    pub->ticket_chunk = e->ticket_chunk;
     pl.remote_rows.clear();
     for (auto& d : pr.plan.descs) pl.remote_rows.push_back((int)d.row);
     if (n && !e->plan) {
@@ -284,9 +364,30 @@ int tsw_wait_ready(tsw_engine* e, const char* func, int64_t timeout_ns) {
     for (auto it = order.rbegin(); it != order.rend(); ++it) {
         int64_t left = deadline - now_ns();
         WaitResult w = wait_row(e, *pl, *it, left > 0 ? left : 0);
-        if (w.rc != TSW_OK) return w.rc;
+        if (w.rc != TSW_OK) {
+            // The bound of every stream-ordered wait on this model: when the whole-model wait gives
+            // up (time-out or kernel error), the streams queued behind its rows are let go as well.
+            const std::string why = tsw::last_error();
+            Lock g1(repo().mu);
+            Lock g2(e->mu);
+            Model* m = repo().find(func);
+            if (m && m->place.count(e->server_id)) release_waiters(e, placement(m, e->server_id));
+            return fail(w.rc, why);
+        }
     }
     return TSW_OK;
+}
+
+int tsw_release_waiters(tsw_engine* e, const char* func) {
+    if (!e || !func) return fail(TSW_ERR_INVALID, "null argument");
+    Lock g1(repo().mu);
+    Lock g2(e->mu);
+    Model* m = repo().find(func);
+    if (!m) return fail(TSW_ERR_UNKNOWN_MODEL, "unknown model");
+    auto it = m->place.find(e->server_id);
+    if (it == m->place.end()) return 0;
+    size_placement(m, it->second);
+    return release_waiters(e, it->second);
 }
 
 int tsw_poll_ready(tsw_engine* e, const char* func) {
@@ -299,8 +400,11 @@ int tsw_poll_ready(tsw_engine* e, const char* func) {
     if (it == m->place.end() || !it->second.readiness_init) return fail(TSW_ERR_STATE, "model has no readiness rows on this engine");
     if (e->h_status && *e->h_status) return fail(TSW_ERR_KERNEL, "placement kernel reported an inconsistent tile table");
     int waiting = 0;
-    for (int pi : m->access_order)
+    for (int pi : m->access_order) {
+        if ((size_t)pi < it->second.failed.size() && it->second.failed[pi])
+            return fail(TSW_ERR_KERNEL, "a parameter of the model did not arrive; the streams waiting for it were let go");
         if (it->second.has_row[pi] && it->second.flag[pi] != TSW_READY_CUDA) ++waiting;
+    }
     return waiting;
 }
 
@@ -336,8 +440,12 @@ int tsw_evict(tsw_engine* e, const char* func, int writeback) {
     size_placement(m, pl);
 
     if (!e->plan) {
-        int drc = drain_placement(e, pl);
+        int drc = absorb_kernel_status(e);
         if (drc != TSW_OK) return drc;
+        drc = drain_placement(e, pl);
+        if (drc != TSW_OK) return drc;
+        drc = release_waiters(e, pl);   // rows that never arrived (an abandoned plan, a kernel error): nothing may wait on
+        if (drc < 0) return drc;
         TSW_CUDA(cudaSetDevice(e->cfg.device));
         if (writeback) {
             // Eviction write-back: resident parameter bytes -> host store, through the same kernel.
@@ -396,6 +504,8 @@ int tsw_evict(tsw_engine* e, const char* func, int writeback) {
         }
     }
     e->pool->finish_release_block();
+    std::fill(pl.failed.begin(), pl.failed.end(), false);
+    pl.remote_rows.clear();
     return TSW_OK;
 }
 
@@ -426,6 +536,8 @@ int tsw_translate(tsw_engine* e, const char* func, uint64_t vptr, int search_ami
             *out = vptr;
             return TSW_OK;
         }
+        if ((size_t)pi < pl.failed.size() && pl.failed[pi])
+            return fail(TSW_ERR_KERNEL, "the parameter did not arrive; the streams waiting for it were let go");
         if (e->active_params.count(vptr) && pl.has_row[pi]) {
             wait_pl = &pl;
             wait_idx = pi;
@@ -473,7 +585,10 @@ int tsw_translate_async(tsw_engine* e, const char* func, uint64_t vptr, void* st
     *out = pl.params[pi].cuda;
     if (!(e->active_params.count(vptr) && pl.has_row[pi])) return TSW_OK;   // as check_param_readiness: not part of the last swap
     if (pl.flag[pi] == TSW_READY_CUDA) return TSW_OK;                       // already there
-    if (!pl.in_flight) return fail(TSW_ERR_STATE, "parameter is neither on the device nor on its way: swap the model in first");
+    if ((size_t)pi < pl.failed.size() && pl.failed[pi])
+        return fail(TSW_ERR_KERNEL, "the parameter did not arrive; the streams waiting for it were let go");
+    if (!pl.in_flight && pl.remote_rows.empty())
+        return fail(TSW_ERR_STATE, "parameter is neither on the device nor on its way: swap the model in first");
     typedef int (*wait_fn_t)(cudaStream_t, unsigned long long, unsigned int, unsigned int);
     static wait_fn_t wait_fn = nullptr;
     if (!wait_fn) {
@@ -487,6 +602,7 @@ int tsw_translate_async(tsw_engine* e, const char* func, uint64_t vptr, void* st
     TSW_CUDA(cudaSetDevice(e->cfg.device));
     const int rc = wait_fn((cudaStream_t)stream, (unsigned long long)(uintptr_t)&pl.d_table_flag[pi], pl.epoch, 0x0 /* GEQ */);
     if (rc != 0) return fail(TSW_ERR_CUDA, "cuStreamWaitValue32 failed with driver error " + std::to_string(rc));
+    pl.waited_rows.push_back(pi);
     if (waited) *waited = 1;
     return TSW_OK;
 }

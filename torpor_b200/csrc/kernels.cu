@@ -481,7 +481,10 @@ cudaError_t launch_checksum(const SumDesc* descs, uint32_t n_descs, uint32_t tot
 // to a kernel: the host-side symbol is a stand-in, not a device address.  The address is
 // looked up once per device, with that device current, by cudaGetSymbolAddress; that
 // happens in the first call made for a device, so make that first call outside of any
-// stream capture.
+// stream capture.  The address is cached for the life of the process: it does not survive
+// a cudaDeviceReset of that device.  Every call uploads its table from host arrays that
+// belong to the library and are reused by the next call on that device.  Calls lock per
+// device, and the caller's current device is the same after the call as before it.
 namespace tsw {
 namespace {
 
@@ -492,15 +495,47 @@ constexpr size_t kStaticScratchBytes = 1u << 20;
 static_assert(kStaticDescBytes + kStaticFirstBytes <= kStaticScratchBytes, "static scratch too small");
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+// Where the kernel reports a table that does not fit its tile numbering (the sign of two calls
+// that overlapped on the GPU and overwrote each other's table); read by tsw_place_segments_static_status.
+static __device__ __align__(256) uint32_t g_static_status[64];
 
-constexpr int kMaxDevices = 64;
-unsigned char* g_static_scratch_addr[kMaxDevices];   // device address of the array, per device
-bool g_static_scratch_known[kMaxDevices];
-std::mutex g_static_mu;
+constexpr int kMaxDevices = 16;
 
-// Host-side staging of one call's table; guarded by g_static_mu.
-PlaceDesc g_static_host_descs[kStaticMaxSegments];
-uint32_t g_static_host_first[kStaticMaxSegments + 1];
+// Per device: the device addresses of the two arrays above, a lock, and the host-side staging
+// of one call's table -- so a caller blocked on one GPU's stream does not hold up callers on others.
+struct StaticDevice {
+    std::mutex mu;
+    bool known = false;
+    unsigned char* scratch = nullptr;
+    uint32_t* status = nullptr;
+    PlaceDesc host_descs[kStaticMaxSegments];
+    uint32_t host_first[kStaticMaxSegments + 1];
+};
+StaticDevice g_static_dev[kMaxDevices];
+
+// Puts the caller's current device back when the entry point returns.
+struct DeviceRestore {
+    int prev = -1;
+    DeviceRestore() { if (cudaGetDevice(&prev) != cudaSuccess) { prev = -1; cudaGetLastError(); } }
+    ~DeviceRestore() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+// Set-up, once per device, with that device current: the device addresses of the arrays.
+int static_setup(StaticDevice& sd) {
+    if (sd.known) return TSW_OK;
+    unsigned char* p = nullptr;
+    uint32_t* st = nullptr;
+    cudaError_t err = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+    if (err != cudaSuccess || !p)
+        return fail(TSW_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(err));
+    err = cudaGetSymbolAddress((void**)&st, g_static_status);
+    if (err != cudaSuccess || !st)
+        return fail(TSW_ERR_CUDA, std::string("cudaGetSymbolAddress(static status): ") + cudaGetErrorString(err));
+    sd.scratch = p;
+    sd.status = st;
+    sd.known = true;
+    return TSW_OK;
+}
 
 }  // namespace
 }  // namespace tsw
@@ -522,34 +557,29 @@ extern "C" int tsw_place_segments_static(int device, const tsw_segment* segs, in
         return fail(TSW_ERR_INVALID, "publish block needs both table columns");
     if (n == 0) return TSW_OK;
 
-    std::lock_guard<std::mutex> guard(g_static_mu);
+    StaticDevice& sd = g_static_dev[device];
+    std::lock_guard<std::mutex> guard(sd.mu);
+    DeviceRestore restore;   // the caller's current device is put back on return
     cudaError_t err = cudaSetDevice(device);
     if (err != cudaSuccess) return fail(TSW_ERR_NO_DEVICE, std::string("cudaSetDevice: ") + cudaGetErrorString(err));
-    if (!g_static_scratch_known[device]) {
-        // set-up, once per device, with that device current
-        unsigned char* p = nullptr;
-        err = cudaGetSymbolAddress((void**)&p, g_static_scratch);
-        if (err != cudaSuccess || !p)
-            return fail(TSW_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(err));
-        g_static_scratch_addr[device] = p;
-        g_static_scratch_known[device] = true;
-    }
-    unsigned char* scratch = g_static_scratch_addr[device];
+    int rc = static_setup(sd);
+    if (rc != TSW_OK) return rc;
+    unsigned char* scratch = sd.scratch;
 
     // Tile numbering.  A segment that does not say how many tiles complete its row is its own row.
     uint64_t t = 0;
     for (int i = 0; i < n; ++i) {
-        PlaceDesc& d = g_static_host_descs[i];
+        PlaceDesc& d = sd.host_descs[i];
         memcpy(&d, &segs[i], sizeof(PlaceDesc));
         const uint64_t tiles = (d.bytes + tile_bytes - 1) / tile_bytes;
-        g_static_host_first[i] = (uint32_t)t;
+        sd.host_first[i] = (uint32_t)t;
         t += tiles;
         if (d.row_tiles == 0) {
             d.row_tiles = (uint32_t)tiles;
             d.row_dst = d.dst;
         }
     }
-    g_static_host_first[n] = (uint32_t)t;
+    sd.host_first[n] = (uint32_t)t;
     if (t > 0xffffffffull) return fail(TSW_ERR_INVALID, "too many tiles for one call");
 
     cudaStream_t s = (cudaStream_t)stream;
@@ -557,9 +587,9 @@ extern "C" int tsw_place_segments_static(int device, const tsw_segment* segs, in
     uint32_t* d_first = reinterpret_cast<uint32_t*>(scratch + kStaticDescBytes);
     // Pageable source: the runtime has taken its copy when these calls return, so the
     // host-side staging arrays can be reused by the next call.
-    err = cudaMemcpyAsync(d_descs, g_static_host_descs, sizeof(PlaceDesc) * (size_t)n, cudaMemcpyHostToDevice, s);
+    err = cudaMemcpyAsync(d_descs, sd.host_descs, sizeof(PlaceDesc) * (size_t)n, cudaMemcpyHostToDevice, s);
     if (err == cudaSuccess)
-        err = cudaMemcpyAsync(d_first, g_static_host_first, sizeof(uint32_t) * ((size_t)n + 1), cudaMemcpyHostToDevice, s);
+        err = cudaMemcpyAsync(d_first, sd.host_first, sizeof(uint32_t) * ((size_t)n + 1), cudaMemcpyHostToDevice, s);
     if (err != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("table upload: ") + cudaGetErrorString(err));
 
     PlaceArgs a;
@@ -572,6 +602,7 @@ extern "C" int tsw_place_segments_static(int device, const tsw_segment* segs, in
     a.tile_hi = (uint32_t)t;
     a.tile_stride = tile_stride;
     a.system_scope = 1;
+    a.status = sd.status;
     if (pub) {
         a.done_count = (uint32_t*)pub->done_count;
         a.table_phys = (uint64_t*)pub->table_phys;
@@ -585,5 +616,30 @@ extern "C" int tsw_place_segments_static(int device, const tsw_segment* segs, in
     }
     err = launch_place(a, default_grid_ctas(device), s);
     if (err != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(err));
+    return TSW_OK;
+}
+
+extern "C" int tsw_place_segments_static_status(int device, void* stream, uint32_t* status, int clear) {
+    using namespace tsw;
+    if (!status) return fail(TSW_ERR_INVALID, "null argument");
+    if (device < 0 || device >= kMaxDevices) return fail(TSW_ERR_INVALID, "device ordinal out of range");
+    StaticDevice& sd = g_static_dev[device];
+    std::lock_guard<std::mutex> guard(sd.mu);
+    DeviceRestore restore;
+    cudaError_t err = cudaSetDevice(device);
+    if (err != cudaSuccess) return fail(TSW_ERR_NO_DEVICE, std::string("cudaSetDevice: ") + cudaGetErrorString(err));
+    int rc = static_setup(sd);
+    if (rc != TSW_OK) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    uint32_t word = 0;
+    err = cudaMemcpyAsync(&word, sd.status, sizeof(word), cudaMemcpyDeviceToHost, s);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+    if (err == cudaSuccess && clear && word) {
+        const uint32_t zero = 0;
+        err = cudaMemcpyAsync(sd.status, &zero, sizeof(zero), cudaMemcpyHostToDevice, s);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+    }
+    if (err != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("static status read: ") + cudaGetErrorString(err));
+    *status = word;
     return TSW_OK;
 }

@@ -79,6 +79,11 @@ struct Placement {
     uint32_t epoch = 1;
     std::vector<tsw_engine*> helpers;   // engines whose kernels still write into these blocks
     std::vector<int> remote_rows;       // rows handed out by a plan and not yet committed
+    // Stream-ordered waits (tsw_translate_async) enqueued for rows of the current generation, and
+    // rows whose waiters were let go without their bytes: translation and polling report those as
+    // failed until the model is swapped in again or evicted.
+    std::vector<int> waited_rows;
+    std::vector<bool> failed;
 };
 
 struct Model {                  // HostModelInfo (model_repo.hpp:37-46)

@@ -82,7 +82,7 @@ class MemoryManager:
     def __init__(self, budget: int = 25 << 30, *, device: int = 0, server_id: int = 0, gpu_count: int = 1,
                  block_manager: str = "Buddy", host_arena_bytes: int = 0, host_arena_shm: Optional[str] = None,
                  grid_ctas: int = 0, tile_bytes_host: int = 0, tile_bytes_device: int = 0, shard_static: bool = False,
-                 mover: int = 0):
+                 mover: int = 0, host_store_mode: int = 0, ticket_chunk: int = 0):
         self.L = _cabi.lib()
         cfg = _cabi.Config()
         self.L.tsw_config_default(C.byref(cfg))
@@ -99,6 +99,8 @@ class MemoryManager:
         cfg.tile_bytes_device = tile_bytes_device
         cfg.shard_static = 1 if shard_static else 0
         cfg.mover = mover
+        cfg.host_store_mode = host_store_mode
+        cfg.ticket_chunk = ticket_chunk
         h = C.c_void_p()
         check(self.L.tsw_engine_create(C.byref(cfg), C.byref(h)))
         self.h = h
@@ -177,6 +179,10 @@ class MemoryManager:
         out, waited = C.c_uint64(), C.c_int()
         check(self.L.tsw_translate_async(self.h, func.encode(), ptr, stream, C.byref(out), C.byref(waited)))
         return out.value, bool(waited.value)
+
+    def release_waiters(self, func: str) -> int:
+        """Let go of every stream still waiting for a parameter of ``func`` (tsw_release_waiters)."""
+        return check(self.L.tsw_release_waiters(self.h, func.encode()))
 
     def is_model_address(self, func: str, ptr: int) -> bool:
         return check(self.L.tsw_is_model_address(self.h, func.encode(), ptr)) == 1
