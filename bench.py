@@ -3,21 +3,25 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-A step is one swap-in of the workload's weight set into the target GPU's pool
-(block placement, pointer-table rebind, data movement, readiness publish) followed
-by the eviction that makes room for the next step.  Two arms are timed with the
-same engine and kernel:
+A step is one swap-in of the workload's weight set from the page-locked host model store
+into the target GPU's pool (block placement, pointer-table rebind, data movement over
+PCIe, readiness publish) followed by the eviction that makes room for the next step.
+Every byte crosses PCIe inside the timed region at every N; at N > 1 each rank's GPU
+pulls tiles over its own link and stores them into the target's pool over NVLink.
 
-  value  source = a resident replica in HBM (the reference's replica swap,
-         memory_manager.hpp:394-396; at N > 1 each rank's staged share, gathered
-         over NVLink) -- inputs already on the device, HBM / NVLink bound;
-  e2e    source = the page-locked host model store, through the public swap-in call
-         -- every byte crosses PCIe inside the timed region.
+  value  bytes of the set x K / time of K steps (tsw_swap_in + tsw_wait_ready + tsw_evict);
+  e2e    the same through the executor-facing calls: the swap signal, then the translation
+         of every parameter in access order as the launch path does it (each waits for its
+         row of the pointer table, which the kernel writes into host-mapped memory), evict;
+  roofline      the host -> pool launch against the PCIe links of the participating GPUs;
+  kernel_hbm    the same kernel with both ends in HBM (a replica on the same GPU), against
+                the measured HBM copy peak -- a figure about the kernel, not about the metric;
+  gather_stage  (N > 1) each rank's share resident in its HBM, stored into the target over NVLink.
 
-`--impl reference` times the reference's own swap path (its headers compiled where
-they lie, oracle/_ref) on a bounded sample of the same workload with all host
-threads; if that checker is absent the CPU restatement is timed instead.
-Prints ONE JSON line on rank 0.
+`--impl reference` times the reference's own swap path (its headers compiled where they
+lie, oracle/_ref) on the same weight set with its default IO_THREAD_NUM = 4, from the swap
+signal to the last parameter's readiness plus the eviction; if that checker is absent the
+CPU restatement is timed instead.  Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
@@ -44,6 +48,9 @@ HBM_FALLBACK_GBS = 6650.0
 # dram__bytes_write of one launch in an ncu capture of the llama_mid case, over that launch's
 # 2 x parameter bytes.  The kernel streams, so the ratio carries to the full-size launch.
 DRAM_TRAFFIC_PER_ALGO_BYTE = 0.989
+# The same for the host -> pool launch: DRAM bytes written per parameter byte (the reads come over
+# PCIe and touch no DRAM of the GPU), from the ncu capture of the llama_mid case.
+DRAM_WRITE_PER_ALGO_BYTE_HOST = 0.973
 
 
 def measured_peaks():
@@ -102,36 +109,64 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def generate_tensors(ws, threads):
+def generate_tensors(ws, threads, with_sums=False):
+    """Seeded tensors of `ws`, generated ahead on a thread pool.  Returns the pool and data(i);
+    with_sums also returns a dict that fills with every tensor's checksum as it is produced."""
     from torpor_b200 import workloads as W
+    from torpor_b200.memory_manager import checksum_host
     pool = ThreadPoolExecutor(max(1, threads))
-    futs = {i: pool.submit(W.tensor_bytes, ws, i) for i in range(len(ws.tensors))}
-    return pool, (lambda i: futs.pop(i).result())
+    sums = {}
+
+    def make(i):
+        b = W.tensor_bytes(ws, i)
+        if with_sums:
+            sums[i] = checksum_host(b)
+        return b
+    futs = {i: pool.submit(make, i) for i in range(len(ws.tensors))}
+    data = lambda i: futs.pop(i).result()
+    return (pool, data, sums) if with_sums else (pool, data)
 
 
 # ------------------------------------------------------------------ reference arm
 
-def run_reference(args, quiet=False):
-    """The reference's host-driven swap path (I/O threads staging into pinned memory,
-    per-parameter cudaMemcpyAsync, event sync per 2 MiB group) on a bounded sample."""
+def _json_line_of(cmd, timeout=1500):
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=timeout)
+    for ln in r.stdout.splitlines():
+        if ln.startswith("{"):
+            return json.loads(ln)
+    return {"failed": (r.stderr or r.stdout)[-300:]}
+
+
+def _have_gpu():
+    try:
+        import torch
+        return torch.cuda.is_available()
+    except Exception:
+        return False
+
+
+def run_reference(args):
+    """The reference's host-driven swap path (I/O threads packing into pinned memory,
+    per-parameter cudaMemcpyAsync, event sync per 2 MiB group; memory_manager.hpp:213-449)
+    on the workload itself, with its default IO_THREAD_NUM unless told otherwise.  A step is
+    timed where the reference logs it: from the swap signal to the readiness of the last
+    parameter in access order (:352,413), plus the eviction (:240-259).  Between the two the
+    harness waits, untimed, for the transfer thread to hand its pinned mirrors back (:414-423)."""
     from oracle import tso
     from torpor_b200 import workloads as W
     ncpu = os.cpu_count() or 1
-    have_gpu = False
-    try:
-        import torch
-        have_gpu = torch.cuda.is_available()
-    except Exception:
-        pass
-    if tso.available("ref_cuda") and have_gpu:
-        kind, lib, io_threads = "reference", tso.load("ref_cuda"), (args.ref_io_threads or max(1, ncpu))
+    io_threads = args.ref_io_threads or 4          # default_num_io_thread (memory_manager.hpp:22-23)
+    if tso.available("ref_cuda") and _have_gpu():
+        kind, lib = "reference", tso.load("ref_cuda")
         what = "reference headers (memory_manager.hpp:213-449) + CUDA runtime"
     else:
         kind, lib, io_threads = "port", tso.load("oracle"), 1
         what = "CPU restatement (oracle/torpor_oracle.cpp), host memcpy into the block layout"
-    ws = W.weight_set(args.ref_sample)
+    sample_name = args.ref_sample or args.workload
+    ws = W.weight_set(sample_name)
     lib.reset_world()
     src = args.ref_src_gpu
+    budget = W.pool_budget_for(ws)
     pool, data = generate_tensors(ws, min(ncpu, 16))
     if src >= 0:
         # the reference's replica swap (memory_manager.hpp:394-396): the model is resident on GPU `src`,
@@ -140,13 +175,13 @@ def run_reference(args, quiet=False):
             return {"impl": "reference", "unavailable": "the replica-swap baseline needs the reference library and two GPUs"}
         pairs = lib.enable_peer_access(src + 1)          # as the controller does at start-up (controller.hpp:63-75)
         what += f"; peer access enabled for {pairs} directed pairs"
-        holder = lib.manager(server_id=src, budget=0, gpu_count=src + 1, io_threads=io_threads)
-        m = lib.manager(server_id=0, budget=0, gpu_count=src + 1, io_threads=io_threads)
+        holder = lib.manager(server_id=src, budget=budget, gpu_count=src + 1, io_threads=io_threads)
+        m = lib.manager(server_id=0, budget=budget, gpu_count=src + 1, io_threads=io_threads)
         W.cold_start(holder, "ref", ws, tensor_data=data)
         lib.set_model_status("ref", src, True)
         what += f"; replica swap from GPU {src} (cudaMemcpyPeerAsync per parameter)"
     else:
-        m = lib.manager(budget=0, io_threads=io_threads)
+        m = lib.manager(budget=budget, io_threads=io_threads)
         W.cold_start(m, "ref", ws, tensor_data=data)
         m.evict("ref")
     pool.shutdown()
@@ -155,102 +190,232 @@ def run_reference(args, quiet=False):
     t_sig, t_evict = [], []
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        t_sig.append(m.swap_in_timed("ref", src))
+        t_sig.append(m.swap_in_timed("ref", src))      # microseconds, signal -> last parameter ready
         te = time.perf_counter()
         m.evict("ref")
         t_evict.append((time.perf_counter() - te) * 1e6)
     wall = time.perf_counter() - t0
-    gbs = ws.nbytes * args.steps / wall / 1e9
+    step_s = (sum(t_sig) + sum(t_evict)) / 1e6           # what the reference itself spends per step
+    gbs = ws.nbytes * args.steps / step_s / 1e9
     cores = io_threads + 1 if kind == "reference" else 1
-    sample = (f"{args.ref_sample}: {len(ws.tensors)} tensors, {ws.nbytes} B of the workload's shape; "
-              f"{args.warmup} warm-up + {args.steps} swap-ins with forced evict between; {what}; "
-              f"IO_THREAD_NUM={io_threads}")
+    sample = (f"{sample_name}: {len(ws.tensors)} tensors, {ws.nbytes} B; {args.warmup} warm-up + {args.steps} swap-ins "
+              f"with forced evict between; {what}; IO_THREAD_NUM={io_threads}"
+              + (" (the reference's default)" if io_threads == 4 else ""))
+    cfg = workload_config(args, args.gpus, sample_name)
+    cfg["reference_settings"] = {"IO_THREAD_NUM": io_threads, "BUFFER_SIZE": 2 << 20, "pool_budget_bytes": budget}
     line = {
         # the reference's swap uses one GPU's link whatever N is; n_gpus names the configuration compared
         "impl": "reference", "metric": "model_swap_in_throughput", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": workload_config(args, args.gpus),
+        "config": cfg,
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample,
                          "host_cores": ncpu, "signal_to_ready_ms_median": statistics.median(t_sig) / 1e3,
+                         "signal_to_ready_ms_mean": statistics.mean(t_sig) / 1e3,
                          "signal_to_ready_gbs": ws.nbytes / (statistics.median(t_sig) / 1e6) / 1e9,
-                         "swap_out_metadata_only_us_median": statistics.median(t_evict)},
+                         "swap_out_metadata_only_us_median": statistics.median(t_evict),
+                         "untimed_harness_wait_ms_per_step": (wall - step_s) / args.steps * 1e3},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     return line
 
 
+def run_reference_pack(args):
+    """BASELINE config 1's CPU baseline: the reference's host-side pack of a weight set into the
+    pool-block layout -- pageable host store -> pinned block mirrors by its I/O threads alone
+    (pinned_io_thread, memory_manager.hpp:311-329) -- nothing crossing to the GPU."""
+    from oracle import tso
+    from torpor_b200 import workloads as W
+    ncpu = os.cpu_count() or 1
+    kind = "ref_cuda" if (tso.available("ref_cuda") and _have_gpu()) else ("ref_fake" if tso.available("ref_fake") else None)
+    if kind is None:
+        return {"impl": "reference", "unavailable": "the reference's headers are not built here (oracle/_ref)"}
+    lib = tso.load(kind)
+    lib.reset_world()
+    name = args.ref_sample or "resnet50"
+    ws = W.weight_set(name)
+    io_threads = args.ref_io_threads or 4
+    m = lib.manager(budget=W.pool_budget_for(ws), io_threads=io_threads)
+    W.cold_start(m, "ref", ws)
+    m.evict("ref")
+    for _ in range(max(1, args.warmup)):
+        m.pack_timed("ref")
+    us = [m.pack_timed("ref") for _ in range(max(3, args.steps))]
+    med = statistics.median(us)
+    return {"impl": "reference", "pack": {"value": ws.nbytes / (med / 1e6) / 1e9, "unit": "GB/s", "ms_median": med / 1e3,
+                                          "cores": io_threads, "host_cores": ncpu, "kind": "reference",
+                                          "sample": f"{name}: {len(ws.tensors)} tensors, {ws.nbytes} B; pageable -> pinned "
+                                                    f"memcpy by IO_THREAD_NUM={io_threads} threads, {len(us)} timed packs",
+                                          "pinned": "cudaMallocHost" if kind == "ref_cuda" else "host malloc (no GPU here)"}}
+
+
+def cpu_baselines(args, steps=5, warmup=1):
+    """The reported baselines of the bench line, each reference run in its own process (the
+    reference's threads and pool cannot be torn down): the full swap-in at the reference's stock
+    IO_THREAD_NUM = 4 (the primary one) and with one staging thread per host core, and the
+    host-side pack of config 1's ResNet-50 set at both thread counts."""
+    ncpu = os.cpu_count() or 1
+    me = [sys.executable, os.path.abspath(__file__), "--impl", "reference", "--workload", args.workload]
+    if args.ref_sample:
+        me += ["--ref-sample", args.ref_sample]
+    full = me + ["--steps", str(steps), "--warmup", str(warmup)]
+    try:
+        primary = _json_line_of(full + ["--ref-io-threads", "4"])
+        base = primary.get("cpu_baseline") or {"value": None, "unit": "GB/s", "cores": 0, "kind": "port",
+                                               "sample": f"failed: {primary}"}
+        if not args.quick_baseline:
+            allc = _json_line_of(full + ["--ref-io-threads", str(ncpu)]).get("cpu_baseline")
+            if allc:
+                base["all_cores_variant"] = {k: allc[k] for k in ("value", "unit", "cores", "signal_to_ready_ms_median", "sample") if k in allc}
+        pack = ["--ref-pack", "--ref-sample", "resnet50", "--steps", "10", "--warmup", "2", "--impl", "reference"]
+        me0 = [sys.executable, os.path.abspath(__file__)]
+        base["config1_host_side_pack"] = {
+            "io4": _json_line_of(me0 + pack + ["--ref-io-threads", "4"]).get("pack"),
+            f"io{ncpu}": _json_line_of(me0 + pack + ["--ref-io-threads", str(ncpu)]).get("pack"),
+            "what": "pinned_io_thread (memory_manager.hpp:311-329) alone on the ResNet-50 set: pageable -> pinned pool-block mirrors"}
+        return base
+    except Exception as ex:  # reported, never fatal for the GPU arm
+        return {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
+
+
+# ------------------------------------------------------------------ measured peaks of the box
+
+def feed_matrix(seconds=1.5, chunk=256 << 20):
+    """How fast this box feeds its GPUs from page-locked host memory with the copy engines:
+    every GPU alone, then groups of GPUs streaming continuously for a fixed time at once
+    (the sum of their rates, not equal shares), and every other GPU's copy engine pushing
+    into GPU 0 at once.  These are the measured ceilings the swap is compared with."""
+    import torch
+    n = torch.cuda.device_count()
+    host = [torch.empty(chunk, dtype=torch.uint8).pin_memory() for _ in range(n)]
+    dev = [torch.empty(chunk, dtype=torch.uint8, device=f"cuda:{g}") for g in range(n)]
+    streams = [torch.cuda.Stream(device=g) for g in range(n)]
+
+    def stream_for(gpus, secs, src_of=None):
+        """GPUs in `gpus` copy host -> device back to back for `secs`; GB/s per GPU."""
+        done = {g: 0 for g in gpus}
+        start = threading.Barrier(len(gpus))
+
+        def work(g):
+            src = host[g] if src_of is None else host[src_of(g)]
+            with torch.cuda.device(g), torch.cuda.stream(streams[g]):
+                dev[g].copy_(src, non_blocking=True)
+                streams[g].synchronize()
+                start.wait()
+                t_end = time.perf_counter() + secs
+                while time.perf_counter() < t_end:
+                    for _ in range(2):
+                        dev[g].copy_(src, non_blocking=True)
+                    streams[g].synchronize()
+                    done[g] += 2 * chunk
+        ts = [threading.Thread(target=work, args=(g,)) for g in gpus]
+        t0 = time.perf_counter()
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        return {g: done[g] / secs / 1e9 for g in gpus}
+
+    out = {"gpus": n, "seconds_per_cell": seconds, "chunk_bytes": chunk}
+    alone = {}
+    for g in range(n):
+        alone.update(stream_for([g], seconds / 3))
+    out["h2d_alone_gbs"] = [round(alone[g], 2) for g in range(n)]
+    out["h2d_alone_sum_gbs"] = round(sum(alone.values()), 1)
+    groups = {"all": list(range(n))}
+    if n >= 4:
+        groups["first_half"] = list(range(n // 2))
+        groups["second_half"] = list(range(n // 2, n))
+        groups["even"] = list(range(0, n, 2))
+    for name, gpus in groups.items():
+        r = stream_for(gpus, seconds)
+        out[f"h2d_concurrent_{name}"] = {"gpus": gpus, "per_gpu_gbs": [round(r[g], 2) for g in gpus],
+                                         "sum_gbs": round(sum(r.values()), 1)}
+    # does the rate depend on WHICH page-locked buffer is read?  (a guest that hides its NUMA layout
+    # would show it here): GPU g reading each of the n buffers in turn, alone
+    if n >= 2:
+        by_buf = []
+        for g in range(n):
+            row = []
+            for b in range(n):
+                row.append(round(stream_for([g], 0.12, src_of=lambda _g, b=b: b)[g], 1))
+            by_buf.append(row)
+        out["h2d_alone_by_buffer_gbs"] = by_buf
+        # (n-1) -> 1: every other GPU's copy engine pushes into GPU 0 at once
+        nb = 1 << 30
+        dst = [torch.empty(nb, dtype=torch.uint8, device="cuda:0") for _ in range(n - 1)]
+        src = [torch.empty(nb, dtype=torch.uint8, device=f"cuda:{i}") for i in range(1, n)]
+        best = 0.0
+        for _ in range(4):
+            for i in range(n):
+                torch.cuda.synchronize(i)
+            t0 = time.perf_counter()
+            for d, s_, i in zip(dst, src, range(1, n)):
+                with torch.cuda.stream(streams[i]):
+                    d.copy_(s_, non_blocking=True)
+            for i in range(n):
+                torch.cuda.synchronize(i)
+            best = max(best, nb * (n - 1) / (time.perf_counter() - t0) / 1e9)
+        out["peer_gather_to_gpu0_gbs"] = {"value": round(best, 1), "what": f"{n - 1} -> 1 concurrent cudaMemcpyPeerAsync of 1 GiB each, wall clock, best of 4"}
+        del dst, src
+    return out
+
+
+def link_probe(seconds=0.4, chunk=64 << 20):
+    """Per-GPU rate of page-locked host -> device copies while EVERY GPU of the box copies at once
+    (the rate a GPU's link really gets when its neighbours are busy too), for choosing which GPUs
+    take part in a swap when fewer are asked for than the box has."""
+    import torch
+    n = torch.cuda.device_count()
+    host = [torch.empty(chunk, dtype=torch.uint8).pin_memory() for _ in range(n)]
+    dev = [torch.empty(chunk, dtype=torch.uint8, device=f"cuda:{g}") for g in range(n)]
+    streams = [torch.cuda.Stream(device=g) for g in range(n)]
+    done = [0] * n
+    start = threading.Barrier(n)
+
+    def work(g):
+        with torch.cuda.device(g), torch.cuda.stream(streams[g]):
+            dev[g].copy_(host[g], non_blocking=True)
+            streams[g].synchronize()
+            start.wait()
+            t_end = time.perf_counter() + seconds
+            while time.perf_counter() < t_end:
+                for _ in range(4):
+                    dev[g].copy_(host[g], non_blocking=True)
+                streams[g].synchronize()
+                done[g] += 4 * chunk
+    ts = [threading.Thread(target=work, args=(g,)) for g in range(n)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    return {"link_probe": {"gpus": n, "concurrent_h2d_gbs": [round(d / seconds / 1e9, 2) for d in done]}}
+
+
 def run_baselines(args):
-    """Reported baselines around the path, each reference run in its own process (the reference's
-    threads cannot be joined): swap-in with the reference's default IO_THREAD_NUM=4 and with one
-    staging thread per host core, its replica swap over cudaMemcpyPeerAsync when a second GPU is
-    there, its metadata-only swap-out, and plain copy-engine rates of this box."""
+    """Reported baselines around the path, each reference run in its own process: swap-in with the
+    reference's default IO_THREAD_NUM=4 and with one staging thread per host core, its host-side
+    pack alone, its replica swap over cudaMemcpyPeerAsync when a second GPU is there, and the
+    copy-engine feed matrix of this box."""
     import torch
     ncpu = os.cpu_count() or 1
     me = os.path.abspath(__file__)
+    sample = args.ref_sample or args.workload
 
     def ref(*extra):
-        r = subprocess.run([sys.executable, me, "--impl", "reference", "--steps", str(args.steps), "--warmup",
-                            str(args.warmup), "--ref-sample", args.ref_sample, "--workload", args.workload, *extra],
-                           stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)
-        for ln in r.stdout.splitlines():
-            if ln.startswith("{"):
-                d = json.loads(ln)
-                return d.get("cpu_baseline", d)
-        return {"failed": r.stderr[-300:]}
+        d = _json_line_of([sys.executable, me, "--impl", "reference", "--steps", str(args.steps), "--warmup",
+                           str(args.warmup), "--ref-sample", sample, "--workload", args.workload, *extra])
+        return d.get("cpu_baseline", d.get("pack", d))
 
-    out = {"host_cores": ncpu, "gpus": torch.cuda.device_count(), "sample": args.ref_sample,
-           "reference_swap_in_io4": ref("--ref-io-threads", "4"),
-           "reference_swap_in_io_all": ref("--ref-io-threads", str(ncpu))}
-    nbytes = 1 << 30
-    host = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
-    dev0 = torch.empty(nbytes, dtype=torch.uint8, device="cuda:0")
-
-    def timed(fn, dev=0, reps=5):
-        torch.cuda.synchronize(dev)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        fn()
-        with torch.cuda.device(dev):
-            a.record()
-            for _ in range(reps):
-                fn()
-            b.record()
-        torch.cuda.synchronize(dev)
-        return nbytes * reps / (a.elapsed_time(b) / 1e3) / 1e9
-
-    out["copy_engine_h2d_pinned_gbs"] = timed(lambda: dev0.copy_(host, non_blocking=True))
-    out["copy_engine_d2h_pinned_gbs"] = timed(lambda: host.copy_(dev0, non_blocking=True))
-    if torch.cuda.device_count() >= 2:
+    out = {"host_cores": ncpu, "gpus": torch.cuda.device_count(), "sample": sample}
+    if not args.feed_only:
+        out["reference_swap_in_io4"] = ref("--ref-io-threads", "4")
+        out["reference_swap_in_io_all"] = ref("--ref-io-threads", str(ncpu))
+        out["reference_pack_resnet50_io4"] = ref("--ref-pack", "--ref-sample", "resnet50", "--ref-io-threads", "4")
+        out["reference_pack_resnet50_io_all"] = ref("--ref-pack", "--ref-sample", "resnet50", "--ref-io-threads", str(ncpu))
+    out["feed_matrix"] = feed_matrix()
+    if torch.cuda.device_count() >= 2 and not args.feed_only:
         out["reference_replica_swap"] = ref("--ref-src-gpu", "1")
-        dev1 = torch.empty(nbytes, dtype=torch.uint8, device="cuda:1")
-        out["copy_engine_peer_gbs"] = timed(lambda: dev0.copy_(dev1, non_blocking=True))
-        del dev1
-        n = torch.cuda.device_count()
-        if n > 2:
-            # every other GPU's copy engine pushes 1 GiB into GPU 0 at once: the (n-1) -> 1 gather ceiling
-            dst = [torch.empty(nbytes, dtype=torch.uint8, device="cuda:0") for _ in range(n - 1)]
-            src = [torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{i}") for i in range(1, n)]
-            streams = [torch.cuda.Stream(device=i) for i in range(1, n)]
-
-            def gather():
-                for d, s_, st in zip(dst, src, streams):
-                    with torch.cuda.stream(st):
-                        d.copy_(s_, non_blocking=True)
-            best = 0.0
-            for _ in range(4):
-                for i in range(n):
-                    torch.cuda.synchronize(i)
-                t0 = time.perf_counter()
-                gather()
-                for i in range(n):
-                    torch.cuda.synchronize(i)
-                best = max(best, nbytes * (n - 1) / (time.perf_counter() - t0) / 1e9)
-            out["copy_engine_gather_gbs"] = {"value": best, "what": f"{n - 1} -> 1 concurrent peer copies of 1 GiB each, wall clock, best of 4"}
-            del dst, src
         # the same replica swap through this library: GPU 0 places the model from GPU 1's pool over NVLink
         from torpor_b200 import workloads as W
         from torpor_b200.memory_manager import MemoryManager, ModelRepo, repo_reset
-        ws = W.weight_set(args.ref_sample)
+        ws = W.weight_set(sample)
         repo_reset()
         holder = MemoryManager(W.pool_budget_for(ws), device=1, server_id=1, gpu_count=2, host_arena_bytes=W.host_store_bytes(ws))
         target = MemoryManager(W.pool_budget_for(ws), device=0, server_id=0, gpu_count=2)
@@ -274,13 +439,63 @@ def run_baselines(args):
     return {"baselines": out}
 
 
-def workload_config(args, n):
+def workload_config(args, n, name=None):
     from torpor_b200 import workloads as W
-    ws = W.weight_set(args.workload)
-    return {"workload": f"{args.workload}: {len(ws.tensors)} tensors, {ws.nbytes} B, N(0,0.02) seeded, "
+    name = name or args.workload
+    ws = W.weight_set(name)
+    return {"workload": f"{name}: {len(ws.tensors)} tensors, {ws.nbytes} B, N(0,0.02) seeded, "
                         f"client-allocator block layout ({len(W.pack_blocks(ws)[0])} model blocks)",
             "target_gpus": 1, "participating_gpus": n, "l2": "inputs larger than L2 (no flush needed)",
+            "source": "the host model store (every byte crosses PCIe in the timed region)",
             "step": "swap-in (place, rebind, move, publish) + evict"}
+
+
+# ------------------------------------------------------------------ checking what was swapped in
+
+class Verifier:
+    """Holds what a swap-in must produce -- the checksum of every tensor of the set and, per
+    swap-in since the engines were made, the block and pointer tables in canonical addresses
+    (worked out beforehand on plan-only engines) -- and compares the target engine with it."""
+
+    def __init__(self, ws, sums, tables):
+        self.ws, self.sums, self.tables = ws, sums, tables
+        self.swaps = 0          # swap-ins the target has done so far
+        self.checks = 0
+
+    def swapped(self):
+        self.swaps += 1
+
+    def check(self, eng, func, where):
+        got = eng.checksum_resident(func)
+        for i in range(len(self.ws.tensors)):
+            if not np.array_equal(got[i], self.sums[i]):
+                raise RuntimeError(f"{where}: resident bytes of tensor {i} differ from the host store")
+        blocks, params = self.tables[self.swaps - 1]
+        if not np.array_equal(eng.dump_blocks(func, canonical=True), blocks):
+            raise RuntimeError(f"{where}: block table differs from the plan-only engine's after swap-in {self.swaps}")
+        if not np.array_equal(eng.dump_params(func, canonical=True), params):
+            raise RuntimeError(f"{where}: pointer table differs from the plan-only engine's after swap-in {self.swaps}")
+        self.checks += 1
+
+    def record(self, after_timed):
+        return {"tensors": len(self.ws.tensors), "table": True, "after_timed": bool(after_timed), "checks": self.checks,
+                "how": "64-bit position-weighted checksums of every tensor's resident bytes against the host copy; "
+                       "block and pointer tables word for word (canonical addresses) against a plan-only engine "
+                       "replaying the same swap sequence; a mismatch fails the run"}
+
+
+def copy_engine_h2d_gbs(device=0, nbytes=1 << 30, reps=3):
+    """cudaMemcpyAsync from page-locked memory on this GPU's link, best of `reps` (CUDA events)."""
+    import torch
+    x = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    y = torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{device}")
+    best = 0.0
+    with torch.cuda.device(device):
+        for _ in range(reps + 1):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(); y.copy_(x, non_blocking=True); e.record(); torch.cuda.synchronize()
+            best = max(best, nbytes / (s.elapsed_time(e) / 1e3) / 1e9)
+    return best
 
 
 # ------------------------------------------------------------------ our arm, one GPU
@@ -288,136 +503,136 @@ def workload_config(args, n):
 def run_single(args):
     import torch
     from torpor_b200 import workloads as W
-    from torpor_b200.memory_manager import MemoryManager, ModelRepo, repo_reset, checksum_host
+    from torpor_b200.memory_manager import MemoryManager, ModelRepo, repo_reset
 
     peaks, peak_kind = measured_peaks()
     ncpu = os.cpu_count() or 1
-
-    # CPU / reference baseline first, in its own process (its threads and pool cannot be torn down)
-    cpu_baseline = None
-    if not args.no_cpu_baseline:
-        try:
-            r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "5",
-                                "--warmup", "1", "--ref-sample", args.ref_sample, "--workload", args.workload],
-                               stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
-            for ln in r.stdout.splitlines():
-                if ln.startswith("{"):
-                    cpu_baseline = json.loads(ln)["cpu_baseline"]
-        except Exception as ex:  # reported, never fatal for the GPU arm
-            cpu_baseline = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
+    # CPU / reference baselines first, in their own processes
+    cpu_baseline = None if args.no_cpu_baseline else cpu_baselines(args)
 
     torch.cuda.set_device(0)
     ws = W.weight_set(args.workload)
     budget = W.pool_budget_for(ws)
     arena = W.host_store_bytes(ws)
+    K, Wm = args.steps, args.warmup
+    K_hbm = min(K, 10)
     repo_reset()
-    replica = MemoryManager(budget, device=0, server_id=1, gpu_count=2, host_arena_bytes=arena)
-    target = MemoryManager(budget, device=0, server_id=0, gpu_count=2)
+    total_swaps = 2 + 2 * (Wm + K) + (Wm + K_hbm) + 3 + 4
+    tables = W.plan_tables(ws, "model", budget=budget, target_server=0, holder_server=1, gpu_count=2, swaps=total_swaps)
+    repo_reset()
+    replica = MemoryManager(budget, device=0, server_id=1, gpu_count=2, host_arena_bytes=arena,
+                            host_store_mode=args.host_store, tile_bytes_host=args.tile_kib * 1024)
+    target = MemoryManager(budget, device=0, server_id=0, gpu_count=2, tile_bytes_host=args.tile_kib * 1024, mover=args.mover)
 
-    pool, data = generate_tensors(ws, min(ncpu, 16))
-    sums = {}
-
-    def data_and_sum(i):
-        b = data(i)
-        if i % 16 == 0:
-            sums[i] = checksum_host(b)
-        return b
-
+    pool, data, sums = generate_tensors(ws, min(ncpu, 16), with_sums=True)
     t0 = time.time()
-    W.cold_start(replica, "model", ws, tensor_data=data_and_sum)
+    loaded = W.cold_start(replica, "model", ws, tensor_data=data)
     pool.shutdown()
     torch.cuda.synchronize()
     cold_s = time.time() - t0
     ModelRepo.add_model_info("model", 1)
+    ver = Verifier(ws, sums, tables)
+    vaddrs = loaded.tensor_vaddr
 
-    def verify():
-        got = target.checksum_resident("model")
-        for i, s in sums.items():
-            if not np.array_equal(got[i], s):
-                raise RuntimeError(f"resident bytes of tensor {i} differ from the host store")
-
-    def cycle(src):
+    def swap(src):
         target.swap_in("model", src)
-        target.wait_ready("model")
-        target.evict("model")
+        ver.swapped()
 
-    def timed(src, steps, warmup):
+    def timed(src, steps, warmup, through_translate=False, where=""):
         for _ in range(warmup):
-            cycle(src)
-        dev_ns = []
+            swap(src); target.wait_ready("model"); target.evict("model")
+        dev_ns, ready_s = [], []
+        pause = 0.0
         launches0 = target.stats()["kernel_launches"]
         torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            target.swap_in("model", src)
-            target.wait_ready("model")
+        t_begin = time.perf_counter()
+        for k in range(steps):
+            ts = time.perf_counter()
+            swap(src)
+            if through_translate:
+                for v in vaddrs:                     # the launch path: every parameter, in access order
+                    target.translate("model", v)
+            else:
+                target.wait_ready("model")
+            ready_s.append(time.perf_counter() - ts)
             dev_ns.append(target.stats()["last_swap_device_ns"])
+            if k == steps - 1:                       # the last timed swap-in is the one that is checked; clock paused
+                tp = time.perf_counter()
+                l1 = target.stats()["kernel_launches"]
+                ver.check(target, "model", where)
+                launches0 += target.stats()["kernel_launches"] - l1
+                pause = time.perf_counter() - tp
             target.evict("model")
         torch.cuda.synchronize()
-        wall = time.perf_counter() - t0
-        return wall, dev_ns, target.stats()["kernel_launches"] - launches0
+        wall = time.perf_counter() - t_begin - pause
+        return wall, dev_ns, ready_s, target.stats()["kernel_launches"] - launches0
 
-    # correctness of both arms before anything is timed
-    target.swap_in("model", 1); target.wait_ready("model"); verify(); target.evict("model")
-    target.swap_in("model", -1); target.wait_ready("model"); verify(); target.evict("model")
+    # correctness of both sources before anything is timed
+    swap(-1); target.wait_ready("model"); ver.check(target, "model", "before timing, from the host store"); target.evict("model")
+    swap(1); target.wait_ready("model"); ver.check(target, "model", "before timing, from the replica"); target.evict("model")
 
     sampler = ClockSampler(0)
     sampler.start()
-    wall_v, dev_v, launches_v = timed(1, args.steps, args.warmup)
-    wall_e, dev_e, launches_e = timed(-1, args.steps, args.warmup)
+    wall_v, dev_v, ready_v, launches_v = timed(-1, K, Wm, where="after the timed swap-ins from the host store")
+    wall_e, dev_e, ready_e, launches_e = timed(-1, K, Wm, through_translate=True, where="after the timed executor-path swap-ins")
+    wall_h, dev_h, _, _ = timed(1, K_hbm, Wm, where="after the timed replica swap-ins")
     # swap-out with write-back (no counterpart in the reference, whose swap-out moves nothing):
     # resident bytes -> host store through the same kernel, PCIe D2H bound
     wb = []
     for _ in range(3):
-        target.swap_in("model", 1); target.wait_ready("model")
+        swap(-1); target.wait_ready("model")
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         target.evict("model", writeback=True)
         wb.append(time.perf_counter() - t0)
     clocks = sampler.stop()
+    swap(-1); target.wait_ready("model"); ver.check(target, "model", "after the write-back evictions"); target.evict("model")
 
-    # measured DMA peak of this box's link, for context next to the theoretical 63 GB/s
-    x = torch.empty(1 << 30, dtype=torch.uint8).pin_memory()
-    y = torch.empty(1 << 30, dtype=torch.uint8, device="cuda")
-    best = 0.0
-    for _ in range(3):
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record(); y.copy_(x, non_blocking=True); e.record(); torch.cuda.synchronize()
-        best = max(best, (1 << 30) / (s.elapsed_time(e) / 1e3) / 1e9)
-    del x, y
+    ce = copy_engine_h2d_gbs(0)     # measured DMA rate of this box's link, next to the theoretical 63 GB/s
 
     B = ws.nbytes
-    value = B * args.steps / wall_v / 1e9
-    e2e = B * args.steps / wall_e / 1e9
-    kern_v = statistics.mean(dev_v) / 1e9
-    kern_e = statistics.mean(dev_e) / 1e9
-    achieved = 2 * B / kern_v / 1e9
     n_params = len(ws.tensors)
+    value = B * K / wall_v / 1e9
+    e2e = B * K / wall_e / 1e9
+    kern_v = statistics.mean(dev_v) / 1e9
+    kern_h = statistics.mean(dev_h) / 1e9
+    achieved = B / kern_v / 1e9
+    hbm = 2 * B / kern_h / 1e9
     line = {
         "metric": "model_swap_in_throughput", "value": value, "unit": "GB/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall_v / args.steps * 1e3,
+        "steps": K, "warmup": Wm, "ms_per_step": wall_v / K * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": workload_config(args, 1),
-        "value_arm": "swap-in from a resident HBM replica on the same GPU (replica swap path)",
-        "e2e": {"value": e2e, "unit": "GB/s", "ms_per_model": wall_e / args.steps * 1e3,
+        "value_arm": "tsw_swap_in from the page-locked host store + tsw_wait_ready + tsw_evict, K steps on the wall clock",
+        "signal_to_ready_ms": {"median": statistics.median(ready_v) * 1e3, "mean": statistics.mean(ready_v) * 1e3,
+                               "gbs_at_median": B / statistics.median(ready_v) / 1e9},
+        "e2e": {"value": e2e, "unit": "GB/s", "ms_per_model": wall_e / K * 1e3,
                 "h2d_bytes_per_step": B + 44 * n_params, "d2h_bytes_per_step": 12 * n_params,
-                "device_ms_per_model": kern_e * 1e3,
-                "what": "tsw_swap_in from the page-locked host store + tsw_wait_ready + tsw_evict through the C ABI"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "peak_kind": f"{peak_kind} copy bandwidth (burst)",
-                     "kernel": "place_kernel (HBM -> HBM)", "algorithmic_bytes_per_launch": 2 * B,
-                     "launch_ms": kern_v * 1e3,
-                     "traffic": (DRAM_TRAFFIC_PER_ALGO_BYTE * 2 * B) if DRAM_TRAFFIC_PER_ALGO_BYTE else None},
-        "link_roofline": {"bound": "pcie", "achieved": B / kern_e / 1e9, "achieved_wall": e2e,
-                          "peak": PCIE_GEN5_X16_GBS, "unit": "GB/s", "frac": (B / kern_e / 1e9) / PCIE_GEN5_X16_GBS,
-                          "frac_wall": e2e / PCIE_GEN5_X16_GBS, "peak_kind": "theoretical PCIe Gen5 x16, one direction",
-                          "cudaMemcpyAsync_pinned_h2d_gbs": best, "kernel": "place_kernel (host store -> HBM, zero-copy)"},
-        "swap_out_writeback": {"value": ws.nbytes / min(wb) / 1e9, "unit": "GB/s", "ms_per_model": min(wb) * 1e3,
-                               "frac_of_pcie": ws.nbytes / min(wb) / 1e9 / PCIE_GEN5_X16_GBS,
+                "device_ms_per_model": statistics.mean(dev_e) / 1e6,
+                "what": "executor path through the C ABI: swap signal (tsw_swap_in), then tsw_translate of every parameter in "
+                        "access order (each waits for its pointer-table row, written by the kernel into host-mapped memory), "
+                        "then tsw_evict; source = the page-locked host store"},
+        "roofline": {"bound": "pcie", "achieved": achieved, "peak": PCIE_GEN5_X16_GBS, "unit": "GB/s",
+                     "frac": achieved / PCIE_GEN5_X16_GBS, "peak_kind": "theoretical PCIe Gen5 x16, one direction (no PCIe figure in MEASURED_PEAKS.json)",
+                     "kernel": "place_kernel (host store -> pool, zero-copy reads over PCIe)",
+                     "algorithmic_bytes_per_launch": B, "launch_ms": kern_v * 1e3,
+                     "traffic": DRAM_WRITE_PER_ALGO_BYTE_HOST * B,
+                     "copy_engine_same_run_gbs": ce, "frac_of_copy_engine": achieved / ce if ce else None,
+                     "frac_wall": value / PCIE_GEN5_X16_GBS},
+        "kernel_hbm": {"bound": "hbm", "achieved": hbm, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": hbm / peaks["hbm_gbs"],
+                       "peak_kind": f"{peak_kind} copy bandwidth (burst)", "kernel": "place_kernel (replica in HBM -> pool, same GPU)",
+                       "algorithmic_bytes_per_launch": 2 * B, "launch_ms": kern_h * 1e3,
+                       "traffic": DRAM_TRAFFIC_PER_ALGO_BYTE * 2 * B, "steps": K_hbm,
+                       "swap_gbs_wall": B * K_hbm / wall_h / 1e9,
+                       "what": "not the metric: the mover with both ends in HBM, no reference path does this on one GPU"},
+        "swap_out_writeback": {"value": B / min(wb) / 1e9, "unit": "GB/s", "ms_per_model": min(wb) * 1e3,
+                               "frac_of_pcie": B / min(wb) / 1e9 / PCIE_GEN5_X16_GBS,
                                "what": "tsw_evict(writeback=1): pool -> host store, D2H over PCIe; the reference's swap-out is metadata only"},
+        "verified": ver.record(after_timed=True),
         "cpu_baseline": cpu_baseline,
         "gpu_launches": launches_v, "gpu_launches_e2e": launches_e,
         "clocks": clocks, "host_cores": ncpu, "cold_start_s": cold_s,
+        "settings": {"tile_bytes_host": args.tile_kib * 1024 or 65536, "host_store_mode": args.host_store, "mover": args.mover},
     }
     target.close(); replica.close(); repo_reset()
     return line
@@ -430,17 +645,34 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama2_7b")
-    ap.add_argument("--ref-sample", default="llama_mid")
+    ap.add_argument("--ref-sample", default=None, help="reference arm: weight set to time (default: the workload itself)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ref-io-threads", type=int, default=0, help="IO_THREAD_NUM of the reference arm (0 = host cores)")
+    ap.add_argument("--quick-baseline", action="store_true", help="cpu_baseline without the all-cores variant")
+    ap.add_argument("--ref-io-threads", type=int, default=0, help="IO_THREAD_NUM of the reference arm (0 = its default, 4)")
     ap.add_argument("--ref-src-gpu", type=int, default=-1, help="reference arm: swap from a replica on this GPU instead of the host store")
+    ap.add_argument("--ref-pack", action="store_true", help="reference arm: time its host-side pack alone (pageable -> pinned)")
     ap.add_argument("--baselines", action="store_true",
                     help="print the reported baselines around the path (reference with its default 4 and with all "
-                         "staging threads, its replica swap, copy-engine rates) as one JSON line; not the contract line")
+                         "staging threads, its pack, its replica swap, the copy-engine feed matrix) as one JSON line; not the contract line")
+    ap.add_argument("--feed-only", action="store_true", help="--baselines: the copy-engine feed matrix only")
+    ap.add_argument("--link-probe", action="store_true", help="print every GPU's host-link rate under full contention and exit")
+    ap.add_argument("--devices", default="", help="N > 1: comma-separated CUDA ordinals to use, target first "
+                                                   "(default: measured -- the best-fed GPUs when the box has more than N)")
+    ap.add_argument("--tile-kib", type=int, default=0, help="host-side tile size of the mover in KiB (0 = the library's default, 64)")
+    ap.add_argument("--ticket-chunk", type=int, default=0, help="sharded swaps: tiles per draw from the shared counter (0 = 1)")
+    ap.add_argument("--mover", type=int, default=0, help="0 placement kernel (default), 1 bulk-copy unit, 2 kernel + copy engine for large parameters")
+    ap.add_argument("--host-store", type=int, default=0, help="host store mode: 0 page-locked, 1 write-combined, 2 huge pages")
+    ap.add_argument("--sweep", action="store_true", help="N > 1: also time tile sizes and draw sizes of the mover (extra key)")
+    ap.add_argument("--nccl-gather", action="store_true", help="N > 1: also time the gather stage over NCCL send/recv (extra key)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.link_probe:
+        if rank == 0:
+            print(json.dumps(link_probe()), flush=True)
+        return 0
 
     if args.baselines:
         if rank == 0:
@@ -450,7 +682,7 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
-        print(json.dumps(run_reference(args)), flush=True)
+        print(json.dumps(run_reference_pack(args) if args.ref_pack else run_reference(args)), flush=True)
         return 0
 
     if world > 1 or args.gpus > 1:

@@ -69,7 +69,12 @@ typedef struct {
     int tile_bytes_device;  /* bytes per tile when the source is device memory; 0 = default */
     int mover;              /* 0 = tiles moved by loads/stores of the SMs' threads (default); 1 = by the bulk
                                asynchronous copy unit through shared memory where every end is 16-byte
-                               aligned (else falls back to 0).  Env TORPOR_SWAP_MOVER overrides. */
+                               aligned (else falls back to 0); 2 = as 0, but on a single-GPU swap-in
+                               from the host store the parameters of 4 MiB and more are moved by the
+                               copy engine (cudaMemcpyAsync in access order on a second stream, a
+                               small kernel behind each rewriting the parameter's table row), for
+                               links on which the copy engine reads host memory faster than the SMs
+                               do.  Env TORPOR_SWAP_MOVER overrides. */
     int shard_static;       /* tsw_swap_in_sharded: 0 = participants draw tiles from a shared counter
                                (default), 1 = tile t is fixed to participant t mod n */
     int host_store_mode;    /* how the host model store is made page-locked (model_repo.hpp:124-141,173-177
@@ -109,7 +114,8 @@ int tsw_malloc(tsw_engine* e, const char* func, uint64_t size, int load_model_fl
                uint64_t* vptr);                                   /* cudaMallocBackend, :85-94 */
 int tsw_free(tsw_engine* e, const char* func, uint64_t vptr);    /* cudaFreeBackend, :97-110 */
 /* cudaMemcpyAsyncBackendHtoD with load_model_flag = true (:124-135,141): records the
- * parameter in the host store and uploads it.  stream is a cudaStream_t. */
+ * parameter in the host store and uploads it.  stream is a cudaStream_t.  On a plan-only
+ * engine (device = -1) payload may be null: address and size are recorded, no byte is kept. */
 int tsw_memcpy_h2d_model(tsw_engine* e, const char* func, uint64_t dst_vptr,
                          const void* payload, uint64_t size, void* stream);
 int tsw_sync_done(tsw_engine* e, const char* func);              /* init_model_readiness(func), :234-238 */
@@ -155,7 +161,14 @@ int tsw_translate(tsw_engine* e, const char* func, uint64_t vptr, int search_ami
  * (replaces the blocking wait of cuda_server.hpp:1265-1268 -> memory_manager.hpp:527-540).
  * *waited = 1 if a wait was enqueued.  TSW_ERR_STATE if the parameter is neither resident nor
  * part of a swap in flight (a wait on it could never be satisfied).
- * The wait is bounded from the host.  The rows waited for are remembered; they are let go -- the
+ * The wait is bounded from the host.  The word waited on is the row's generation word in
+ * host-mapped memory, which the kernel writes when the row completes and which the host can write
+ * with a plain store -- no CUDA call, so the release cannot be queued behind the wait it ends (CUDA
+ * does not see the ordering a stream memory wait creates; work submitted after it, on any stream,
+ * may share its hardware queue).  For the same reason enqueue waits only for swaps whose kernels
+ * this process has already launched: after tsw_swap_in / tsw_swap_in_sharded returned, or, with a
+ * plan handed to other processes (tsw_swap_plan), after this process's own share was launched.
+ * The rows waited for are remembered; they are let go -- the
  * host writes the generation word they wait for, the stream runs on WITHOUT the bytes, and the
  * row is marked failed -- when the whole-model wait gives up (tsw_wait_ready times out or sees a
  * kernel error), when a kernel error is taken note of at the next swap or eviction on the engine,

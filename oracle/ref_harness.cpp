@@ -229,6 +229,41 @@ int64_t tso_swap_in_timed(void* hv, const char* func, int src_gpu) {
     return us;
 }
 
+// The host-side pack alone: every accessed parameter copied from the pageable model store into
+// the pinned mirror of its pool block by the reference's own I/O threads (pinned_io_thread,
+// memory_manager.hpp:311-329; addresses from :481-483), timed from the first enqueue to the last
+// completion token.  Nothing crosses to the GPU.  The model must be evicted on entry and is
+// evicted again on return, with its pinned mirrors back on the free list (:414-423).
+int64_t tso_pack_timed(void* hv, const char* func) {
+    auto* h = (Handle*)hv;
+    string f(func);
+    cudaSetDevice(h->server_id);
+    h->mm->check_and_malloc_model(f, true);
+    auto& dev = repo().device_model_info_map_[h->server_id][f];
+    auto& host = repo().model_host_info_map_[f];
+    int count = 0;
+    auto t0 = std::chrono::steady_clock::now();
+    for (auto& ptr : repo().model_access_order_map_[f]) {
+        h->mm->io_queue_->enqueue({f, ptr, dev.param_virtual_to_cuda_[ptr].pinned_addr_, host.model_param_info_[ptr].host_addr_,
+                                   host.model_param_info_[ptr].size_});
+        ++count;
+    }
+    // wait as the transfer thread does (:380-383): per parameter, on its readiness, taking completion
+    // tokens while it is not packed yet (tokens left over from earlier swaps are never cleared, :412)
+    for (auto& ptr : repo().model_access_order_map_[f])
+        while (h->mm->model_param_readiness_[f]->at(ptr).first < server::manager::ParamReadiness_Pinned) h->mm->sync_io_queue_->dequeue();
+    int64_t us = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+    for (auto& info : host.model_block_info_) {
+        auto& b = dev.block_virtual_to_cuda_[info.first];
+        if (b.in_pin_) {
+            h->mm->free_pinend_memory(b.pinned_addr_, host.virtual_blocks_[info.first].size_);
+            b.in_pin_ = false;
+        }
+    }
+    h->mm->evict_model(f);
+    return us;
+}
+
 void tso_evict(void* hv, const char* func) {
     auto* h = (Handle*)hv;
     string f(func);

@@ -73,6 +73,12 @@ uint64_t dev_malloc(int dev, uint64_t size) {
     if (d.bump > kBackingSpan) { fprintf(stderr, "oracle: device address space exhausted\n"); abort(); }
     return kCanonBase + (uint64_t)dev * kCanonStride + off;
 }
+// TORPOR_ORACLE_TABLES_ONLY=1: placement and tables only -- no parameter byte is stored or moved
+// (payloads may then be null), so a 13.5 GB weight set can be held to its tables in a few MB.
+bool tables_only() {
+    const char* v = getenv("TORPOR_ORACLE_TABLES_ONLY");
+    return v && v[0] == '1';
+}
 byte* dev_bytes(uint64_t addr) {
     int dev = (int)((addr - kCanonBase) / kCanonStride);
     return g_dev[dev].backing + (addr - kCanonBase - (uint64_t)dev * kCanonStride);
@@ -300,11 +306,11 @@ struct Manager {
             if (dst >= b && dst < b + h.blocks[(void*)b].size) {
                 byte* host = kv.second.host + (dst - b);
                 kv.second.params.insert(dst);
-                memcpy(host, payload, size);
+                if (!tables_only()) memcpy(host, payload, size);
                 h.params[dst] = ParamInfo{size, host};
                 h.data_block[dst] = b;
                 g_repo.dev[id][f].params[dst] = ParamDev{dst};
-                memcpy(dev_bytes(dst), payload, size);
+                if (!tables_only()) memcpy(dev_bytes(dst), payload, size);
                 return 0;
             }
         }
@@ -357,7 +363,7 @@ struct Manager {
             auto r = ready[f].find(p);
             if (r == ready[f].end() || r->second.first == kCuda) continue;
             const byte* from = src < 0 ? h.params[p].host : dev_bytes(g_repo.dev[src][f].params[p].cuda);
-            memcpy(dev_bytes(d.params[p].cuda), from, h.params[p].size);   // :389-396
+            if (!tables_only()) memcpy(dev_bytes(d.params[p].cuda), from, h.params[p].size);   // :389-396
             r->second = std::make_pair((int)kCuda, d.params[p].cuda);      // :445
         }
     }

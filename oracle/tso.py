@@ -107,6 +107,8 @@ class TsoLib:
             "tso_exec_completions": (i32, [C.POINTER(C.c_int), i32]),
             "tso_exec_reset": (None, []),
         }
+        if hasattr(L, "tso_pack_timed"):     # the reference's headers only
+            sig["tso_pack_timed"] = (i64, [vp, cp])
         self.has_executor = hasattr(L, "tso_exec_create")
         if self.has_executor:
             sig.update(executor)
@@ -170,7 +172,11 @@ class TsoManager:
     def malloc(self, f, size, is_model): return self.L.tso_malloc(self.h, f.encode(), size, 1 if is_model else 0)
     def free(self, f, vptr): self.L.tso_free(self.h, f.encode(), vptr)
 
-    def memcpy_h2d_model(self, f, dst, data: np.ndarray) -> int:
+    def memcpy_h2d_model(self, f, dst, data) -> int:
+        if not isinstance(data, np.ndarray) and hasattr(data, "nbytes"):   # a size without bytes (TORPOR_ORACLE_TABLES_ONLY=1)
+            if os.environ.get("TORPOR_ORACLE_TABLES_ONLY") != "1":
+                raise ValueError("a payload without bytes needs TORPOR_ORACLE_TABLES_ONLY=1")
+            return self.L.tso_memcpy_h2d_model(self.h, f.encode(), dst, None, int(data.nbytes))
         data = np.ascontiguousarray(data).view(np.uint8)
         return self.L.tso_memcpy_h2d_model(self.h, f.encode(), dst, data.ctypes.data, data.nbytes)
 
@@ -181,6 +187,7 @@ class TsoManager:
     def wait_ready(self, f): return self.L.tso_wait_ready(self.h, f.encode())
     def swap_in_timed(self, f, src_gpu=-1): return self.L.tso_swap_in_timed(self.h, f.encode(), src_gpu)
     def evict(self, f): self.L.tso_evict(self.h, f.encode())
+    def pack_timed(self, f): return self.L.tso_pack_timed(self.h, f.encode())
     def translate(self, f, vptr): return self.L.tso_translate(self.h, f.encode(), vptr)
     def check_alloc(self, f): return bool(self.L.tso_check_alloc(self.h, f.encode()))
     def is_model_address(self, f, vptr): return bool(self.L.tso_is_model_address(self.h, f.encode(), vptr))

@@ -51,6 +51,8 @@ int64_t tso_wait_ready(void* h, const char* func);
 /* swap_in + wait for readiness; returns microseconds from the signal to the
  * last parameter being published (what the reference logs at :352,:413). */
 int64_t tso_swap_in_timed(void* h, const char* func, int src_gpu);
+/* reference headers only: the pageable -> pinned pack by the I/O threads alone (:311-329), microseconds */
+int64_t tso_pack_timed(void* h, const char* func);
 void tso_evict(void* h, const char* func);                       /* :240-259 */
 uint64_t tso_translate(void* h, const char* func, uint64_t vptr); /* :261-271 */
 int tso_check_alloc(void* h, const char* func);                  /* :195-210 */

@@ -343,6 +343,26 @@ def test_full_size_llama2_7b_properties(fresh):
         assert np.array_equal(eng.checksum_resident("llama"), host_sums)
         tables.append((tab, blk))
     assert eng.stats()["bytes_moved"] >= 3 * ws.nbytes
+    # ... and the tables of both swap-ins equal the CPU checker's, word for word, at full size: the
+    # checker replays the same calls holding tables only (no parameter byte is stored or moved)
+    import os
+    from oracle import tso
+    from torpor_b200.memory_manager import SizeOnly
+    os.environ["TORPOR_ORACLE_TABLES_ONLY"] = "1"
+    try:
+        orc_lib = tso.load("oracle")
+        orc_lib.reset_world()
+        orc = orc_lib.manager(budget=12 << 30)
+        W.cold_start(orc, "llama", ws, tensor_data=lambda i: SizeOnly(ws.tensors[i].nbytes))
+        for it in range(2):
+            orc.evict("llama")
+            orc.swap_in("llama")
+            assert np.array_equal(tables[it][0], orc.dump_params("llama")), f"pointer table of swap-in {it}"
+            assert np.array_equal(tables[it][1], orc.dump_blocks("llama")), f"block table of swap-in {it}"
+        orc.close()
+        orc_lib.reset_world()
+    finally:
+        del os.environ["TORPOR_ORACLE_TABLES_ONLY"]
     # host store untouched by the write-back of unmodified weights
     for i in (0, 1, 150, 290):
         v, n = lm.tensor_vaddr[i], min(ws.tensors[i].nbytes, 1 << 20)
@@ -418,6 +438,86 @@ def test_stream_ordered_translation(fresh):
     eng.close()
 
 
+def _drained(stream, seconds):
+    """Poll a stream (never block on it) until it has run dry or `seconds` have passed."""
+    import time
+    deadline = time.perf_counter() + seconds
+    while time.perf_counter() < deadline:
+        if stream.query():
+            return True
+        time.sleep(0.002)
+    return stream.query()
+
+
+def test_stream_ordered_wait_is_let_go_when_the_swap_never_completes(fresh):
+    """The wait that tsw_translate_async enqueues has a way out.  A swap is planned (blocks placed,
+    table rebound, rows handed out) but nobody moves its tiles, so the generation word is never
+    written by a kernel.  When the whole-model wait gives up, the host writes the word: the stream
+    drains, the work queued behind the wait runs, and translation and polling report the row as
+    failed until the model is swapped in for real.  Nothing spins on the device, and whatever an
+    assertion says, the teardown lets the stream go before anything blocks on it."""
+    import time
+    import torch
+    ws = W.weight_set("bert_base", seed=77)
+    eng = MemoryManager(0, device=0)
+    lm = W.cold_start(eng, "A", ws)
+    eng.evict("A")
+    last = len(ws.tensors) - 2
+    vaddr = lm.tensor_vaddr[last]
+    stream = torch.cuda.Stream()
+    marker = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # The kernel that will sit behind the wait is launched once beforehand: the first launch of a
+    # kernel loads its module, which synchronises the whole device -- behind a pending wait that
+    # would never return.  (True of any stream-ordered wait, whoever enqueues it.)
+    with torch.cuda.stream(stream):
+        marker.add_(1)
+        marker.sub_(1)
+    torch.cuda.synchronize()
+    assert int(marker.cpu()[0]) == 0
+    try:
+        segs, tile, pub = eng.swap_plan("A")            # planned; no tile will ever be moved
+        assert len(segs) > 0
+        addr, waited = eng.get_cuda_addr_async("A", vaddr, stream.cuda_stream)
+        assert waited and addr != 0
+        with torch.cuda.stream(stream):
+            marker.add_(1)                              # queued behind the wait
+        time.sleep(0.05)
+        assert not stream.query(), "the stream did not wait for the parameter"
+        with pytest.raises(SwapError) as e:             # the bound: the whole-model wait runs out ...
+            eng.wait_ready("A", timeout_ns=50_000_000)
+        assert e.value.code == _cabi.ERR_TIMEOUT
+        assert _drained(stream, 5.0), "the waiting stream was not let go"      # ... and takes the waiters with it
+        assert int(marker.cpu()[0]) == 1
+        with pytest.raises(SwapError) as e:             # the row is known to have failed
+            eng.get_cuda_addr("A", vaddr)
+        assert e.value.code == _cabi.ERR_KERNEL
+        with pytest.raises(SwapError) as e:
+            eng.poll_ready("A")
+        assert e.value.code == _cabi.ERR_KERNEL
+        # a second waiter, let go on request this time
+        addr2, waited2 = None, False
+        with pytest.raises(SwapError) as e:             # a failed row takes no new waiters
+            eng.get_cuda_addr_async("A", vaddr, stream.cuda_stream)
+        assert e.value.code == _cabi.ERR_KERNEL
+    finally:
+        eng.release_waiters("A")                        # unconditionally: no stream stays behind a wait
+        eng.swap_in("A")                                # the real swap: generations only grow, so it satisfies any wait
+        eng.wait_ready("A")
+        assert _drained(stream, 5.0)
+    # after the real swap the parameter is there, and translation works again
+    got = eng.read_phys(eng.get_cuda_addr("A", vaddr), ws.tensors[last].nbytes)
+    assert np.array_equal(got, W.tensor_bytes(ws, last))
+    assert eng.poll_ready("A") == 0
+    # eviction lets waiters of an abandoned plan go as well
+    eng.evict("A")
+    eng.swap_plan("A")
+    addr, waited = eng.get_cuda_addr_async("A", vaddr, stream.cuda_stream)
+    assert waited
+    eng.evict("A")
+    assert _drained(stream, 5.0), "eviction left a stream waiting"
+    eng.close()
+
+
 def test_bulk_copy_mover_is_bit_exact(fresh):
     """The opt-in bulk-copy mover (cp.async.bulk through shared memory, one thread per CTA)
     moves the same bytes and publishes the same table as the load/store kernel: swap-in from
@@ -448,3 +548,67 @@ def test_bulk_copy_mover_is_bit_exact(fresh):
         assert a.stats()["kernel_launches"] >= 5
         a.close(); b.close()
     assert np.array_equal(tables[0], tables[2]) and np.array_equal(tables[1], tables[3])
+
+
+def test_copy_engine_assisted_mover_is_bit_exact(fresh, oracle_backend):
+    """mover = 2: on a swap-in from the host store the parameters of 4 MiB and more are moved by the
+    copy engine (a publish kernel behind each), the smaller ones by the placement kernel at the same
+    time.  Bytes, tables and readiness equal the checker's, cycle after cycle, and a replica swap or
+    a sharded swap on the same engine still goes through the kernel alone."""
+    oracle_backend.reset()
+    ws = W.weight_set("bert_large")
+    sizes = [t.nbytes for t in ws.tensors]
+    assert min(sizes) < (4 << 20) <= max(sizes)                 # both movers get work
+    eng = MemoryManager(0, device=0, server_id=0, gpu_count=2, mover=2)
+    peer = MemoryManager(0, device=0, server_id=1, gpu_count=2, mover=2)
+    orc = oracle_backend.manager(budget=0, gpu_count=2)
+    lm, _ = load_both(eng, orc, "m", ws)
+    for cycle in range(3):
+        eng.evict("m"); orc.evict("m")
+        eng.swap_in("m"); orc.swap_in("m")
+        # the launch path first: every parameter waits for its own row
+        for v in lm.tensor_vaddr:
+            assert eng.get_cuda_addr("m", v) != 0
+        eng.wait_ready("m")
+        assert_resident_equal(eng, orc, "m", ws, full=(cycle == 0))
+    launches = eng.stats()["kernel_launches"]
+    big = sum(1 for n in sizes if n >= (4 << 20))
+    assert launches >= 3 * (big + 1)                            # one publish kernel per large parameter + the mover, per swap-in
+    # the other sources are untouched by the setting
+    ModelRepo.add_model_info("m", 0)
+    peer.swap_in("m", 0); peer.wait_ready("m")
+    sums = np.array([checksum_host(W.tensor_bytes(ws, i)) for i in range(len(ws.tensors))])
+    assert np.array_equal(peer.checksum_resident("m"), sums)
+    peer.evict("m")
+    eng.evict("m", writeback=True)
+    eng.swap_in_sharded("m", [peer]); eng.wait_ready("m")
+    assert np.array_equal(eng.checksum_resident("m"), sums)
+    eng.close(); peer.close()
+    oracle_backend.reset()
+
+
+def test_topology_discovery_on_this_box(fresh):
+    """tsw_topology_discover on however many GPUs the box has (one is enough): a PCIe uplink group
+    per GPU, a link class per ordered pair, nothing on the diagonal -- and tables the scheduler and
+    controller accept in place of the reference's 4-GPU constants (controller.hpp:116-118)."""
+    import torch
+    from torpor_b200.memory_manager import Scheduler, discover_topology
+    n = torch.cuda.device_count()
+    pairs, nv = discover_topology(n)
+    assert len(pairs) == n and all(0 <= p < n for p in pairs)
+    assert len(nv) == n and all(len(r) == n for r in nv)
+    assert all(nv[i][i] == 0 for i in range(n))
+    assert all(nv[i][j] in (-1, 1, 2) for i in range(n) for j in range(n) if i != j)
+    for policy in ("IA", "Random"):
+        s = Scheduler(n, policy, pairs, nv)
+        gpu, src = s.decide("never_seen")[:2]
+        assert 0 <= gpu < n and src == -1                     # a function no GPU holds: a cold start, no source
+        s.close()
+    # one engine on one GPU opens a context on that GPU only
+    eng = MemoryManager(0, device=0, server_id=0, gpu_count=n)
+    ws = W.weight_set("bert_tiny")
+    W.cold_start(eng, "t", ws)
+    eng.evict("t"); eng.swap_in("t"); eng.wait_ready("t")
+    sums = np.array([checksum_host(W.tensor_bytes(ws, i)) for i in range(len(ws.tensors))])
+    assert np.array_equal(eng.checksum_resident("t"), sums)
+    eng.close()

@@ -217,3 +217,39 @@ def test_guard_against_granting_a_blocks_name_again(monkeypatch):
     spans = sorted((int(r[4]), int(r[4] + r[1])) for r in table if r[3])
     assert len(spans) == 3 and all(spans[i][1] <= spans[i + 1][0] for i in range(2))     # three live, disjoint blocks
     assert all(a != 0 for a in moved)
+
+
+def test_full_size_llama_tables_equal_the_restatement(built, monkeypatch):
+    """The 13.5 GB Llama-2-7B-shaped set at full size, tables only: the plan-only engine and the CPU
+    restatement, both given sizes without bytes, agree word for word on the block and pointer
+    tables of four swap-ins with evictions between (the placement changes from one to the next)."""
+    import numpy as np
+    from oracle import tso
+    from torpor_b200 import workloads as W
+    from torpor_b200.memory_manager import MemoryManager, SizeOnly, repo_reset
+    monkeypatch.setenv("TORPOR_ORACLE_TABLES_ONLY", "1")
+    ws = W.weight_set("llama2_7b")
+    budget = W.pool_budget_for(ws)
+    repo_reset()
+    lib = tso.load("oracle")
+    lib.reset_world()
+    eng = MemoryManager(budget, device=-1)
+    orc = lib.manager(budget=budget)
+    sizes = lambda i: SizeOnly(ws.tensors[i].nbytes)
+    W.cold_start(eng, "llama", ws, tensor_data=sizes)
+    W.cold_start(orc, "llama", ws, tensor_data=sizes)
+    seen = []
+    for it in range(4):
+        eng.evict("llama"); orc.evict("llama")
+        eng.swap_in("llama"); orc.swap_in("llama")
+        tab = eng.dump_params("llama", canonical=True)
+        assert np.array_equal(tab, orc.dump_params("llama")), it
+        assert np.array_equal(eng.dump_blocks("llama", canonical=True), orc.dump_blocks("llama")), it
+        seen.append(tab)
+    assert len(tab) == 291 and not np.array_equal(seen[0], seen[1])
+    # and the helper the benchmark uses gives the same tables
+    eng.close(); orc.close(); lib.reset_world(); repo_reset()
+    replay = W.plan_tables(ws, "llama", budget=budget, swaps=4)
+    for it in range(4):
+        assert np.array_equal(replay[it][1], seen[it])
+    repo_reset()

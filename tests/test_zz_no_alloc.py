@@ -77,6 +77,11 @@ def test_allocation_free_entry_point_matches_the_allocating_one(built):
     try:
         run_both(torch, eng, seed=21, n_seg=300)     # first call on the device: looks the scratch address up
         run_both(torch, eng, seed=22, n_seg=57)      # second call: finds the first call's table in the scratch
+        # calls that did not overlap leave nothing in the word the kernel reports a clobbered table in,
+        # and the entry points give the caller's current device back as they found it
+        from torpor_b200.memory_manager import place_segments_static_status
+        assert place_segments_static_status(0) == 0
+        assert torch.cuda.current_device() == 0
     finally:
         eng.close()
         repo_reset()

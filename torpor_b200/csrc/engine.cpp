@@ -78,13 +78,16 @@ int ensure_rows(tsw_engine* e, Model* m, Placement& pl) {
     uint32_t cap = std::max<uint32_t>(need, 16);
     volatile uint32_t* flag;
     volatile uint64_t* phys;
+    volatile uint32_t* gen;
     if (e->plan) {
         flag = (volatile uint32_t*)calloc(cap, sizeof(uint32_t));
         phys = (volatile uint64_t*)calloc(cap, sizeof(uint64_t));
-        if (!flag || !phys) return fail(TSW_ERR_INVALID, "out of host memory for the pointer table");
+        gen = (volatile uint32_t*)calloc(cap, sizeof(uint32_t));
+        if (!flag || !phys || !gen) return fail(TSW_ERR_INVALID, "out of host memory for the pointer table");
     } else {
         flag = (volatile uint32_t*)e->host_slab.take(sizeof(uint32_t) * cap);
         phys = (volatile uint64_t*)e->host_slab.take(sizeof(uint64_t) * cap);
+        gen = (volatile uint32_t*)e->host_slab.take(sizeof(uint32_t) * cap);
         void* hd = e->host_slab.take(sizeof(PlaceDesc) * cap);
         void* hf = e->host_slab.take(sizeof(uint32_t) * (cap + 1));
         void* dp = e->dev_slab.take(sizeof(uint64_t) * cap);
@@ -93,10 +96,11 @@ int ensure_rows(tsw_engine* e, Model* m, Placement& pl) {
         void* dk = e->dev_slab.take(256);
         void* dd = e->dev_slab.take(sizeof(PlaceDesc) * cap);
         void* dt = e->dev_slab.take(sizeof(uint32_t) * (cap + 1));
-        if (!flag || !phys || !hd || !hf || !dp || !df || !dc || !dd || !dt || !dk)
+        if (!flag || !phys || !gen || !hd || !hf || !dp || !df || !dc || !dd || !dt || !dk)
             return fail(TSW_ERR_POOL_EXHAUSTED, "pointer-table slab exhausted");
         memset((void*)flag, 0, sizeof(uint32_t) * cap);
         memset((void*)phys, 0, sizeof(uint64_t) * cap);
+        memset((void*)gen, 0, sizeof(uint32_t) * cap);
         if (pl.capacity) {
             // a model that gained parameters after its first placement: the rows published so far
             // move to the larger device table as well (the old arrays stay in the slab until a reset)
@@ -119,13 +123,16 @@ int ensure_rows(tsw_engine* e, Model* m, Placement& pl) {
     for (uint32_t i = 0; i < pl.capacity; ++i) {
         flag[i] = pl.flag[i];
         phys[i] = pl.phys[i];
+        gen[i] = pl.gen[i];
     }
     if (e->plan && pl.capacity) {   // freed with the placement: a waiter outside the lock may still be reading them
         pl.retired_rows.push_back((void*)pl.flag);
         pl.retired_rows.push_back((void*)pl.phys);
+        pl.retired_rows.push_back((void*)pl.gen);
     }
     pl.flag = flag;
     pl.phys = phys;
+    pl.gen = gen;
     pl.capacity = cap;
     return TSW_OK;
 }
@@ -673,6 +680,7 @@ int tsw_engine_destroy(tsw_engine* e) {
             if (e->plan && it->second.capacity) {
                 free((void*)it->second.flag);
                 free((void*)it->second.phys);
+                free((void*)it->second.gen);
                 for (void* p : it->second.retired_rows) free(p);
             }
             kv.second->place.erase(it);
@@ -694,6 +702,11 @@ int tsw_engine_destroy(tsw_engine* e) {
         if (e->host_slab.base) cudaFreeHost(e->host_slab.base);
         if (e->ev_start) cudaEventDestroy((cudaEvent_t)e->ev_start);
         if (e->ev_stop) cudaEventDestroy((cudaEvent_t)e->ev_stop);
+        if (e->stream_ce) {
+            cudaStreamSynchronize((cudaStream_t)e->stream_ce);
+            cudaStreamDestroy((cudaStream_t)e->stream_ce);
+        }
+        if (e->ev_ce) cudaEventDestroy((cudaEvent_t)e->ev_ce);
         if (e->stream) cudaStreamDestroy((cudaStream_t)e->stream);
         // The host model store outlives the engine only as long as the repository
         // refers to it; callers reset the repository before destroying engines.
@@ -837,7 +850,8 @@ int tsw_free(tsw_engine* e, const char* func, uint64_t vptr) {
 
 int tsw_memcpy_h2d_model(tsw_engine* e, const char* func, uint64_t dst, const void* payload, uint64_t size,
                          void* stream) {
-    if (!e || !func || (!payload && size)) return fail(TSW_ERR_INVALID, "null argument");
+    // A plan-only engine may be given sizes without bytes (payload null): it records the parameter.
+    if (!e || !func || (!payload && size && !e->plan)) return fail(TSW_ERR_INVALID, "null argument");
     Lock g1(repo().mu);
     Lock g2(e->mu);
     Model* m = repo().get_or_create(func);
@@ -854,7 +868,7 @@ int tsw_memcpy_h2d_model(tsw_engine* e, const char* func, uint64_t dst, const vo
     VBlock& b = m->blocks[bi];
     if (dst + size > b.vaddr + b.size) return fail(TSW_ERR_INVALID, "upload runs past the end of its block");
     uint8_t* host = b.mirror + (dst - b.vaddr);
-    if (size) memcpy(host, payload, size);
+    if (size && payload) memcpy(host, payload, size);
     int pi;
     auto pit = m->param_by_vaddr.find(dst);
     if (pit == m->param_by_vaddr.end()) {

@@ -63,6 +63,8 @@ struct tsw_engine {
     std::unordered_set<uint64_t> active_params;
 
     void* stream = nullptr;       // transfer stream (cudaStream_t), high priority
+    void* stream_ce = nullptr;    // second transfer stream, made on first use: copy-engine moves of mover 2
+    void* ev_ce = nullptr;        // joins stream_ce back into the transfer stream
     void* ev_start = nullptr;     // cudaEvent_t pair around the last swap
     void* ev_stop = nullptr;
     bool ev_valid = false;
@@ -74,7 +76,9 @@ struct tsw_engine {
 
     int grid_ctas = 0;
     int grid_bulk = 0;   // CTAs of the bulk-copy mover
-    int mover = 0;       // 0 = load/store kernel, 1 = bulk-copy kernel where alignment allows
+    int mover = 0;       // 0 = load/store kernel, 1 = bulk-copy kernel where alignment allows,
+                         // 2 = load/store kernel + the copy engine for large parameters read from the host store
+    uint64_t ce_min_bytes = 4ull << 20;   // mover 2: parameters of at least this size go to the copy engine
     bool guard_names = false;   // TORPOR_SWAP_GUARD_NAMES=1: never grant an address that names another live block of the model
     uint32_t tile_host = 0, tile_dev = 0;
     int host_store_mode = 0;     // TSW_STORE_*

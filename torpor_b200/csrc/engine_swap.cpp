@@ -14,6 +14,7 @@ struct Prepared {
     Plan plan;
     uint32_t tile = 0;
     int src_device = -1;   // device ordinal of the replica the swap reads, if any
+    bool from_host = true; // the swap reads the host store (asked for, or the source replica was unhealthy)
 };
 
 // Wait for whatever still writes into this placement's blocks: the engine's own stream and
@@ -22,6 +23,7 @@ static int drain_placement(tsw_engine* e, Placement& pl) {
     if (e->plan || !pl.in_flight) return TSW_OK;
     TSW_CUDA(cudaSetDevice(e->cfg.device));
     TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+    if (e->stream_ce) TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream_ce));   // joined into the transfer stream, unless a launch failed half way
     for (tsw_engine* h : pl.helpers) {
         TSW_CUDA(cudaSetDevice(h->cfg.device));
         TSW_CUDA(cudaStreamSynchronize((cudaStream_t)h->stream));
@@ -33,25 +35,24 @@ static int drain_placement(tsw_engine* e, Placement& pl) {
 }
 
 // Let go of every stream that waits (tsw_translate_async) for a row of this placement that has
-// not arrived, and remember those rows as failed: the generation word each of them waits for is
-// written by the host, on the engine's own stream (non-blocking, so it cannot queue up behind a
-// waiting stream).  The released streams run on WITHOUT the parameter's bytes; tsw_translate and
-// tsw_poll_ready answer TSW_ERR_KERNEL for such rows until the model is swapped in again or
-// evicted, and callers check one of them after synchronising.  Returns the number of rows let go.
+// not arrived, and remember those rows as failed.  The generation word each of them waits for is
+// host-mapped memory, and the host writes it with a plain store: no CUDA call is made, because the
+// driver gives no promise that work submitted after a stream memory wait -- on whatever stream --
+// is not queued behind that wait (streams share a small number of hardware queues), and a release
+// that can get stuck behind the wait it ends is no release.  The released streams run on WITHOUT
+// the parameter's bytes; tsw_translate and tsw_poll_ready answer TSW_ERR_KERNEL for such rows
+// until the model is swapped in again or evicted, and callers check one of them after
+// synchronising.  Returns the number of rows let go.
 static int release_waiters(tsw_engine* e, Placement& pl) {
     std::vector<int> stuck;
     for (int row : pl.waited_rows)
         if (row >= 0 && (uint32_t)row < pl.capacity && pl.flag[row] != TSW_READY_CUDA) stuck.push_back(row);
     pl.waited_rows.clear();
-    if (e->plan || stuck.empty()) return 0;
-    TSW_CUDA(cudaSetDevice(e->cfg.device));
-    cudaStream_t s = (cudaStream_t)e->stream;
-    const uint32_t generation = pl.epoch;
+    if (e->plan || stuck.empty() || !pl.gen) return 0;
     for (int row : stuck) {
         if ((size_t)row < pl.failed.size()) pl.failed[row] = true;
-        TSW_CUDA(cudaMemcpyAsync(&pl.d_table_flag[row], &generation, sizeof(uint32_t), cudaMemcpyHostToDevice, s));
+        __atomic_store_n(const_cast<uint32_t*>(&pl.gen[row]), pl.epoch, __ATOMIC_RELEASE);
     }
-    TSW_CUDA(cudaStreamSynchronize(s));
     return (int)stuck.size();
 }
 
@@ -146,6 +147,7 @@ static int prepare_swap(tsw_engine* e, const char* func, int src_gpu, Prepared& 
 
     // transfer_model (:331-438): every accessed parameter that is not on the device yet, in access order
     const bool from_host = src_gpu < 0;
+    out.from_host = from_host;
     if (!from_host && src_engine && !src_engine->plan) out.src_device = src_engine->cfg.device;
     out.tile = pick_tile(e, from_host);
     for (int pi : m->access_order) {
@@ -206,6 +208,7 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
     a.table_flag = pl.d_table_flag;
     a.host_phys = (uint64_t*)pl.phys;
     a.host_flag = (uint32_t*)pl.flag;
+    a.host_gen = (uint32_t*)pl.gen;
     pl.epoch += 1;
     a.flag_value = pl.epoch;
     a.host_flag_value = TSW_READY_CUDA;
@@ -255,6 +258,45 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
             w->kernel_launches++;
         }
         TSW_CUDA(cudaSetDevice(e->cfg.device));
+    } else if (e->mover == 2 && pr.from_host) {
+        // Copy-engine-assisted swap-in from the host store.  On this platform the SMs' reads of host
+        // memory reach the link in smaller requests than the copy engine's, which costs about 7 % of
+        // the rate.  So the large parameters go through the copy engine, in access order, on a second
+        // stream, each followed by the publish step for its row; the kernel moves the small
+        // parameters (and skips the large ones) at the same time on the transfer stream.
+        if (!e->stream_ce) {
+            cudaStream_t s2;
+            cudaEvent_t ev;
+            int lo_prio = 0, hi_prio = 0;
+            TSW_CUDA(cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio));
+            TSW_CUDA(cudaStreamCreateWithPriority(&s2, cudaStreamNonBlocking, hi_prio));
+            TSW_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+            e->stream_ce = s2;
+            e->ev_ce = ev;
+        }
+        cudaStream_t s2 = (cudaStream_t)e->stream_ce;
+        TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_ce, s));       // the descriptor upload precedes the publish kernels
+        TSW_CUDA(cudaStreamWaitEvent(s2, (cudaEvent_t)e->ev_ce, 0));
+        a.skip_min_bytes = e->ce_min_bytes;
+        bool any_small = false;
+        for (size_t k = 0; k < plan.descs.size(); ++k) {
+            const PlaceDesc& d = plan.descs[k];
+            if (d.bytes < e->ce_min_bytes) {
+                any_small = true;
+                continue;
+            }
+            TSW_CUDA(cudaMemcpyAsync((void*)d.dst, (const void*)d.src, d.bytes, cudaMemcpyDefault, s2));
+            cudaError_t pe = launch_publish_rows(a, (uint32_t)k, (uint32_t)k + 1, s2);
+            if (pe != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("publish kernel launch: ") + cudaGetErrorString(pe));
+            e->kernel_launches++;
+        }
+        if (any_small) {
+            cudaError_t le = launch_place(a, e->grid_ctas, s, 0);
+            if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
+            e->kernel_launches++;
+        }
+        TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_ce, s2));       // the transfer stream ends when both have
+        TSW_CUDA(cudaStreamWaitEvent(s, (cudaEvent_t)e->ev_ce, 0));
     } else {
         const int mv = pick_mover(e, plan.descs);
         cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, s, mv);
@@ -324,8 +366,14 @@ int tsw_swap_commit(tsw_engine* e, const char* func) {
     TSW_CUDA(cudaMemcpy(phys.data(), pl.d_table_phys, sizeof(uint64_t) * pl.capacity, cudaMemcpyDeviceToHost));
     std::vector<int> missing;
     for (int row : pl.remote_rows) {
-        if (flag[row] == pl.epoch) set_row(pl, row, TSW_READY_CUDA, phys[row]);
-        else missing.push_back(row);
+        if (flag[row] == pl.epoch) {
+            set_row(pl, row, TSW_READY_CUDA, phys[row]);
+            // kernels of other processes cannot reach the host-mapped generation word: streams that wait
+            // for the row are let through here, now that its bytes are known to have landed
+            if (pl.gen) __atomic_store_n(const_cast<uint32_t*>(&pl.gen[row]), pl.epoch, __ATOMIC_RELEASE);
+        } else {
+            missing.push_back(row);
+        }
     }
     // Rows still on their way stay listed: the caller may commit again once the participants have
     // finished, or give up and swap the model in by itself (which starts the counters afresh).
@@ -556,8 +604,8 @@ int tsw_translate(tsw_engine* e, const char* func, uint64_t vptr, int search_ami
 // as its block is placed; what the executor has to wait for is the bytes.  Instead of blocking
 // the host (check_param_readiness, memory_manager.hpp:527-540) this returns the address at once
 // and, if the parameter is still on its way, makes `stream` wait for it: a stream memory
-// operation on the row's generation word in the device pointer table, which the placement
-// kernel writes when the row's last tile has landed.  Kernels that use the parameter can then
+// operation on the row's generation word (host-mapped, next to the host-visible table columns),
+// which the placement kernel writes when the row's last tile has landed.  Kernels that use the parameter can then
 // be enqueued behind it before the weights have arrived.  Nothing spins on the device.
 int tsw_translate_async(tsw_engine* e, const char* func, uint64_t vptr, void* stream, uint64_t* out, int* waited) {
     if (!e || !func || !out) return fail(TSW_ERR_INVALID, "null argument");
@@ -600,7 +648,9 @@ int tsw_translate_async(tsw_engine* e, const char* func, uint64_t vptr, void* st
         wait_fn = (wait_fn_t)fn;
     }
     TSW_CUDA(cudaSetDevice(e->cfg.device));
-    const int rc = wait_fn((cudaStream_t)stream, (unsigned long long)(uintptr_t)&pl.d_table_flag[pi], pl.epoch, 0x0 /* GEQ */);
+    // the row's host-mapped generation word (page-locked, mapped, portable: its host address is its
+    // device address), so that the host can end the wait with a plain store
+    const int rc = wait_fn((cudaStream_t)stream, (unsigned long long)(uintptr_t)&pl.gen[pi], pl.epoch, 0x0 /* GEQ */);
     if (rc != 0) return fail(TSW_ERR_CUDA, "cuStreamWaitValue32 failed with driver error " + std::to_string(rc));
     pl.waited_rows.push_back(pi);
     if (waited) *waited = 1;

@@ -128,6 +128,7 @@ __device__ __forceinline__ void move_tile(const PlaceArgs& a, const uint32_t* s_
         if (threadIdx.x == 0 && a.status) *reinterpret_cast<volatile uint32_t*>(a.status) = 1u;
         return;
     }
+    if (a.skip_min_bytes && d.bytes >= a.skip_min_bytes) return;   // the copy engine's share
     const uint64_t left = d.bytes - off;
     const uint32_t len = left < a.tile_bytes ? (uint32_t)left : a.tile_bytes;
     copy_span(d.src + off, d.dst + off, len);
@@ -150,6 +151,7 @@ __device__ __forceinline__ void move_tile(const PlaceArgs& a, const uint32_t* s_
                 __threadfence_system();
                 a.table_flag[d.row] = a.flag_value;
                 if (a.host_flag) a.host_flag[d.row] = a.host_flag_value;
+                if (a.host_gen) a.host_gen[d.row] = a.flag_value;
                 __threadfence_system();
             }
         }
@@ -179,6 +181,21 @@ __global__ void __launch_bounds__(kThreads) place_kernel(const PlaceArgs a) {
         const uint32_t last = (a.tile_hi - first < a.ticket_chunk) ? a.tile_hi : first + a.ticket_chunk;
         for (uint32_t t = first; t < last; ++t) move_tile(a, s_first, t);
     }
+}
+
+// The publish step alone.  One thread per segment of [lo, hi); the bytes were moved by a copy
+// that precedes this kernel in its stream, so they are complete when it runs.
+__global__ void publish_rows_kernel(const PlaceArgs a, uint32_t lo, uint32_t hi) {
+    const uint32_t k = lo + blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= hi) return;
+    const PlaceDesc d = a.descs[k];
+    a.table_phys[d.row] = d.row_dst;
+    if (a.host_phys) a.host_phys[d.row] = d.row_dst;
+    __threadfence_system();
+    a.table_flag[d.row] = a.flag_value;
+    if (a.host_flag) a.host_flag[d.row] = a.host_flag_value;
+    if (a.host_gen) a.host_gen[d.row] = a.flag_value;
+    __threadfence_system();
 }
 
 // ------------------------------------------------------------------ bulk-copy mover
@@ -278,6 +295,7 @@ __global__ void __launch_bounds__(kBulkThreads) place_kernel_bulk(const PlaceArg
             if (a.status) *reinterpret_cast<volatile uint32_t*>(a.status) = 1u;
             continue;
         }
+        if (a.skip_min_bytes && d.bytes >= a.skip_min_bytes) continue;   // the copy engine's share
         const uint64_t left = d.bytes - off;
         const uint32_t len = left < a.tile_bytes ? (uint32_t)left : a.tile_bytes;
         const uint32_t body = len & ~15u;
@@ -338,6 +356,7 @@ __global__ void __launch_bounds__(kBulkThreads) place_kernel_bulk(const PlaceArg
                 __threadfence_system();
                 a.table_flag[d.row] = a.flag_value;
                 if (a.host_flag) a.host_flag[d.row] = a.host_flag_value;
+                if (a.host_gen) a.host_gen[d.row] = a.flag_value;
                 __threadfence_system();
             }
         }
@@ -442,6 +461,14 @@ cudaError_t launch_place(const PlaceArgs& a, int grid_ctas, cudaStream_t stream,
         if (e != cudaSuccess) return e;
     }
     place_kernel<<<grid, kThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_publish_rows(const PlaceArgs& a, uint32_t lo, uint32_t hi, cudaStream_t stream) {
+    if (hi <= lo) return cudaSuccess;
+    if (!a.table_phys || !a.table_flag) return cudaErrorInvalidValue;
+    const uint32_t n = hi - lo;
+    publish_rows_kernel<<<(n + 63) / 64, 64, 0, stream>>>(a, lo, hi);
     return cudaGetLastError();
 }
 

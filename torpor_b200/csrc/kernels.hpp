@@ -33,6 +33,7 @@ struct PlaceArgs {
     uint32_t* table_flag;         //                       readiness per param
     uint64_t* host_phys;          // host-mapped mirror of the two columns (may be null)
     uint32_t* host_flag;
+    uint32_t* host_gen;           // host-mapped generation word per param: what stream-ordered waits wait on (may be null)
     uint32_t flag_value;          // written to the device flag column when a param completes
     uint32_t host_flag_value;     // written to the host-mapped flag column
     uint32_t system_scope;        // 1: stores may target a peer GPU / host memory
@@ -42,6 +43,9 @@ struct PlaceArgs {
     uint32_t* ticket;
     uint32_t ticket_chunk;
     uint32_t* status;             // device word, set non-zero on an internal inconsistency
+    // Segments of at least this many bytes are left alone by this launch (0 = none): the copy engine
+    // moves them, and publish_rows rewrites their table rows behind each copy.
+    uint64_t skip_min_bytes;
 };
 
 // Descriptor-driven placement copy: host store -> pool blocks (swap-in), pool ->
@@ -49,6 +53,11 @@ struct PlaceArgs {
 // mover: 0 = loads and stores by the SMs' threads (place_kernel), 1 = the bulk asynchronous copy
 // unit through shared memory (place_kernel_bulk; needs 16-byte aligned sources and destinations).
 cudaError_t launch_place(const PlaceArgs& a, int grid_ctas, cudaStream_t stream, int mover = 0);
+
+// Rewrite the table rows of segments [lo, hi) of a.descs as the placement kernel does for a
+// completed parameter (device table, host-mapped mirror, generation word): the publish step on
+// its own, for parameters whose bytes a copy engine moved earlier in the same stream.
+cudaError_t launch_publish_rows(const PlaceArgs& a, uint32_t lo, uint32_t hi, cudaStream_t stream);
 
 // Per-parameter checksums of device-resident bytes; out has 2 words per row and must be
 // zeroed by the caller.

@@ -62,6 +62,11 @@ struct Placement {
     std::vector<void*> retired_rows;     // plan-only: smaller tables replaced by growth; a waiter may still read them
     volatile uint32_t* flag = nullptr;   // TSW_READY_*
     volatile uint64_t* phys = nullptr;   // readiness address (0 = none)
+    // Generation word per row, host-mapped like the two columns above: the swap generation that last
+    // completed the row.  Stream-ordered waits (tsw_translate_async) wait on THIS word, because it is
+    // the one the host can write with a plain store when a wait has to be let go: a release that went
+    // through a CUDA stream could be queued by the driver behind the very wait it is meant to end.
+    volatile uint32_t* gen = nullptr;
     std::vector<bool> has_row;           // row exists in the readiness map
     // device-side twins and launch scratch (CUDA engines only)
     uint64_t* d_table_phys = nullptr;

@@ -71,6 +71,14 @@ class ModelRepo:
         return sorted(buf[i] for i in range(min(n, 64)))
 
 
+class SizeOnly:
+    """Stands for ``nbytes`` bytes that are not supplied: what a plan-only engine is given as a
+    parameter's payload when only placement and tables are wanted."""
+
+    def __init__(self, nbytes: int):
+        self.nbytes = int(nbytes)
+
+
 class MemoryManager:
     """One swap engine (one per GPU).
 
@@ -137,6 +145,8 @@ class MemoryManager:
         check(self.L.tsw_free(self.h, func.encode(), ptr))
 
     def cudaMemcpyAsyncBackendHtoD(self, dst: int, payload, stream: int, load_model_flag: bool, func: str) -> int:
+        if isinstance(payload, SizeOnly):     # plan-only engines: the parameter's size without its bytes
+            return self.L.tsw_memcpy_h2d_model(self.h, func.encode(), dst, None, payload.nbytes, stream)
         data = np.ascontiguousarray(payload).view(np.uint8).reshape(-1)
         fn = self.L.tsw_memcpy_h2d_model if load_model_flag else self.L.tsw_memcpy_h2d
         return fn(self.h, func.encode(), dst, data.ctypes.data, data.nbytes, stream)
@@ -334,6 +344,15 @@ def place_segments_static(device: int, src, dst, nbytes, rows=None, tile_bytes: 
     segs = make_segments(src, dst, nbytes, rows)
     check(_cabi.lib().tsw_place_segments_static(device, segs.ctypes.data, len(segs), tile_bytes, tile_first, tile_stride,
                                                 C.byref(publish) if publish is not None else None, stream))
+
+
+def place_segments_static_status(device: int, stream: int = 0, clear: bool = False) -> int:
+    """The word in which the allocation-free mover reports a table that did not fit its tile
+    numbering (what overlapping calls on one device produce); 0 = nothing reported.  Synchronises
+    ``stream``.  (``tsw_place_segments_static_status``)"""
+    word = C.c_uint32()
+    check(_cabi.lib().tsw_place_segments_static_status(device, stream, C.byref(word), 1 if clear else 0))
+    return word.value
 
 
 class Evictor:

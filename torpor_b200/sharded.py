@@ -8,7 +8,8 @@ own PCIe link and storing straight into the target's pool blocks across NVLink (
 is opened through CUDA IPC).  Completion counters and the pointer table sit on the target,
 so whichever GPU finishes a parameter publishes it; the target then commits the rows
 (``tsw_swap_commit``).  No collective moves data: ``torch.distributed`` (a gloo group)
-carries only the few KB of control messages.
+carries only the few KB of control messages.  (An NCCL send/recv gather was measured beside the peer
+stores and is slower; ``bench.py --nccl-gather`` repeats the measurement.)
 
 Two ways of dealing out the tiles:
   direct  tile t goes to rank t mod N; host store -> target pool in one kernel per rank.
@@ -127,6 +128,10 @@ class ShardedSwap:
         self.dry = engine is None or engine.device < 0
         self.dynamic = True         # direct mode: draw tiles from a shared counter instead of t mod N
         self.staged_tile = 512 * 1024
+        # the target's overrides of the engine's host-side tile size and of the tiles taken per draw
+        # from the shared counter, for one swap to the next (measurement sweeps); 0 = the engine's own
+        self.tile_override = 0
+        self.chunk_override = 0
         # Helpers only lend bandwidth.  When a control message to them fails (a helper process is gone,
         # or the group's timeout ran out) the target stops asking and from then on swaps by itself.
         self.alone = world == 1
@@ -210,9 +215,11 @@ class ShardedSwap:
                 raise RuntimeError("raise max_segments")
             bases = [] if self.dry else sorted(b for b, _, _ in self.engine.ipc_regions())
             changed = bases != self.region_bases
+            if self.tile_override and mode == 0:
+                tile = self.tile_override
             buf[0], buf[1], buf[2], buf[3] = len(segs), tile, 1 if changed else 0, mode
             buf[HEADER_WORDS:HEADER_WORDS + PUB_WORDS] = [pub.done_count, pub.table_phys, pub.table_flag, 0, 0,
-                                                          pub.flag_value, pub.ticket_chunk, pub.ticket]
+                                                          pub.flag_value, self.chunk_override or pub.ticket_chunk, pub.ticket]
             raw = segs.view(np.uint64)
             buf[HEADER_WORDS + PUB_WORDS:HEADER_WORDS + PUB_WORDS + raw.size] = raw
         buf = self._bcast_words(buf)
@@ -323,90 +330,251 @@ class ShardedSwap:
 
 # ------------------------------------------------------------------ benchmark driver (torchrun)
 
+class _RawDevice:
+    """A run of device memory that no torch allocation owns, as an object torch can wrap."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 3}
+
+
+def nccl_gather(sw: "ShardedSwap", func: str, group, reps: int = 5) -> Optional[dict]:
+    """The gather stage over NCCL instead of peer stores, for comparison: every helper sends its
+    staged share (resident in its HBM) with ncclSend, the target receives (a) each share into one
+    contiguous buffer -- NCCL's best case, the scatter into pool blocks would still have to follow --
+    and (b) piece by piece straight into the pool blocks of the current placement.  Call right after
+    a staged swap-in of ``func`` (the placement and the staged shares are then in place).
+    Device time on the target (CUDA events), best of ``reps``."""
+    import torch
+    import torch.distributed as dist
+    segs, tile = sw.last_plan
+    first = tiles_of(segs, tile)
+    n_tiles = int(first[-1])
+    dev = torch.device(f"cuda:{sw.engine.device}")
+    shares = [contiguous_share(n_tiles, r, sw.world) for r in range(sw.world)]
+
+    def share_bytes(r):
+        lo, hi = shares[r]
+        return sum(max(0, min(int(segs["bytes"][k]), (min(hi, int(first[k + 1])) - int(first[k])) * tile)
+                          - max(0, (max(lo, int(first[k])) - int(first[k])) * tile)) for k in range(len(segs))
+                   if min(hi, int(first[k + 1])) > max(lo, int(first[k])))
+
+    def pieces(r):
+        """(offset in rank r's staging buffer, destination address on the target, bytes)"""
+        lo, hi = shares[r]
+        out = []
+        for k in range(len(segs)):
+            a, b = max(lo, int(first[k])), min(hi, int(first[k + 1]))
+            if b <= a:
+                continue
+            off0 = (a - int(first[k])) * tile
+            off1 = min(int(segs["bytes"][k]), (b - int(first[k])) * tile)
+            if off1 > off0:
+                out.append(((a - lo) * tile, int(segs["dst"][k]) + off0, off1 - off0))
+        return out
+
+    my_lo, my_hi = shares[sw.rank]
+    mine = sw.staging.get((func, my_lo, my_hi, tile))
+    if mine is None:
+        return None
+    inbound = sum(share_bytes(r) for r in range(1, sw.world))
+    result = {"inbound_bytes": inbound}
+    for mode in ("contiguous", "into_pool_blocks"):
+        ops, keep = [], []
+        if sw.rank == 0:
+            for r in range(1, sw.world):
+                if mode == "contiguous":
+                    buf = torch.empty((shares[r][1] - shares[r][0]) * tile, dtype=torch.uint8, device=dev)
+                    keep.append(buf)
+                    ops.append(dist.P2POp(dist.irecv, buf, r, group=group))
+                else:
+                    for _, dst, n in pieces(r):
+                        t = torch.as_tensor(_RawDevice(dst, n), device=dev)
+                        keep.append(t)
+                        ops.append(dist.P2POp(dist.irecv, t, r, group=group))
+        else:
+            if mode == "contiguous":
+                ops.append(dist.P2POp(dist.isend, mine, 0, group=group))
+            else:
+                for off, _, n in pieces(sw.rank):
+                    ops.append(dist.P2POp(dist.isend, mine[off:off + n], 0, group=group))
+        best = None
+        for _ in range(reps + 1):
+            dist.barrier(group=sw.group)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+            b.record()
+            torch.cuda.synchronize()
+            ms = sw._max_over_ranks(a.elapsed_time(b))
+            best = ms if best is None else min(best, ms)
+        result[mode] = {"ms": best, "inbound_gbs": inbound / (best / 1e3) / 1e9, "ops_per_helper": len(ops) if sw.rank else None}
+        del keep
+    return result
+
+
 def bench_main(args, bench):
     """bench.py at N > 1: one rank per GPU; rank 0's GPU is the target."""
     import statistics
     import torch
     import torch.distributed as dist
     from . import workloads as W
-    from .memory_manager import checksum_host, repo_reset
+    from .memory_manager import repo_reset
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
     if world == 1:
         raise SystemExit("bench.py --gpus N with N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    # Control messages only: the data plane is the placement kernel's peer stores, no collective.
+    dist.init_process_group("gloo")
+    ctrl = dist.group.WORLD
+    # Which GPU each rank drives.  With as many GPUs as ranks: rank r drives GPU r.  On a box with more
+    # GPUs than ranks the links are not equal (GPUs behind a busier or farther root port are fed at half
+    # the rate of the others), so the target measures every GPU's host-link rate with all of them
+    # copying at once -- in a child process, so that no context stays open on GPUs the job does not use
+    # -- and the best-fed N take part, the best of them as the target.
+    devices, probe = None, None
+    if rank == 0:
+        if args.devices:
+            devices = [int(d) for d in args.devices.split(",")]
+        elif torch.cuda.device_count() > world:
+            import json
+            import subprocess
+            import sys
+            r = subprocess.run([sys.executable, os.path.abspath(bench.__file__), "--link-probe"], stdout=subprocess.PIPE,
+                               stderr=subprocess.PIPE, text=True, timeout=300)
+            for ln in r.stdout.splitlines():
+                if ln.startswith("{"):
+                    probe = json.loads(ln)["link_probe"]["concurrent_h2d_gbs"]
+            if probe:
+                devices = sorted(range(len(probe)), key=lambda g: -probe[g])[:world]
+    box = [devices, probe]
+    dist.broadcast_object_list(box, src=0)
+    devices, probe = box
+    if not devices or len(devices) != world:
+        devices = list(range(world))
+    local_rank = devices[rank]
     torch.cuda.set_device(local_rank)
-    dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
-    ctrl = dist.new_group(backend="gloo")
     ncpu = os.cpu_count() or 1
     peaks, peak_kind = bench.measured_peaks()
 
     ws = W.weight_set(args.workload)
+    K, Wm = args.steps, args.warmup
+    K_g = min(K, 10)
+    B = ws.nbytes
+
+    # the reference on this box's host cores, rank 0 only, before the engines take the GPU's memory
+    cpu_baseline = None
+    if rank == 0 and not args.no_cpu_baseline:
+        cpu_baseline = bench.cpu_baselines(args)
+    dist.barrier(group=ctrl)
+
     shm = f"/torpor_swap_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}"
     repo_reset()
+    tile_host = args.tile_kib * 1024
+    budget = W.pool_budget_for(ws)
+    sums, tables, vaddrs = {}, [], []
+    cold_s = 0.0
     if rank == 0:
-        eng = MemoryManager(W.pool_budget_for(ws), device=local_rank, server_id=0, gpu_count=world,
-                            host_arena_bytes=W.host_store_bytes(ws), host_arena_shm=shm)
+        sweep_swaps = 40 if args.sweep else 0
+        tables = W.plan_tables(ws, "model", budget=budget, gpu_count=world, swaps=4 + 2 * (Wm + K) + (Wm + K_g) + sweep_swaps + 8)
+        repo_reset()
+        eng = MemoryManager(budget, device=local_rank, server_id=0, gpu_count=world, host_arena_bytes=W.host_store_bytes(ws),
+                            host_arena_shm=shm, tile_bytes_host=tile_host, ticket_chunk=args.ticket_chunk, host_store_mode=args.host_store)
     else:
         eng = MemoryManager(0, device=local_rank, server_id=rank, gpu_count=world, block_manager="Fixed")
     sw = ShardedSwap(eng, rank, world, ctrl, shm_name=shm, max_segments=max(1024, len(ws.tensors) + 16))
 
-    sums = {}
-    cold_s = 0.0
     if rank == 0:
-        pool, data = bench.generate_tensors(ws, min(ncpu, 16))
-
-        def data_and_sum(i):
-            b = data(i)
-            if i % 16 == 0:
-                sums[i] = checksum_host(b)
-            return b
+        pool, data, sums = bench.generate_tensors(ws, min(ncpu, 16), with_sums=True)
         t0 = time.time()
-        W.cold_start(eng, "model", ws, tensor_data=data_and_sum)
+        loaded = W.cold_start(eng, "model", ws, tensor_data=data)
+        vaddrs = loaded.tensor_vaddr
         pool.shutdown()
         torch.cuda.synchronize()
         cold_s = time.time() - t0
         eng.evict("model")
+    ver = bench.Verifier(ws, sums, tables)
     dist.barrier(group=ctrl)
     sw.attach_arena()
     sw.share_regions()
 
-    def verify():
-        if rank == 0:
-            got = eng.checksum_resident("model")
-            for i, s in sums.items():
-                if not np.array_equal(got[i], s):
-                    raise RuntimeError(f"resident bytes of tensor {i} differ from the host store")
+    def swap(mode):
+        r = sw.swap_in("model", mode)
+        ver.swapped()
+        return r
 
-    def timed(mode, steps, warmup):
+    def check(where):
+        """The target checks every tensor and both tables; every rank waits.  Returns the seconds it took."""
+        t0 = time.perf_counter()
+        failure = None
+        if rank == 0:
+            try:
+                ver.check(eng, "model", where)
+            except RuntimeError as ex:
+                failure = str(ex)
+        failure = sw._bcast_obj(failure)
+        if failure:
+            raise RuntimeError(failure)
+        return time.perf_counter() - t0
+
+    def timed(mode, steps, warmup, through_translate=False, where="", verify=True):
         for _ in range(warmup):
-            sw.swap_in("model", mode); sw.evict("model")
-        dev = []
+            swap(mode); sw.evict("model")
+        dev, pause = [], 0.0
         launches0 = eng.stats()["kernel_launches"]
         dist.barrier(group=ctrl)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        for _ in range(steps):
-            r = sw.swap_in("model", mode)
+        for k in range(steps):
+            r = swap(mode)
+            if through_translate and rank == 0:
+                for v in vaddrs:                 # the launch path: every parameter, in access order
+                    eng.translate("model", v)
             dev.append(r["device_ns_max"])
+            if verify and k == steps - 1:        # the last timed swap-in is the one that is checked; clock paused
+                l1 = eng.stats()["kernel_launches"]
+                pause = check(where)
+                launches0 += eng.stats()["kernel_launches"] - l1
             sw.evict("model")
         torch.cuda.synchronize()
         dist.barrier(group=ctrl)
-        wall = time.perf_counter() - t0
+        wall = time.perf_counter() - t0 - pause
         wall = sw._max_over_ranks(wall)
         return wall, dev, eng.stats()["kernel_launches"] - launches0
 
-    # correctness of both arms before anything is timed (also fills the staged shares)
-    sw.swap_in("model", "direct"); verify(); sw.evict("model")
-    sw.swap_in("model", "staged"); verify(); sw.evict("model")
+    # correctness of both ways of dealing before anything is timed (also fills the staged shares)
+    swap("direct"); check("before timing, direct"); sw.evict("model")
+    swap("staged"); check("before timing, staged"); sw.evict("model")
 
     sampler = bench.ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    wall_v, dev_v, launches_v = timed("staged", args.steps, args.warmup)
-    wall_e, dev_e, launches_e = timed("direct", args.steps, args.warmup)
+    wall_v, dev_v, launches_v = timed("direct", K, Wm, where="after the timed sharded swap-ins")
+    wall_e, dev_e, launches_e = timed("direct", K, Wm, through_translate=True, where="after the timed executor-path swap-ins")
+    wall_g, dev_g, _ = timed("staged", K_g, Wm, where="after the timed gathers")
     clocks = sampler.stop() if rank == 0 else None
+
+    sweep = None
+    if args.sweep:
+        sweep = []
+        for tile_kib in (64, 128, 256):
+            for chunk in (1, 4, 16):
+                sw.tile_override, sw.chunk_override = tile_kib * 1024, chunk
+                w_s, d_s, _ = timed("direct", 3, 1, where=f"sweep tile {tile_kib} KiB, {chunk} tiles per draw")
+                sweep.append({"tile_kib": tile_kib, "tiles_per_draw": chunk, "gbs_wall": B * 3 / w_s / 1e9,
+                              "gbs_device": B / (statistics.mean(d_s) / 1e9) / 1e9})
+        sw.tile_override = sw.chunk_override = 0
+
+    nccl = None
+    if args.nccl_gather:
+        g = dist.new_group(backend="nccl")
+        swap("staged")
+        nccl = nccl_gather(sw, "model", g)
+        check("after the NCCL gather comparison")
+        sw.evict("model")
 
     # what the box's copy engines reach when every participating GPU pulls page-locked host
     # memory at once: the practical ceiling of the links, next to the theoretical one
@@ -421,6 +589,17 @@ def bench_main(args, bench):
         torch.cuda.synchronize()
         dt = sw._max_over_ranks(time.perf_counter() - t0)
         dma_best = max(dma_best, world * (1 << 30) / dt / 1e9)
+    # ... and when each keeps pulling for a fixed time (the sum of the rates, not equal shares)
+    dist.barrier(group=ctrl)
+    t_end = time.perf_counter() + 1.0
+    pulled = 0
+    while time.perf_counter() < t_end:
+        y.copy_(x, non_blocking=True)
+        torch.cuda.synchronize()
+        pulled += 1 << 30
+    rates = torch.zeros(world, dtype=torch.float64)
+    rates[rank] = pulled / 1.0 / 1e9
+    dist.all_reduce(rates, group=ctrl)
     del x, y
 
     total_launches = torch.tensor([launches_v, launches_e], dtype=torch.int64)
@@ -428,40 +607,54 @@ def bench_main(args, bench):
 
     line = None
     if rank == 0:
-        B = ws.nbytes
-        value = B * args.steps / wall_v / 1e9
-        e2e = B * args.steps / wall_e / 1e9
+        value = B * K / wall_v / 1e9
+        e2e = B * K / wall_e / 1e9
         kern_v = statistics.mean(dev_v) / 1e9
-        kern_e = statistics.mean(dev_e) / 1e9
+        kern_g = statistics.mean(dev_g) / 1e9
         inbound = B * (world - 1) / world
+        peak = bench.PCIE_GEN5_X16_GBS * world
+        feed_sum = float(rates.sum())
         line = {
             "metric": "model_swap_in_throughput", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall_v / args.steps * 1e3,
+            "steps": K, "warmup": Wm, "ms_per_step": wall_v / K * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": bench.workload_config(args, world),
-            "value_arm": f"gather stage: each rank's 1/{world} share resident in its HBM, stored into the target's pool over NVLink",
-            "e2e": {"value": e2e, "unit": "GB/s", "ms_per_model": wall_e / args.steps * 1e3,
+            "value_arm": "sharded swap-in from the shared page-locked host store: every rank's GPU reads tiles over its own PCIe "
+                         "link and stores them into the target's pool over NVLink; plan, control messages, commit and evict "
+                         "inside the timed region, max over ranks",
+            "e2e": {"value": e2e, "unit": "GB/s", "ms_per_model": wall_e / K * 1e3,
                     "h2d_bytes_per_step": B + 40 * len(ws.tensors) * world, "d2h_bytes_per_step": 12 * len(ws.tensors),
-                    "device_ms_per_model": kern_e * 1e3,
-                    "what": "sharded swap-in from the shared host store: every rank reads its tiles over its own PCIe link and stores them into the target's pool over NVLink; plan + control messages + commit + evict inside the timed region"},
-            "roofline": {"bound": "nvlink", "achieved": inbound / kern_v / 1e9, "peak": 770.0, "unit": "GB/s",
-                         "frac": inbound / kern_v / 1e9 / 770.0,
-                         "peak_kind": "measured peer-copy bandwidth per direction on this pool (nominal 900)",
-                         "kernel": "place_kernel (local HBM -> target pool over NVLink)",
-                         "algorithmic_bytes_per_launch": inbound, "launch_ms": kern_v * 1e3, "traffic": None},
-            "link_roofline": {"bound": "pcie", "achieved": B / kern_e / 1e9, "achieved_wall": e2e,
-                              "peak": bench.PCIE_GEN5_X16_GBS * world, "unit": "GB/s",
-                              "frac": (B / kern_e / 1e9) / (bench.PCIE_GEN5_X16_GBS * world),
-                              "frac_wall": e2e / (bench.PCIE_GEN5_X16_GBS * world),
-                              "peak_kind": f"theoretical PCIe Gen5 x16 x {world} participating GPUs",
-                              "cudaMemcpyAsync_pinned_h2d_concurrent_gbs": dma_best,
-                              "frac_of_concurrent_memcpy": e2e / dma_best if dma_best else None,
-                              "dealing": "tiles drawn from a shared counter on the target (faster links move more)",
-                              "kernel": "place_kernel (host store -> target pool, zero-copy over PCIe, peer stores over NVLink)"},
-            "cpu_baseline": None,
+                    "device_ms_per_model": statistics.mean(dev_e) / 1e6,
+                    "what": "the same sharded swap-in followed, on the target, by tsw_translate of every parameter in access "
+                            "order (the launch path), then tsw_evict"},
+            "roofline": {"bound": "pcie", "achieved": B / kern_v / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": (B / kern_v / 1e9) / peak, "frac_wall": value / peak,
+                         "peak_kind": f"theoretical PCIe Gen5 x16 x {world} participating GPUs (no PCIe figure in MEASURED_PEAKS.json)",
+                         "kernel": "place_kernel (host store -> target pool: zero-copy reads over PCIe, peer stores over NVLink)",
+                         "algorithmic_bytes_per_launch": B, "launch_ms": kern_v * 1e3,
+                         "traffic": bench.DRAM_WRITE_PER_ALGO_BYTE_HOST * B,
+                         "copy_engines_equal_shares_gbs": dma_best,
+                         "copy_engines_continuous_per_gpu_gbs": [round(float(v), 2) for v in rates],
+                         "copy_engines_continuous_sum_gbs": feed_sum,
+                         "frac_of_measured_feed": value / max(feed_sum, dma_best) if max(feed_sum, dma_best) else None,
+                         "dealing": "tiles drawn from a shared counter on the target (faster links move more)"},
+            "gather_stage": {"bound": "nvlink", "achieved": inbound / kern_g / 1e9, "peak": 900.0, "unit": "GB/s",
+                             "frac": inbound / kern_g / 1e9 / 900.0, "peak_measured": 770.0,
+                             "frac_of_measured": inbound / kern_g / 1e9 / 770.0,
+                             "peak_kind": "nominal NVLink 5 per direction per GPU; measured peer-copy rate on this pool beside it",
+                             "kernel": "place_kernel (each rank's share in its HBM -> target pool over NVLink)",
+                             "algorithmic_bytes_per_launch": inbound, "launch_ms": kern_g * 1e3, "steps": K_g,
+                             "swap_gbs_wall": B * K_g / wall_g / 1e9, "nccl": nccl,
+                             "what": "not the metric: the gather on its own, inputs already in the helpers' HBM"},
+            "verified": ver.record(after_timed=True),
+            "cpu_baseline": cpu_baseline,
             "gpu_launches": int(total_launches[0]), "gpu_launches_e2e": int(total_launches[1]),
             "clocks": clocks, "host_cores": ncpu, "cold_start_s": cold_s,
+            "settings": {"tile_bytes_host": tile_host or 65536, "tiles_per_draw": args.ticket_chunk or 1, "host_store_mode": args.host_store,
+                         "devices": devices, "link_probe_concurrent_h2d_gbs": probe},
         }
+        if sweep is not None:
+            line["sweep"] = sweep
     dist.barrier(group=ctrl)
     eng.close()
     repo_reset()

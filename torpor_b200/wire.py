@@ -169,6 +169,9 @@ class WireExecutor:
         # kernel_model_access_loc (src/server/kernel_lookup.cpp): func -> kernel -> {(arg, word)}
         self.access_loc: Dict[str, Dict[str, set]] = {}
         self.launched: List[Tuple[str, List[bytes]]] = []
+        # lookup() (src/server/kernel_lookup.cpp): kernel name -> launcher(args, grid, block, shared_mem).
+        # A kernel registered here is really launched, on the argument words as rewritten below.
+        self.kernels: Dict[str, object] = {}
         self.async_results: list = []        # stream_async_msg_: (client's destination, array being read into)
 
     # ---- signals from the controller (cuda_server.hpp:212-255)
@@ -250,7 +253,12 @@ class WireExecutor:
             return encode("AsyncResponse", {"error": 0, "responses": [{"ptr": p, "payload": b.tobytes()} for p, b in pending]})
         if qtype == Q_LAUNCH_KERNEL:
             q = decode("cudaLaunchKernelQuery", body)
-            self.launched.append((q["function"], self.rewrite_args(q["function"], q["args"])))
+            args = self.rewrite_args(q["function"], q["args"])
+            self.launched.append((q["function"], args))
+            launcher = self.kernels.get(q["function"])
+            if launcher is not None:                # cudaLaunchKernel(ptr, gridDim, blockDim, args, sharedMem, stream), :1302
+                launcher(args, (q["grid_dim_x"], q["grid_dim_y"], q["grid_dim_z"]),
+                         (q["block_dim_x"], q["block_dim_y"], q["block_dim_z"]), q["shared_mem"])
             return None
         raise ValueError(f"query type {qtype} is not part of the swap path")
 

@@ -382,3 +382,31 @@ def host_store_bytes(ws: WeightSet) -> int:
     """Bytes of page-locked host store one copy of ``ws`` needs (block mirrors, 4 KiB aligned)."""
     total = sum((b.size + 4095) // 4096 * 4096 for b in pack_blocks(ws)[0])
     return ((total >> 30) + 1) << 30
+
+
+def plan_tables(ws: WeightSet, func: str, *, budget: int, target_server: int = 0, holder_server: int = 0,
+                gpu_count: int = 1, swaps: int = 1, block_manager: str = "Buddy"):
+    """Block and pointer tables (canonical addresses) that the target engine must show after each of
+    ``swaps`` swap-ins of ``ws`` with an eviction between them, worked out on plan-only engines: the
+    same placement and rebind decisions, no byte moved, no GPU needed.  ``holder_server`` is the
+    engine that cold-starts the model (the target itself evicts it first when they are the same).
+    Uses the process-wide model repository: call it while no other engine holds ``func``.
+    Returns a list of (blocks, params) pairs, one per swap-in."""
+    from .memory_manager import MemoryManager, SizeOnly
+    engines = {}
+    for sid in sorted({target_server, holder_server}):
+        engines[sid] = MemoryManager(budget, device=-1, server_id=sid, gpu_count=gpu_count, block_manager=block_manager)
+    out = []
+    try:
+        cold_start(engines[holder_server], func, ws, tensor_data=lambda i: SizeOnly(ws.tensors[i].nbytes))
+        target = engines[target_server]
+        if holder_server == target_server:
+            target.evict(func)
+        for _ in range(swaps):
+            target.swap_in(func, -1)
+            out.append((target.dump_blocks(func, canonical=True), target.dump_params(func, canonical=True)))
+            target.evict(func)
+    finally:
+        for e in engines.values():
+            e.close()
+    return out
