@@ -585,8 +585,25 @@ def run_single(args):
         t0 = time.perf_counter()
         target.evict("model", writeback=True)
         wb.append(time.perf_counter() - t0)
-    clocks = sampler.stop()
     swap(-1); target.wait_ready("model"); ver.check(target, "model", "after the write-back evictions"); target.evict("model")
+
+    # The same executor path with the copy engine carrying the large parameters (tsw_config.mover = 2;
+    # the kernel moves the small ones and publishes every row): a fresh engine under the same server id,
+    # so the placement sequence -- and the tables it is checked against -- start over.
+    assisted = None
+    if args.mover == 0:
+        target.close()
+        target = MemoryManager(budget, device=0, server_id=0, gpu_count=2, tile_bytes_host=args.tile_kib * 1024, mover=2)
+        ver.swaps = 0
+        swap(-1); target.wait_ready("model"); ver.check(target, "model", "before timing, copy-engine-assisted"); target.evict("model")
+        wall_a, dev_a, ready_a, launches_a = timed(-1, K, Wm, through_translate=True,
+                                                   where="after the timed copy-engine-assisted swap-ins")
+        assisted = {"value": ws.nbytes * K / wall_a / 1e9, "unit": "GB/s", "ms_per_model": wall_a / K * 1e3,
+                    "device_ms_per_model": statistics.mean(dev_a) / 1e6, "gpu_launches": launches_a,
+                    "frac_of_pcie": ws.nbytes / (statistics.mean(dev_a) / 1e9) / 1e9 / PCIE_GEN5_X16_GBS,
+                    "what": "executor path with tsw_config.mover = 2: parameters of 4 MiB and more by cudaMemcpyAsync in "
+                            "access order with a publish kernel behind each, the rest by place_kernel at the same time"}
+    clocks = sampler.stop()
 
     ce = copy_engine_h2d_gbs(0)     # measured DMA rate of this box's link, next to the theoretical 63 GB/s
 
@@ -594,6 +611,12 @@ def run_single(args):
     n_params = len(ws.tensors)
     value = B * K / wall_v / 1e9
     e2e = B * K / wall_e / 1e9
+    e2e_ms, e2e_dev_ms, e2e_mover = wall_e / K * 1e3, statistics.mean(dev_e) / 1e6, args.mover
+    e2e_by_mover = {str(args.mover): e2e}
+    if assisted:
+        e2e_by_mover["2"] = assisted["value"]
+        if assisted["value"] > e2e:      # what a deployment on this box would configure: the faster of the two, as measured here
+            e2e, e2e_ms, e2e_dev_ms, e2e_mover = assisted["value"], assisted["ms_per_model"], assisted["device_ms_per_model"], 2
     kern_v = statistics.mean(dev_v) / 1e9
     kern_h = statistics.mean(dev_h) / 1e9
     achieved = B / kern_v / 1e9
@@ -606,12 +629,13 @@ def run_single(args):
         "value_arm": "tsw_swap_in from the page-locked host store + tsw_wait_ready + tsw_evict, K steps on the wall clock",
         "signal_to_ready_ms": {"median": statistics.median(ready_v) * 1e3, "mean": statistics.mean(ready_v) * 1e3,
                                "gbs_at_median": B / statistics.median(ready_v) / 1e9},
-        "e2e": {"value": e2e, "unit": "GB/s", "ms_per_model": wall_e / K * 1e3,
+        "e2e": {"value": e2e, "unit": "GB/s", "ms_per_model": e2e_ms,
                 "h2d_bytes_per_step": B + 44 * n_params, "d2h_bytes_per_step": 12 * n_params,
-                "device_ms_per_model": statistics.mean(dev_e) / 1e6,
+                "device_ms_per_model": e2e_dev_ms, "mover": e2e_mover, "gbs_by_mover": e2e_by_mover,
                 "what": "executor path through the C ABI: swap signal (tsw_swap_in), then tsw_translate of every parameter in "
-                        "access order (each waits for its pointer-table row, written by the kernel into host-mapped memory), "
-                        "then tsw_evict; source = the page-locked host store"},
+                        "access order (each waits for its pointer-table row, written on the device into host-mapped memory), "
+                        "then tsw_evict; source = the page-locked host store; measured with the placement kernel alone "
+                        "(mover 0) and with the copy engine carrying the large parameters (mover 2), the faster one reported"},
         "roofline": {"bound": "pcie", "achieved": achieved, "peak": PCIE_GEN5_X16_GBS, "unit": "GB/s",
                      "frac": achieved / PCIE_GEN5_X16_GBS, "peak_kind": "theoretical PCIe Gen5 x16, one direction (no PCIe figure in MEASURED_PEAKS.json)",
                      "kernel": "place_kernel (host store -> pool, zero-copy reads over PCIe)",
@@ -628,6 +652,7 @@ def run_single(args):
         "swap_out_writeback": {"value": B / min(wb) / 1e9, "unit": "GB/s", "ms_per_model": min(wb) * 1e3,
                                "frac_of_pcie": B / min(wb) / 1e9 / PCIE_GEN5_X16_GBS,
                                "what": "tsw_evict(writeback=1): pool -> host store, D2H over PCIe; the reference's swap-out is metadata only"},
+        "copy_engine_assisted": assisted,
         "verified": ver.record(after_timed=True),
         "cpu_baseline": cpu_baseline,
         "gpu_launches": launches_v, "gpu_launches_e2e": launches_e,

@@ -18,6 +18,7 @@
 
 namespace tsw {
 cudaError_t launch_place(const PlaceArgs&, int, cudaStream_t, int) { return cudaErrorNotSupported; }
+cudaError_t launch_publish_rows(const PlaceArgs&, uint32_t, uint32_t, cudaStream_t) { return cudaErrorNotSupported; }
 cudaError_t launch_checksum(const SumDesc*, uint32_t, uint32_t, uint32_t, unsigned long long*, int, cudaStream_t) { return cudaErrorNotSupported; }
 int default_grid_ctas(int) { return 1; }
 }  // namespace tsw

@@ -83,6 +83,24 @@ def test_topology_discovery_feeds_the_scheduler(built):
     s.close()
 
 
+@needs2
+def test_mixed_stream_evicts_and_swaps_across_gpus(built):
+    """The mixed serverless stream at reduced scale over the real GPUs of the box (up to four), with a
+    cap small enough for steady LRU eviction: every request completes, victims are unloaded, swap-ins
+    come from the host store over PCIe and from other GPUs' replicas over NVLink, concurrently."""
+    from torpor_b200 import serving
+    from torpor_b200.memory_manager import discover_topology
+    n = min(gpu_count(), 4)
+    pairs, nv = discover_topology(n)
+    out = serving.run_stream(n_gpus=n, n_models=16, rate=300.0, duration_s=3.0, cap_bytes=300 << 20, seed=4,
+                             archs=("bert_tiny", "llama_tiny", "resnet50"), zero_weights=True,
+                             pcie_pairs=pairs, nvlink=nv)
+    assert out["completed"] == out["requests"] > 600
+    assert out["evictions_in_service"] > 5
+    assert out["swaps_from_host"] > 0 and out["swaps_from_replica"] > 0
+    assert out["swap_ms_p99"] < 2000 and out["sustained_swap_gbs"] > 0.1
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))

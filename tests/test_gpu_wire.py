@@ -106,15 +106,21 @@ def test_launches_run_on_rewritten_addresses(built):
     ex.signal(wire.SIG_LOAD + 1 - 1, "f")           # Load + 1 + src, src = -1: from the host store
     ex.signal(wire.SIG_EXECUTE, "f")
     ex.launched.clear()
-    cl.upload(act, x2)
-    cl.launch("wire_saxpy", [struct.pack("<Q", wp), struct.pack("<Q", act), struct.pack("<Q", act + 2 * MiB),
+    # A later request allocates its activations afresh, as the client's allocator does once its cached
+    # blocks went with the eviction: only the pointer words that named model parameters during the
+    # first run are rewritten at launch (valid_memory_address never answers yes, memory_manager.hpp:293-298),
+    # so a pointer into a cold-start workspace block would still name that block's old place.
+    act2 = cl.malloc(4 * MiB)
+    cl.upload(act2, x2)
+    cl.launch("wire_saxpy", [struct.pack("<Q", wp), struct.pack("<Q", act2), struct.pack("<Q", act2 + 2 * MiB),
                              struct.pack("<Q", n), struct.pack("<f", 4.0)])
-    y = cl.result(act + 2 * MiB, 4 * n)
+    y = cl.result(act2 + 2 * MiB, 4 * n)
     assert np.array_equal(y, np.float32(4.0) * w + x2)
     name, sent = ex.launched[-1]
     new_w = struct.unpack("<Q", sent[0])[0]
     assert name == "wire_saxpy" and new_w == eng.get_cuda_addr("f", wp)
     assert new_w != wp, "the weights came back at their old address: the test did not exercise the rewrite"
+    assert struct.unpack("<Q", sent[1])[0] == act2 and struct.unpack("<Q", sent[2])[0] == act2 + 2 * MiB   # not parameters: as sent
     assert struct.unpack("<Q", sent[3])[0] == n and sent[4] == struct.pack("<f", 4.0)     # scalars untouched
 
     # pointer words inside one argument (a struct of two pointers and a count)
@@ -132,9 +138,10 @@ def test_launches_run_on_rewritten_addresses(built):
     ex.signal(wire.SIG_LOAD + 1 - 1, "g")            # g first, so that h finds its old blocks taken
     ex.signal(wire.SIG_LOAD + 1 - 1, "h")
     ex.signal(wire.SIG_EXECUTE, "h")
-    cl.launch("wire_scale_pair", pair())
-    assert np.array_equal(cl.result(act_h, 4 * n), np.float32(0.5) * w)
+    out_h = cl.malloc(2 * MiB)
+    cl.launch("wire_scale_pair", [struct.pack("<QQQ", wp_h, out_h, n), struct.pack("<f", 0.25)])
+    assert np.array_equal(cl.result(out_h, 4 * n), np.float32(0.25) * w)
     words = struct.unpack("<QQQ", ex.launched[-1][1][0])
-    assert words[0] == eng.get_cuda_addr("h", wp_h) and words[2] == n
+    assert words[0] == eng.get_cuda_addr("h", wp_h) and words[1] == out_h and words[2] == n
     eng.close()
     repo_reset()
