@@ -216,6 +216,12 @@ inline cudaError_t cudaDeviceEnablePeerAccess(int, unsigned int) { return cudaSu
 // message classes (stand-ins generated from the reference's .proto files by gen_pb_shim.py),
 // cuDNN / cuBLAS names, and the rest of the CUDA calls its services make.  Only the memory
 // services and the kernel launch are exercised; everything else merely has to compile.
+#ifndef TORPOR_REF_FAKE_CUDA
+// the executor against the real runtime (tests/executor_gpu_probe.cpp): its driver-API services need
+// <cuda.h>, and its logger prints a cudaMemcpyKind
+#include <cuda.h>
+inline int format_as(cudaMemcpyKind k) { return (int)k; }
+#endif
 #include "cudarpc.pb.h"
 #include "signal.pb.h"
 #include "cudarpc.using.h"

@@ -141,6 +141,7 @@ def _rank_main(rank, world, port, shm, out_dir):
     launches = eng.stats()["kernel_launches"]
     np.save(os.path.join(out_dir, f"r{rank}.npy"), np.array([int(ok), launches]))
     dist.barrier()
+    sw.close()
     eng.close()
     dist.destroy_process_group()
 
@@ -195,6 +196,7 @@ def _rank_losing_helper(rank, world, port, shm, out_dir):
     eng.swap_in("m"); eng.wait_ready("m")           # and the engine's ordinary path is intact afterwards
     ok = ok and np.array_equal(eng.checksum_resident("m"), sums)
     np.save(os.path.join(out_dir, "r0.npy"), np.array([int(ok)]))
+    sw.close()
     eng.close()
     os._exit(0)
 

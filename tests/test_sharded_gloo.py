@@ -61,6 +61,7 @@ def _worker(rank, world, port, out_dir):
         repo_reset()
     np.save(os.path.join(out_dir, f"r{rank}.npy"), np.array([res], dtype=object), allow_pickle=True)
     dist.barrier()
+    sw.close()
     dist.destroy_process_group()
 
 
@@ -144,6 +145,8 @@ def _worker_losing_a_helper(rank, world, port, out_dir):
     res["alone_after"], res["reason"] = sw.alone, sw.lost_reason
     eng.swap_in("m"); eng.wait_ready("m")
     res["plain"] = eng.dump_params("m", canonical=True).tolist()
+    res["board_said_gone"] = not sw.board.still_at_work(1, sw.seq)      # the helper's process is gone: nothing to wait for
+    sw.close()
     eng.close()
     repo_reset()
     np.save(os.path.join(out_dir, "r0.npy"), np.array([res], dtype=object), allow_pickle=True)
@@ -165,6 +168,7 @@ def test_target_carries_on_alone_when_its_helper_goes_away(built, tmp_path):
         assert p.exitcode == 0
     res = np.load(os.path.join(str(tmp_path), "r0.npy"), allow_pickle=True)[0]
     assert res["alone_before"] is False and res["alone_after"] is True and res["reason"]
+    assert res["board_said_gone"] is True
     for mine, total in res["tiles"]:
         assert mine == total > 161                                       # the target took every tile
     assert all(res["alloc"])

@@ -102,6 +102,57 @@ class AddressMap:
         return int(self.rebase(np.array([addr], dtype=np.uint64))[0]) if addr else 0
 
 
+class ProgressBoard:
+    """A few words of POSIX shared memory beside the control plane: every rank's process id and the
+    number of the last swap whose share it has finished (its kernel drained).  When a control message
+    fails in the middle of a swap, the target reads here whether a helper is gone or is still moving
+    tiles into the pool -- instead of guessing by the clock -- before it takes the swap over."""
+
+    def __init__(self, name: str, world: int, rank: int, create: bool):
+        import mmap
+        self.path = "/dev/shm/" + name.lstrip("/")
+        self.world, self.rank = world, rank
+        size = 16 * world
+        fd = os.open(self.path, os.O_RDWR | (os.O_CREAT if create else 0), 0o600)
+        try:
+            if create:
+                os.ftruncate(fd, size)
+            self.mm = mmap.mmap(fd, size)
+        finally:
+            os.close(fd)
+        self.words = np.frombuffer(self.mm, dtype=np.int64)      # [pid_0, done_0, pid_1, done_1, ...]
+        self.words[2 * rank] = os.getpid()
+        self.words[2 * rank + 1] = 0
+        self.owner = create
+
+    def finished(self, seq: int):
+        self.words[2 * self.rank + 1] = seq
+
+    def still_at_work(self, rank: int, seq: int) -> bool:
+        """True while ``rank`` is a live process that has not finished swap ``seq``."""
+        pid, done = int(self.words[2 * rank]), int(self.words[2 * rank + 1])
+        if done >= seq or pid <= 0:
+            return False
+        try:
+            with open(f"/proc/{pid}/stat") as f:
+                state = f.read().rsplit(")", 1)[1].split()[0]
+            return state not in ("Z", "X")                       # exited and not yet reaped counts as gone
+        except OSError:
+            return False
+
+    def close(self):
+        self.words = None
+        try:
+            self.mm.close()
+        except BufferError:
+            pass
+        if self.owner:
+            try:
+                os.unlink(self.path)
+            except OSError:
+                pass
+
+
 class ShardedSwap:
     """Collective swap-in over the ranks of ``group`` (a gloo process group for control).
 
@@ -136,7 +187,9 @@ class ShardedSwap:
         # or the group's timeout ran out) the target stops asking and from then on swaps by itself.
         self.alone = world == 1
         self.lost_reason = ""
-        self.settle_s = 2.0         # how long the target waits for helpers still at work before it takes over
+        self.settle_s = 10.0        # upper bound on the target's wait for helpers that are alive and still at work
+        self.board: Optional[ProgressBoard] = None
+        self.seq = 0                # swaps begun; the same on every rank
 
     # ---- control plane
     def _collective(self, fn, mine):
@@ -181,6 +234,14 @@ class ShardedSwap:
         """Map the target's host store into every rank (once)."""
         info = self.engine.arena_info() if (self.rank == 0 and self.engine) else None
         info = self._bcast_obj(info)
+        # the progress board: made by the target, opened by everyone
+        name = None
+        if self.rank == 0:
+            name = f"torpor_swap_board_{os.getpid()}_{id(self) & 0xffffff:x}"
+            self.board = ProgressBoard(name, self.world, 0, create=True)
+        name = self._bcast_obj(name)
+        if self.rank != 0 and name:
+            self.board = ProgressBoard(name, self.world, self.rank, create=False)
         if self.dry:
             self.arena_entry = None
             return
@@ -251,6 +312,7 @@ class ShardedSwap:
         """Collective swap-in of ``func`` into the target's pool.  Returns timing of this rank's
         kernel and the maximum over ranks (device time, CUDA events)."""
         t0 = time.perf_counter()
+        self.seq += 1
         segs, tile, pubw = self.plan(func, 0 if mode == "direct" else 1)
         n_tiles = int(tiles_of(segs, tile)[-1]) if len(segs) else 0
         dev_ns = 0.0
@@ -280,6 +342,8 @@ class ShardedSwap:
                 if hi > lo:
                     self.engine.place_segment_array(local, tile, lo, 1, hi, pub, sync=True)
             dev_ns = float(self.engine.stats()["last_swap_device_ns"])
+        if self.board is not None:
+            self.board.finished(self.seq)       # this rank's kernel has drained (the launches above are synchronous)
         t_done = time.perf_counter()
         was_alone = self.alone
         dev_max = self._max_over_ranks(dev_ns)          # doubles as the completion barrier
@@ -290,20 +354,24 @@ class ShardedSwap:
         return self.last
 
     def _commit(self, func: str, lost_now: bool):
-        """Take the published rows over.  If the helpers were lost during this very swap, those still alive
-        may be finishing their tiles: give them ``settle_s``, then move what is missing alone."""
+        """Take the published rows over.  If the control plane was lost during this very swap, helpers
+        that are still alive may be moving tiles into the pool: the progress board says who has
+        finished and who is gone, and the target waits for the rest (at most ``settle_s``) before it
+        moves what is missing alone -- nobody may still be storing into blocks that the take-over,
+        or a later eviction, hands to someone else."""
         from ._cabi import SwapError
-        deadline = time.perf_counter() + (self.settle_s if lost_now else 0.0)
-        while True:
-            try:
-                self.engine.swap_commit(func)
-                return
-            except SwapError:
-                if not lost_now:
-                    raise
-                if time.perf_counter() >= deadline:
+        if lost_now:
+            deadline = time.perf_counter() + self.settle_s
+            while time.perf_counter() < deadline:
+                if self.board is None or not any(self.board.still_at_work(r, self.seq) for r in range(1, self.world)):
                     break
-                time.sleep(0.01)
+                time.sleep(0.005)
+        try:
+            self.engine.swap_commit(func)
+            return
+        except SwapError:
+            if not lost_now:
+                raise
         self.engine.swap_in(func)           # clears the abandoned tile counters, moves the unfinished parameters
         self.engine.wait_ready(func)
 
@@ -326,6 +394,11 @@ class ShardedSwap:
     def evict(self, func: str):
         if self.rank == 0 and self.engine is not None:
             self.engine.evict(func)
+
+    def close(self):
+        if self.board is not None:
+            self.board.close()
+            self.board = None
 
 
 # ------------------------------------------------------------------ benchmark driver (torchrun)
@@ -656,6 +729,7 @@ def bench_main(args, bench):
         if sweep is not None:
             line["sweep"] = sweep
     dist.barrier(group=ctrl)
+    sw.close()
     eng.close()
     repo_reset()
     dist.destroy_process_group()
