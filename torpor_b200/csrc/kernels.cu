@@ -427,7 +427,7 @@ __global__ void __launch_bounds__(kThreads) checksum_kernel(const SumDesc* descs
 int default_grid_ctas(int device) {
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    // 60 registers x 256 threads keep 4 CTAs resident per SM; six per SM in the grid (two queued
+    // 58 registers x 256 threads keep 4 CTAs resident per SM; six per SM in the grid (two queued
     // behind the resident four) measured best for HBM-to-HBM moves: fewer concurrent streams keep
     // DRAM rows open, the queued CTAs fill the tail.  Forcing 5 or 6 resident CTAs per SM with a
     // register bound was 8-25 % slower.  PCIe-bound moves do not depend on the grid.
