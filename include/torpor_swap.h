@@ -268,6 +268,15 @@ int tsw_pointer_info(tsw_engine* e, uint64_t addr, int* type, int* device, uint6
 int tsw_arena_info(tsw_engine* e, uint64_t* host_base, uint64_t* dev_base, uint64_t* size, uint64_t* used);
 int tsw_arena_attach(tsw_engine* e, const char* shm_name, uint64_t size, uint64_t* dev_base);
 
+/* tsw_place_segments in two pipelined steps, for a helper whose link the copy engine reads faster than
+ * the SMs do: each chunk of `chunk_tiles` tiles (0 = 64 MiB worth) of the range [tile_first, tile_end) is
+ * brought from its host source into this engine's GPU by cudaMemcpyAsync on a second stream, then stored
+ * to its destination and counted by the placement kernel while the next chunk is being fetched.  Tiles
+ * are dealt by range, not drawn (pub->ticket is ignored).  The engine keeps a staging area of the size
+ * of the largest range it was given.  No counterpart in the reference. */
+int tsw_place_segments_pipelined(tsw_engine* e, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
+                                 uint32_t tile_end, const tsw_publish* pub, uint32_t chunk_tiles, int sync);
+
 /* tsw_place_segments for callers that must not allocate.  No counterpart in the reference.
  *
  * Meant for code on the steady-state swap path of a GPU-sharing server -- an executor that

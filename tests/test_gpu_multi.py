@@ -130,7 +130,8 @@ def _rank_main(rank, world, port, shm, out_dir):
     ok = True
     sums = np.array([checksum_host(W.tensor_bytes(ws, i)) for i in range(len(ws.tensors))]) if rank == 0 else None
     tables = []
-    for mode in ("direct", "staged", "direct", "staged"):
+    sw.chunk_tiles = 3                      # pipelined mode: several copy-engine chunks even for this small set
+    for mode in ("direct", "staged", "pipelined", "direct", "pipelined", "staged"):
         sw.swap_in("m", mode)
         if rank == 0:
             ok = ok and np.array_equal(eng.checksum_resident("m"), sums)

@@ -587,6 +587,62 @@ def test_copy_engine_assisted_mover_is_bit_exact(fresh, oracle_backend):
     oracle_backend.reset()
 
 
+def test_pipelined_mover_is_bit_exact(fresh):
+    """tsw_place_segments_pipelined: copy engine host -> this GPU's staging area, chunk by chunk, and the
+    placement kernel staging -> destination behind it.  Ragged segments, odd alignments, a tile range
+    that starts and ends inside segments, chunks smaller than a segment and chunks spanning several:
+    the bytes inside the range arrive, nothing outside it is touched, and rows complete when the
+    remaining tiles are moved by the ordinary entry point."""
+    import torch
+    rng = np.random.default_rng(31)
+    sizes = [int(x) for x in rng.choice([1, 7, 16, 100, 4096, 65536, 65537, 300000, 1 << 20, 3 << 20], size=60)]
+    span = [((s + 15) // 16) * 16 + 64 for s in sizes]
+    offs = np.concatenate([[0], np.cumsum(span)]).astype(np.int64)
+    total = int(offs[-1]) + 64
+    host = torch.from_numpy(rng.integers(0, 256, size=total, dtype=np.uint8)).pin_memory()
+    shift = [int(x) for x in rng.integers(0, 16, size=len(sizes))]
+    s_off = [int(offs[i]) + 16 + shift[i] for i in range(len(sizes))]
+    d_off = [int(offs[i]) + 32 + shift[i] for i in range(len(sizes))]
+    tile = 64 * 1024
+    n_tiles = sum((s + tile - 1) // tile for s in sizes)
+    eng = MemoryManager(0, device=0)
+    inp = host.numpy()
+    from torpor_b200.memory_manager import make_segments
+    for lo, hi, chunk in ((0, 0, 5), (7, n_tiles - 9, 3), (n_tiles // 3, 2 * n_tiles // 3, 64)):
+        hi_eff = hi if hi else n_tiles
+        dst = torch.full((total,), 0xA5, dtype=torch.uint8, device="cuda")
+        done = torch.zeros(len(sizes), dtype=torch.int32, device="cuda")
+        t_phys = torch.zeros(len(sizes), dtype=torch.int64, device="cuda")
+        t_flag = torch.zeros(len(sizes), dtype=torch.int32, device="cuda")
+        pub = _cabi.Publish(done.data_ptr(), t_phys.data_ptr(), t_flag.data_ptr(), 0, 0, _cabi.READY_CUDA, 0)
+        segs = make_segments([host.data_ptr() + o for o in s_off], [dst.data_ptr() + o for o in d_off], sizes, list(range(len(sizes))))
+        torch.cuda.synchronize()
+        eng.place_segment_array_pipelined(segs, tile, lo, hi, pub, chunk_tiles=chunk, sync=True)
+        got = dst.cpu().numpy()
+        want = np.full(total, 0xA5, dtype=np.uint8)
+        t = 0
+        for so, do, n in zip(s_off, d_off, sizes):
+            for k in range((n + tile - 1) // tile):
+                if lo <= t < hi_eff:
+                    a, b = k * tile, min(n, (k + 1) * tile)
+                    want[do + a:do + b] = inp[so + a:so + b]
+                t += 1
+        assert np.array_equal(got, want), (lo, hi, chunk)
+        # the rest of the tiles through the ordinary entry point: now every row completes and is published
+        if lo > 0:
+            eng.place_segment_array(segs, tile, 0, 1, lo, pub, sync=True)
+        if hi_eff < n_tiles:
+            eng.place_segment_array(segs, tile, hi_eff, 1, 0, pub, sync=True)
+        full = np.full(total, 0xA5, dtype=np.uint8)
+        for so, do, n in zip(s_off, d_off, sizes):
+            full[do:do + n] = inp[so:so + n]
+        assert np.array_equal(dst.cpu().numpy(), full)
+        assert (t_flag.cpu().numpy() == _cabi.READY_CUDA).all() and (done.cpu().numpy() == 0).all()
+        assert np.array_equal((t_phys - dst.data_ptr()).cpu().numpy(), np.array(d_off))
+    assert eng.stats()["kernel_launches"] > 10
+    eng.close()
+
+
 def test_topology_discovery_on_this_box(fresh):
     """tsw_topology_discover on however many GPUs the box has (one is enough): a PCIe uplink group
     per GPU, a link class per ordered pair, nothing on the diagonal -- and tables the scheduler and

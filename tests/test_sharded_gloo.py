@@ -41,7 +41,7 @@ def _worker(rank, world, port, out_dir):
     sw.attach_arena()
     sw.share_regions()
     res = {}
-    for mode in ("direct", "staged"):
+    for mode in ("direct", "staged", "pipelined"):
         r = sw.swap_in("m", mode)
         segs, tile = sw.last_plan
         first = sharded.tiles_of(segs, tile)
@@ -71,7 +71,7 @@ def test_two_ranks_cover_every_tile_once_and_commit_the_reference_table(built, t
     port = _free_port()
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     res = [np.load(os.path.join(str(tmp_path), f"r{r}.npy"), allow_pickle=True)[0] for r in range(world)]
-    for mode in ("direct", "staged"):
+    for mode in ("direct", "staged", "pipelined"):
         a, b = res[0][mode], res[1][mode]
         assert a["n_segs"] == b["n_segs"] == 161 and a["n_tiles"] == b["n_tiles"] > 161
         assert a["rows"] == b["rows"] and a["dst"] == b["dst"]        # every rank got the same moves

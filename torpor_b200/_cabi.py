@@ -122,6 +122,7 @@ SIGNATURES = {
     "tsw_pointer_info": (_i32, [_vp, _u64, C.POINTER(C.c_int), C.POINTER(C.c_int), _pu64, _pu64]),
     "tsw_arena_info": (_i32, [_vp, _pu64, _pu64, _pu64, _pu64]),
     "tsw_arena_attach": (_i32, [_vp, _cp, _u64, _pu64]),
+    "tsw_place_segments_pipelined": (_i32, [_vp, _vp, _i32, C.c_uint32, C.c_uint32, C.c_uint32, _vp, C.c_uint32, _i32]),
     "tsw_place_segments_static": (_i32, [_i32, _vp, _i32, C.c_uint32, C.c_uint32, C.c_uint32, _vp, _vp]),
     "tsw_place_segments_static_status": (_i32, [_i32, _vp, C.POINTER(C.c_uint32), _i32]),
     "tsw_stats": (_i32, [_vp, _pu64, _pu64, _pu64]),

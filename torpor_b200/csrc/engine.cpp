@@ -384,6 +384,21 @@ int ensure_peer(tsw_engine* e, int to_device) {
     return TSW_OK;
 }
 
+// The second transfer stream (copy-engine moves) and the event that joins it to the first; made on first use.
+int ensure_ce_stream(tsw_engine* e) {
+    if (e->stream_ce) return TSW_OK;
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    cudaStream_t s2;
+    cudaEvent_t ev;
+    int lo_prio = 0, hi_prio = 0;
+    TSW_CUDA(cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio));
+    TSW_CUDA(cudaStreamCreateWithPriority(&s2, cudaStreamNonBlocking, hi_prio));
+    TSW_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    e->stream_ce = s2;
+    e->ev_ce = ev;
+    return TSW_OK;
+}
+
 uint32_t pick_tile(tsw_engine* e, bool host_side) { return host_side ? e->tile_host : e->tile_dev; }
 
 // The bulk-copy mover needs 16-byte aligned ends; anything else goes to the load/store kernel.
@@ -707,6 +722,7 @@ int tsw_engine_destroy(tsw_engine* e) {
             cudaStreamDestroy((cudaStream_t)e->stream_ce);
         }
         if (e->ev_ce) cudaEventDestroy((cudaEvent_t)e->ev_ce);
+        if (e->stage_buf) cudaFree(e->stage_buf);
         if (e->stream) cudaStreamDestroy((cudaStream_t)e->stream);
         // The host model store outlives the engine only as long as the repository
         // refers to it; callers reset the repository before destroying engines.

@@ -65,6 +65,8 @@ struct tsw_engine {
     void* stream = nullptr;       // transfer stream (cudaStream_t), high priority
     void* stream_ce = nullptr;    // second transfer stream, made on first use: copy-engine moves of mover 2
     void* ev_ce = nullptr;        // joins stream_ce back into the transfer stream
+    void* stage_buf = nullptr;    // tsw_place_segments_pipelined: this GPU's share of a swap while it is on its way
+    uint64_t stage_cap = 0;
     void* ev_start = nullptr;     // cudaEvent_t pair around the last swap
     void* ev_stop = nullptr;
     bool ev_valid = false;

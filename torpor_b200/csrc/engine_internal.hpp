@@ -57,6 +57,7 @@ int make_arena(tsw_engine* e);
 tsw_engine* engine_of_block_mirror(const uint8_t* p);
 int place_blocks(tsw_engine* e, Model* m, Placement& pl);
 int ensure_peer(tsw_engine* e, int to_device);
+int ensure_ce_stream(tsw_engine* e);
 uint32_t pick_tile(tsw_engine* e, bool host_side);
 int pick_mover(const tsw_engine* e, const std::vector<PlaceDesc>& descs);
 

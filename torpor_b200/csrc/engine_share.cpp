@@ -403,6 +403,116 @@ int tsw_place_segments(tsw_engine* e, const tsw_segment* segs, int n, uint32_t t
     return TSW_OK;
 }
 
+// The same tiles moved in two pipelined steps: the copy engine brings each chunk of the tile range
+// from its (host) source into this GPU's memory, and the placement kernel stores the chunk to its
+// destination -- another GPU's pool across NVLink, as a rule -- and counts its tiles, while the copy
+// engine is already fetching the next chunk.  For a helper whose link the copy engine reads faster
+// than the SMs do; the peer stores stay with the kernel, which also publishes completed rows.
+int tsw_place_segments_pipelined(tsw_engine* e, const tsw_segment* segs, int n, uint32_t tile_bytes, uint32_t tile_first,
+                                 uint32_t tile_end, const tsw_publish* pub, uint32_t chunk_tiles, int sync) {
+    if (!e || (n > 0 && !segs) || n < 0) return fail(TSW_ERR_INVALID, "bad segment list");
+    if (e->plan) return fail(TSW_ERR_NO_DEVICE, "plan-only engine moves no bytes");
+    if (n == 0) return TSW_OK;
+    if (tile_bytes == 0) tile_bytes = e->tile_dev;
+    if (tile_bytes & 15u) return fail(TSW_ERR_INVALID, "tile size must be a multiple of 16");
+    if (chunk_tiles == 0) chunk_tiles = std::max<uint32_t>(1u, (64u << 20) / tile_bytes);
+    Lock g2(e->mu);
+    Plan plan;
+    plan.descs.resize(n);
+    memcpy(plan.descs.data(), segs, sizeof(PlaceDesc) * n);
+    finish_plan(plan, tile_bytes);
+    const uint32_t lo = tile_first;
+    const uint32_t hi = (tile_end != 0 && tile_end < plan.first.back()) ? tile_end : plan.first.back();
+    if (hi <= lo) return TSW_OK;
+    TSW_CUDA(cudaSetDevice(e->cfg.device));
+    int rc = ensure_ce_stream(e);
+    if (rc != TSW_OK) return rc;
+    cudaStream_t s = (cudaStream_t)e->stream, s2 = (cudaStream_t)e->stream_ce;
+    TSW_CUDA(cudaStreamSynchronize(s));     // scratch, staging and the previous call's kernels
+    TSW_CUDA(cudaStreamSynchronize(s2));
+    // this call's share, resident in this GPU's memory while it is on its way: tile t at (t - lo) * tile_bytes
+    const uint64_t share = (uint64_t)(hi - lo) * tile_bytes;
+    if (e->stage_cap < share) {
+        if (e->stage_buf) cudaFree(e->stage_buf);
+        e->stage_buf = nullptr;
+        e->stage_cap = 0;
+        const uint64_t cap = (share + (256ull << 20) - 1) / (256ull << 20) * (256ull << 20);
+        TSW_CUDA(cudaMalloc(&e->stage_buf, cap));
+        e->stage_cap = cap;
+    }
+    const uint64_t need_d = sizeof(PlaceDesc) * (uint64_t)n, need_f = sizeof(uint32_t) * ((uint64_t)n + 1);
+    if (e->raw_cap < (uint64_t)n) {
+        if (e->raw_d_descs) cudaFree(e->raw_d_descs);
+        if (e->raw_d_first) cudaFree(e->raw_d_first);
+        if (e->raw_h) cudaFreeHost(e->raw_h);
+        e->raw_d_descs = e->raw_d_first = e->raw_h = nullptr;
+        e->raw_cap = 0;
+        const uint64_t cap = std::max<uint64_t>((uint64_t)n, 1024);
+        TSW_CUDA(cudaMalloc(&e->raw_d_descs, sizeof(PlaceDesc) * cap));
+        TSW_CUDA(cudaMalloc(&e->raw_d_first, sizeof(uint32_t) * (cap + 1)));
+        TSW_CUDA(cudaHostAlloc(&e->raw_h, sizeof(PlaceDesc) * cap + sizeof(uint32_t) * (cap + 1), cudaHostAllocDefault));
+        e->raw_cap = cap;
+    }
+    // the kernel's table: every segment reads from where its bytes will sit in the staging area
+    const uint64_t stage = (uint64_t)e->stage_buf;
+    std::vector<uint64_t> host_src(n);
+    for (int i = 0; i < n; ++i) {
+        host_src[i] = plan.descs[i].src;
+        plan.descs[i].src = stage + ((uint64_t)plan.first[i] - (uint64_t)lo) * tile_bytes;   // modulo 2^64 below `lo`: never touched there
+    }
+    uint8_t* hs = (uint8_t*)e->raw_h;
+    memcpy(hs, plan.descs.data(), need_d);
+    memcpy(hs + sizeof(PlaceDesc) * e->raw_cap, plan.first.data(), need_f);
+    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_start, s));
+    TSW_CUDA(cudaMemcpyAsync(e->raw_d_descs, hs, need_d, cudaMemcpyHostToDevice, s));
+    TSW_CUDA(cudaMemcpyAsync(e->raw_d_first, hs + sizeof(PlaceDesc) * e->raw_cap, need_f, cudaMemcpyHostToDevice, s));
+    PlaceArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = (const PlaceDesc*)e->raw_d_descs;
+    a.first_tile = (const uint32_t*)e->raw_d_first;
+    a.n_descs = (uint32_t)n;
+    a.tile_bytes = tile_bytes;
+    a.tile_stride = 1;
+    a.system_scope = 1;
+    a.status = e->d_status;
+    if (pub) {
+        a.done_count = (uint32_t*)pub->done_count;
+        a.table_phys = (uint64_t*)pub->table_phys;
+        a.table_flag = (uint32_t*)pub->table_flag;
+        a.host_phys = (uint64_t*)pub->host_phys;
+        a.host_flag = (uint32_t*)pub->host_flag;
+        a.flag_value = pub->flag_value;
+        a.host_flag_value = pub->flag_value;
+        if (a.done_count && (!a.table_phys || !a.table_flag)) return fail(TSW_ERR_INVALID, "publish block needs both table columns");
+    }
+    int seg = 0;    // first segment that reaches into the current chunk
+    for (uint32_t t0 = lo; t0 < hi; t0 += chunk_tiles) {
+        const uint32_t t1 = (hi - t0 > chunk_tiles) ? t0 + chunk_tiles : hi;
+        while (seg < n && plan.first[seg + 1] <= t0) ++seg;
+        for (int i = seg; i < n && plan.first[i] < t1; ++i) {
+            const uint64_t a0 = std::max<uint64_t>(t0, plan.first[i]), a1 = std::min<uint64_t>(t1, plan.first[i + 1]);
+            if (a1 <= a0) continue;
+            const uint64_t off0 = (a0 - plan.first[i]) * tile_bytes;
+            const uint64_t off1 = std::min<uint64_t>((a1 - plan.first[i]) * tile_bytes, plan.descs[i].bytes);
+            if (off1 <= off0) continue;
+            TSW_CUDA(cudaMemcpyAsync((void*)(plan.descs[i].src + off0), (const void*)(host_src[i] + off0), off1 - off0,
+                                     cudaMemcpyDefault, s2));
+        }
+        TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_ce, s2));
+        TSW_CUDA(cudaStreamWaitEvent(s, (cudaEvent_t)e->ev_ce, 0));
+        a.tile_lo = t0;
+        a.tile_hi = t1;
+        cudaError_t le = launch_place(a, e->grid_ctas, s, 0);
+        if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
+        e->kernel_launches++;
+    }
+    TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_stop, s));
+    e->ev_valid = true;
+    e->bytes_moved += (uint64_t)((double)plan.bytes * (double)(hi - lo) / (double)plan.first.back());
+    if (sync) TSW_CUDA(cudaStreamSynchronize(s));
+    return TSW_OK;
+}
+
 int tsw_stats(tsw_engine* e, uint64_t* kernel_launches, uint64_t* bytes_moved, uint64_t* last_swap_device_ns) {
     if (!e) return fail(TSW_ERR_INVALID, "null argument");
     if (kernel_launches) *kernel_launches = e->kernel_launches.load();

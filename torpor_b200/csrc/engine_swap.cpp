@@ -264,16 +264,8 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
         // the rate.  So the large parameters go through the copy engine, in access order, on a second
         // stream, each followed by the publish step for its row; the kernel moves the small
         // parameters (and skips the large ones) at the same time on the transfer stream.
-        if (!e->stream_ce) {
-            cudaStream_t s2;
-            cudaEvent_t ev;
-            int lo_prio = 0, hi_prio = 0;
-            TSW_CUDA(cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio));
-            TSW_CUDA(cudaStreamCreateWithPriority(&s2, cudaStreamNonBlocking, hi_prio));
-            TSW_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
-            e->stream_ce = s2;
-            e->ev_ce = ev;
-        }
+        rc = ensure_ce_stream(e);
+        if (rc != TSW_OK) return rc;
         cudaStream_t s2 = (cudaStream_t)e->stream_ce;
         TSW_CUDA(cudaEventRecord((cudaEvent_t)e->ev_ce, s));       // the descriptor upload precedes the publish kernels
         TSW_CUDA(cudaStreamWaitEvent(s2, (cudaEvent_t)e->ev_ce, 0));

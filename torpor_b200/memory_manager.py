@@ -232,6 +232,15 @@ class MemoryManager:
                                         tile_end, C.byref(publish) if publish is not None else None,
                                         1 if sync else 0))
 
+    def place_segment_array_pipelined(self, segs: np.ndarray, tile_bytes: int, tile_first: int, tile_end: int,
+                                      publish: Optional[_cabi.Publish] = None, chunk_tiles: int = 0, sync: bool = True) -> None:
+        """Tiles [tile_first, tile_end) of ``segs`` in two pipelined steps: copy engine host -> this GPU,
+        placement kernel this GPU -> destination (``tsw_place_segments_pipelined``)."""
+        segs = np.ascontiguousarray(segs, dtype=SEGMENT_DTYPE)
+        check(self.L.tsw_place_segments_pipelined(self.h, segs.ctypes.data, len(segs), tile_bytes, tile_first, tile_end,
+                                                  C.byref(publish) if publish is not None else None, chunk_tiles,
+                                                  1 if sync else 0))
+
     # ---- one process per GPU: plan here, move elsewhere, commit here
     def swap_plan(self, func: str):
         """Place and rebind like ``sig_trans_thread`` but return the moves instead of running

@@ -11,11 +11,16 @@ so whichever GPU finishes a parameter publishes it; the target then commits the 
 carries only the few KB of control messages.  (An NCCL send/recv gather was measured beside the peer
 stores and is slower; ``bench.py --nccl-gather`` repeats the measurement.)
 
-Two ways of dealing out the tiles:
-  direct  tile t goes to rank t mod N; host store -> target pool in one kernel per rank.
-  staged  rank r owns the contiguous tile range r; its share is first pulled into local HBM
-          (``prepare``), and the timed move is local HBM -> target pool across NVLink -- the
-          gather stage on its own.
+Three ways of dealing out the tiles:
+  direct     every rank's CTAs draw tiles from one counter on the target (or, statically, tile t goes
+             to rank t mod N); host store -> target pool in one kernel per rank.
+  pipelined  rank r owns the contiguous tile range r; its copy engine brings the range into local HBM
+             chunk by chunk while the placement kernel stores the chunks already there into the
+             target's pool across NVLink (``tsw_place_segments_pipelined``): for boxes whose links are
+             fed evenly, where the copy engine reads host memory a few per cent faster than the SMs.
+  staged     rank r owns the contiguous tile range r; its share is first pulled into local HBM
+             (``prepare``), and the timed move is local HBM -> target pool across NVLink -- the
+             gather stage on its own.
 
 The reference has no counterpart (its swap uses one GPU's link, memory_manager.hpp:331-438);
 the result must equal that single-GPU swap-in, which the tests check.
@@ -179,6 +184,7 @@ class ShardedSwap:
         self.dry = engine is None or engine.device < 0
         self.dynamic = True         # direct mode: draw tiles from a shared counter instead of t mod N
         self.staged_tile = 512 * 1024
+        self.chunk_tiles = 128      # pipelined mode: tiles per copy-engine chunk (64 MiB)
         # the target's overrides of the engine's host-side tile size and of the tiles taken per draw
         # from the shared counter, for one swap to the next (measurement sweeps); 0 = the engine's own
         self.tile_override = 0
@@ -316,6 +322,8 @@ class ShardedSwap:
         segs, tile, pubw = self.plan(func, 0 if mode == "direct" else 1)
         n_tiles = int(tiles_of(segs, tile)[-1]) if len(segs) else 0
         dev_ns = 0.0
+        if mode not in ("direct", "pipelined", "staged"):
+            raise ValueError(f"unknown dealing mode {mode!r}")
         if mode == "direct":
             self.my_tiles = range(self.rank, n_tiles, self.world)
         else:
@@ -334,6 +342,10 @@ class ShardedSwap:
                 self.engine.place_segment_array(local, tile, 0, 1, 0, pub, sync=True)
             elif mode == "direct":
                 self.engine.place_segment_array(local, tile, self.rank, self.world, 0, pub, sync=True)
+            elif mode == "pipelined":
+                lo, hi = contiguous_share(n_tiles, self.rank, self.world)
+                if hi > lo:
+                    self.engine.place_segment_array_pipelined(local, tile, lo, hi, pub, self.chunk_tiles, sync=True)
             else:
                 lo, hi = contiguous_share(n_tiles, self.rank, self.world)
                 buf = self._staging(func, segs, tile, lo, hi)
@@ -552,7 +564,7 @@ def bench_main(args, bench):
     cold_s = 0.0
     if rank == 0:
         sweep_swaps = 40 if args.sweep else 0
-        tables = W.plan_tables(ws, "model", budget=budget, gpu_count=world, swaps=4 + 2 * (Wm + K) + (Wm + K_g) + sweep_swaps + 8)
+        tables = W.plan_tables(ws, "model", budget=budget, gpu_count=world, swaps=4 + 3 * (Wm + K) + (Wm + K_g) + sweep_swaps + 8)
         repo_reset()
         eng = MemoryManager(budget, device=local_rank, server_id=0, gpu_count=world, host_arena_bytes=W.host_store_bytes(ws),
                             host_arena_shm=shm, tile_bytes_host=tile_host, ticket_chunk=args.ticket_chunk, host_store_mode=args.host_store)
@@ -628,6 +640,8 @@ def bench_main(args, bench):
     wall_v, dev_v, launches_v = timed("direct", K, Wm, where="after the timed sharded swap-ins")
     wall_e, dev_e, launches_e = timed("direct", K, Wm, through_translate=True, where="after the timed executor-path swap-ins")
     wall_g, dev_g, _ = timed("staged", K_g, Wm, where="after the timed gathers")
+    # the executor path once more with the copy engines pulling (contiguous shares, pipelined with the peer stores)
+    wall_p, dev_p, launches_p = timed("pipelined", K, Wm, through_translate=True, where="after the timed pipelined swap-ins")
     clocks = sampler.stop() if rank == 0 else None
 
     sweep = None
@@ -675,13 +689,18 @@ def bench_main(args, bench):
     dist.all_reduce(rates, group=ctrl)
     del x, y
 
-    total_launches = torch.tensor([launches_v, launches_e], dtype=torch.int64)
+    total_launches = torch.tensor([launches_v, launches_e, launches_p], dtype=torch.int64)
     dist.all_reduce(total_launches, group=ctrl)
 
     line = None
     if rank == 0:
         value = B * K / wall_v / 1e9
         e2e = B * K / wall_e / 1e9
+        e2e_ms, e2e_dev_ms, e2e_dealing = wall_e / K * 1e3, statistics.mean(dev_e) / 1e6, "direct"
+        piped = B * K / wall_p / 1e9
+        e2e_by_dealing = {"direct": e2e, "pipelined": piped}
+        if piped > e2e:         # what a deployment on this box would configure: the faster of the two, as measured here
+            e2e, e2e_ms, e2e_dev_ms, e2e_dealing = piped, wall_p / K * 1e3, statistics.mean(dev_p) / 1e6, "pipelined"
         kern_v = statistics.mean(dev_v) / 1e9
         kern_g = statistics.mean(dev_g) / 1e9
         inbound = B * (world - 1) / world
@@ -695,11 +714,13 @@ def bench_main(args, bench):
             "value_arm": "sharded swap-in from the shared page-locked host store: every rank's GPU reads tiles over its own PCIe "
                          "link and stores them into the target's pool over NVLink; plan, control messages, commit and evict "
                          "inside the timed region, max over ranks",
-            "e2e": {"value": e2e, "unit": "GB/s", "ms_per_model": wall_e / K * 1e3,
+            "e2e": {"value": e2e, "unit": "GB/s", "ms_per_model": e2e_ms,
                     "h2d_bytes_per_step": B + 40 * len(ws.tensors) * world, "d2h_bytes_per_step": 12 * len(ws.tensors),
-                    "device_ms_per_model": statistics.mean(dev_e) / 1e6,
-                    "what": "the same sharded swap-in followed, on the target, by tsw_translate of every parameter in access "
-                            "order (the launch path), then tsw_evict"},
+                    "device_ms_per_model": e2e_dev_ms, "dealing": e2e_dealing, "gbs_by_dealing": e2e_by_dealing,
+                    "what": "the sharded swap-in followed, on the target, by tsw_translate of every parameter in access "
+                            "order (the launch path), then tsw_evict; measured with tiles drawn from the shared counter and "
+                            "read by the kernels (direct) and with contiguous shares pulled by each GPU's copy engine and "
+                            "stored to the target by the kernel behind it (pipelined), the faster one reported"},
             "roofline": {"bound": "pcie", "achieved": B / kern_v / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": (B / kern_v / 1e9) / peak, "frac_wall": value / peak,
                          "peak_kind": f"theoretical PCIe Gen5 x16 x {world} participating GPUs (no PCIe figure in MEASURED_PEAKS.json)",
@@ -721,7 +742,8 @@ def bench_main(args, bench):
                              "what": "not the metric: the gather on its own, inputs already in the helpers' HBM"},
             "verified": ver.record(after_timed=True),
             "cpu_baseline": cpu_baseline,
-            "gpu_launches": int(total_launches[0]), "gpu_launches_e2e": int(total_launches[1]),
+            "gpu_launches": int(total_launches[0]),
+            "gpu_launches_e2e": int(total_launches[2] if e2e_dealing == "pipelined" else total_launches[1]),
             "clocks": clocks, "host_cores": ncpu, "cold_start_s": cold_s,
             "settings": {"tile_bytes_host": tile_host or 65536, "tiles_per_draw": args.ticket_chunk or 1, "host_store_mode": args.host_store,
                          "devices": devices, "link_probe_concurrent_h2d_gbs": probe},
