@@ -176,3 +176,27 @@ def test_target_carries_on_alone_when_its_helper_goes_away(built, tmp_path):
     for params in res["params"]:
         p = np.array(params, dtype=np.uint64)
         assert (p[:, 4] == 2).all() and np.array_equal(p[:, [0, 1, 2, 4, 6]], plain[:, [0, 1, 2, 4, 6]])
+
+
+def test_progress_board_tells_finished_from_gone():
+    """The shared-memory board the target reads when a control message failed in mid-swap: a rank is
+    'still at work' only while its process lives and it has not finished the swap in question."""
+    import subprocess
+    from torpor_b200 import sharded
+    name = f"torpor_swap_board_test_{os.getpid()}"
+    owner = sharded.ProgressBoard(name, 3, 0, create=True)
+    peer = sharded.ProgressBoard(name, 3, 1, create=False)          # same process here: its pid is alive
+    assert owner.still_at_work(1, 5)
+    peer.finished(5)
+    assert not owner.still_at_work(1, 5) and owner.still_at_work(1, 6)
+    # rank 2: a process that has already exited
+    child = subprocess.Popen([sys.executable, "-c", "pass"])
+    child.wait()
+    owner.words[4], owner.words[5] = child.pid, 0
+    assert not owner.still_at_work(2, 1)
+    # a rank that never registered
+    owner.words[4] = 0
+    assert not owner.still_at_work(2, 1)
+    peer.close()
+    owner.close()
+    assert not os.path.exists("/dev/shm/" + name)
