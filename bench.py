@@ -598,7 +598,16 @@ def run_single(args):
         swap(-1); target.wait_ready("model"); ver.check(target, "model", "before timing, copy-engine-assisted"); target.evict("model")
         wall_a, dev_a, ready_a, launches_a = timed(-1, K, Wm, through_translate=True,
                                                    where="after the timed copy-engine-assisted swap-ins")
+        wb_a = []
+        for _ in range(3):
+            swap(-1); target.wait_ready("model")
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            target.evict("model", writeback=True)
+            wb_a.append(time.perf_counter() - t0)
+        swap(-1); target.wait_ready("model"); ver.check(target, "model", "after the copy-engine-assisted write-backs"); target.evict("model")
         assisted = {"value": ws.nbytes * K / wall_a / 1e9, "unit": "GB/s", "ms_per_model": wall_a / K * 1e3,
+                    "swap_out_writeback_gbs": ws.nbytes / min(wb_a) / 1e9,
                     "device_ms_per_model": statistics.mean(dev_a) / 1e6, "gpu_launches": launches_a,
                     "frac_of_pcie": ws.nbytes / (statistics.mean(dev_a) / 1e9) / 1e9 / PCIE_GEN5_X16_GBS,
                     "what": "executor path with tsw_config.mover = 2: parameters of 4 MiB and more by cudaMemcpyAsync in "

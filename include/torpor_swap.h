@@ -74,7 +74,8 @@ typedef struct {
                                copy engine (cudaMemcpyAsync in access order on a second stream, a
                                small kernel behind each rewriting the parameter's table row), for
                                links on which the copy engine reads host memory faster than the SMs
-                               do.  Env TORPOR_SWAP_MOVER overrides. */
+                               do; the write-back of tsw_evict is split the same way.  Env
+                               TORPOR_SWAP_MOVER overrides. */
     int shard_static;       /* tsw_swap_in_sharded: 0 = participants draw tiles from a shared counter
                                (default), 1 = tile t is fixed to participant t mod n */
     int host_store_mode;    /* how the host model store is made page-locked (model_repo.hpp:124-141,173-177

@@ -521,12 +521,32 @@ int tsw_evict(tsw_engine* e, const char* func, int writeback) {
                 a.tile_stride = 1;
                 a.system_scope = 1;
                 a.status = e->d_status;
-                const int mv = pick_mover(e, plan.descs);
-                cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, (cudaStream_t)e->stream, mv);
-                if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("write-back kernel launch: ") + cudaGetErrorString(le));
-                e->kernel_launches++;
+                bool kernel_has_work = true;
+                if (e->mover == 2) {
+                    // as on the way in: the copy engine carries the large parameters (pool -> host store),
+                    // the kernel the small ones at the same time
+                    rc = ensure_ce_stream(e);
+                    if (rc != TSW_OK) return rc;
+                    cudaStream_t s2 = (cudaStream_t)e->stream_ce;
+                    a.skip_min_bytes = e->ce_min_bytes;
+                    kernel_has_work = false;
+                    for (const PlaceDesc& d : plan.descs) {
+                        if (d.bytes < e->ce_min_bytes) {
+                            kernel_has_work = true;
+                            continue;
+                        }
+                        TSW_CUDA(cudaMemcpyAsync((void*)d.dst, (const void*)d.src, d.bytes, cudaMemcpyDefault, s2));
+                    }
+                }
+                if (kernel_has_work) {
+                    const int mv = e->mover == 2 ? 0 : pick_mover(e, plan.descs);
+                    cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, (cudaStream_t)e->stream, mv);
+                    if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("write-back kernel launch: ") + cudaGetErrorString(le));
+                    e->kernel_launches++;
+                }
                 e->bytes_moved += plan.bytes;
                 TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream));
+                if (e->mover == 2) TSW_CUDA(cudaStreamSynchronize((cudaStream_t)e->stream_ce));
             }
         }
     }
