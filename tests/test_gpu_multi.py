@@ -109,21 +109,22 @@ def _free_port():
     return p
 
 
-def _rank_main(rank, world, port, shm, out_dir):
+def _rank_main(rank, world, port, shm, out_dir, devices=None):
     sys.path.insert(0, ROOT)
     import torch
     import torch.distributed as dist
     from torpor_b200 import sharded
-    torch.cuda.set_device(rank)
+    dev = devices[rank] if devices else rank        # CUDA ordinal of this rank's engine
+    torch.cuda.set_device(dev)
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     ws = W.weight_set("llama_tiny")
     repo_reset()
     if rank == 0:
-        eng = MemoryManager(0, device=0, server_id=0, gpu_count=world, host_arena_bytes=W.host_store_bytes(ws), host_arena_shm=shm)
+        eng = MemoryManager(0, device=dev, server_id=0, gpu_count=world, host_arena_bytes=W.host_store_bytes(ws), host_arena_shm=shm)
         W.cold_start(eng, "m", ws)
         eng.evict("m")
     else:
-        eng = MemoryManager(0, device=rank, server_id=rank, gpu_count=world, block_manager="Fixed")
+        eng = MemoryManager(0, device=dev, server_id=rank, gpu_count=world, block_manager="Fixed")
     dist.barrier()
     sw = sharded.ShardedSwap(eng, rank, world, None, shm_name=shm, max_segments=256)
     sw.attach_arena(); sw.share_regions()
@@ -160,23 +161,44 @@ def test_sharded_swap_one_process_per_gpu(built, tmp_path):
     assert res[1][1] >= 4, "the helper rank launched no kernels"
 
 
-def _rank_losing_helper(rank, world, port, shm, out_dir):
+needs1 = pytest.mark.skipif(gpu_count() < 1, reason="needs a GPU")
+
+
+@needs1
+@pytest.mark.timeout(600)
+def test_sharded_swap_one_process_per_rank_sharing_one_gpu(built, tmp_path):
+    """The same two processes on a box with ONE GPU: both engines on device 0, the target's pool
+    opened by the helper process over CUDA IPC, the host store in shared memory, tiles drawn from
+    the counter in the target's memory.  The links are not separate, everything else is the
+    multi-GPU path (all three dealings).  No kernel waits for another kernel, so the two
+    processes' launches may run in any order on the shared device."""
+    import torch.multiprocessing as mp
+    world = 2
+    shm = f"/torpor_swap_test1_{os.getpid()}"
+    mp.spawn(_rank_main, args=(world, _free_port(), shm, str(tmp_path), [0, 0]), nprocs=world, join=True)
+    res = [np.load(os.path.join(str(tmp_path), f"r{r}.npy")) for r in range(world)]
+    assert res[0][0] == 1, "resident bytes or pointer table wrong after a sharded swap"
+    assert res[1][1] >= 4, "the helper rank launched no kernels"
+
+
+def _rank_losing_helper(rank, world, port, shm, out_dir, devices=None):
     sys.path.insert(0, ROOT)
     import datetime
     import torch
     import torch.distributed as dist
     from torpor_b200 import sharded
-    torch.cuda.set_device(rank)
+    dev = devices[rank] if devices else rank
+    torch.cuda.set_device(dev)
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
                             timeout=datetime.timedelta(seconds=5))
     ws = W.weight_set("llama_tiny")
     repo_reset()
     if rank == 0:
-        eng = MemoryManager(0, device=0, server_id=0, gpu_count=world, host_arena_bytes=W.host_store_bytes(ws), host_arena_shm=shm)
+        eng = MemoryManager(0, device=dev, server_id=0, gpu_count=world, host_arena_bytes=W.host_store_bytes(ws), host_arena_shm=shm)
         W.cold_start(eng, "m", ws)
         eng.evict("m")
     else:
-        eng = MemoryManager(0, device=rank, server_id=rank, gpu_count=world, block_manager="Fixed")
+        eng = MemoryManager(0, device=dev, server_id=rank, gpu_count=world, block_manager="Fixed")
     dist.barrier()
     sw = sharded.ShardedSwap(eng, rank, world, None, shm_name=shm, max_segments=256)
     sw.attach_arena(); sw.share_regions()
@@ -213,6 +235,25 @@ def test_target_swaps_alone_after_its_helper_process_is_gone(built, tmp_path):
     shm = f"/torpor_swap_lost_{os.getpid()}"
     port = _free_port()
     procs = [ctx.Process(target=_rank_losing_helper, args=(r, 2, port, shm, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    assert np.load(os.path.join(str(tmp_path), "r0.npy"))[0] == 1
+
+
+@needs1
+@pytest.mark.timeout(600)
+def test_target_swaps_alone_after_its_helper_process_is_gone_on_one_gpu(built, tmp_path):
+    """The lost-helper case with both processes on device 0 (a box with one GPU): the helper leaves
+    between two swaps with nothing in flight; the target notices on its next control message and
+    carries on alone, bit-exact."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    shm = f"/torpor_swap_lost1_{os.getpid()}"
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_losing_helper, args=(r, 2, port, shm, str(tmp_path), [0, 0])) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:

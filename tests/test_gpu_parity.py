@@ -269,6 +269,41 @@ def test_tiles_dealt_to_several_launches_publish_once(fresh):
     eng.close()
 
 
+@pytest.mark.parametrize("name,static", [("resnet50", False), ("llama_tiny", True)])
+def test_sharded_swap_with_the_helper_engines_on_this_gpu(fresh, oracle_backend, name, static):
+    """The sharded swap-in of the multi-GPU tests on a box with one GPU: the target and three helper
+    engines (server ids 0-3) all sit on device 0, so the whole mechanism runs -- four launches
+    of the placement kernel on four streams, tiles drawn from the counter on the target (or dealt
+    t mod 4), system-scope tile counters, each row published once by whichever launch finishes
+    it -- only the links are not separate.  No launch waits for another, so they may run in any
+    order or one after the other.  Result: the single-GPU table of the checker, and the bytes."""
+    n = 4
+    oracle_backend.reset()
+    ws = W.weight_set(name)
+    engines = [MemoryManager(0, device=0, server_id=d, gpu_count=n, shard_static=static,
+                             host_arena_bytes=(W.host_store_bytes(ws) if d == 0 else 0))
+               for d in range(n)]
+    orc = oracle_backend.manager(budget=0, gpu_count=n)
+    W.cold_start(engines[0], "m", ws); W.cold_start(orc, "m", ws)
+    sums = np.array([checksum_host(W.tensor_bytes(ws, i)) for i in range(len(ws.tensors))])
+    for cycle in range(3):
+        engines[0].evict("m"); orc.evict("m")
+        engines[0].swap_in_sharded("m", engines[1:]); engines[0].wait_ready("m"); orc.swap_in("m")
+        assert np.array_equal(engines[0].dump_params("m", canonical=True), orc.dump_params("m"))
+        assert np.array_equal(engines[0].dump_blocks("m", canonical=True), orc.dump_blocks("m"))
+        assert np.array_equal(engines[0].checksum_resident("m"), sums)
+    for d in range(1, n):
+        assert engines[d].stats()["kernel_launches"] == 3       # every helper took part in every cycle, one launch each
+    # and a plain swap-in on the target afterwards starts from clean tile counters
+    engines[0].evict("m"); orc.evict("m")
+    engines[0].swap_in("m"); engines[0].wait_ready("m"); orc.swap_in("m")
+    assert np.array_equal(engines[0].dump_params("m", canonical=True), orc.dump_params("m"))
+    assert np.array_equal(engines[0].checksum_resident("m"), sums)
+    for e in engines:
+        e.close()
+    oracle_backend.reset()
+
+
 def test_more_segments_than_the_launch_scratch_holds_at_first(fresh):
     """A raw segment list longer than the engine's initial launch scratch (4096 entries) makes the
     scratch grow; the host store and the rest of the engine must come through that untouched."""
