@@ -404,38 +404,44 @@ def run_baselines(args):
         return d.get("cpu_baseline", d.get("pack", d))
 
     out = {"host_cores": ncpu, "gpus": torch.cuda.device_count(), "sample": sample}
-    if not args.feed_only:
+    if not args.feed_only and not args.replica_only:
         out["reference_swap_in_io4"] = ref("--ref-io-threads", "4")
         out["reference_swap_in_io_all"] = ref("--ref-io-threads", str(ncpu))
         out["reference_pack_resnet50_io4"] = ref("--ref-pack", "--ref-sample", "resnet50", "--ref-io-threads", "4")
         out["reference_pack_resnet50_io_all"] = ref("--ref-pack", "--ref-sample", "resnet50", "--ref-io-threads", str(ncpu))
-    out["feed_matrix"] = feed_matrix()
+    if not args.replica_only:
+        out["feed_matrix"] = feed_matrix()
     if torch.cuda.device_count() >= 2 and not args.feed_only:
         out["reference_replica_swap"] = ref("--ref-src-gpu", "1")
         # the same replica swap through this library: GPU 0 places the model from GPU 1's pool over NVLink
         from torpor_b200 import workloads as W
         from torpor_b200.memory_manager import MemoryManager, ModelRepo, repo_reset
         ws = W.weight_set(sample)
-        repo_reset()
-        holder = MemoryManager(W.pool_budget_for(ws), device=1, server_id=1, gpu_count=2, host_arena_bytes=W.host_store_bytes(ws))
-        target = MemoryManager(W.pool_budget_for(ws), device=0, server_id=0, gpu_count=2)
-        pool, data = generate_tensors(ws, min(ncpu, 16))
-        W.cold_start(holder, "m", ws, tensor_data=data)
-        pool.shutdown()
-        ModelRepo.add_model_info("m", 1)
-        wall, dev = [], []
-        for it in range(args.warmup + args.steps):
-            t0 = time.perf_counter()
-            target.swap_in("m", 1); target.wait_ready("m")
-            if it >= args.warmup:
-                wall.append(time.perf_counter() - t0)
-                dev.append(target.stats()["last_swap_device_ns"] / 1e9)
-            target.evict("m")
-        out["ours_replica_swap"] = {"signal_to_ready_gbs": ws.nbytes / statistics.median(wall) / 1e9,
-                                    "signal_to_ready_ms_median": statistics.median(wall) * 1e3,
-                                    "kernel_gbs": ws.nbytes / statistics.median(dev) / 1e9,
-                                    "what": "tsw_swap_in(func, src_gpu=1) + tsw_wait_ready on GPU 0: place_kernel reads GPU 1's pool over NVLink"}
-        target.close(); holder.close(); repo_reset()
+
+        def ours(tile_dev):
+            repo_reset()
+            holder = MemoryManager(W.pool_budget_for(ws), device=1, server_id=1, gpu_count=2, host_arena_bytes=W.host_store_bytes(ws))
+            target = MemoryManager(W.pool_budget_for(ws), device=0, server_id=0, gpu_count=2, tile_bytes_device=tile_dev)
+            pool, data = generate_tensors(ws, min(ncpu, 16))
+            W.cold_start(holder, "m", ws, tensor_data=data)
+            pool.shutdown()
+            ModelRepo.add_model_info("m", 1)
+            wall, dev = [], []
+            for it in range(args.warmup + args.steps):
+                t0 = time.perf_counter()
+                target.swap_in("m", 1); target.wait_ready("m")
+                if it >= args.warmup:
+                    wall.append(time.perf_counter() - t0)
+                    dev.append(target.stats()["last_swap_device_ns"] / 1e9)
+                target.evict("m")
+            r = {"signal_to_ready_gbs": ws.nbytes / statistics.median(wall) / 1e9,
+                 "signal_to_ready_ms_median": statistics.median(wall) * 1e3,
+                 "kernel_gbs": ws.nbytes / statistics.median(dev) / 1e9, "kernel_ms_median": statistics.median(dev) * 1e3,
+                 "tile_bytes_device": tile_dev or 512 * 1024,
+                 "what": "tsw_swap_in(func, src_gpu=1) + tsw_wait_ready on GPU 0: place_kernel reads GPU 1's pool over NVLink"}
+            target.close(); holder.close(); repo_reset()
+            return r
+        out["ours_replica_swap"] = ours(0)
     return {"baselines": out}
 
 
@@ -689,6 +695,8 @@ def main():
                     help="print the reported baselines around the path (reference with its default 4 and with all "
                          "staging threads, its pack, its replica swap, the copy-engine feed matrix) as one JSON line; not the contract line")
     ap.add_argument("--feed-only", action="store_true", help="--baselines: the copy-engine feed matrix only")
+    ap.add_argument("--replica-only", action="store_true", help="--baselines: only the replica swap GPU 1 -> GPU 0 over NVLink, "
+                                                                "the reference's and this library's, on --ref-sample")
     ap.add_argument("--link-probe", action="store_true", help="print every GPU's host-link rate under full contention and exit")
     ap.add_argument("--devices", default="", help="N > 1: comma-separated CUDA ordinals to use, target first "
                                                    "(default: measured -- the best-fed GPUs when the box has more than N)")
