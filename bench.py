@@ -445,6 +445,80 @@ def run_baselines(args):
     return {"baselines": out}
 
 
+def run_corun(args):
+    """What a swap-in from the host store leaves of the GPU to other kernels.  The reference moves
+    weights with the copy engine, so the function's first kernels run while its later weights are
+    still arriving (cuda_server.hpp:1265-1268 with memory_manager.hpp:527-540); a kernel that reads
+    the host store itself occupies SMs instead, and its persistent CTAs hold their registers until
+    the swap is over.  Per grid size of the host-side launch: the swap-in alone, a fixed loop of
+    bf16 matrix products on another stream alone, and both at once (the swap launched first)."""
+    import torch
+    from torpor_b200 import workloads as W
+    from torpor_b200.memory_manager import MemoryManager, ModelRepo, repo_reset
+    torch.cuda.set_device(0)
+    ncpu = os.cpu_count() or 1
+    ws = W.weight_set(args.workload)
+    budget = W.pool_budget_for(ws)
+    grids = [int(g) for g in args.corun_grids.split(",")]
+    repo_reset()
+    holder = MemoryManager(budget, device=0, server_id=len(grids), gpu_count=len(grids) + 1, host_arena_bytes=W.host_store_bytes(ws))
+    pool, data = generate_tensors(ws, min(ncpu, 16))
+    W.cold_start(holder, "model", ws, tensor_data=data)
+    pool.shutdown()
+    ModelRepo.add_model_info("model", len(grids))
+
+    side = torch.cuda.Stream()
+    a = torch.randn(4096, 4096, dtype=torch.bfloat16, device="cuda")
+    b = torch.randn(4096, 4096, dtype=torch.bfloat16, device="cuda")
+    c = torch.empty_like(a)
+
+    def products(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(side):
+            e0.record()
+            for _ in range(reps):
+                torch.matmul(a, b, out=c)
+            e1.record()
+        return e0, e1
+
+    e0, e1 = products(20); torch.cuda.synchronize()            # module load, clocks
+    e0, e1 = products(200); torch.cuda.synchronize()
+    per = e0.elapsed_time(e1) / 200
+    rows = []
+    for k, g in enumerate(grids):
+        eng = MemoryManager(budget, device=0, server_id=k, gpu_count=len(grids) + 1, grid_ctas_host=g, mover=args.mover)
+        for _ in range(max(1, args.warmup)):
+            eng.swap_in("model", -1); eng.wait_ready("model"); eng.evict("model")
+        alone = []
+        for _ in range(max(1, args.steps)):
+            eng.swap_in("model", -1); eng.wait_ready("model")
+            alone.append(eng.stats()["last_swap_device_ns"] / 1e6)
+            eng.evict("model")
+        swap_ms = statistics.median(alone)
+        reps = max(10, int(swap_ms / per))                     # a loop about as long as the swap
+        e0, e1 = products(reps); torch.cuda.synchronize()
+        loop_alone = e0.elapsed_time(e1)
+        both_swap, both_loop = [], []
+        for _ in range(max(1, args.steps)):
+            torch.cuda.synchronize()
+            eng.swap_in("model", -1)                           # returns once the kernel is launched
+            e0, e1 = products(reps)
+            eng.wait_ready("model")
+            torch.cuda.synchronize()
+            both_swap.append(eng.stats()["last_swap_device_ns"] / 1e6)
+            both_loop.append(e0.elapsed_time(e1))
+            eng.evict("model")
+        rows.append({"grid_ctas_host": g or "default", "swap_alone_ms": swap_ms, "swap_alone_gbs": ws.nbytes / swap_ms / 1e6,
+                     "products": reps, "loop_alone_ms": loop_alone,
+                     "swap_with_loop_ms": statistics.median(both_swap), "swap_with_loop_gbs": ws.nbytes / statistics.median(both_swap) / 1e6,
+                     "loop_with_swap_ms": statistics.median(both_loop),
+                     "loop_slowdown": statistics.median(both_loop) / loop_alone})
+        eng.close()
+    holder.close(); repo_reset()
+    return {"corun": {"workload": f"{args.workload}: {ws.nbytes} B", "mover": args.mover, "product": "4096^3 bf16 torch.matmul",
+                      "product_ms": per, "rows": rows}}
+
+
 def workload_config(args, n, name=None):
     from torpor_b200 import workloads as W
     name = name or args.workload
@@ -528,7 +602,8 @@ def run_single(args):
     repo_reset()
     replica = MemoryManager(budget, device=0, server_id=1, gpu_count=2, host_arena_bytes=arena,
                             host_store_mode=args.host_store, tile_bytes_host=args.tile_kib * 1024)
-    target = MemoryManager(budget, device=0, server_id=0, gpu_count=2, tile_bytes_host=args.tile_kib * 1024, mover=args.mover)
+    target = MemoryManager(budget, device=0, server_id=0, gpu_count=2, tile_bytes_host=args.tile_kib * 1024, mover=args.mover,
+                           grid_ctas=args.grid_ctas, grid_ctas_host=args.grid_ctas_host)
 
     pool, data, sums = generate_tensors(ws, min(ncpu, 16), with_sums=True)
     t0 = time.time()
@@ -599,7 +674,8 @@ def run_single(args):
     assisted = None
     if args.mover == 0:
         target.close()
-        target = MemoryManager(budget, device=0, server_id=0, gpu_count=2, tile_bytes_host=args.tile_kib * 1024, mover=2)
+        target = MemoryManager(budget, device=0, server_id=0, gpu_count=2, tile_bytes_host=args.tile_kib * 1024, mover=2,
+                               grid_ctas=args.grid_ctas, grid_ctas_host=args.grid_ctas_host)
         ver.swaps = 0
         swap(-1); target.wait_ready("model"); ver.check(target, "model", "before timing, copy-engine-assisted"); target.evict("model")
         wall_a, dev_a, ready_a, launches_a = timed(-1, K, Wm, through_translate=True,
@@ -672,7 +748,8 @@ def run_single(args):
         "cpu_baseline": cpu_baseline,
         "gpu_launches": launches_v, "gpu_launches_e2e": launches_e,
         "clocks": clocks, "host_cores": ncpu, "cold_start_s": cold_s,
-        "settings": {"tile_bytes_host": args.tile_kib * 1024 or 65536, "host_store_mode": args.host_store, "mover": args.mover},
+        "settings": {"tile_bytes_host": args.tile_kib * 1024 or 65536, "host_store_mode": args.host_store, "mover": args.mover,
+                     "grid_ctas_host": args.grid_ctas_host or args.grid_ctas or 16, "grid_ctas": args.grid_ctas or "6 per SM"},
     }
     target.close(); replica.close(); repo_reset()
     return line
@@ -697,10 +774,16 @@ def main():
     ap.add_argument("--feed-only", action="store_true", help="--baselines: the copy-engine feed matrix only")
     ap.add_argument("--replica-only", action="store_true", help="--baselines: only the replica swap GPU 1 -> GPU 0 over NVLink, "
                                                                 "the reference's and this library's, on --ref-sample")
+    ap.add_argument("--corun", action="store_true", help="time a loop of matrix products on another stream while a swap-in from "
+                                                          "the host store runs, per grid size of the host-side launch; not the contract line")
+    ap.add_argument("--corun-grids", default="0,148,296,592,888", help="--corun: CTAs of the host-side launch to try (0 = the library's default)")
     ap.add_argument("--link-probe", action="store_true", help="print every GPU's host-link rate under full contention and exit")
     ap.add_argument("--devices", default="", help="N > 1: comma-separated CUDA ordinals to use, target first "
                                                    "(default: measured -- the best-fed GPUs when the box has more than N)")
     ap.add_argument("--tile-kib", type=int, default=0, help="host-side tile size of the mover in KiB (0 = the library's default, 64)")
+    ap.add_argument("--grid-ctas", type=int, default=0, help="persistent CTAs of every placement-kernel launch (0 = the library's defaults: "
+                                                             "6 per SM, 16 for single-GPU launches with one end in the host store)")
+    ap.add_argument("--grid-ctas-host", type=int, default=0, help="N = 1: CTAs of the launches with one end in the host store only (0 = default)")
     ap.add_argument("--ticket-chunk", type=int, default=0, help="sharded swaps: tiles per draw from the shared counter (0 = 1)")
     ap.add_argument("--mover", type=int, default=0, help="0 placement kernel (default), 1 bulk-copy unit, 2 kernel + copy engine for large parameters")
     ap.add_argument("--host-store", type=int, default=0, help="host store mode: 0 page-locked, 1 write-combined, 2 huge pages")
@@ -719,6 +802,11 @@ def main():
     if args.baselines:
         if rank == 0:
             print(json.dumps(run_baselines(args)), flush=True)
+        return 0
+
+    if args.corun:
+        if rank == 0:
+            print(json.dumps(run_corun(args)), flush=True)
         return 0
 
     if args.impl == "reference":

@@ -87,6 +87,13 @@ typedef struct {
                                overrides.  Huge pages apply to the arena only (host_arena_bytes > 0). */
     int ticket_chunk;       /* sharded swaps that draw tiles from the shared counter: tiles taken per
                                draw; 0 = 1 */
+    int grid_ctas_host;     /* persistent CTAs of the placement kernel when one end of a single-GPU move is
+                               the host store (swap-in from it, write-back into it).  Such a move is bound
+                               by PCIe, which a fraction of the SMs saturates, and the CTAs hold their
+                               registers for the whole swap: the fewer there are, the more of every SM is
+                               left to the function's own kernels that run while its later weights are
+                               still arriving (cuda_server.hpp:1265-1268 launches them as soon as their
+                               parameters are ready).  0 = default.  Env TORPOR_SWAP_GRID_HOST overrides. */
 } tsw_config;
 enum { TSW_STORE_DEFAULT = 0, TSW_STORE_WRITE_COMBINED = 1, TSW_STORE_HUGE_PAGES = 2 };
 

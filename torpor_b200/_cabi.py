@@ -50,6 +50,7 @@ class Config(C.Structure):
         ("shard_static", C.c_int),
         ("host_store_mode", C.c_int),
         ("ticket_chunk", C.c_int),
+        ("grid_ctas_host", C.c_int),
     ]
 
 

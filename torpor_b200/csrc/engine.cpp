@@ -585,6 +585,10 @@ static int engine_setup(const tsw_config* cfg, tsw_engine* e) {
         TSW_CUDA(cudaSetDevice(cfg->device));
         e->mem.reset(new CudaMemory(cfg->device));
         e->grid_ctas = cfg->grid_ctas > 0 ? cfg->grid_ctas : default_grid_ctas(cfg->device);
+        e->grid_host = cfg->grid_ctas_host > 0 ? cfg->grid_ctas_host : (cfg->grid_ctas > 0 ? cfg->grid_ctas : default_grid_ctas_host(cfg->device));
+        if (const char* gh = getenv("TORPOR_SWAP_GRID_HOST")) {
+            if (atoi(gh) > 0) e->grid_host = atoi(gh);
+        }
         e->mover = cfg->mover;
         if (const char* mv = getenv("TORPOR_SWAP_MOVER")) e->mover = atoi(mv);
         e->grid_bulk = cfg->grid_ctas > 0 ? cfg->grid_ctas : default_grid_ctas(cfg->device) / 2;

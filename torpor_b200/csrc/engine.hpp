@@ -77,6 +77,7 @@ struct tsw_engine {
     volatile uint32_t* h_status = nullptr;
 
     int grid_ctas = 0;
+    int grid_host = 0;   // CTAs of single-GPU launches with one end in the host store (PCIe-bound)
     int grid_bulk = 0;   // CTAs of the bulk-copy mover
     int mover = 0;       // 0 = load/store kernel, 1 = bulk-copy kernel where alignment allows,
                          // 2 = load/store kernel + the copy engine for large parameters read from the host store

@@ -283,7 +283,7 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
             e->kernel_launches++;
         }
         if (any_small) {
-            cudaError_t le = launch_place(a, e->grid_ctas, s, 0);
+            cudaError_t le = launch_place(a, e->grid_host, s, 0);
             if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
             e->kernel_launches++;
         }
@@ -291,7 +291,7 @@ static int swap_in_impl(tsw_engine* e, const char* func, int src_gpu, tsw_engine
         TSW_CUDA(cudaStreamWaitEvent(s, (cudaEvent_t)e->ev_ce, 0));
     } else {
         const int mv = pick_mover(e, plan.descs);
-        cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, s, mv);
+        cudaError_t le = launch_place(a, mv ? e->grid_bulk : (pr.from_host ? e->grid_host : e->grid_ctas), s, mv);
         if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("placement kernel launch: ") + cudaGetErrorString(le));
         e->kernel_launches++;
     }
@@ -540,7 +540,7 @@ int tsw_evict(tsw_engine* e, const char* func, int writeback) {
                 }
                 if (kernel_has_work) {
                     const int mv = e->mover == 2 ? 0 : pick_mover(e, plan.descs);
-                    cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_ctas, (cudaStream_t)e->stream, mv);
+                    cudaError_t le = launch_place(a, mv ? e->grid_bulk : e->grid_host, (cudaStream_t)e->stream, mv);
                     if (le != cudaSuccess) return fail(TSW_ERR_CUDA, std::string("write-back kernel launch: ") + cudaGetErrorString(le));
                     e->kernel_launches++;
                 }

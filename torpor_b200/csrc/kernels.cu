@@ -434,6 +434,18 @@ int default_grid_ctas(int device) {
     return sms * 6;
 }
 
+int default_grid_ctas_host(int device) {
+    // A move across PCIe is bound by the link whatever the grid: measured, 8 CTAs already read the
+    // host store at the full 51 GB/s, and 12 to 888 all give 51.2-51.4.  But every resident CTA
+    // holds a quarter of its SM's registers until the swap is over, and a large matrix-product
+    // kernel wants a whole SM: with 148 CTAs or more the swapped-in function's first kernels did
+    // not start before the swap had finished (a loop of products beside the swap took 1.95 x as
+    // long); with 16 CTAs it took 1.21 x and the swap still ran at 50.7 GB/s.  Sixteen CTAs keep
+    // 512 KiB of reads in flight, a few times what the link needs to stay busy.
+    (void)device;
+    return 16;
+}
+
 cudaError_t launch_place(const PlaceArgs& a, int grid_ctas, cudaStream_t stream, int mover) {
     if (a.n_descs == 0 || a.tile_hi <= a.tile_lo) return cudaSuccess;
     if (a.tile_bytes == 0 || (a.tile_bytes & 15u) || a.tile_stride == 0) return cudaErrorInvalidValue;

@@ -71,6 +71,7 @@ cudaError_t launch_checksum(const SumDesc* descs, uint32_t n_descs, uint32_t tot
                             unsigned long long* out, int grid_ctas, cudaStream_t stream);
 
 int default_grid_ctas(int device);
+int default_grid_ctas_host(int device);   // for moves with one end in host memory
 
 }  // namespace tsw
 #endif

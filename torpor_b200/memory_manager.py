@@ -90,7 +90,7 @@ class MemoryManager:
     def __init__(self, budget: int = 25 << 30, *, device: int = 0, server_id: int = 0, gpu_count: int = 1,
                  block_manager: str = "Buddy", host_arena_bytes: int = 0, host_arena_shm: Optional[str] = None,
                  grid_ctas: int = 0, tile_bytes_host: int = 0, tile_bytes_device: int = 0, shard_static: bool = False,
-                 mover: int = 0, host_store_mode: int = 0, ticket_chunk: int = 0):
+                 mover: int = 0, host_store_mode: int = 0, ticket_chunk: int = 0, grid_ctas_host: int = 0):
         self.L = _cabi.lib()
         cfg = _cabi.Config()
         self.L.tsw_config_default(C.byref(cfg))
@@ -109,6 +109,7 @@ class MemoryManager:
         cfg.mover = mover
         cfg.host_store_mode = host_store_mode
         cfg.ticket_chunk = ticket_chunk
+        cfg.grid_ctas_host = grid_ctas_host
         h = C.c_void_p()
         check(self.L.tsw_engine_create(C.byref(cfg), C.byref(h)))
         self.h = h

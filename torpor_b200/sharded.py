@@ -567,9 +567,11 @@ def bench_main(args, bench):
         tables = W.plan_tables(ws, "model", budget=budget, gpu_count=world, swaps=4 + 3 * (Wm + K) + (Wm + K_g) + sweep_swaps + 8)
         repo_reset()
         eng = MemoryManager(budget, device=local_rank, server_id=0, gpu_count=world, host_arena_bytes=W.host_store_bytes(ws),
-                            host_arena_shm=shm, tile_bytes_host=tile_host, ticket_chunk=args.ticket_chunk, host_store_mode=args.host_store)
+                            host_arena_shm=shm, tile_bytes_host=tile_host, ticket_chunk=args.ticket_chunk, host_store_mode=args.host_store,
+                            grid_ctas=getattr(args, "grid_ctas", 0))
     else:
-        eng = MemoryManager(0, device=local_rank, server_id=rank, gpu_count=world, block_manager="Fixed")
+        eng = MemoryManager(0, device=local_rank, server_id=rank, gpu_count=world, block_manager="Fixed",
+                            grid_ctas=getattr(args, "grid_ctas", 0))
     sw = ShardedSwap(eng, rank, world, ctrl, shm_name=shm, max_segments=max(1024, len(ws.tensors) + 16))
 
     if rank == 0:
