@@ -749,7 +749,7 @@ def run_single(args):
         "gpu_launches": launches_v, "gpu_launches_e2e": launches_e,
         "clocks": clocks, "host_cores": ncpu, "cold_start_s": cold_s,
         "settings": {"tile_bytes_host": args.tile_kib * 1024 or 65536, "host_store_mode": args.host_store, "mover": args.mover,
-                     "grid_ctas_host": args.grid_ctas_host or args.grid_ctas or 16, "grid_ctas": args.grid_ctas or "6 per SM"},
+                     "grid_ctas_host": args.grid_ctas_host or args.grid_ctas or 32, "grid_ctas": args.grid_ctas or "6 per SM"},
     }
     target.close(); replica.close(); repo_reset()
     return line
@@ -782,7 +782,7 @@ def main():
                                                    "(default: measured -- the best-fed GPUs when the box has more than N)")
     ap.add_argument("--tile-kib", type=int, default=0, help="host-side tile size of the mover in KiB (0 = the library's default, 64)")
     ap.add_argument("--grid-ctas", type=int, default=0, help="persistent CTAs of every placement-kernel launch (0 = the library's defaults: "
-                                                             "6 per SM, 16 for single-GPU launches with one end in the host store)")
+                                                             "6 per SM, 32 for single-GPU launches with one end in the host store)")
     ap.add_argument("--grid-ctas-host", type=int, default=0, help="N = 1: CTAs of the launches with one end in the host store only (0 = default)")
     ap.add_argument("--ticket-chunk", type=int, default=0, help="sharded swaps: tiles per draw from the shared counter (0 = 1)")
     ap.add_argument("--mover", type=int, default=0, help="0 placement kernel (default), 1 bulk-copy unit, 2 kernel + copy engine for large parameters")

@@ -436,14 +436,15 @@ int default_grid_ctas(int device) {
 
 int default_grid_ctas_host(int device) {
     // A move across PCIe is bound by the link whatever the grid: measured, 8 CTAs already read the
-    // host store at the full 51 GB/s, and 12 to 888 all give 51.2-51.4.  But every resident CTA
+    // host store at the link's full rate, and 12 to 888 differ by about 1 %.  But every resident CTA
     // holds a quarter of its SM's registers until the swap is over, and a large matrix-product
     // kernel wants a whole SM: with 148 CTAs or more the swapped-in function's first kernels did
     // not start before the swap had finished (a loop of products beside the swap took 1.95 x as
-    // long); with 16 CTAs it took 1.21 x and the swap still ran at 50.7 GB/s.  Sixteen CTAs keep
-    // 512 KiB of reads in flight, a few times what the link needs to stay busy.
+    // long); with 32 CTAs it took 1.43 x, with 16 CTAs 1.21 x.  On the 13.5 GB Llama-shaped set, same
+    // box: 888 CTAs 262.4 ms, 32 CTAs 263.1 ms, 16 CTAs 265.7 ms -- so 32: a megabyte of reads in
+    // flight, several times what the link needs to stay busy, at 0.3 % of the rate.
     (void)device;
-    return 16;
+    return 32;
 }
 
 cudaError_t launch_place(const PlaceArgs& a, int grid_ctas, cudaStream_t stream, int mover) {
