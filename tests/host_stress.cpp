@@ -21,6 +21,7 @@ cudaError_t launch_place(const PlaceArgs&, int, cudaStream_t, int) { return cuda
 cudaError_t launch_publish_rows(const PlaceArgs&, uint32_t, uint32_t, cudaStream_t) { return cudaErrorNotSupported; }
 cudaError_t launch_checksum(const SumDesc*, uint32_t, uint32_t, uint32_t, unsigned long long*, int, cudaStream_t) { return cudaErrorNotSupported; }
 int default_grid_ctas(int) { return 1; }
+int default_grid_ctas_host(int) { return 1; }
 }  // namespace tsw
 extern "C" int tsw_place_segments_static(int, const tsw_segment*, int, uint32_t, uint32_t, uint32_t, const tsw_publish*, void*) { return TSW_ERR_NO_DEVICE; }
 
