@@ -748,6 +748,7 @@ def bench_main(args, bench):
             "gpu_launches_e2e": int(total_launches[2] if e2e_dealing == "pipelined" else total_launches[1]),
             "clocks": clocks, "host_cores": ncpu, "cold_start_s": cold_s,
             "settings": {"tile_bytes_host": tile_host or 65536, "tiles_per_draw": args.ticket_chunk or 1, "host_store_mode": args.host_store,
+                         "grid_ctas": getattr(args, "grid_ctas", 0) or "6 per SM",
                          "devices": devices, "link_probe_concurrent_h2d_gbs": probe},
         }
         if sweep is not None:
