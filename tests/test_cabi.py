@@ -24,6 +24,38 @@ def test_header_and_binding_agree(built):
     assert sorted(_cabi.SIGNATURES) == decl
 
 
+def header_struct_fields(name):
+    """Member names and C types of `typedef struct { ... } <name>;` in the header, in order."""
+    text = open(os.path.join(ROOT, "include", "torpor_swap.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    body = re.search(r"typedef\s+struct\s*\{([^}]*)\}\s*" + name + r"\s*;", text).group(1)
+    out = []
+    for decl in body.split(";"):
+        decl = " ".join(decl.split())
+        if not decl:
+            continue
+        m = re.match(r"((?:const )?(?:unsigned )?\w+\s*\*?)\s*(.+)$", decl)
+        ctype = m.group(1).replace(" *", "*").strip()
+        for d in m.group(2).split(","):
+            d = d.strip()
+            arr = re.match(r"(\w+)(\[\d+\])$", d)
+            out.append((arr.group(1), ctype + arr.group(2)) if arr else (d, ctype))
+    return out
+
+
+@pytest.mark.parametrize("c_name,binding", [("tsw_config", "Config"), ("tsw_segment", "Segment"),
+                                            ("tsw_publish", "Publish"), ("tsw_ipc_region", "IpcRegion")])
+def test_struct_layouts_of_header_and_binding_agree(c_name, binding):
+    """Every struct that crosses the C ABI has the same members, in the same order and of the same
+    width, in include/torpor_swap.h and in the ctypes binding."""
+    width = {"int": 4, "uint32_t": 4, "uint64_t": 8, "const char*": 8, "unsigned char[64]": 64}
+    fields = header_struct_fields(c_name)
+    cls = getattr(_cabi, binding)
+    assert [f[0] for f in fields] == [f[0] for f in cls._fields_]
+    for (name, ctype), bound in zip(fields, cls._fields_):
+        assert width[ctype] == ctypes.sizeof(bound[1]), (name, ctype)
+
+
 def test_library_exports_every_declared_symbol(built):
     lib = ctypes.CDLL(_cabi.LIB_PATH)
     for name in declared_symbols():
