@@ -463,9 +463,10 @@ def run_corun(args):
     repo_reset()
     holder = MemoryManager(budget, device=0, server_id=len(grids), gpu_count=len(grids) + 1, host_arena_bytes=W.host_store_bytes(ws))
     pool, data = generate_tensors(ws, min(ncpu, 16))
-    W.cold_start(holder, "model", ws, tensor_data=data)
+    vaddrs = W.cold_start(holder, "model", ws, tensor_data=data).tensor_vaddr
     pool.shutdown()
     ModelRepo.add_model_info("model", len(grids))
+    marks = sorted({0, len(vaddrs) // 4, len(vaddrs) // 2, len(vaddrs) - 1})     # positions in the access order
 
     side = torch.cuda.Stream()
     a = torch.randn(4096, 4096, dtype=torch.bfloat16, device="cuda")
@@ -495,6 +496,20 @@ def run_corun(args):
             alone.append(eng.stats()["last_swap_device_ns"] / 1e6)
             eng.evict("model")
         swap_ms = statistics.median(alone)
+        # when the launch path gets its parameters: swap signal -> tsw_translate returns, for the first
+        # parameter of the access order, the one a quarter and half way in, and the last
+        arrive = []
+        for _ in range(max(1, args.steps)):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            eng.swap_in("model", -1)
+            ts = []
+            for i in marks:
+                eng.translate("model", vaddrs[i])
+                ts.append((time.perf_counter() - t0) * 1e3)
+            eng.wait_ready("model"); eng.evict("model")
+            arrive.append(ts)
+        arrive_ms = [statistics.median(col) for col in zip(*arrive)]
         reps = max(10, int(swap_ms / per))                     # a loop about as long as the swap
         e0, e1 = products(reps); torch.cuda.synchronize()
         loop_alone = e0.elapsed_time(e1)
@@ -509,6 +524,7 @@ def run_corun(args):
             both_loop.append(e0.elapsed_time(e1))
             eng.evict("model")
         rows.append({"grid_ctas_host": g or "default", "swap_alone_ms": swap_ms, "swap_alone_gbs": ws.nbytes / swap_ms / 1e6,
+                     "ready_ms_at_parameter": dict(zip(map(str, marks), arrive_ms)),
                      "products": reps, "loop_alone_ms": loop_alone,
                      "swap_with_loop_ms": statistics.median(both_swap), "swap_with_loop_gbs": ws.nbytes / statistics.median(both_swap) / 1e6,
                      "loop_with_swap_ms": statistics.median(both_loop),
