@@ -445,9 +445,11 @@ int default_grid_ctas_host(int device) {
     // holds a quarter of its SM's registers until the swap is over, and a large matrix-product
     // kernel wants a whole SM: with 148 CTAs or more the swapped-in function's first kernels did
     // not start before the swap had finished (a loop of products beside the swap took 1.95 x as
-    // long); with 32 CTAs it took 1.43 x, with 16 CTAs 1.21 x.  On the 13.5 GB Llama-shaped set, same
-    // box: 888 CTAs 262.4 ms, 32 CTAs 263.1 ms, 16 CTAs 265.7 ms -- so 32: a megabyte of reads in
-    // flight, several times what the link needs to stay busy, at 0.3 % of the rate.
+    // long); with 32 CTAs it took 1.43 x, with 16 CTAs 1.21 x.  On the 13.5 GB Llama-shaped set 32
+    // CTAs are level with 888 (262.3 against 262.4 ms); sets of many small tensors land 2-3 % later
+    // (BERT-large 13.34 against 13.07 ms).  A small grid also keeps the tiles in flight within 2 MiB
+    // of the access order, so parameters arrive in the order the first inference needs them
+    // instead of all at the end.
     (void)device;
     return 32;
 }
