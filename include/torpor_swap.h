@@ -64,7 +64,9 @@ typedef struct {
                                0 = one page-locked allocation per model block */
     const char* host_arena_shm; /* optional POSIX shm name: the arena is created there so that other
                                processes can attach it (tsw_arena_attach) for sharded swaps */
-    int grid_ctas;          /* persistent CTAs of the placement kernel; 0 = default */
+    int grid_ctas;          /* persistent CTAs of the placement kernel; 0 = default (6 per SM; see grid_ctas_host for
+                               single-GPU moves with one end in the host store).  A value given here applies to
+                               both unless grid_ctas_host is given too */
     int tile_bytes_host;    /* bytes per tile when the source is host memory; 0 = default */
     int tile_bytes_device;  /* bytes per tile when the source is device memory; 0 = default */
     int mover;              /* 0 = tiles moved by loads/stores of the SMs' threads (default); 1 = by the bulk
@@ -93,7 +95,7 @@ typedef struct {
                                registers for the whole swap: the fewer there are, the more of every SM is
                                left to the function's own kernels that run while its later weights are
                                still arriving (cuda_server.hpp:1265-1268 launches them as soon as their
-                               parameters are ready).  0 = default.  Env TORPOR_SWAP_GRID_HOST overrides. */
+                               parameters are ready).  0 = default (32).  Env TORPOR_SWAP_GRID_HOST overrides. */
 } tsw_config;
 enum { TSW_STORE_DEFAULT = 0, TSW_STORE_WRITE_COMBINED = 1, TSW_STORE_HUGE_PAGES = 2 };
 
